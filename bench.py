@@ -1,0 +1,405 @@
+"""Benchmark of the decode-step sparse-KV retrieval path (pool -> score -> top-k -> gather).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--graph]
+
+Workload (default): 64 decode requests with context lengths uniform in [8192, 131072] tokens
+(seeded, rounded up to 128-token blocks), Llama-3-8B KV shapes (32 query heads, 8 KV heads,
+head_dim 128, bf16), a paged K/V pool with a randomly permuted block table, top-k = 5 % of each
+request's blocks (at least 16), all 32 layers per step.  A step is, for every layer: pool the 64
+newest blocks, score every block of every request, select the per-request top-k and gather the
+selected K and V blocks into a contiguous working set.  All data is synthetic (seeded normal).
+
+One JSON line is printed by rank 0.  `value` = KV tokens scored per second over all GPUs with every
+input resident in HBM; `e2e` = the same with queries coming from pinned host memory and the selected
+block ids going back to it each layer.  With N > 1 each rank runs its own batch (data parallel over
+requests, no data-path collective): weak scaling.
+
+`--impl reference` times the reference's own CPU retrieval (its compiled RetrievalWorkerBackend:
+fp32 dot scores + partial_sort top-k) on the host cores for the same batch, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "unified-cache-management_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+METRIC = "decode_step_retrieval_scored_kv_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM bytes per launch of the dominant kernel (xfer_bulk_kernel gathering one layer's selected K and
+# V blocks) read from an ncu capture; see profiles/.  None until a capture has been summarised.
+NCU_GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as fh:
+                d = json.load(fh)
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="ucmx_clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            rows = [ln.strip().split(",") for ln in open(self.path) if ln.strip()]
+            os.remove(self.path)
+        except Exception:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------ reference arm
+
+def reference_cpu_run(batch, layers_per_step: int, steps: int, warmup: int, distinct_tables: int = 4):
+    """The reference's CPU retrieval for this batch: one RetrievalWorkerBackend per layer table, one
+    submit per request (what ESA does, ucm/sparse/esa/esa.py:286-301), all in flight at once, so
+    that every host core its thread pool owns has work.  Returns (tokens_per_s, sec_per_step, cores)."""
+    import numpy as np
+    from oracle import oracle as orc
+    rb = orc.ref_retrieval_backend()
+    rng = np.random.default_rng(2002)
+    dim = 1024
+    n_tables = min(distinct_tables, layers_per_step)
+    backends = []
+    for _ in range(n_tables):
+        data = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((batch.n_slots, dim), dtype=np.float32) * np.float32(0.0884)))
+        backends.append((rb.RetrievalWorkerBackend(data), data))
+    queries = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((layers_per_step, batch.n_req, dim), dtype=np.float32)))
+    slot_lists = [np.ascontiguousarray(batch.block_table[batch.offsets[r]:batch.offsets[r + 1]][None, :]) for r in range(batch.n_req)]
+
+    def one_step():
+        for l in range(layers_per_step):
+            be = backends[l % n_tables][0]
+            rids = [be.submit(queries[l, r:r + 1], int(batch.k_per_req[r]), slot_lists[r]) for r in range(batch.n_req)]
+            for rid in rids:
+                be.wait(rid)
+                be.get_result(rid)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    tokens = batch.total * 128 * layers_per_step
+    return tokens / dt, dt, os.cpu_count()
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    from ucmx.workloads import ragged_decode_batch
+    from oracle import oracle as orc
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic"}
+    if not orc.have_ref():
+        base["unavailable"] = "oracle/_ref (the compiled reference CPU sources) is not present on this machine"
+        print(json.dumps(base))
+        return
+    batch = ragged_decode_batch(seed=2002)
+    layers = 8
+    tps, dt, cores = reference_cpu_run(batch, layers, args.steps, args.warmup)
+    base.update({
+        "value": tps, "ms_per_step": dt * 1e3,
+        "config": workload_config(batch, extra={"sample": f"{layers} of 32 layers per step"}),
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "reference",
+                         "sample": f"{layers} of 32 layers of the 64-request batch per step, score + top-k only "
+                                   "(RetrievalWorkerBackend, one submit per request, all in flight)"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    })
+    print(json.dumps(base))
+
+
+def workload_config(batch, extra=None):
+    cfg = {
+        "workload": "ESA batched decode, 64 requests, ctx U[8192,131072] tokens, Llama-3-8B KV (32q/8kv heads, "
+                    "head_dim 128, block 128), paged pool with permuted block table, top-k 5% (min 16), 32 layers/step",
+        "n_req": int(batch.n_req), "blocks_total_per_layer": int(batch.total), "selected_per_layer": int(batch.total_k),
+        "layers": 32, "stages": "pool(64 new blocks)+score+topk+gather(K,V of selected) per layer",
+        "l2_policy": "inputs larger than L2: 2.3 GB of representatives and an 18 GB K/V pool are cycled per step",
+        "parallelism": "dp over requests",
+    }
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# ----------------------------------------------------------------------------------------- our arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=32, help=argparse.SUPPRESS)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = env_int("RANK", 0)
+    world = env_int("WORLD_SIZE", 1)
+    local_rank = env_int("LOCAL_RANK", 0)
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from ucmx import _native
+    from ucmx.engine import DecodeRetrievalEngine
+    from ucmx.workloads import LLAMA3_8B, ragged_decode_batch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+
+    batch = ragged_decode_batch(seed=2002 + rank)
+    eng = DecodeRetrievalEngine(LLAMA3_8B, batch, dev, n_layers=args.layers, seed=1000 + rank)
+    eng.make_queries()
+    torch.cuda.synchronize()
+
+    # prefill-time pooling of the whole pool (layer 0's table is really pooled), timed on its own
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    eng.prefill_pool_all(0)
+    torch.cuda.synchronize()
+    e0.record()
+    eng.prefill_pool_all(0)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    prefill_gbs = batch.total * (LLAMA3_8B.slice_bytes + 2048) / prefill_ms / 1e6
+
+    if args.graph:
+        eng.capture()
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, device-resident inputs; the gather launches carry their own events
+    n_gather = args.steps * eng.L
+    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_gather)] \
+        if not args.graph else []
+    sampler = ClockSampler(local_rank)
+    launches_before = _native.launch_count
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    if args.graph:
+        for _ in range(args.steps):
+            eng.step()
+    else:
+        gi = 0
+        for _ in range(args.steps):
+            for l in range(eng.L):
+                eng.pool_layer(l)
+                eng.score_layer(l)
+                eng.topk_layer(l)
+                a, b = gev[gi]
+                gi += 1
+                a.record()
+                eng.gather_layer(l)
+                b.record()
+    t_end.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    launches = (_native.launch_count - launches_before) if not args.graph else eng.launches_per_step * args.steps
+    elapsed_ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    tokens_per_step_all = eng.tokens_scored_per_step() * world   # same batch size on every rank (weak scaling)
+    if world > 1:
+        tt = torch.tensor([float(eng.tokens_scored_per_step())], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.SUM)
+        tokens_per_step_all = float(tt.item())
+    value = tokens_per_step_all / (ms_per_step * 1e-3)
+
+    gather_ms = [a.elapsed_time(b) for a, b in gev]
+    gather_avg_ms = statistics.fmean(gather_ms) if gather_ms else None
+
+    # ---- per-stage breakdown (separate instrumented pass, same inputs)
+    stage_names = ("pool", "score", "topk", "gather")
+    acc = {s: [] for s in stage_names}
+    evs = []
+    for l in range(eng.L):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        marks[0].record()
+        eng.pool_layer(l)
+        marks[1].record()
+        eng.score_layer(l)
+        marks[2].record()
+        eng.topk_layer(l)
+        marks[3].record()
+        eng.gather_layer(l)
+        marks[4].record()
+        evs.append(marks)
+    torch.cuda.synchronize()
+    for marks in evs:
+        for i, s in enumerate(stage_names):
+            acc[s].append(marks[i].elapsed_time(marks[i + 1]) * 1e3)
+    stages_us = {s: statistics.median(v) for s, v in acc.items()}
+    retrieval_us = stages_us["pool"] + stages_us["score"] + stages_us["topk"]
+
+    # ---- end to end with host buffers
+    eng.graph = None
+    eng.alloc_host()
+    for _ in range(2):
+        eng.step_host()
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step_host()
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = tokens_per_step_all / e2e_s
+
+    peak, peak_kind = measured_peaks()
+    roofline = None
+    if gather_avg_ms:
+        achieved = eng.bytes_gather_layer() / (gather_avg_ms * 1e-3) / 1e9
+        traffic = None
+        if NCU_GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE is not None:
+            traffic = eng.bytes_gather_layer() * NCU_GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE
+        roofline = {"kernel": "xfer_bulk_kernel (gather of selected K,V blocks, one layer)", "bound": "hbm",
+                    "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": traffic, "algorithmic_bytes_per_launch": eng.bytes_gather_layer(),
+                    "avg_launch_us": gather_avg_ms * 1e3}
+    stage_gbs = {
+        "score": eng.bytes_score_layer() / (stages_us["score"] * 1e-6) / 1e9,
+        "gather": eng.bytes_gather_layer() / (stages_us["gather"] * 1e-6) / 1e9,
+        "pool_decode": eng.bytes_pool_layer() / (stages_us["pool"] * 1e-6) / 1e9,
+        "pool_prefill": prefill_gbs,
+    }
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            from oracle import oracle as orc
+            if orc.have_ref():
+                tps, dt, cores = reference_cpu_run(batch, 8, 10, 1)
+                cpu_baseline = {"value": tps, "unit": UNIT, "cores": cores, "kind": "reference",
+                                "sample": "10 timed passes over 8 of the 32 layers of the same 64-request batch, "
+                                          "score + top-k only (compiled RetrievalWorkerBackend, one submit per request)",
+                                "ms_per_layer": dt * 1e3 / 8}
+            else:
+                cpu_baseline = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                "sample": "oracle/_ref not present"}
+        except Exception as exc:  # the baseline must never take the benchmark down
+            cpu_baseline = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                            "sample": f"failed: {exc}"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(batch, extra={"cuda_graph": bool(args.graph), "layers": eng.L}),
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
+                       "samples": clocks["samples"]},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_s * 1e3,
+                    "h2d_bytes_per_step": eng.h2d_bytes_per_step, "d2h_bytes_per_step": eng.d2h_bytes_per_step},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "cpu_baseline": cpu_baseline,
+            "stages_us_per_layer": stages_us,
+            "retrieval_us_per_layer": retrieval_us,
+            "stage_gbs": stage_gbs,
+            "device_error": _native.device_error(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

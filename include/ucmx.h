@@ -1,0 +1,273 @@
+/*
+ * ucmx — C ABI of the B200 (sm_100a) sparse-KV retrieval and block-transfer library.
+ *
+ * Plain C: raw pointers, sizes and a CUDA stream handle; no C++ or framework types cross this
+ * boundary.  Every function returns an int32 status and never throws or aborts:
+ *     0        OK
+ *    -1        generic failure (a CUDA launch or runtime call failed, a wait timed out)
+ *    -50000    invalid parameter          -50001  out of memory
+ *    -50002    OS / CUDA runtime error    -50005  object not found
+ *    -50008    unsupported configuration
+ * These are the values of UC::Status in the reference (ucm/store/infra/status/status.h:32-45).
+ *
+ * Unless a comment says "host", every pointer is a device pointer valid on the device that owns
+ * `stream`.  All launches are asynchronous on `stream`; nothing here synchronises unless stated.
+ * "Reference" paths are relative to the UCM project root.
+ */
+#ifndef UCMX_H
+#define UCMX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UCMX_OK 0
+#define UCMX_ERROR (-1)
+#define UCMX_EPARAM (-50000)
+#define UCMX_EOOM (-50001)
+#define UCMX_EOSERROR (-50002)
+#define UCMX_ENOOBJ (-50005)
+#define UCMX_EUNSUPPORTED (-50008)
+
+typedef void* ucmx_stream_t; /* a cudaStream_t */
+
+/* Layout of one layer's paged K (or V) cache of bf16 elements: element (block, token, head, d) is
+ * at block*block_stride + token*token_stride + head*head_dim + d (strides in elements).  This is
+ * vLLM's [num_blocks, block_size, num_kv_heads, head_size] cache, the tensor the reference indexes
+ * as k_cache[ids] (ucm/sparse/esa/esa.py:265-266). */
+typedef struct ucmx_kv_geometry {
+    int64_t block_stride;
+    int64_t token_stride;
+    int32_t block_tokens;
+    int32_t n_kv_heads;
+    int32_t head_dim;
+    int32_t reserved;
+} ucmx_kv_geometry;
+
+/* Library version and the SM architecture the kernels were compiled for (100 for sm_100a). */
+int32_t ucmx_version(void);
+int32_t ucmx_compiled_arch(void);
+/* Text of the last CUDA error this thread's calls met ("" if none). Host. */
+const char* ucmx_last_error(void);
+/* Kernels never spin without limit: a wait on an asynchronous copy that does not complete gives
+ * up and records a code here (1 = a bulk copy did not land, 2 = a misaligned pointer pair was
+ * skipped) instead of hanging the device.  Reads the code (0 = none) and optionally clears it. */
+int32_t ucmx_device_error(int32_t* code, int32_t clear);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 1a — per-block key representatives by pooling.
+ * Replaces: `k_cache[ids].mean(1)` (ucm/sparse/esa/esa.py:265-266), GSA `copy_k`
+ * (ucm/sparse/gsa/gsa.py:640-652), KRepreComputer::ComputeKRepreBlock
+ * (ucm/sparse/gsa/offload_ops/src/k_repre.cpp:15-35) with VectorMeanImpl
+ * (.../vec_product.cpp:39-85), and the max/min/sum chunk_repre_method variants
+ * (ucm/sparse/kvcomp/kvcomp_config.py:56,116-120).
+ *
+ * For i in [0,n): rep = reduce over the tokens of block block_ids[i]; written to row
+ * out_slots[i] (or i when out_slots is NULL) of a table laid out [slot, n_kv_heads, n_rep, head_dim]
+ * at representative index rep_index.  mode: 0 mean, 1 max, 2 min, 3 sum.  Tokens are accumulated in
+ * fp32 in token order; the mean is sum*(1/block_tokens).  round_bf16 != 0 rounds the result to bf16
+ * (nearest even) before it is stored, which is what the reference keeps; out_f32 then receives the
+ * widened bf16 value.  Either of out_bf16 / out_f32 may be NULL. */
+#define UCMX_POOL_MEAN 0
+#define UCMX_POOL_MAX 1
+#define UCMX_POOL_MIN 2
+#define UCMX_POOL_SUM 3
+int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry* geom /* host */,
+                         const int32_t* block_ids, const int32_t* out_slots, int32_t n, int32_t mode,
+                         int32_t round_bf16, int32_t n_rep, int32_t rep_index, void* out_bf16,
+                         float* out_f32, ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 1b — KVComp sign-bit hash codes.
+ * Replaces: HashEncoder.compute_hash (ucm/sparse/kvcomp/hash_encoder.py:99-157) and its use on key
+ * blocks, extract_block_repre + transpose (ucm/sparse/kvcomp/kvcomp.py:314-318,342).
+ *
+ * Bit j of vector x is (sum_d x[d]*W[d][j] > 0), the sum taken as an fp32 fused-multiply-add chain
+ * over d = 0..dim-1; bits are packed LSB first (bit 8b+i is bit i of byte b).
+ * ucmx_hash_encode: x is bf16 [n_vec, dim] with row stride x_stride elements; out is
+ *   uint8 [n_vec, bits/8].
+ * ucmx_hash_encode_blocks: vectors are the (token, head) rows of paged blocks block_ids[i]; codes
+ *   of block i go to row out_slots[i] (or i) of a table uint8 [slot, n_kv_heads, block_tokens,
+ *   bits/8] when head_major != 0 (the layout KVComp keeps) or [slot, block_tokens, n_kv_heads,
+ *   bits/8] when head_major == 0 (compute_hash's own output order).
+ * w is bf16 [dim, bits] row major.  dim and bits must be multiples of 32; dim = head_dim. */
+int32_t ucmx_hash_encode(const void* x, int64_t n_vec, int64_t x_stride, const void* w, int32_t dim,
+                         int32_t bits, uint8_t* out, ucmx_stream_t stream);
+int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_geometry* geom /* host */,
+                                const int32_t* block_ids, const int32_t* out_slots, int32_t n,
+                                const void* w, int32_t bits, int32_t head_major, uint8_t* out,
+                                ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 2 prologue — per-KV-head query mean.
+ * Replaces: `query.view(ntok, kvH, -1, D).mean(2)` + fp32 cast (ucm/sparse/esa/esa.py:291-296,
+ * ucm/sparse/esa/retrieval/retrieval_worker.py:15-20) and TopkBlockSelector::ComputeQHeadMean
+ * (ucm/sparse/gsa/offload_ops/src/select_topk_block.cpp:101-114).
+ * q is bf16 [n_tok, n_q_heads, head_dim], tok_stride elements between tokens; out is fp32
+ * [n_tok, n_kv_heads*head_dim].  round_bf16 != 0 rounds each mean to bf16 first (the ESA/KVComp
+ * behaviour); 0 keeps fp32 (the GSA native behaviour).  If n_q_heads < n_kv_heads heads repeat. */
+int32_t ucmx_query_group_mean(const void* q, int32_t n_tok, int32_t n_q_heads, int32_t n_kv_heads,
+                              int32_t head_dim, int64_t tok_stride, int32_t round_bf16, float* out,
+                              ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 2a — query-to-block dot scores over a ragged batch.
+ * Replaces: the scoring loop of RetrievalWorkerBackend::worker_loop
+ * (ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:170-181) and
+ * TopkBlockSelector::ComputeBlockScore / ComputeKQDotScores
+ * (ucm/sparse/gsa/offload_ops/src/select_topk_block.cpp:53-99).
+ *
+ * Request r owns candidates [req_offsets[r], req_offsets[r+1]) (req_offsets has n_req+1 entries,
+ * total = req_offsets[n_req]).  Candidate c reads table row slot_ids[c] (or c if slot_ids is NULL);
+ * a negative slot id scores -inf.  The table is [slot, n_kv_heads, n_rep, head_dim], bf16
+ * (reps_dtype 0) or fp32 (reps_dtype 1).  q is fp32 [n_req, n_kv_heads*head_dim].
+ * score = scale * sum_h max_r dot(q[r,h,:], rep[slot,h,r,:]); with n_rep == 1 that is the plain
+ * dot product over n_kv_heads*head_dim the ESA backend takes. */
+#define UCMX_DT_BF16 0
+#define UCMX_DT_F32 1
+#define UCMX_DT_I32 2
+int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t n_rep,
+                       int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
+                       const float* q, int32_t n_req, int32_t total, float scale, float* out_scores,
+                       ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 2b — Hamming-similarity scores on packed hash codes (integer exact).
+ * Replaces: HashEncoder._unpack_hash + einsum("tid,njsd->tijsn") + sum
+ * (ucm/sparse/kvcomp/hash_encoder.py:159-219, ucm/sparse/kvcomp/kvcomp.py:233-247).
+ *
+ * codes is uint8 [slot, n_kv_heads, block_tokens, bits/8]; q_codes is uint8 [n_req, n_q_heads,
+ * bits/8].  score = sum over (i, j, s) of (bits - 2*popcount(q_i xor k_{j,s})) over every
+ * (query head i, key head j) pair when cross_head != 0 (what the reference's einsum does), or over
+ * matching heads only (i == j, needs n_q_heads == n_kv_heads) when cross_head == 0.
+ * bits must be a multiple of 128.  Ragged batch and slot_ids as in ucmx_score_dot. */
+int32_t ucmx_score_hamming(const uint8_t* codes, int32_t n_kv_heads, int32_t block_tokens,
+                           int32_t bits, const int32_t* req_offsets, const int32_t* slot_ids,
+                           const uint8_t* q_codes, int32_t n_q_heads, int32_t n_req, int32_t total,
+                           int32_t cross_head, int32_t* out_scores, ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 3 — per-request top-k over a ragged batch (radix select, one thread block per request).
+ * Replaces: std::partial_sort in RetrievalWorkerBackend::worker_loop (retrieval_backend.cpp:182-189),
+ * TopkBlockSelector::TopKImpl (select_topk_block.cpp:20-51), and torch.topk + sort
+ * (ucm/sparse/kvcomp/kvcomp.py:249-254).
+ *
+ * scores: fp32 (score_dtype UCMX_DT_F32) or int32 (UCMX_DT_I32), flat, ragged by req_offsets.
+ * k_per_req[r]: how many to select for request r.
+ * window_mode:
+ *   UCMX_WIN_NONE    plain top-k of all candidates (ESA); returns min(k, n) entries.
+ *   UCMX_WIN_FORCE   GSA TopKImpl: positions [0,start_win) and [n-end_win,n) are always selected
+ *                    and count toward k; the other k-start-end come from the middle.  If
+ *                    start+end >= n, k >= n or k == 0 every position is returned (identity).
+ *   UCMX_WIN_EXCLUDE KVComp: candidates are positions [start_win, n-end_win); min(k, size) of them
+ *                    are returned; if k >= n all of them are.  (KVComp's init_window_sz and
+ *                    local_window_sz-1.)
+ * order: UCMX_ORDER_SCORE_DESC (best first; needs k <= 8192) or UCMX_ORDER_INDEX_ASC.
+ * Equal scores: the candidate with the lower position wins (the reference's stable_sort does the
+ * same; partial_sort and torch.topk leave it unspecified).  -0.0 and +0.0 compare equal.
+ * Output row r starts at r*out_stride and holds at most out_stride entries; or, when out_offsets
+ * (n_req+1 entries) is given, it starts at out_offsets[r] and holds at most
+ * out_offsets[r+1]-out_offsets[r] (<= out_stride) entries, which packs the rows back to back.
+ * Entries beyond out_counts[r] are left untouched.  out_idx[j] is the candidate's position within
+ * its request, or id_map[req_offsets[r]+position] when id_map is given.  out_scores (same dtype as
+ * scores) may be NULL. */
+#define UCMX_WIN_NONE 0
+#define UCMX_WIN_FORCE 1
+#define UCMX_WIN_EXCLUDE 2
+#define UCMX_ORDER_SCORE_DESC 0
+#define UCMX_ORDER_INDEX_ASC 1
+int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
+                         const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
+                         int32_t window_mode, int32_t order, const int32_t* id_map,
+                         int32_t out_stride, const int32_t* out_offsets, int32_t* out_idx,
+                         void* out_scores, int32_t* out_counts, ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stage 4 — gather / scatter of paged KV block slices.
+ * Replaces: the per-block copies of UcmDramStore.load/dump
+ * (ucm/store/dramstore/dramstore_connector.py:112-166), PosixQueue::S2D/D2S's memcpy leg
+ * (ucm/store/nfsstore/tsf_task/posix_queue.cc:98-124) and CudaDevice::H2DBatchSync/D2HBatchSync with
+ * H2DKernel/D2HKernel (ucm/store/device/cuda/cuda_device.cu:47-81,180-211).
+ *
+ * planes: host array of n_planes (<= 8) base pointers (K cache, V cache, ... of one layer).
+ * For i in [0,n), p in [0,n_planes): slice_bytes bytes at planes[p] + block_ids[i]*block_stride_bytes
+ * are copied to (gather) or from (scatter) staging + (i*n_planes + p)*slice_bytes.  block_ids is a
+ * device array; negative ids are skipped.  staging may be device memory or page-locked host memory
+ * mapped into the device's address space (direct zero-copy transfer); pass staging_is_host != 0 in
+ * the latter case so that plain loads/stores are used instead of bulk async copies.
+ * slice_bytes, block_stride_bytes and all pointers must be multiples of 16. */
+int32_t ucmx_gather_blocks(const void* const* planes /* host */, int32_t n_planes,
+                           int64_t block_stride_bytes, const int32_t* block_ids, int32_t n,
+                           int64_t slice_bytes, void* staging, int32_t staging_is_host,
+                           ucmx_stream_t stream);
+int32_t ucmx_scatter_blocks(void* const* planes /* host */, int32_t n_planes,
+                            int64_t block_stride_bytes, const int32_t* block_ids, int32_t n,
+                            int64_t slice_bytes, const void* staging, int32_t staging_is_host,
+                            ucmx_stream_t stream);
+/* Pointer-pair form, the signature of IDevice::H2DBatchSync / D2HBatchSync
+ * (ucm/store/device/idevice.h:48-51) minus the blocking allocation: dst_ptrs/src_ptrs are DEVICE
+ * arrays of `number` addresses, `count` bytes each (multiple of 16). Asynchronous on stream. */
+int32_t ucmx_copy_batch(void* const* dst_ptrs, const void* const* src_ptrs, int32_t number,
+                        int64_t count, int32_t any_host_memory, ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Pinned host ring — IBufferedDevice::GetBuffer (ucm/store/device/ibuffered_device.h:32-62):
+ * one page-locked slab cut into n_slots slots of slot_bytes, handed out by index.
+ * acquire returns UCMX_ENOOBJ when no slot is free (the reference falls back to a fresh
+ * cudaMallocHost; callers here wait or split the batch instead). All host-side, thread safe. */
+typedef struct ucmx_ring ucmx_ring;
+int32_t ucmx_ring_create(size_t slot_bytes, size_t n_slots, ucmx_ring** out);
+int32_t ucmx_ring_acquire(ucmx_ring* ring, void** host_ptr, int32_t* slot_index);
+int32_t ucmx_ring_release(ucmx_ring* ring, int32_t slot_index);
+int32_t ucmx_ring_base(ucmx_ring* ring, void** host_ptr, size_t* slot_bytes, size_t* n_slots);
+int32_t ucmx_ring_destroy(ucmx_ring* ring);
+
+/* ---------------------------------------------------------------------------------------------
+ * Transfer tasks — TaskWaiter::Wait / TaskManager::Wait / Check
+ * (ucm/store/task/task_waiter.h:41-55, ucm/store/task/task_manager.cc:57-96): a task completes when
+ * the work recorded on its stream so far has run.  wait returns 0 on completion, -1 on timeout or
+ * CUDA failure (timeout_ms < 0 waits without limit); check never blocks. */
+typedef struct ucmx_task ucmx_task;
+int32_t ucmx_task_create(ucmx_task** out);
+int32_t ucmx_task_record(ucmx_task* task, ucmx_stream_t stream);
+int32_t ucmx_task_check(ucmx_task* task, int32_t* finished);
+int32_t ucmx_task_wait(ucmx_task* task, int64_t timeout_ms);
+int32_t ucmx_task_destroy(ucmx_task* task);
+
+/* ---------------------------------------------------------------------------------------------
+ * Retrieval back-end object — RetrievalWorkerBackend
+ * (ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:17-225): a table of n_items representatives
+ * of `dim` fp32 values; submit(query[b,dim], topk, indexes[b,max_idx] with -1 padding) -> request
+ * id; poll / wait / get_result(indices int32[b,topk], scores fp32[b,topk]).
+ * Here the table lives on the device (kept as bf16 when table_dtype == UCMX_DT_BF16, which is
+ * lossless for bf16-rounded representatives, else fp32) and a request is a stream-ordered
+ * score + top-k on a private stream instead of a job for a thread pool.
+ * Pointers named host_* are host memory; get_result copies min(topk, n_allowed) entries per row and
+ * pads the rest of the row with -1 / -inf, then forgets the request (as the reference does). */
+typedef struct ucmx_retrieval ucmx_retrieval;
+int32_t ucmx_retrieval_create(const float* host_data, int64_t n_items, int32_t dim,
+                              int32_t table_dtype, int32_t device, ucmx_retrieval** out);
+/* Overwrite rows slots[i] of the table with host_rows[i] (fp32 [n, dim]); stream-ordered with
+ * later submits. */
+int32_t ucmx_retrieval_update_rows(ucmx_retrieval* r, const int32_t* host_slots, int32_t n,
+                                   const float* host_rows);
+/* Device pointer of the table, for kernels (e.g. ucmx_pool_blocks) that fill it in place. */
+int32_t ucmx_retrieval_table(ucmx_retrieval* r, void** table, int32_t* table_dtype);
+int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_query, int32_t batch,
+                              int32_t query_dim, int32_t topk, const int32_t* host_indexes,
+                              int32_t max_idx, int32_t* req_id);
+int32_t ucmx_retrieval_poll(ucmx_retrieval* r, int32_t req_id, int32_t* ready);
+int32_t ucmx_retrieval_wait(ucmx_retrieval* r, int32_t req_id);
+int32_t ucmx_retrieval_result_shape(ucmx_retrieval* r, int32_t req_id, int32_t* batch,
+                                    int32_t* topk);
+int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, int32_t* host_indices,
+                                  float* host_scores);
+int32_t ucmx_retrieval_destroy(ucmx_retrieval* r);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UCMX_H */

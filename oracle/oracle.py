@@ -1,0 +1,293 @@
+"""numpy front-end of the CPU checker (oracle/ucm_oracle.c and, when built, oracle/_ref).
+
+TEST INFRASTRUCTURE ONLY.  The shipped package never imports this module; the test-suite, the
+smoke check and the benchmark's CPU-baseline leg do.  Each function forwards to the C restatement
+whose comment names the reference lines it follows.  bf16 arrays are carried as numpy uint16.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import importlib.util
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libucm_oracle.so")
+_REF_DIR = os.path.join(_HERE, "_ref")
+
+POOL_MEAN, POOL_MAX, POOL_MIN, POOL_SUM = 0, 1, 2, 3
+
+
+def build(ref: bool = True) -> None:
+    """Compile the C restatement, and the reference's own CPU sources when a checkout is present."""
+    targets = ["oracle"]
+    if ref and os.path.isdir(os.environ.get("UCM_REFERENCE", "/root/reference")):
+        targets.append("ref")
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    cmd = ["make", "-s", "-C", _HERE] + targets
+    if "UCM_REFERENCE" in os.environ:
+        cmd.append("REF=" + os.environ["UCM_REFERENCE"])
+    subprocess.run(cmd, check=True, env=env)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build(ref=False)
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.orc_bf16_round.restype = C.c_float
+        _lib.orc_bf16_round.argtypes = [C.c_float]
+        _lib.orc_store_offset.restype = C.c_int64
+        for n in ("orc_topk_esa", "orc_topk_gsa", "orc_topk_kvcomp", "orc_remap_resident"):
+            getattr(_lib, n).restype = C.c_int32
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return None if a is None else np.ascontiguousarray(a, dtype=dt)
+
+
+# ---------------------------------------------------------------- bf16 helpers
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even fp32 -> bf16 bit patterns (uint16)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    return ((u + 0x7FFF + lsb) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(h, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# --------------------------------------------------------------------- stages
+
+def pool_blocks(k_u16, block_ids, mode=POOL_MEAN, round_bf16=True):
+    """k_u16: uint16 [num_blocks, T, H, D] (dense paged cache). Returns fp32 [n, H*D]."""
+    k = _c(k_u16, np.uint16)
+    nb, T, H, D = k.shape
+    ids = _c(block_ids, np.int32)
+    out = np.empty((len(ids), H * D), np.float32)
+    lib().orc_pool_blocks(_p(k), C.c_int64(T * H * D), C.c_int64(H * D), C.c_int32(T),
+                          C.c_int32(H), C.c_int32(D), _p(ids), C.c_int32(len(ids)),
+                          C.c_int32(mode), C.c_int32(int(round_bf16)), _p(out))
+    return out
+
+
+def query_group_mean(q_u16, n_kv_heads, round_bf16=True):
+    """q_u16: uint16 [n_tok, Hq, D]. Returns fp32 [n_tok, n_kv_heads*D]."""
+    q = _c(q_u16, np.uint16)
+    nt, Hq, D = q.shape
+    out = np.empty((nt, n_kv_heads * D), np.float32)
+    lib().orc_query_group_mean(_p(q), C.c_int32(nt), C.c_int32(Hq), C.c_int32(n_kv_heads),
+                               C.c_int32(D), C.c_int64(Hq * D), C.c_int32(int(round_bf16)), _p(out))
+    return out
+
+
+def score_dot_esa(data_f32, req_offsets, slot_ids, q_f32):
+    data = _c(data_f32, np.float32)
+    off = _c(req_offsets, np.int32)
+    sl = _c(slot_ids, np.int32)
+    q = _c(q_f32, np.float32)
+    out = np.empty(int(off[-1]), np.float32)
+    lib().orc_score_dot_esa(_p(data), C.c_int32(data.shape[1]), _p(off), _p(sl), _p(q),
+                            C.c_int32(len(off) - 1), _p(out))
+    return out
+
+
+def score_dot_gsa(reps_f32, n_kv_heads, n_rep, head_dim, req_offsets, slot_ids, q_f32):
+    reps = _c(reps_f32, np.float32)
+    off = _c(req_offsets, np.int32)
+    sl = _c(slot_ids, np.int32)
+    q = _c(q_f32, np.float32)
+    out = np.empty(int(off[-1]), np.float32)
+    lib().orc_score_dot_gsa(_p(reps), C.c_int32(n_kv_heads), C.c_int32(n_rep), C.c_int32(head_dim),
+                            _p(off), _p(sl), _p(q), C.c_int32(len(off) - 1), _p(out))
+    return out
+
+
+def topk_esa(scores, k, id_map=None):
+    s = _c(scores, np.float32)
+    m = _c(id_map, np.int32)
+    n = len(s)
+    idx = np.empty(max(min(k, n), 1), np.int32)
+    sc = np.empty(max(min(k, n), 1), np.float32)
+    cnt = lib().orc_topk_esa(_p(s), C.c_int32(n), C.c_int32(k), _p(m), _p(idx), _p(sc))
+    return idx[:cnt], sc[:cnt]
+
+
+def topk_gsa(scores, k, start, end, cap=None):
+    s = _c(scores, np.float32)
+    n = len(s)
+    cap = n if cap is None else cap
+    idx = np.empty(max(cap, 1), np.int32)
+    cnt = lib().orc_topk_gsa(_p(s), C.c_int32(n), C.c_int32(k), C.c_int32(start), C.c_int32(end),
+                             C.c_int32(cap), _p(idx))
+    return idx[:cnt]
+
+
+def topk_kvcomp(scores_i32, k, init_win=1, local_win=2):
+    s = _c(scores_i32, np.int32)
+    n = len(s)
+    idx = np.empty(max(n, 1), np.int32)
+    cnt = lib().orc_topk_kvcomp(_p(s), C.c_int32(n), C.c_int32(k), C.c_int32(init_win),
+                                C.c_int32(local_win), _p(idx))
+    return idx[:cnt]
+
+
+def hash_encode(x_u16, w_u16):
+    """x_u16: uint16 [..., dim]; w_u16: uint16 [dim, bits]. Returns uint8 [..., bits/8]."""
+    x = _c(x_u16, np.uint16)
+    w = _c(w_u16, np.uint16)
+    dim, bits = w.shape
+    nv = x.size // dim
+    out = np.empty(x.shape[:-1] + (bits // 8,), np.uint8)
+    lib().orc_hash_encode(_p(x), C.c_int64(nv), _p(w), C.c_int32(dim), C.c_int32(bits), _p(out))
+    return out
+
+
+def hash_project(x_u16, w_u16):
+    x = _c(x_u16, np.uint16)
+    w = _c(w_u16, np.uint16)
+    dim, bits = w.shape
+    nv = x.size // dim
+    out = np.empty(x.shape[:-1] + (bits,), np.float32)
+    lib().orc_hash_project(_p(x), C.c_int64(nv), _p(w), C.c_int32(dim), C.c_int32(bits), _p(out))
+    return out
+
+
+def score_hamming(codes_u8, req_offsets, slot_ids, q_codes_u8, cross_head=True):
+    """codes_u8: uint8 [slots, H, T, bits/8]; q_codes_u8: uint8 [n_req, Hq, bits/8]."""
+    codes = _c(codes_u8, np.uint8)
+    _, H, T, nb = codes.shape
+    qc = _c(q_codes_u8, np.uint8)
+    off = _c(req_offsets, np.int32)
+    sl = _c(slot_ids, np.int32)
+    out = np.empty(int(off[-1]), np.int32)
+    lib().orc_score_hamming(_p(codes), C.c_int32(H), C.c_int32(T), C.c_int32(nb * 8), _p(off),
+                            _p(sl), _p(qc), C.c_int32(qc.shape[1]), C.c_int32(len(off) - 1),
+                            C.c_int32(int(cross_head)), _p(out))
+    return out
+
+
+def _plane_array(planes):
+    arr = (C.c_void_p * len(planes))()
+    for i, p in enumerate(planes):
+        arr[i] = p.ctypes.data
+    return arr
+
+
+def gather_blocks(planes, block_ids, slice_bytes, block_stride):
+    """planes: list of uint8 arrays (one per K/V plane). Returns uint8 [n, n_planes, slice_bytes]."""
+    ids = _c(block_ids, np.int32)
+    out = np.empty((len(ids), len(planes), slice_bytes), np.uint8)
+    lib().orc_gather_blocks(_plane_array(planes), C.c_int32(len(planes)), C.c_int64(block_stride),
+                            _p(ids), C.c_int32(len(ids)), C.c_int64(slice_bytes), _p(out))
+    return out
+
+
+def scatter_blocks(planes, block_ids, slice_bytes, block_stride, staging):
+    ids = _c(block_ids, np.int32)
+    st = _c(staging, np.uint8)
+    lib().orc_scatter_blocks(_plane_array(planes), C.c_int32(len(planes)), C.c_int64(block_stride),
+                             _p(ids), C.c_int32(len(ids)), C.c_int64(slice_bytes), _p(st))
+
+
+def remap_resident(resident_logical, slot_ids, selected):
+    res = _c(resident_logical, np.int32).copy()
+    sl = _c(slot_ids, np.int32)
+    sel = _c(selected, np.int32)
+    sel_phys = np.empty(max(len(sel), 1), np.int32)
+    ll = np.empty(max(len(sel), 1), np.int32)
+    lp = np.empty(max(len(sel), 1), np.int32)
+    n = lib().orc_remap_resident(_p(res), _p(sl), C.c_int32(len(sl)), _p(sel), C.c_int32(len(sel)),
+                                 _p(sel_phys), _p(ll), _p(lp))
+    return res, sel_phys[:len(sel)], ll[:n], lp[:n]
+
+
+def store_offset(block_tokens, heads_per_rank, head_dim, rank, tp_size, elem_bytes, layer, is_v,
+                 is_mla=False):
+    return int(lib().orc_store_offset(C.c_int32(block_tokens), C.c_int32(heads_per_rank),
+                                      C.c_int32(head_dim), C.c_int32(rank), C.c_int32(tp_size),
+                                      C.c_int32(elem_bytes), C.c_int32(layer), C.c_int32(int(is_v)),
+                                      C.c_int32(int(is_mla))))
+
+
+# ------------------------------------------------------- the compiled reference
+
+def have_ref() -> bool:
+    return (os.path.isdir(_REF_DIR)
+            and any(f.startswith("retrieval_backend") for f in os.listdir(_REF_DIR))
+            and os.path.exists(os.path.join(_REF_DIR, "libgsa_ref.so")))
+
+
+def ref_retrieval_backend():
+    """The reference's ESA pybind11 module (retrieval_backend.cpp), compiled unmodified."""
+    name = [f for f in os.listdir(_REF_DIR) if f.startswith("retrieval_backend")][0]
+    spec = importlib.util.spec_from_file_location("retrieval_backend", os.path.join(_REF_DIR, name))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules.setdefault("retrieval_backend", mod)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_gsa = None
+
+
+def ref_gsa() -> C.CDLL:
+    """The reference's GSA offload arithmetic (vec_product/k_repre/select_topk_block)."""
+    global _gsa
+    if _gsa is None:
+        _gsa = C.CDLL(os.path.join(_REF_DIR, "libgsa_ref.so"))
+    return _gsa
+
+
+def ref_gsa_k_repre(k_f32):
+    """k_f32: fp32 [n, H, T, D] (the layout the reference's KRepreComputer takes)."""
+    k = _c(k_f32, np.float32)
+    n, H, T, D = k.shape
+    out = np.empty((n, H * D), np.float32)
+    ref_gsa().gsa_ref_k_repre(_p(k), C.c_int64(H * T * D), C.c_uint32(n), C.c_uint32(H),
+                              C.c_uint32(T), C.c_uint32(D), _p(out))
+    return out
+
+
+def ref_gsa_scores(q_mean_f32, reps_f32, n_kv_heads, n_rep, head_dim):
+    q = _c(q_mean_f32, np.float32)
+    reps = _c(reps_f32, np.float32)
+    nb = reps.size // (n_kv_heads * n_rep * head_dim)
+    out = np.empty(nb, np.float32)
+    ref_gsa().gsa_ref_scores(_p(q), _p(reps), C.c_uint32(nb), C.c_uint32(n_kv_heads),
+                             C.c_uint32(n_rep), C.c_uint32(head_dim), _p(out))
+    return out
+
+
+def ref_gsa_select_topk(q_f32, reps_f32, n_kv_heads, n_q_heads, n_rep, head_dim, start, end, k):
+    q = _c(q_f32, np.float32).copy()
+    reps = _c(reps_f32, np.float32)
+    nb = reps.size // (n_kv_heads * n_rep * head_dim)
+    out = np.full(max(nb, k), -1, np.int32)
+    ref_gsa().gsa_ref_select_topk(_p(q), _p(reps), C.c_uint32(nb), C.c_uint32(n_kv_heads),
+                                  C.c_uint32(n_q_heads), C.c_uint32(n_rep), C.c_uint32(head_dim),
+                                  C.c_uint32(start), C.c_uint32(end), C.c_uint32(k), _p(out))
+    return out
+
+
+def ref_gsa_q_head_mean(q_f32, n_kv_heads):
+    q = _c(q_f32, np.float32).copy()
+    Hq, D = q.shape
+    ref_gsa().gsa_ref_q_head_mean(_p(q), C.c_uint32(n_kv_heads), C.c_uint32(Hq), C.c_uint32(D))
+    return q[:n_kv_heads].copy()

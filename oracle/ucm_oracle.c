@@ -1,0 +1,460 @@
+/*
+ * CPU restatement of the UCM sparse-KV retrieval and block-transfer path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are
+ * compared against.  Nothing in the shipped package imports, links or runs
+ * it; only the test-suite, the smoke check and the benchmark's CPU-baseline
+ * leg may.
+ *
+ * Every function names the reference lines (paths inside the UCM project)
+ * whose arithmetic it restates.  Parity status of each function:
+ *   - orc_score_dot_esa, orc_topk_esa : pinned against the compiled reference
+ *     ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp (bit-exact scores).
+ *   - orc_pool_blocks (fp32, unrounded), orc_score_dot_gsa, orc_topk_gsa :
+ *     pinned against the compiled reference ucm/sparse/gsa/offload_ops/src.
+ *   - orc_hash_encode, orc_unpack/hamming : pinned against vectors produced by
+ *     importing ucm/sparse/kvcomp/hash_encoder.py on CPU (tests/golden).
+ *   - torch expressions with no native twin (bf16-rounded mean, bf16 GQA query
+ *     mean, KVComp top-k slicing): pinned against vectors produced by running
+ *     those torch expressions on CPU (tests/golden); the reference ships no
+ *     known-answer test for them.
+ *
+ * Build: see oracle/Makefile (plain C99, -ffp-contract=off so that a*b+c is
+ * never fused and the summation matches the reference's x86-64 build).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ bf16 */
+
+static inline float bf16_to_f32(uint16_t h)
+{
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* round-to-nearest-even, NaN kept quiet: what torch's .to(bfloat16) does */
+static inline uint16_t f32_to_bf16(float f)
+{
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+float orc_bf16_round(float f) { return bf16_to_f32(f32_to_bf16(f)); }
+
+/* ------------------------------------------------------------ stage 1: pool
+ *
+ * rep[b, h, :] = reduce over the block's tokens of K[block_ids[b], t, h, :].
+ *
+ * mode 0 mean, 1 max, 2 min, 3 sum.
+ * Mean follows VectorMeanImpl (ucm/sparse/gsa/offload_ops/src/vec_product.cpp
+ * :349-387): start from token 0, add tokens 1..T-1 in order, multiply by
+ * 1.0f/T.  With round_bf16 != 0 the result is rounded to bf16 and widened
+ * again, which is what ESA stores: `k_cache[ids].mean(1)` in bf16 followed by
+ * `.to(float32)` (ucm/sparse/esa/esa.py:265-266, 363-364; GSA gsa.py:640-652).
+ * max/min/sum are the chunk_repre_method variants of
+ * ucm/sparse/kvcomp/kvcomp_config.py:56,116-120 (element-wise over tokens).
+ *
+ * k: bf16 paged cache; element (blk, t, h, d) at
+ *    blk*block_stride + t*token_stride + h*head_dim + d.
+ * out: fp32 [n, n_kv_heads*head_dim].
+ */
+void orc_pool_blocks(const uint16_t *k, int64_t block_stride, int64_t token_stride,
+                     int32_t block_tokens, int32_t n_kv_heads, int32_t head_dim,
+                     const int32_t *block_ids, int32_t n, int32_t mode, int32_t round_bf16,
+                     float *out)
+{
+    const int64_t E = (int64_t)n_kv_heads * head_dim;
+    const float inv = 1.0f / (float)block_tokens;
+    for (int32_t b = 0; b < n; ++b) {
+        const uint16_t *blk = k + (int64_t)block_ids[b] * block_stride;
+        float *o = out + (int64_t)b * E;
+        for (int64_t e = 0; e < E; ++e) o[e] = bf16_to_f32(blk[e]);
+        for (int32_t t = 1; t < block_tokens; ++t) {
+            const uint16_t *row = blk + (int64_t)t * token_stride;
+            for (int64_t e = 0; e < E; ++e) {
+                float v = bf16_to_f32(row[e]);
+                if (mode == 1) o[e] = v > o[e] ? v : o[e];
+                else if (mode == 2) o[e] = v < o[e] ? v : o[e];
+                else o[e] += v;
+            }
+        }
+        for (int64_t e = 0; e < E; ++e) {
+            if (mode == 0) o[e] *= inv;
+            if (round_bf16) o[e] = orc_bf16_round(o[e]);
+        }
+    }
+}
+
+/* ------------------------------------------------- stage 2 prologue: query
+ *
+ * qbar[t, h, :] = mean over the q-heads of KV group h.
+ * ESA/KVComp take it in bf16 (esa.py:291-293, kvcomp.py:220-223): fp32 sum,
+ * bf16 result, then cast to fp32 (retrieval_worker.py:16-18).  The GSA native
+ * path keeps fp32 (ComputeQHeadMean, select_topk_block.cpp:101-114).
+ * When n_q_heads < n_kv_heads the query head is repeated (esa.py:294-295).
+ * q: bf16 [n_tok, n_q_heads, head_dim] with tok_stride elements per token.
+ */
+void orc_query_group_mean(const uint16_t *q, int32_t n_tok, int32_t n_q_heads,
+                          int32_t n_kv_heads, int32_t head_dim, int64_t tok_stride,
+                          int32_t round_bf16, float *out)
+{
+    for (int32_t t = 0; t < n_tok; ++t) {
+        const uint16_t *qt = q + (int64_t)t * tok_stride;
+        float *o = out + (int64_t)t * n_kv_heads * head_dim;
+        if (n_q_heads >= n_kv_heads) {
+            int32_t g = n_q_heads / n_kv_heads;
+            float inv = 1.0f / (float)g;
+            for (int32_t h = 0; h < n_kv_heads; ++h)
+                for (int32_t d = 0; d < head_dim; ++d) {
+                    float acc = bf16_to_f32(qt[(int64_t)(h * g) * head_dim + d]);
+                    for (int32_t j = 1; j < g; ++j)
+                        acc += bf16_to_f32(qt[(int64_t)(h * g + j) * head_dim + d]);
+                    acc *= inv;
+                    o[h * head_dim + d] = round_bf16 ? orc_bf16_round(acc) : acc;
+                }
+        } else {
+            int32_t r = n_kv_heads / n_q_heads;
+            for (int32_t h = 0; h < n_kv_heads; ++h)
+                for (int32_t d = 0; d < head_dim; ++d)
+                    o[h * head_dim + d] = bf16_to_f32(qt[(int64_t)(h / r) * head_dim + d]);
+        }
+    }
+}
+
+/* ------------------------------------------------------ stage 2: dot scores
+ *
+ * ESA (retrieval_backend.cpp:170-181): for each allowed slot,
+ * score = sum over d of q[d]*data[slot*dim+d], accumulated left to right in
+ * fp32 starting from 0.
+ * Ragged batch: request r owns candidates [req_offsets[r], req_offsets[r+1]);
+ * slot_ids may be NULL (slot = flat candidate index).
+ */
+void orc_score_dot_esa(const float *data, int32_t dim, const int32_t *req_offsets,
+                       const int32_t *slot_ids, const float *q, int32_t n_req, float *out)
+{
+    for (int32_t r = 0; r < n_req; ++r) {
+        const float *qr = q + (int64_t)r * dim;
+        for (int32_t c = req_offsets[r]; c < req_offsets[r + 1]; ++c) {
+            int64_t slot = slot_ids ? slot_ids[c] : c;
+            const float *row = data + slot * dim;
+            float s = 0.0f;
+            for (int32_t d = 0; d < dim; ++d) s += qr[d] * row[d];
+            out[c] = s;
+        }
+    }
+}
+
+/* GSA (select_topk_block.cpp:53-76): reps [slot, kvH, n_rep, D];
+ * score = sum over kv heads of max over reps of dot(qbar_h, rep).
+ * The dot is taken left to right here; the reference's SIMD variants use a
+ * 16-lane (AVX-512) or 8-lane tree, so agreement is to rounding, not bits. */
+void orc_score_dot_gsa(const float *reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                       const int32_t *req_offsets, const int32_t *slot_ids, const float *q,
+                       int32_t n_req, float *out)
+{
+    const int64_t row = (int64_t)n_kv_heads * n_rep * head_dim;
+    for (int32_t r = 0; r < n_req; ++r) {
+        const float *qr = q + (int64_t)r * n_kv_heads * head_dim;
+        for (int32_t c = req_offsets[r]; c < req_offsets[r + 1]; ++c) {
+            int64_t slot = slot_ids ? slot_ids[c] : c;
+            const float *blk = reps + slot * row;
+            float total = 0.0f;
+            for (int32_t h = 0; h < n_kv_heads; ++h) {
+                float best = -3.402823466e+38f;
+                for (int32_t j = 0; j < n_rep; ++j) {
+                    const float *kv = blk + ((int64_t)h * n_rep + j) * head_dim;
+                    float s = 0.0f;
+                    for (int32_t d = 0; d < head_dim; ++d) s += qr[h * head_dim + d] * kv[d];
+                    best = fmaxf(best, s);
+                }
+                total += best;
+            }
+            out[c] = total;
+        }
+    }
+}
+
+/* ------------------------------------------------------------ stage 3: top-k */
+
+typedef struct { float s; int32_t i; } orc_pair;
+
+static int cmp_desc_stable(const void *a, const void *b)
+{
+    const orc_pair *x = (const orc_pair *)a, *y = (const orc_pair *)b;
+    if (x->s > y->s) return -1;
+    if (x->s < y->s) return 1;
+    return (x->i > y->i) - (x->i < y->i);
+}
+
+/* ESA (retrieval_backend.cpp:182-189): the k best of one request's candidates
+ * in descending score order; returns min(k, n) entries.  std::partial_sort is
+ * not stable, so equal scores may come out in any order there; this
+ * restatement breaks ties by the lower candidate position.
+ * out_idx holds id_map[position] when id_map is given (the reference returns
+ * slot ids), else the position. Returns the count written. */
+int32_t orc_topk_esa(const float *scores, int32_t n, int32_t k, const int32_t *id_map,
+                     int32_t *out_idx, float *out_scores)
+{
+    orc_pair *p = (orc_pair *)malloc(sizeof(orc_pair) * (size_t)(n > 0 ? n : 1));
+    for (int32_t i = 0; i < n; ++i) { p[i].s = scores[i]; p[i].i = i; }
+    qsort(p, (size_t)n, sizeof(orc_pair), cmp_desc_stable);
+    int32_t m = k < n ? k : n;
+    if (m < 0) m = 0;
+    for (int32_t j = 0; j < m; ++j) {
+        out_idx[j] = id_map ? id_map[p[j].i] : p[j].i;
+        if (out_scores) out_scores[j] = p[j].s;
+    }
+    free(p);
+    return m;
+}
+
+static int cmp_int(const void *a, const void *b)
+{
+    int32_t x = *(const int32_t *)a, y = *(const int32_t *)b;
+    return (x > y) - (x < y);
+}
+
+/* GSA (TopkBlockSelector::TopKImpl, select_topk_block.cpp:20-51): force the
+ * first `start` and last `end` blocks, fill the rest of k from the middle by
+ * descending score (stable: lower index wins ties), return ascending indices.
+ * Degenerate inputs (start+end >= n, k >= n, k == 0) return the identity.
+ * The reference writes n entries in the degenerate case even when its buffer
+ * holds fewer; here at most `cap` entries are written.  Returns the count. */
+int32_t orc_topk_gsa(const float *scores, int32_t n, int32_t k, int32_t start, int32_t end,
+                     int32_t cap, int32_t *out_idx)
+{
+    int32_t cnt = 0;
+    if (start + end >= n || k >= n || k == 0) {
+        for (int32_t i = 0; i < n && cnt < cap; ++i) out_idx[cnt++] = i;
+        return cnt;
+    }
+    int32_t mid = k - start - end;
+    int32_t total = start + (mid > 0 ? mid : 0) + end;
+    int32_t *tmp = (int32_t *)malloc(sizeof(int32_t) * (size_t)total);
+    int32_t w = 0;
+    for (int32_t i = 0; i < start; ++i) tmp[w++] = i;
+    if (mid > 0) {
+        int32_t m = n - start - end;
+        orc_pair *p = (orc_pair *)malloc(sizeof(orc_pair) * (size_t)m);
+        for (int32_t i = 0; i < m; ++i) { p[i].s = scores[start + i]; p[i].i = start + i; }
+        qsort(p, (size_t)m, sizeof(orc_pair), cmp_desc_stable);
+        for (int32_t j = 0; j < mid; ++j) tmp[w++] = p[j].i;
+        free(p);
+    }
+    for (int32_t i = 0; i < end; ++i) tmp[w++] = n - end + i;
+    qsort(tmp, (size_t)w, sizeof(int32_t), cmp_int);
+    for (int32_t i = 0; i < w && cnt < cap; ++i) out_idx[cnt++] = tmp[i];
+    free(tmp);
+    return cnt;
+}
+
+/* KVComp (kvcomp.py:202-254): candidates are blocks [init, n-local+1); when
+ * k >= n every one of them is returned; otherwise the k best of that range,
+ * reported as ascending block ids.  torch.topk's tie order is unspecified;
+ * ties go to the lower block here.  Scores are exact integers.  */
+int32_t orc_topk_kvcomp(const int32_t *scores, int32_t n, int32_t k, int32_t init_win,
+                        int32_t local_win, int32_t *out_idx)
+{
+    int32_t lo = init_win, hi = n - local_win + 1;
+    int32_t cnt = 0;
+    if (k >= n) {
+        for (int32_t i = lo; i < hi; ++i) out_idx[cnt++] = i;
+        return cnt;
+    }
+    int32_t m = hi - lo;
+    if (m <= 0) return 0;
+    orc_pair *p = (orc_pair *)malloc(sizeof(orc_pair) * (size_t)m);
+    for (int32_t i = 0; i < m; ++i) { p[i].s = (float)scores[lo + i]; p[i].i = lo + i; }
+    /* |score| <= 2^24 is exact in fp32 for the sizes used; guard anyway */
+    qsort(p, (size_t)m, sizeof(orc_pair), cmp_desc_stable);
+    int32_t take = k < m ? k : m;
+    for (int32_t j = 0; j < take; ++j) out_idx[cnt++] = p[j].i;
+    free(p);
+    qsort(out_idx, (size_t)cnt, sizeof(int32_t), cmp_int);
+    return cnt;
+}
+
+/* ------------------------------------------------------- stage 1: hash codes
+ *
+ * HashEncoder.compute_hash (ucm/sparse/kvcomp/hash_encoder.py:99-157):
+ * bit j of a vector x is (sum_d x[d]*W[d,j] > 0); bits are packed LSB first,
+ * 8 per byte (:139-149).  The reference takes the sum inside a library GEMM
+ * whose accumulation order is unspecified; this restatement fixes it as the
+ * fp32 fused multiply-add chain over d = 0..dim-1 starting from 0 (each bf16
+ * product is exact in fp32, so only the order of additions is a choice).
+ * x: bf16 [n_vec, dim]; w: bf16 [dim, bits]; out: uint8 [n_vec, bits/8].
+ */
+void orc_hash_encode(const uint16_t *x, int64_t n_vec, const uint16_t *w, int32_t dim,
+                     int32_t bits, uint8_t *out)
+{
+    const int32_t nbytes = bits / 8;
+    float *wf = (float *)malloc(sizeof(float) * (size_t)dim * bits);
+    float *acc = (float *)malloc(sizeof(float) * (size_t)bits);
+    for (int64_t i = 0; i < (int64_t)dim * bits; ++i) wf[i] = bf16_to_f32(w[i]);
+    for (int64_t v = 0; v < n_vec; ++v) {
+        const uint16_t *xv = x + v * dim;
+        for (int32_t j = 0; j < bits; ++j) acc[j] = 0.0f;
+        for (int32_t d = 0; d < dim; ++d) {
+            float xd = bf16_to_f32(xv[d]);
+            const float *wr = wf + (int64_t)d * bits;
+            for (int32_t j = 0; j < bits; ++j) acc[j] = fmaf(xd, wr[j], acc[j]);
+        }
+        uint8_t *o = out + v * nbytes;
+        for (int32_t b = 0; b < nbytes; ++b) {
+            uint8_t byte = 0;
+            for (int32_t i = 0; i < 8; ++i)
+                if (acc[b * 8 + i] > 0.0f) byte |= (uint8_t)(1u << i);
+            o[b] = byte;
+        }
+    }
+    free(wf);
+    free(acc);
+}
+
+/* The projection margins themselves, for tests that want to know how close to
+ * zero a bit's pre-sign value was.  out: fp32 [n_vec, bits]. */
+void orc_hash_project(const uint16_t *x, int64_t n_vec, const uint16_t *w, int32_t dim,
+                      int32_t bits, float *out)
+{
+    for (int64_t v = 0; v < n_vec; ++v)
+        for (int32_t j = 0; j < bits; ++j) {
+            float a = 0.0f;
+            for (int32_t d = 0; d < dim; ++d)
+                a = fmaf(bf16_to_f32(x[v * dim + d]), bf16_to_f32(w[(int64_t)d * bits + j]), a);
+            out[v * bits + j] = a;
+        }
+}
+
+/* --------------------------------------------------- stage 2: Hamming scores
+ *
+ * kvcomp.py:233-247: codes are unpacked to +-1 (hash_encoder.py:159-219) and
+ * contracted with einsum "tid,njsd->tijsn", then summed over t, i, j, s.  For
+ * one query token that is
+ *   score[n] = sum_i sum_j sum_s (bits - 2*popcount(q_i xor k_{n,j,s}))
+ * over EVERY (query head i, key head j) pair when cross_head != 0.  With
+ * cross_head == 0 only matching heads (i == j) are paired.
+ * codes: uint8 [slot, n_kv_heads, block_tokens, bits/8]
+ * q_codes: uint8 [n_req, n_q_heads, bits/8]; out: int32 per candidate.
+ */
+void orc_score_hamming(const uint8_t *codes, int32_t n_kv_heads, int32_t block_tokens,
+                       int32_t bits, const int32_t *req_offsets, const int32_t *slot_ids,
+                       const uint8_t *q_codes, int32_t n_q_heads, int32_t n_req,
+                       int32_t cross_head, int32_t *out)
+{
+    const int32_t nb = bits / 8;
+    const int64_t row = (int64_t)n_kv_heads * block_tokens * nb;
+    for (int32_t r = 0; r < n_req; ++r) {
+        const uint8_t *qr = q_codes + (int64_t)r * n_q_heads * nb;
+        for (int32_t c = req_offsets[r]; c < req_offsets[r + 1]; ++c) {
+            int64_t slot = slot_ids ? slot_ids[c] : c;
+            const uint8_t *blk = codes + slot * row;
+            int64_t total = 0;
+            for (int32_t j = 0; j < n_kv_heads; ++j)
+                for (int32_t s = 0; s < block_tokens; ++s) {
+                    const uint8_t *kc = blk + ((int64_t)j * block_tokens + s) * nb;
+                    for (int32_t i = 0; i < n_q_heads; ++i) {
+                        if (!cross_head && i != j) continue;
+                        const uint8_t *qc = qr + (int64_t)i * nb;
+                        int32_t ham = 0;
+                        for (int32_t b = 0; b < nb; ++b)
+                            ham += __builtin_popcount((unsigned)(qc[b] ^ kc[b]));
+                        total += bits - 2 * ham;
+                    }
+                }
+            out[c] = (int32_t)total;
+        }
+    }
+}
+
+/* ------------------------------------------------ stage 4: gather / scatter
+ *
+ * What UcmDramStore.dump/load (ucm/store/dramstore/dramstore_connector.py
+ * :112-166) and H2DKernel/D2HKernel (ucm/store/device/cuda/cuda_device.cu
+ * :47-69) do per block: copy slice_bytes between block slot id*block_stride of
+ * each plane (K, V) and a contiguous staging area laid out
+ * [i][plane][slice_bytes].
+ */
+void orc_gather_blocks(const uint8_t *const *planes, int32_t n_planes, int64_t block_stride,
+                       const int32_t *block_ids, int32_t n, int64_t slice_bytes, uint8_t *staging)
+{
+    for (int32_t i = 0; i < n; ++i)
+        for (int32_t p = 0; p < n_planes; ++p)
+            memcpy(staging + ((int64_t)i * n_planes + p) * slice_bytes,
+                   planes[p] + (int64_t)block_ids[i] * block_stride, (size_t)slice_bytes);
+}
+
+void orc_scatter_blocks(uint8_t *const *planes, int32_t n_planes, int64_t block_stride,
+                        const int32_t *block_ids, int32_t n, int64_t slice_bytes,
+                        const uint8_t *staging)
+{
+    for (int32_t i = 0; i < n; ++i)
+        for (int32_t p = 0; p < n_planes; ++p)
+            memcpy(planes[p] + (int64_t)block_ids[i] * block_stride,
+                   staging + ((int64_t)i * n_planes + p) * slice_bytes, (size_t)slice_bytes);
+}
+
+/* ---------------------------------------- stage 3 -> 4 glue: resident remap
+ *
+ * GSAPrefetchEngineC::GetHitAndMissBlock / RunPrefetchH2D / RunOneBsPrefetch /
+ * LoadKVToHBM (ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp:206-322), for one
+ * (request, layer):
+ *   resident_logical[s] = logical block held by physical slot s of this
+ *   request (-1 = holds nothing), slot_ids[s] = its physical block id.
+ *   Selected logical blocks already resident are hits and stay where they are;
+ *   the misses, in selection order, take the free slots (slots whose logical
+ *   block is not selected) in ascending slot position.
+ * Outputs: sel_phys[j] = physical block id serving selected[j] (or -1 when no
+ * free slot was left), load_logical/load_phys = the (miss -> slot) load list,
+ * resident_logical updated in place.  Returns the number of loads.
+ */
+int32_t orc_remap_resident(int32_t *resident_logical, const int32_t *slot_ids, int32_t n_slots,
+                           const int32_t *selected, int32_t n_sel, int32_t *sel_phys,
+                           int32_t *load_logical, int32_t *load_phys)
+{
+    uint8_t *keep = (uint8_t *)calloc((size_t)(n_slots > 0 ? n_slots : 1), 1);
+    for (int32_t j = 0; j < n_sel; ++j) {
+        sel_phys[j] = -1;
+        for (int32_t s = 0; s < n_slots; ++s)
+            if (resident_logical[s] == selected[j] && selected[j] >= 0) {
+                sel_phys[j] = slot_ids[s];
+                keep[s] = 1;
+                break;
+            }
+    }
+    int32_t n_load = 0, s = 0;
+    for (int32_t j = 0; j < n_sel; ++j) {
+        if (sel_phys[j] != -1) continue;
+        while (s < n_slots && keep[s]) ++s;
+        if (s >= n_slots) break;
+        keep[s] = 1;
+        resident_logical[s] = selected[j];
+        sel_phys[j] = slot_ids[s];
+        load_logical[n_load] = selected[j];
+        load_phys[n_load] = slot_ids[s];
+        ++n_load;
+    }
+    free(keep);
+    return n_load;
+}
+
+/* Byte offset of one rank's K (or V) slice of one layer inside a stored block:
+ * get_offset, ucm/sparse/esa/esa.py:124-135. */
+int64_t orc_store_offset(int32_t block_tokens, int32_t heads_per_rank, int32_t head_dim,
+                         int32_t rank, int32_t tp_size, int32_t elem_bytes, int32_t layer,
+                         int32_t is_v, int32_t is_mla)
+{
+    int64_t k_sz = (int64_t)block_tokens * heads_per_rank * head_dim * elem_bytes;
+    int64_t v_sz = is_mla ? 0 : k_sz;
+    int64_t layer_sz = (k_sz + v_sz) * tp_size;
+    int64_t k_off = is_mla ? layer_sz * layer : layer_sz * layer + layer_sz / tp_size * rank;
+    return is_v ? k_off + k_sz : k_off;
+}

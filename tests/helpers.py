@@ -1,0 +1,70 @@
+"""Seeded inputs shared by the golden-vector generator and the tests (numpy only, so that the
+same bits come out on every machine). bf16 tensors are carried as uint16 bit patterns."""
+import numpy as np
+
+
+def f32_to_bf16(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    return ((u + 0x7FFF + lsb) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(h):
+    return (np.ascontiguousarray(h, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def randn_bf16(rng, shape, scale=1.0):
+    return f32_to_bf16(rng.standard_normal(shape, dtype=np.float32) * np.float32(scale))
+
+
+def bf16_ulp_distance(a_u16, b_u16):
+    """Distance in bf16 steps between two bf16 bit arrays (sign-magnitude aware)."""
+    def key(u):
+        u = u.astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
+    return np.abs(key(a_u16) - key(b_u16))
+
+
+def ragged_offsets(counts):
+    off = np.zeros(len(counts) + 1, np.int32)
+    off[1:] = np.cumsum(counts)
+    return off
+
+
+# ---- the fixed small cases behind tests/golden/golden.npz ---------------------------------------
+
+def case_pool(seed=1001):
+    rng = np.random.default_rng(seed)
+    k = randn_bf16(rng, (12, 128, 8, 128))
+    ids = rng.permutation(12)[:9].astype(np.int32)
+    return k, ids
+
+
+def case_qmean(seed=1002):
+    rng = np.random.default_rng(seed)
+    return randn_bf16(rng, (5, 32, 128))
+
+
+def case_esa(seed=1003):
+    rng = np.random.default_rng(seed)
+    data = bf16_to_f32(randn_bf16(rng, (300, 1024), 0.09))
+    query = bf16_to_f32(randn_bf16(rng, (3, 1024)))
+    idx = np.full((3, 100), -1, np.int32)
+    for r, n in enumerate((100, 37, 64)):
+        idx[r, :n] = rng.permutation(300)[:n]
+    return data, query, idx, 16
+
+
+def case_gsa(seed=1004, n_rep=1):
+    rng = np.random.default_rng(seed + n_rep)
+    reps = bf16_to_f32(randn_bf16(rng, (40, 8, n_rep, 128), 0.09))
+    q = bf16_to_f32(randn_bf16(rng, (32, 128)))
+    return q, reps, dict(start=2, end=4, k=12)
+
+
+def case_hash(seed=1005):
+    rng = np.random.default_rng(seed)
+    w = randn_bf16(rng, (128, 128), 2.0)           # HashEncoder draws N(0, std=2)
+    q = randn_bf16(rng, (1, 8, 128))                # one decode token, 8 (group-mean) heads
+    keys = randn_bf16(rng, (7, 16, 8, 128))         # 7 blocks of 16 tokens, 8 kv heads
+    return w, q, keys

@@ -1,0 +1,282 @@
+// Stage 3: per-request top-k over a ragged batch — one thread block per request.
+//
+// Selection is a most-significant-digit radix select (4 passes of 8 bits over order-preserving
+// uint32 keys) that finds the k-th largest key exactly; an ordered compaction then emits every
+// candidate above the threshold plus the first few equal to it, so ties always go to the lower
+// position (what std::stable_sort gives in TopkBlockSelector::TopKImpl,
+// ucm/sparse/gsa/offload_ops/src/select_topk_block.cpp:39-42).  Index-ascending output falls out of
+// the compaction; score-descending output (RetrievalWorkerBackend's partial_sort order,
+// ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:182-189) adds a bitonic sort of the k winners
+// in shared memory.  Scores were written by the scoring kernel a moment earlier and are re-read
+// from L2, so the passes cost latency, not HBM traffic.
+#include "common.cuh"
+
+namespace ucmx {
+namespace {
+
+struct TopkParams {
+    const uint32_t* scores;  // raw 32-bit words (fp32 or int32)
+    int32_t is_float;
+    const int32_t* offsets;
+    const int32_t* k_per_req;
+    int32_t start_win, end_win, window_mode, order;
+    const int32_t* id_map;
+    int32_t out_stride;
+    const int32_t* out_offsets;
+    int32_t* out_idx;
+    uint32_t* out_scores;
+    int32_t* out_counts;
+};
+
+__device__ __forceinline__ uint32_t to_key(uint32_t bits, bool is_float)
+{
+    if (!is_float) return bits ^ 0x80000000u;
+    if ((bits << 1) == 0) bits = 0;  // -0.0 == +0.0
+    return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
+__device__ __forceinline__ uint32_t from_key(uint32_t key, bool is_float)
+{
+    if (!is_float) return key ^ 0x80000000u;
+    return (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+}
+
+// exclusive prefix sum of a 0/1 flag over the thread block, in thread order; returns the prefix
+// and leaves the block total in `total`.  s_warp needs 32 ints.  Two barriers.
+__device__ __forceinline__ int block_excl_scan_flag(bool flag, int* s_warp, int& total)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    const unsigned b = __ballot_sync(0xffffffffu, flag);
+    const int in_warp = __popc(b & ((1u << lane) - 1u));
+    if (lane == 0) s_warp[warp] = __popc(b);
+    __syncthreads();
+    int before = 0, tot = 0;
+    for (int w = 0; w < nwarp; ++w) {
+        const int v = s_warp[w];
+        if (w < warp) before += v;
+        tot += v;
+    }
+    __syncthreads();
+    total = tot;
+    return before + in_warp;
+}
+
+__global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
+{
+    extern __shared__ __align__(16) unsigned long long s_sort[];  // score-descending order only
+    __shared__ uint32_t s_hist[256];
+    __shared__ int s_warp[32];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_krem;
+
+    const int r = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int base = __ldg(p.offsets + r);
+    const int n = __ldg(p.offsets + r + 1) - base;
+    const int k = __ldg(p.k_per_req + r);
+    const bool is_float = p.is_float != 0;
+    const uint32_t* sc = p.scores + base;
+    const int64_t orow = p.out_offsets ? (int64_t)__ldg(p.out_offsets + r) : (int64_t)r * p.out_stride;
+    const int cap = p.out_offsets ? min(__ldg(p.out_offsets + r + 1) - (int)orow, p.out_stride) : p.out_stride;
+
+    int lo = 0, hi = n, kk = 0, fstart = 0, fend = 0;
+    bool identity = false;
+    if (p.window_mode == UCMX_WIN_FORCE) {
+        if (p.start_win + p.end_win >= n || k >= n || k == 0) {
+            identity = true;
+        } else {
+            lo = p.start_win;
+            hi = n - p.end_win;
+            kk = max(k - p.start_win - p.end_win, 0);
+            fstart = p.start_win;
+            fend = p.end_win;
+        }
+    } else if (p.window_mode == UCMX_WIN_EXCLUDE) {
+        lo = min(max(p.start_win, 0), n);
+        hi = max(n - max(p.end_win, 0), lo);
+        kk = (k >= n) ? (hi - lo) : min(max(k, 0), hi - lo);
+    } else {
+        kk = min(max(k, 0), n);
+    }
+
+    if (identity) {
+        const int cnt = min(n, cap);
+        for (int i = tid; i < cnt; i += blockDim.x) {
+            p.out_idx[orow + i] = p.id_map ? __ldg(p.id_map + base + i) : i;
+            if (p.out_scores) p.out_scores[orow + i] = sc[i];
+        }
+        if (tid == 0) p.out_counts[r] = cnt;
+        return;
+    }
+
+    const int range = hi - lo;
+    const bool all = kk >= range;  // everything in [lo, hi) is selected
+    uint32_t T = 0;
+    int need = 0;
+
+    if (!all && kk > 0) {
+        if (tid == 0) {
+            s_prefix = 0;
+            s_krem = kk;
+        }
+        uint32_t mask = 0;
+#pragma unroll 1
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = tid; i < 256; i += blockDim.x) s_hist[i] = 0;
+            __syncthreads();
+            const uint32_t prefix = s_prefix;
+            for (int i = lo + tid; i < hi; i += blockDim.x) {
+                const uint32_t key = to_key(sc[i], is_float);
+                if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid < 32) {
+                // lane l owns buckets 255-8l .. 248-8l, scanned from the largest digit down
+                uint32_t h[8];
+                uint32_t sum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    h[j] = s_hist[255 - 8 * tid - j];
+                    sum += h[j];
+                }
+                uint32_t incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (tid >= o) incl += v;
+                }
+                uint32_t before = incl - sum;
+                const uint32_t krem = (uint32_t)s_krem;
+                if (before < krem && krem <= incl) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (before < krem && krem <= before + h[j]) {
+                            s_prefix = prefix | ((uint32_t)(255 - 8 * tid - j) << shift);
+                            s_krem = (int)(krem - before);
+                            before = 0xffffffffu;  // stop
+                        } else if (before != 0xffffffffu) {
+                            before += h[j];
+                        }
+                    }
+                }
+            }
+            mask |= 0xffu << shift;
+            __syncthreads();
+        }
+        T = s_prefix;
+        need = s_krem;
+    }
+
+    // ordered compaction over all positions
+    const bool desc = p.order == UCMX_ORDER_SCORE_DESC;
+    int out_base = 0, eq_base = 0;
+    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
+        const int i = c0 + tid;
+        bool forced = false, gt = false, eq = false;
+        uint32_t key = 0;
+        if (i < n) {
+            forced = (i < fstart) || (i >= n - fend);
+            const bool in_range = i >= lo && i < hi;
+            if (in_range || forced) key = to_key(sc[i], is_float);
+            if (in_range && kk > 0) {
+                if (all) gt = true;
+                else {
+                    gt = key > T;
+                    eq = key == T;
+                }
+            }
+        }
+        int eq_total = 0;
+        int eq_rank = 0;
+        if (!all && kk > 0) eq_rank = eq_base + block_excl_scan_flag(eq, s_warp, eq_total);
+        const bool take = forced || gt || (eq && eq_rank < need);
+        int take_total = 0;
+        const int pos = out_base + block_excl_scan_flag(take, s_warp, take_total);
+        if (take && pos < cap) {
+            if (desc) {
+                s_sort[pos] = ((unsigned long long)key << 32) | (unsigned long long)(~(uint32_t)i);
+            } else {
+                p.out_idx[orow + pos] = p.id_map ? __ldg(p.id_map + base + i) : i;
+                if (p.out_scores) p.out_scores[orow + pos] = from_key(key, is_float);
+            }
+        }
+        out_base += take_total;
+        eq_base += eq_total;
+    }
+    const int cnt = min(out_base, cap);
+    if (tid == 0) p.out_counts[r] = cnt;
+
+    if (desc && cnt > 0) {
+        int P = 1;
+        while (P < cnt) P <<= 1;
+        for (int i = cnt + tid; i < P; i += blockDim.x) s_sort[i] = 0ull;
+        __syncthreads();
+        for (int k2 = 2; k2 <= P; k2 <<= 1) {
+            for (int j = k2 >> 1; j > 0; j >>= 1) {
+                for (int i = tid; i < P; i += blockDim.x) {
+                    const int ixj = i ^ j;
+                    if (ixj > i) {
+                        const unsigned long long a = s_sort[i], b = s_sort[ixj];
+                        const bool up = (i & k2) == 0;  // descending overall
+                        if (up ? (a < b) : (a > b)) {
+                            s_sort[i] = b;
+                            s_sort[ixj] = a;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        for (int j = tid; j < cnt; j += blockDim.x) {
+            const unsigned long long v = s_sort[j];
+            const int i = (int)(~(uint32_t)(v & 0xffffffffull));
+            p.out_idx[orow + j] = p.id_map ? __ldg(p.id_map + base + i) : i;
+            if (p.out_scores) p.out_scores[orow + j] = from_key((uint32_t)(v >> 32), is_float);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
+                                    const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
+                                    int32_t window_mode, int32_t order, const int32_t* id_map, int32_t out_stride,
+                                    const int32_t* out_offsets, int32_t* out_idx, void* out_scores,
+                                    int32_t* out_counts, ucmx_stream_t stream)
+{
+    using namespace ucmx;
+    if (n_req < 0) return UCMX_EPARAM;
+    if (n_req == 0) return UCMX_OK;
+    if (!scores || !req_offsets || !k_per_req || !out_idx || !out_counts) return UCMX_EPARAM;
+    if (score_dtype != UCMX_DT_F32 && score_dtype != UCMX_DT_I32) return UCMX_EPARAM;
+    if (window_mode < 0 || window_mode > 2 || (order != 0 && order != 1)) return UCMX_EPARAM;
+    if (start_win < 0 || end_win < 0 || out_stride < 1) return UCMX_EPARAM;
+    size_t smem = 0;
+    if (order == UCMX_ORDER_SCORE_DESC) {
+        if (out_stride > 8192) return UCMX_EUNSUPPORTED;
+        int P = 1;
+        while (P < out_stride) P <<= 1;
+        smem = (size_t)P * 8;
+    }
+    TopkParams p;
+    p.scores = (const uint32_t*)scores;
+    p.is_float = score_dtype == UCMX_DT_F32;
+    p.offsets = req_offsets;
+    p.k_per_req = k_per_req;
+    p.start_win = start_win;
+    p.end_win = end_win;
+    p.window_mode = window_mode;
+    p.order = order;
+    p.id_map = id_map;
+    p.out_stride = out_stride;
+    p.out_offsets = out_offsets;
+    p.out_idx = out_idx;
+    p.out_scores = (uint32_t*)out_scores;
+    p.out_counts = out_counts;
+    if (smem > 48 * 1024)
+        UCMX_CUDA(cudaFuncSetAttribute(topk_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    topk_ragged_kernel<<<n_req, 1024, smem, (cudaStream_t)stream>>>(p);
+    UCMX_LAUNCH_CHECK("topk_ragged_kernel");
+    return UCMX_OK;
+}

@@ -1,0 +1,176 @@
+"""One decode step of sparse-KV retrieval for a ragged batch, layer by layer:
+pool the newly filled blocks -> score every block of every request -> per-request top-k ->
+gather the selected K and V blocks into a contiguous working set.
+
+This is the sequence the reference spreads over ESA's hooks (ucm/sparse/esa/esa.py:286-399: start_retrieval,
+wait_retrieval_and_start_load, block_repre_data, launch_transfer_task) with a CPU thread pool in the
+middle; here every stage is a kernel on one stream and nothing leaves the device unless asked to.
+
+Representatives are kept per layer in a bf16 table indexed by PHYSICAL block id, so the request's
+block table is at once the slot list for scoring and the id map of the top-k output, and the
+selected ids feed the gather directly.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import ops
+from .workloads import KvShape, RaggedBatch
+
+
+class DecodeRetrievalEngine:
+    def __init__(self, shape: KvShape, batch: RaggedBatch, device: torch.device, *, n_layers: Optional[int] = None,
+                 with_kv_pool: bool = True, heads_local: Optional[int] = None, seed: int = 0,
+                 score_reduce=None):
+        """heads_local: KV heads held by this rank under tensor parallelism (default: all).
+        score_reduce: callable applied in place to the fp32 score vector between scoring and top-k
+        (the tensor-parallel all-reduce); None on a single rank."""
+        self.shape, self.batch, self.device = shape, batch, device
+        self.L = n_layers if n_layers is not None else shape.n_layers
+        self.H = heads_local if heads_local is not None else shape.n_kv_heads
+        self.Hq = shape.n_q_heads * self.H // shape.n_kv_heads
+        self.D, self.T = shape.head_dim, shape.block_tokens
+        self.score_reduce = score_reduce
+        i32 = dict(dtype=torch.int32, device=device)
+        self.offsets = torch.from_numpy(batch.offsets).to(device)
+        self.k_per_req = torch.from_numpy(batch.k_per_req).to(device)
+        self.k_offsets = torch.from_numpy(batch.k_offsets).to(device)
+        self.block_table = torch.from_numpy(batch.block_table).to(device)
+        # physical id of each request's newest block (the one a decode step may have just filled)
+        last = torch.from_numpy(batch.offsets[1:] - 1).long().to(device)
+        self.new_block_ids = self.block_table[last].contiguous()
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.gen = g
+        E = self.H * self.D
+        # representatives of every layer stay resident: [L, n_slots, H, 1, D] bf16
+        self.rep_tables = torch.empty((self.L, batch.n_slots, self.H, 1, self.D), dtype=torch.bfloat16, device=device)
+        for l in range(self.L):
+            self.rep_tables[l].copy_((torch.randn((batch.n_slots, self.H, 1, self.D), generator=g, device=device) * 0.0884)
+                                     .to(torch.bfloat16))
+        self.kv_pool = None
+        if with_kv_pool:
+            # one layer's paged K and V pool, reused for every layer: [2, n_slots, T, H, D] bf16
+            self.kv_pool = torch.empty((2, batch.n_slots, self.T, self.H, self.D), dtype=torch.bfloat16, device=device)
+            chunk = 1024
+            for p in range(2):
+                for s in range(0, batch.n_slots, chunk):
+                    e = min(s + chunk, batch.n_slots)
+                    self.kv_pool[p, s:e].copy_(torch.randn((e - s, self.T, self.H, self.D), generator=g, device=device)
+                                               .to(torch.bfloat16))
+            self.staging = torch.empty((batch.total_k, 2, self.T * E * 2), dtype=torch.uint8, device=device)
+        self.qbar = torch.empty((batch.n_req, E), dtype=torch.float32, device=device)
+        self.scores = torch.empty((batch.total,), dtype=torch.float32, device=device)
+        self.sel_ids = torch.full((self.L, batch.total_k), -1, **i32)
+        self.sel_scores = torch.zeros((self.L, batch.total_k), dtype=torch.float32, device=device)
+        self.sel_counts = torch.zeros((self.L, batch.n_req), **i32)
+        self.out_stride = max(batch.max_k, 1)
+        # host side of the end-to-end path
+        self.q_dev = torch.empty((self.L, batch.n_req, self.Hq, self.D), dtype=torch.bfloat16, device=device)
+        self.q_host: Optional[torch.Tensor] = None
+        self.sel_host: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = self.L * (5 if with_kv_pool else 3)
+
+    # ---------------------------------------------------------------------------------- stages
+    def make_queries(self) -> torch.Tensor:
+        q = torch.randn((self.L, self.batch.n_req, self.Hq, self.D), generator=self.gen, device=self.device)
+        self.q_dev.copy_(q.to(torch.bfloat16))
+        return self.q_dev
+
+    def pool_layer(self, layer: int) -> None:
+        ops.pool_blocks(self.kv_pool[0], self.new_block_ids, out_slots=self.new_block_ids,
+                        out_bf16=self.rep_tables[layer])
+
+    def prefill_pool_all(self, layer: int) -> None:
+        """Representatives of every block of the pool (what the last prefill chunk does)."""
+        ops.pool_blocks(self.kv_pool[0], self.block_table, out_slots=self.block_table, out_bf16=self.rep_tables[layer])
+
+    def score_layer(self, layer: int) -> None:
+        ops.query_group_mean(self.q_dev[layer], self.H, out=self.qbar)
+        ops.score_dot(self.rep_tables[layer], self.offsets, self.qbar, total=self.batch.total,
+                      slot_ids=self.block_table, n_kv_heads=self.H, head_dim=self.D, out=self.scores)
+        if self.score_reduce is not None:
+            self.score_reduce(self.scores)
+
+    def topk_layer(self, layer: int) -> None:
+        ops.topk_ragged(self.scores, self.offsets, self.k_per_req, out_stride=self.out_stride,
+                        order=ops.ORDER_SCORE_DESC, id_map=self.block_table, out_offsets=self.k_offsets,
+                        out_idx=self.sel_ids[layer], out_scores=self.sel_scores[layer],
+                        out_counts=self.sel_counts[layer])
+
+    def gather_layer(self, layer: int) -> None:
+        ops.gather_blocks([self.kv_pool[0], self.kv_pool[1]], self.sel_ids[layer], self.staging)
+
+    def layer_step(self, layer: int) -> None:
+        if self.kv_pool is not None:
+            self.pool_layer(layer)
+        self.score_layer(layer)
+        self.topk_layer(layer)
+        if self.kv_pool is not None:
+            self.gather_layer(layer)
+
+    # ------------------------------------------------------------------------------------ steps
+    def step(self) -> None:
+        """All layers, inputs and outputs resident on the device."""
+        if self.graph is not None:
+            self.graph.replay()
+            return
+        for l in range(self.L):
+            self.layer_step(l)
+
+    def capture(self) -> None:
+        """Record the whole step once into a CUDA graph; later steps replay it (one launch)."""
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for l in range(min(self.L, 2)):
+                self.layer_step(l)          # warm up lazily initialised state outside capture
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for l in range(self.L):
+                self.layer_step(l)
+        self.graph = graph
+
+    def alloc_host(self) -> None:
+        self.q_host = torch.empty(self.q_dev.shape, dtype=torch.bfloat16).pin_memory()
+        self.q_host.copy_(self.q_dev)
+        self.sel_host = torch.empty(self.sel_ids.shape, dtype=torch.int32).pin_memory()
+        self.cnt_host = torch.empty(self.sel_counts.shape, dtype=torch.int32).pin_memory()
+
+    def step_host(self) -> torch.Tensor:
+        """End to end with host buffers: each layer's queries come from pinned host memory and its
+        selected block ids and counts go back to pinned host memory; returns after a final sync."""
+        for l in range(self.L):
+            self.q_dev[l].copy_(self.q_host[l], non_blocking=True)
+            self.layer_step(l)
+            self.sel_host[l].copy_(self.sel_ids[l], non_blocking=True)
+            self.cnt_host[l].copy_(self.sel_counts[l], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.sel_host
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return self.q_dev.numel() * 2
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return self.sel_ids.numel() * 4 + self.sel_counts.numel() * 4
+
+    # ------------------------------------------------------------------- algorithmic byte counts
+    def bytes_score_layer(self) -> int:
+        E = self.H * self.D
+        return self.batch.total * (E * 2 + 4 + 4)          # rep row + slot id + score
+
+    def bytes_gather_layer(self) -> int:
+        return 2 * self.batch.total_k * 2 * self.T * self.H * self.D * 2   # K and V, read + write
+
+    def bytes_pool_layer(self) -> int:
+        E = self.H * self.D
+        return self.batch.n_req * (self.T * E * 2 + E * 2)
+
+    def tokens_scored_per_step(self) -> int:
+        return self.batch.total * self.T * self.L

@@ -1,0 +1,283 @@
+"""Tensor-level front-end of the C ABI: each function checks shapes, takes raw device pointers
+from torch tensors and enqueues the CUDA kernel on torch's current stream.
+
+torch is used for device memory and streams only; all arithmetic happens in libucmx.so.  Nothing
+here computes on the CPU and nothing falls back when the library is unavailable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as N
+from ._native import (DT_BF16, DT_F32, DT_I32, ORDER_INDEX_ASC, ORDER_SCORE_DESC, POOL_MAX,  # noqa: F401
+                      POOL_MEAN, POOL_MIN, POOL_SUM, WIN_EXCLUDE, WIN_FORCE, WIN_NONE)
+
+_POOL_MODES = {"mean": POOL_MEAN, "max": POOL_MAX, "min": POOL_MIN, "sum": POOL_SUM}
+
+
+def _stream(t: torch.Tensor) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("ucmx ops take CUDA tensors; there is no CPU path")
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+def kv_geometry(k_cache: torch.Tensor) -> N.KvGeometry:
+    """Geometry of a paged cache tensor [num_blocks, block_tokens, n_kv_heads, head_dim] (bf16)."""
+    if k_cache.dim() != 4 or k_cache.dtype != torch.bfloat16:
+        raise ValueError("k_cache must be bf16 [num_blocks, block_tokens, n_kv_heads, head_dim]")
+    nb, T, H, D = k_cache.shape
+    sb, st, sh, sd = k_cache.stride()
+    if sd != 1 or sh != D:
+        raise ValueError("heads and head_dim of the paged cache must be contiguous")
+    return N.KvGeometry(sb, st, T, H, D, 0)
+
+
+def pool_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, *, mode: str = "mean",
+                out_slots: Optional[torch.Tensor] = None, out_bf16: Optional[torch.Tensor] = None,
+                out_f32: Optional[torch.Tensor] = None, round_bf16: bool = True, n_rep: int = 1,
+                rep_index: int = 0) -> torch.Tensor:
+    """Per-block key representatives. Returns the bf16 table (or the fp32 one if only that is given).
+
+    With no output tensor given, a bf16 [n, n_kv_heads, n_rep, head_dim] table is allocated."""
+    _need_cuda(k_cache, block_ids, out_slots, out_bf16, out_f32)
+    g = kv_geometry(k_cache)
+    ids = _i32(block_ids, "block_ids")
+    n = ids.numel()
+    if out_bf16 is None and out_f32 is None:
+        out_bf16 = torch.empty((n, g.n_kv_heads, n_rep, g.head_dim), dtype=torch.bfloat16, device=k_cache.device)
+    if out_bf16 is not None and (out_bf16.dtype != torch.bfloat16 or not out_bf16.is_contiguous()):
+        raise ValueError("out_bf16 must be contiguous bf16")
+    if out_f32 is not None and (out_f32.dtype != torch.float32 or not out_f32.is_contiguous()):
+        raise ValueError("out_f32 must be contiguous fp32")
+    st = N.lib.ucmx_pool_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+                                _POOL_MODES[mode], int(round_bf16), n_rep, rep_index, _ptr(out_bf16),
+                                _ptr(out_f32), _stream(k_cache))
+    N.check("ucmx_pool_blocks", st, 1 if n else 0)
+    return out_bf16 if out_bf16 is not None else out_f32
+
+
+def query_group_mean(query: torch.Tensor, n_kv_heads: int, *, round_bf16: bool = True,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """query bf16 [n_tok, n_q_heads, head_dim] -> fp32 [n_tok, n_kv_heads*head_dim]."""
+    _need_cuda(query, out)
+    if query.dim() != 3 or query.dtype != torch.bfloat16:
+        raise ValueError("query must be bf16 [n_tok, n_q_heads, head_dim]")
+    nt, Hq, D = query.shape
+    if query.stride(2) != 1 or query.stride(1) != D:
+        query = query.contiguous()
+    if out is None:
+        out = torch.empty((nt, n_kv_heads * D), dtype=torch.float32, device=query.device)
+    st = N.lib.ucmx_query_group_mean(_ptr(query), nt, Hq, n_kv_heads, D, query.stride(0), int(round_bf16),
+                                     _ptr(out), _stream(query))
+    N.check("ucmx_query_group_mean", st, 1 if nt else 0)
+    return out
+
+
+def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *, total: int,
+              slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, head_dim: int, n_rep: int = 1,
+              scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Ragged query-to-block dot scores. reps: bf16 or fp32 table [slots, n_kv_heads, n_rep, head_dim]
+    (any shape with that memory layout); q fp32 [n_req, n_kv_heads*head_dim]. Returns fp32 [total]."""
+    _need_cuda(reps, req_offsets, q, slot_ids, out)
+    if reps.dtype == torch.bfloat16:
+        dt = DT_BF16
+    elif reps.dtype == torch.float32:
+        dt = DT_F32
+    else:
+        raise ValueError("reps must be bf16 or fp32")
+    if not reps.is_contiguous() or q.dtype != torch.float32 or not q.is_contiguous():
+        raise ValueError("reps and q must be contiguous; q must be fp32")
+    n_req = req_offsets.numel() - 1
+    if q.numel() != n_req * n_kv_heads * head_dim:
+        raise ValueError("q must hold n_req rows of n_kv_heads*head_dim values")
+    if out is None:
+        out = torch.empty((total,), dtype=torch.float32, device=reps.device)
+    st = N.lib.ucmx_score_dot(_ptr(reps), dt, n_kv_heads, n_rep, head_dim, _ptr(_i32(req_offsets, "req_offsets")),
+                              _ptr(_i32(slot_ids, "slot_ids")), _ptr(q), n_req, total, float(scale), _ptr(out),
+                              _stream(reps))
+    N.check("ucmx_score_dot", st, 1 if total and n_req else 0)
+    return out
+
+
+def score_hamming(codes: torch.Tensor, req_offsets: torch.Tensor, q_codes: torch.Tensor, *, total: int,
+                  slot_ids: Optional[torch.Tensor] = None, cross_head: bool = True,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """codes uint8 [slots, n_kv_heads, block_tokens, bits/8]; q_codes uint8 [n_req, n_q_heads, bits/8]."""
+    _need_cuda(codes, req_offsets, q_codes, slot_ids, out)
+    if codes.dtype != torch.uint8 or codes.dim() != 4 or not codes.is_contiguous():
+        raise ValueError("codes must be contiguous uint8 [slots, n_kv_heads, block_tokens, bits/8]")
+    if q_codes.dtype != torch.uint8 or q_codes.dim() != 3 or not q_codes.is_contiguous():
+        raise ValueError("q_codes must be contiguous uint8 [n_req, n_q_heads, bits/8]")
+    _, H, T, nb = codes.shape
+    n_req = req_offsets.numel() - 1
+    if q_codes.shape[0] != n_req or q_codes.shape[2] != nb:
+        raise ValueError("q_codes shape does not match")
+    if out is None:
+        out = torch.empty((total,), dtype=torch.int32, device=codes.device)
+    st = N.lib.ucmx_score_hamming(_ptr(codes), H, T, nb * 8, _ptr(_i32(req_offsets, "req_offsets")),
+                                  _ptr(_i32(slot_ids, "slot_ids")), _ptr(q_codes), q_codes.shape[1], n_req, total,
+                                  int(cross_head), _ptr(out), _stream(codes))
+    N.check("ucmx_score_hamming", st, 1 if total and n_req else 0)
+    return out
+
+
+def topk_ragged(scores: torch.Tensor, req_offsets: torch.Tensor, k_per_req: torch.Tensor, *, out_stride: int,
+                start_win: int = 0, end_win: int = 0, window_mode: int = WIN_NONE,
+                order: int = ORDER_SCORE_DESC, id_map: Optional[torch.Tensor] = None, want_scores: bool = True,
+                out_offsets: Optional[torch.Tensor] = None, out_idx: Optional[torch.Tensor] = None, out_scores: Optional[torch.Tensor] = None,
+                out_counts: Optional[torch.Tensor] = None):
+    """Per-request top-k. Returns (idx int32 [n_req, out_stride], scores or None, counts int32 [n_req]).
+    Entries of a row beyond its count are -1 (indices) when this function allocates the output.
+    With out_offsets (int32 [n_req+1]) the rows are packed back to back into flat outputs that the
+    caller provides (out_idx, and out_scores if wanted, of out_offsets[-1] entries)."""
+    _need_cuda(scores, req_offsets, k_per_req, id_map, out_idx, out_scores, out_counts)
+    if scores.dtype == torch.float32:
+        dt = DT_F32
+    elif scores.dtype == torch.int32:
+        dt = DT_I32
+    else:
+        raise ValueError("scores must be fp32 or int32")
+    n_req = req_offsets.numel() - 1
+    dev = scores.device
+    if out_offsets is not None and out_idx is None:
+        raise ValueError("packed output needs caller-provided out_idx")
+    if out_idx is None:
+        out_idx = torch.full((n_req, out_stride), -1, dtype=torch.int32, device=dev)
+    if out_scores is None and want_scores and out_offsets is None:
+        out_scores = torch.zeros((n_req, out_stride), dtype=scores.dtype, device=dev)
+    if out_counts is None:
+        out_counts = torch.zeros((n_req,), dtype=torch.int32, device=dev)
+    st = N.lib.ucmx_topk_ragged(_ptr(scores), dt, _ptr(_i32(req_offsets, "req_offsets")),
+                                _ptr(_i32(k_per_req, "k_per_req")), n_req, start_win, end_win, window_mode, order,
+                                _ptr(_i32(id_map, "id_map")), out_stride, _ptr(_i32(out_offsets, "out_offsets")),
+                                _ptr(out_idx), _ptr(out_scores),
+                                _ptr(out_counts), _stream(scores))
+    N.check("ucmx_topk_ragged", st, 1 if n_req else 0)
+    return out_idx, out_scores, out_counts
+
+
+def hash_encode(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x bf16 [..., dim], w bf16 [dim, bits] -> uint8 [..., bits/8] (LSB-first packed sign bits)."""
+    _need_cuda(x, w, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 2:
+        raise ValueError("x and w must be bf16; w is [dim, bits]")
+    dim, bits = w.shape
+    if x.shape[-1] != dim:
+        raise ValueError(f"x must be of shape (..., {dim}), but got {tuple(x.shape)}")
+    x2 = x.reshape(-1, dim)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    w = w.contiguous()
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (bits // 8,), dtype=torch.uint8, device=x.device)
+    st = N.lib.ucmx_hash_encode(_ptr(x2), x2.shape[0], x2.stride(0), _ptr(w), dim, bits, _ptr(out), _stream(x))
+    N.check("ucmx_hash_encode", st, 1 if x2.shape[0] else 0)
+    return out
+
+
+def hash_encode_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, w: torch.Tensor, *,
+                       out_slots: Optional[torch.Tensor] = None, head_major: bool = True,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Hash codes of whole paged blocks -> uint8 [n, n_kv_heads, block_tokens, bits/8] (head_major) or
+    [n, block_tokens, n_kv_heads, bits/8]."""
+    _need_cuda(k_cache, block_ids, w, out_slots, out)
+    g = kv_geometry(k_cache)
+    ids = _i32(block_ids, "block_ids")
+    dim, bits = w.shape
+    if dim != g.head_dim or w.dtype != torch.bfloat16:
+        raise ValueError("w must be bf16 [head_dim, bits]")
+    n = ids.numel()
+    if out is None:
+        shape = (n, g.n_kv_heads, g.block_tokens, bits // 8) if head_major else (n, g.block_tokens, g.n_kv_heads, bits // 8)
+        out = torch.empty(shape, dtype=torch.uint8, device=k_cache.device)
+    st = N.lib.ucmx_hash_encode_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+                                       _ptr(w.contiguous()), bits, int(head_major), _ptr(out), _stream(k_cache))
+    N.check("ucmx_hash_encode_blocks", st, 1 if n else 0)
+    return out
+
+
+def _planes(planes: Sequence[torch.Tensor]):
+    if not 1 <= len(planes) <= 8:
+        raise ValueError("1..8 planes")
+    arr = (C.c_void_p * len(planes))()
+    for i, p in enumerate(planes):
+        arr[i] = p.data_ptr()
+    return arr
+
+
+def _block_layout(planes: Sequence[torch.Tensor]):
+    p0 = planes[0]
+    esz = p0.element_size()
+    stride_b = p0.stride(0) * esz
+    inner = p0[0]
+    if not inner.is_contiguous():
+        raise ValueError("each block slice of a plane must be contiguous")
+    slice_bytes = inner.numel() * esz
+    for p in planes[1:]:
+        if p.stride(0) * p.element_size() != stride_b or p[0].numel() * p.element_size() != slice_bytes:
+            raise ValueError("planes must share block stride and slice size")
+    return stride_b, slice_bytes
+
+
+def gather_blocks(planes: Sequence[torch.Tensor], block_ids: torch.Tensor, staging: torch.Tensor) -> torch.Tensor:
+    """Copy blocks block_ids[i] of every plane into staging laid out [i][plane][slice bytes].
+
+    staging: a CUDA tensor, or a pinned CPU tensor (written directly over the host link)."""
+    _need_cuda(block_ids, *planes)
+    stride_b, slice_bytes = _block_layout(planes)
+    ids = _i32(block_ids, "block_ids")
+    n = ids.numel()
+    host = not staging.is_cuda
+    if host and not staging.is_pinned():
+        raise ValueError("host staging must be pinned")
+    if staging.numel() * staging.element_size() < n * len(planes) * slice_bytes:
+        raise ValueError("staging too small")
+    st = N.lib.ucmx_gather_blocks(_planes(planes), len(planes), stride_b, _ptr(ids), n, slice_bytes, _ptr(staging),
+                                  int(host), _stream(planes[0]))
+    N.check("ucmx_gather_blocks", st, 1 if n else 0)
+    return staging
+
+
+def scatter_blocks(planes: Sequence[torch.Tensor], block_ids: torch.Tensor, staging: torch.Tensor) -> None:
+    """Inverse of gather_blocks: staging[i][plane] -> block block_ids[i] of each plane."""
+    _need_cuda(block_ids, *planes)
+    stride_b, slice_bytes = _block_layout(planes)
+    ids = _i32(block_ids, "block_ids")
+    n = ids.numel()
+    host = not staging.is_cuda
+    if host and not staging.is_pinned():
+        raise ValueError("host staging must be pinned")
+    if staging.numel() * staging.element_size() < n * len(planes) * slice_bytes:
+        raise ValueError("staging too small")
+    st = N.lib.ucmx_scatter_blocks(_planes(planes), len(planes), stride_b, _ptr(ids), n, slice_bytes, _ptr(staging),
+                                   int(host), _stream(planes[0]))
+    N.check("ucmx_scatter_blocks", st, 1 if n else 0)
+
+
+def copy_batch(dst_ptrs: torch.Tensor, src_ptrs: torch.Tensor, count: int, *, any_host_memory: bool = False) -> None:
+    """dst_ptrs/src_ptrs: CUDA int64 tensors of addresses; copies `count` bytes per pair."""
+    _need_cuda(dst_ptrs, src_ptrs)
+    if dst_ptrs.dtype != torch.int64 or src_ptrs.dtype != torch.int64 or dst_ptrs.numel() != src_ptrs.numel():
+        raise ValueError("pointer tensors must be int64 and of equal length")
+    n = dst_ptrs.numel()
+    st = N.lib.ucmx_copy_batch(_ptr(dst_ptrs), _ptr(src_ptrs), n, count, int(any_host_memory), _stream(dst_ptrs))
+    N.check("ucmx_copy_batch", st, 1 if n and count else 0)
