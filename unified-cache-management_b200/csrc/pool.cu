@@ -229,9 +229,9 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
                                     ucmx_stream_t stream)
 {
     using namespace ucmx;
-    if (!k_cache || !g || n < 0 || (!out_bf16 && !out_f32)) return UCMX_EPARAM;
+    if (n < 0) return UCMX_EPARAM;
     if (n == 0) return UCMX_OK;
-    if (!block_ids) return UCMX_EPARAM;
+    if (!k_cache || !g || !block_ids || (!out_bf16 && !out_f32)) return UCMX_EPARAM;
     if (mode < 0 || mode > 3 || n_rep < 1 || rep_index < 0 || rep_index >= n_rep) return UCMX_EPARAM;
     if (g->block_tokens < 1 || g->n_kv_heads < 1 || g->head_dim < 8 || g->head_dim % 8) return UCMX_EPARAM;
     const int64_t E64 = (int64_t)g->n_kv_heads * g->head_dim;
