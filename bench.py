@@ -204,8 +204,13 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=32, help=argparse.SUPPRESS)
+    ap.add_argument("--profile-case", action="store_true",
+                    help="small case for profiler captures: 8 requests, 2 layers, 1 warm-up + 1 step, no host legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    n_req = 64
+    if args.profile_case:
+        args.layers, args.steps, args.warmup, args.no_cpu_baseline, n_req = 2, 1, 1, True, 8
 
     rank = env_int("RANK", 0)
     world = env_int("WORLD_SIZE", 1)
@@ -233,7 +238,7 @@ def main():
         if world > 1:
             dist.barrier(device_ids=[local_rank])
 
-    batch = ragged_decode_batch(seed=2002 + rank)
+    batch = ragged_decode_batch(seed=2002 + rank, n_req=n_req)
     eng = DecodeRetrievalEngine(LLAMA3_8B, batch, dev, n_layers=args.layers, seed=1000 + rank)
     eng.make_queries()
     torch.cuda.synchronize()
@@ -327,16 +332,18 @@ def main():
 
     # ---- end to end with host buffers
     eng.graph = None
-    eng.alloc_host()
-    for _ in range(2):
-        eng.step_host()
-    barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        eng.step_host()
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_s = float("nan")
+    if not args.profile_case:
+        eng.alloc_host()
+        for _ in range(2):
+            eng.step_host()
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            eng.step_host()
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / args.steps
     if world > 1:
         t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
