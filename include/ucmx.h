@@ -186,6 +186,38 @@ int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t*
                          void* out_scores, int32_t* out_counts, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Score + top-k without any allocation.  (No counterpart in the reference: its retrieval runs on
+ * host threads with std::vector scratch.)
+ *
+ * Same arguments and results as ucmx_score_dot followed by ucmx_topk_ragged on fp32 scores, but the
+ * per-candidate scores in between live in an array that is part of the library image instead of a
+ * buffer the caller provides.  It is meant for callers that cannot allocate device memory at the
+ * point of the call - hooks running inside a serving engine's forward pass after the engine has
+ * given nearly all of HBM to its KV cache, where cudaMalloc may fail and in any case stalls the
+ * device, and callers with no tensor allocator of their own.  This function calls neither
+ * cudaMalloc/cudaFree nor any allocating library routine.
+ * Limits and rules:
+ *  - total must not exceed ucmx_noalloc_max_candidates() (1 048 576 candidates, a 4 MiB array that
+ *    every GPU which loads the library holds until the process exits); larger batches are
+ *    rejected with UCMX_EUNSUPPORTED and a message in ucmx_last_error().
+ *  - The first call on each device looks up the array's device address (the device of `stream`
+ *    must be current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array and it keeps the last call's scores.  Calls are
+ *    safe back to back on one stream; two calls that may overlap on the GPU (different streams
+ *    without an ordering between them) race on it and must be serialised by the caller.
+ *  - Only out_idx / out_scores / out_counts are results; the scores of unselected candidates are
+ *    not returned. */
+int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
+                                   int32_t n_rep, int32_t head_dim, const int32_t* req_offsets,
+                                   const int32_t* slot_ids, const float* q, int32_t n_req,
+                                   int32_t total, float scale, const int32_t* k_per_req,
+                                   int32_t start_win, int32_t end_win, int32_t window_mode,
+                                   int32_t order, const int32_t* id_map, int32_t out_stride,
+                                   const int32_t* out_offsets, int32_t* out_idx, float* out_scores,
+                                   int32_t* out_counts, ucmx_stream_t stream);
+int32_t ucmx_noalloc_max_candidates(void);
+
+/* ---------------------------------------------------------------------------------------------
  * Stage 4 — gather / scatter of paged KV block slices.
  * Replaces: the per-block copies of UcmDramStore.load/dump
  * (ucm/store/dramstore/dramstore_connector.py:112-166), PosixQueue::S2D/D2S's memcpy leg

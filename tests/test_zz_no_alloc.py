@@ -1,0 +1,93 @@
+"""ucmx_retrieve_topk_noalloc: score + top-k for callers that may not allocate device memory
+(code running inside a serving engine's forward pass, when the engine already owns nearly all of
+HBM and a cudaMalloc could fail or stall the device).  The scores between the two kernels sit in
+an array built into the library, so the call allocates nothing.
+
+Checked here, through the C ABI, against the two existing entry points (ucmx_score_dot then
+ucmx_topk_ragged with a caller-owned score buffer): same selected ids, same counts, same scores bit
+for bit, since both routes run the same kernels.  Two different batches are sent one after the other
+to show that what the first call left in the shared array does not leak into the second.
+This file sorts last on purpose: a run that stops at the first failure has then already run
+everything else.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dev(a, dtype=None):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=dtype)).to(DEV)
+
+
+def _ptr(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _both_routes(N, reps, off, slots, q, ks, koff, n_kv_heads, head_dim):
+    n_req = len(ks)
+    total = int(off[-1])
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    d_off, d_slots, d_q, d_k, d_koff = _dev(off), _dev(slots), _dev(q), _dev(ks), _dev(koff)
+    stride = int(ks.max())
+    outs = []
+    for route in ("noalloc", "existing"):
+        idx = torch.full((int(koff[-1]),), -7, dtype=torch.int32, device=DEV)
+        sc = torch.full((int(koff[-1]),), -7.0, dtype=torch.float32, device=DEV)
+        cnt = torch.full((n_req,), -7, dtype=torch.int32, device=DEV)
+        if route == "noalloc":
+            st = N.lib.ucmx_retrieve_topk_noalloc(_ptr(reps), N.DT_BF16, n_kv_heads, 1, head_dim, _ptr(d_off),
+                                                  _ptr(d_slots), _ptr(d_q), n_req, total, 1.0, _ptr(d_k), 0, 0,
+                                                  N.WIN_NONE, N.ORDER_SCORE_DESC, _ptr(d_slots), stride, _ptr(d_koff),
+                                                  _ptr(idx), _ptr(sc), _ptr(cnt), stream)
+            assert st == N.OK, N.last_error()
+        else:
+            scores = torch.empty((total,), dtype=torch.float32, device=DEV)
+            st = N.lib.ucmx_score_dot(_ptr(reps), N.DT_BF16, n_kv_heads, 1, head_dim, _ptr(d_off), _ptr(d_slots),
+                                      _ptr(d_q), n_req, total, 1.0, _ptr(scores), stream)
+            assert st == N.OK, N.last_error()
+            st = N.lib.ucmx_topk_ragged(_ptr(scores), N.DT_F32, _ptr(d_off), _ptr(d_k), n_req, 0, 0, N.WIN_NONE,
+                                        N.ORDER_SCORE_DESC, _ptr(d_slots), stride, _ptr(d_koff), _ptr(idx), _ptr(sc),
+                                        _ptr(cnt), stream)
+            assert st == N.OK, N.last_error()
+        torch.cuda.synchronize()
+        outs.append((idx.cpu().numpy(), sc.cpu().numpy(), cnt.cpu().numpy()))
+    return outs
+
+
+def test_noalloc_matches_existing_entry_points_twice_in_a_row():
+    from ucmx import _native as N
+    rng = np.random.default_rng(71)
+    n_slots, Hkv, D = 3000, 8, 128
+    reps16 = H.randn_bf16(rng, (n_slots, Hkv * D), 0.09)
+    reps = torch.from_numpy(reps16.view(np.int16)).to(DEV).view(torch.bfloat16)
+    # two batches of different size and raggedness: the second is smaller, so stale scores of the
+    # first call remain in the shared array beyond its end
+    for counts, kfrac in (([700, 64, 1, 1200, 333], 0.1), ([90, 0, 256], 0.25)):
+        off = H.ragged_offsets(counts)
+        slots = rng.integers(0, n_slots, int(off[-1])).astype(np.int32)
+        q = H.bf16_to_f32(H.randn_bf16(rng, (len(counts), Hkv * D)))
+        ks = np.maximum(1, np.ceil(np.array(counts) * kfrac)).astype(np.int32)
+        ks = np.minimum(ks, np.maximum(np.array(counts), 1)).astype(np.int32)
+        koff = H.ragged_offsets(ks)
+        (i1, s1, c1), (i2, s2, c2) = _both_routes(N, reps, off, slots, q, ks, koff, Hkv, D)
+        assert np.array_equal(c1, c2)
+        assert np.array_equal(i1, i2)
+        assert np.array_equal(s1, s2)          # tolerance: none needed, the kernels are the same
+        assert c1.sum() == sum(min(k, n) for k, n in zip(ks, counts))
+
+
+def test_noalloc_rejects_batches_beyond_its_scratch():
+    from ucmx import _native as N
+    limit = N.lib.ucmx_noalloc_max_candidates()
+    assert limit == 1 << 20
+    st = N.lib.ucmx_retrieve_topk_noalloc(None, N.DT_BF16, 8, 1, 128, None, None, None, 1, limit + 1, 1.0, None, 0, 0,
+                                          N.WIN_NONE, N.ORDER_SCORE_DESC, None, 1, None, None, None, None, None)
+    assert st == N.EUNSUPPORTED
+    assert "1048576" in N.last_error()

@@ -65,6 +65,9 @@ SIGNATURES = {
     "ucmx_score_dot": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "ucmx_score_hamming": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "ucmx_topk_ragged": [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
+    "ucmx_retrieve_topk_noalloc": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i32, _i32, _i32,
+                                   _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
+    "ucmx_noalloc_max_candidates": [],
     "ucmx_gather_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
     "ucmx_scatter_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
     "ucmx_copy_batch": [_vp, _vp, _i32, _i64, _i32, _vp],
