@@ -44,7 +44,7 @@ typedef struct ucmx_kv_geometry {
     int32_t block_tokens;
     int32_t n_kv_heads;
     int32_t head_dim;
-    int32_t reserved;
+    int32_t reserved; /* number of blocks in the cache if known, else 0; lets small batches use tiled TMA loads */
 } ucmx_kv_geometry;
 
 /* Library version and the SM architecture the kernels were compiled for (100 for sm_100a). */
@@ -133,6 +133,17 @@ int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
                        int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
                        const float* q, int32_t n_req, int32_t total, float scale, float* out_scores,
                        ucmx_stream_t stream);
+
+/* Stages 2-prologue and 2a in one launch: `query` is the raw bf16 decode query [n_req, n_q_heads,
+ * head_dim] (query_stride elements between requests); the per-KV-head mean of
+ * ucmx_query_group_mean (same arithmetic, same round_bf16 switch) is taken inside the scoring
+ * kernel.  n_rep is 1.  Returns UCMX_EUNSUPPORTED for shapes the single-pass kernel does not cover
+ * (n_kv_heads*head_dim not a multiple of 256 for bf16 tables / 128 for fp32 tables, or above 2048);
+ * use the two calls above then. */
+int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t head_dim,
+                             const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+                             int32_t n_q_heads, int64_t query_stride, int32_t round_bf16, int32_t n_req,
+                             int32_t total, float scale, float* out_scores, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Stage 2b — Hamming-similarity scores on packed hash codes (integer exact).

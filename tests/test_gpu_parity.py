@@ -144,6 +144,28 @@ def test_score_dot_ragged(ops, oracle, dtype):
     np.testing.assert_allclose(got1, ref1, **_score_tol(ref1))
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (8, 8, 128), (2, 4, 64), (64, 8, 128)])
+def test_score_dot_query_fused_equals_two_step(ops, oracle, Hq, Hkv, D):
+    """The fused prologue takes the same mean, in the same order, as ucmx_query_group_mean: the scores
+    of the one-launch route equal those of the two-launch route bit for bit, and match the checker."""
+    rng = np.random.default_rng(23)
+    n_slots = 400
+    reps16 = H.randn_bf16(rng, (n_slots, Hkv * D), 0.09)
+    counts = [130, 0, 77, 1, 192]
+    off = H.ragged_offsets(counts)
+    slots = rng.integers(0, n_slots, int(off[-1])).astype(np.int32)
+    q16 = H.randn_bf16(rng, (len(counts), Hq, D))
+    for rnd in (True, False):
+        fused = ops.score_dot_query(dev_bf16(reps16), dev_i32(off), dev_bf16(q16), total=int(off[-1]),
+                                    slot_ids=dev_i32(slots), n_kv_heads=Hkv, round_bf16=rnd)
+        qbar = ops.query_group_mean(dev_bf16(q16), Hkv, round_bf16=rnd)
+        two = ops.score_dot(dev_bf16(reps16), dev_i32(off), qbar, total=int(off[-1]), slot_ids=dev_i32(slots),
+                            n_kv_heads=Hkv, head_dim=D)
+        assert torch.equal(fused, two)
+        ref = oracle.score_dot_esa(H.bf16_to_f32(reps16), off, slots, oracle.query_group_mean(q16, Hkv, rnd))
+        np.testing.assert_allclose(fused.cpu().numpy(), ref, **_score_tol(ref))
+
+
 def test_score_dot_matches_compiled_reference(ops):
     data, query, idx, topk = H.case_esa()
     for r in range(3):

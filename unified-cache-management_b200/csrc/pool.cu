@@ -8,6 +8,11 @@
 // (ucm/sparse/gsa/offload_ops/src/vec_product.cpp:349-387), so the fp32 mean is reproducible bit
 // for bit.  The bf16 rounding the reference applies (ucm/sparse/esa/esa.py:265-266) is fused into
 // the store.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ucmx {
@@ -32,7 +37,10 @@ struct PoolParams {
     float* out_f32;
     int32_t rows_per_stage;
     int32_t chunks_per_block;
-    int32_t dense;  // token_stride == E: one bulk copy per stage
+    int32_t dense;  // token_stride == E and no column split: one bulk copy per stage
+    int32_t stages;      // ring depth actually used (<= kStages)
+    int32_t cs;          // column splits: a block's row is cut into cs pieces, one work item each
+    int32_t cg_per_item; // 16-byte column groups per work item
     int32_t* err;
 };
 
@@ -60,12 +68,13 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
     __shared__ int s_failed;
 
     const int tid = threadIdx.x;
-    const int n_cg = p.E / 8;  // 16-byte column groups per token row
-    const uint32_t row_bytes = (uint32_t)p.E * 2u;
+    const int n_cg = p.cg_per_item;  // 16-byte column groups of a token row this CTA reduces
+    const uint32_t row_bytes = (uint32_t)n_cg * 16u;
 
-    // blocks this CTA owns: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const int my_blocks = (p.n - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total_chunks = my_blocks * p.chunks_per_block;
+    // work items (block, column split) this CTA owns: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int n_items = p.n * p.cs;
+    const int my_items = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total_chunks = my_items * p.chunks_per_block;
 
     if (tid == 0) {
         s_failed = 0;
@@ -73,29 +82,33 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
         mbar_init_fence();
     }
     __syncthreads();
+    const int n_stages = p.stages;
 
+    // Called by every lane of warp 0.  Chunk g of this CTA goes to stage g % kStages.
     auto issue = [&](int g) {
-        // chunk g of this CTA -> stage g % kStages
-        const int lb = g / p.chunks_per_block;
-        const int c = g - lb * p.chunks_per_block;
-        const int blk = (int)blockIdx.x + lb * (int)gridDim.x;
+        const int li = g / p.chunks_per_block;
+        const int c = g - li * p.chunks_per_block;
+        const int item = (int)blockIdx.x + li * (int)gridDim.x;
+        const int blk = item / p.cs, split = item - blk * p.cs;
         const int id = __ldg(p.ids + blk);
         const int t0 = c * p.rows_per_stage;
         const int rows = min(p.rows_per_stage, p.T - t0);
-        const int s = g % kStages;
+        const int s = g % n_stages;
         unsigned char* dst = ring + (size_t)s * kStageBytes;
-        const uint16_t* src = p.k + (int64_t)id * p.block_stride + (int64_t)t0 * p.token_stride;
-        mbar_expect_tx(&full[s], (uint32_t)rows * row_bytes);
+        const uint16_t* src = p.k + (int64_t)id * p.block_stride + (int64_t)t0 * p.token_stride +
+                              (int64_t)split * p.cg_per_item * 8;
+        if (tid == 0) mbar_expect_tx(&full[s], (uint32_t)rows * row_bytes);
+        __syncwarp();
         if (p.dense) {
-            bulk_g2s(dst, src, (uint32_t)rows * row_bytes, &full[s]);
+            if (tid == 0) bulk_g2s(dst, src, (uint32_t)rows * row_bytes, &full[s]);
         } else {
-            for (int r = 0; r < rows; ++r)
+            for (int r = tid; r < rows; r += 32)
                 bulk_g2s(dst + (size_t)r * row_bytes, src + (int64_t)r * p.token_stride, row_bytes, &full[s]);
         }
     };
 
-    if (tid == 0) {
-        const int pre = min(kStages, total_chunks);
+    if (tid < 32) {
+        const int pre = min(n_stages, total_chunks);
         for (int g = 0; g < pre; ++g) issue(g);
     }
 
@@ -108,10 +121,10 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
     const float inv = 1.0f / (float)p.T;
 
     for (int g = 0; g < total_chunks; ++g) {
-        const int s = g % kStages;
-        const uint32_t parity = (uint32_t)(g / kStages) & 1u;
-        const int lb = g / p.chunks_per_block;
-        const int c = g - lb * p.chunks_per_block;
+        const int s = g % n_stages;
+        const uint32_t parity = (uint32_t)(g / n_stages) & 1u;
+        const int li = g / p.chunks_per_block;
+        const int c = g - li * p.chunks_per_block;
         const int rows = min(p.rows_per_stage, p.T - c * p.rows_per_stage);
 
         bool ok = true;
@@ -141,17 +154,18 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
             }
         }
         __syncthreads();  // every thread is done with stage s
-        if (tid == 0 && !s_failed && g + kStages < total_chunks) issue(g + kStages);
+        if (tid < 32 && !s_failed && g + n_stages < total_chunks) issue(g + n_stages);
 
         if (c == p.chunks_per_block - 1) {
             // block finished: finalise and store
-            const int blk = (int)blockIdx.x + lb * (int)gridDim.x;
+            const int item = (int)blockIdx.x + li * (int)gridDim.x;
+            const int blk = item / p.cs, split = item - blk * p.cs;
             const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : (int64_t)blk;
 #pragma unroll
             for (int j = 0; j < CGT; ++j) {
                 const int cg = tid + j * (int)blockDim.x;
                 if (cg < n_cg && slot >= 0) {
-                    const int e0 = cg * 8;
+                    const int e0 = (split * p.cg_per_item + cg) * 8;
                     const int h = e0 / p.D, d = e0 - h * p.D;
                     const int64_t o = ((slot * p.H + h) * p.n_rep + p.rep_index) * (int64_t)p.D + d;
                     float r[8];
@@ -220,6 +234,148 @@ int32_t launch_pool(const PoolParams& p, int threads, int cgt, int grid, size_t 
     return UCMX_OK;
 }
 
+// ------------------------------------------------------------------ small batches: one TMA tile per CTA
+//
+// A decode step pools one freshly filled block per request: a few dozen blocks, far too few to
+// fill the machine one block per CTA, and latency, not bandwidth, is what counts.  Here a block is
+// cut into column pieces of at most 256 elements; each CTA brings its [block_tokens x piece] tile
+// into shared memory with a single tiled TMA load (cp.async.bulk.tensor.3d over a tensor map of the
+// paged cache: columns, tokens, blocks) and every thread owns two adjacent columns, which it sums
+// in token order exactly as the streaming kernel does.
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, int x, int y, int z, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(128) pool_blocks_tile_kernel(const __grid_constant__ CUtensorMap tmap, PoolParams p)
+{
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+    unsigned char* tile = smem + 128;
+    const int tid = threadIdx.x;
+    const int cols = p.cg_per_item * 8;  // elements per piece
+    const int item = blockIdx.x;
+    const int blk = item / p.cs, split = item - blk * p.cs;
+    const int id = __ldg(p.ids + blk);
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        mbar_expect_tx(bar, (uint32_t)cols * 2u * (uint32_t)p.T);
+        // x is a multiple of 8 elements: the 16-byte start alignment tiled TMA needs
+        tma_load_3d(tile, &tmap, split * cols, 0, id, bar);
+    }
+    __syncthreads();
+    bool ok = mbar_wait(bar, 0);
+    if (!ok && p.err) atomicExch(p.err, 1);
+    const int c2 = tid * 2;  // this thread's column pair inside the piece
+    if (ok && c2 < cols) {
+        float a0 = pool_init<MODE>(), a1 = pool_init<MODE>();
+        const unsigned char* col = tile + (size_t)c2 * 2;
+        const size_t pitch = (size_t)cols * 2;
+#pragma unroll 8
+        for (int t = 0; t < p.T; ++t) {
+            const uint32_t v = *reinterpret_cast<const uint32_t*>(col + (size_t)t * pitch);
+            a0 = pool_op<MODE>(a0, bf16lo(v));
+            a1 = pool_op<MODE>(a1, bf16hi(v));
+        }
+        if (MODE == UCMX_POOL_MEAN) {
+            const float inv = 1.0f / (float)p.T;
+            a0 *= inv;
+            a1 *= inv;
+        }
+        const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : (int64_t)blk;
+        if (slot >= 0) {
+            const int e0 = split * cols + c2;
+            const int h = e0 / p.D, d = e0 - h * p.D;
+            const int64_t o = ((slot * p.H + h) * p.n_rep + p.rep_index) * (int64_t)p.D + d;
+            const uint32_t b0 = f32_to_bf16_bits(a0), b1 = f32_to_bf16_bits(a1);
+            if (p.out_bf16) *reinterpret_cast<uint32_t*>(p.out_bf16 + o) = b0 | (b1 << 16);
+            if (p.out_f32) {
+                float2 f = p.round_bf16 ? make_float2(__uint_as_float(b0 << 16), __uint_as_float(b1 << 16))
+                                        : make_float2(a0, a1);
+                *reinterpret_cast<float2*>(p.out_f32 + o) = f;
+            }
+        }
+    }
+    if (!ok && tid == 0) (void)mbar_wait(bar, 0);  // one more bounded wait before the tile memory is released
+}
+
+// Returns UCMX_EUNSUPPORTED when the tile path does not apply (the caller then streams).
+int32_t launch_pool_tile(PoolParams& p, const ucmx_kv_geometry* g, int mode, cudaStream_t st)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc || g->reserved <= 0 || p.T > 256 || (p.D & 1)) return UCMX_EUNSUPPORTED;
+    const int sms = sm_count();
+    // piece width: at most 256 elements (the TMA box limit), as narrow as 64 while the grid is small
+    int cs = 1;
+    while (p.E / cs > 256 || ((int64_t)p.n * cs < 4 * (int64_t)sms && p.E / (cs * 2) >= 64)) {
+        if (p.E % (cs * 2) || (p.E / (cs * 2)) % 8) break;
+        cs *= 2;
+    }
+    const int cols = p.E / cs;
+    if (cols > 256 || cols % 8 || p.E % cs) return UCMX_EUNSUPPORTED;
+    if ((int64_t)p.n * cs > 8 * (int64_t)sms) return UCMX_EUNSUPPORTED;  // large batches stream instead
+    const size_t tile_bytes = (size_t)cols * 2 * p.T;
+    const size_t smem = 128 + tile_bytes;
+    if (smem > 200 * 1024) return UCMX_EUNSUPPORTED;
+
+    alignas(64) CUtensorMap tmap;
+    const cuuint64_t dims[3] = {(cuuint64_t)p.E, (cuuint64_t)p.T, (cuuint64_t)g->reserved};
+    const cuuint64_t strides[2] = {(cuuint64_t)p.token_stride * 2, (cuuint64_t)p.block_stride * 2};  // bytes, dims 1..2
+    const cuuint32_t box[3] = {(cuuint32_t)cols, (cuuint32_t)p.T, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<uint16_t*>(p.k), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
+    p.cs = cs;
+    p.cg_per_item = cols / 8;
+    int threads = ((cols / 2 + 31) / 32) * 32;
+    const int grid = p.n * cs;
+#define UCMX_TILE_CASE(M)                                                                              \
+    case M: {                                                                                          \
+        auto kern = pool_blocks_tile_kernel<M>;                                                        \
+        UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kern<<<grid, threads, smem, st>>>(tmap, p);                                                    \
+    } break;
+    switch (mode) {
+        UCMX_TILE_CASE(UCMX_POOL_MEAN)
+        UCMX_TILE_CASE(UCMX_POOL_MAX)
+        UCMX_TILE_CASE(UCMX_POOL_MIN)
+        default:
+            UCMX_TILE_CASE(UCMX_POOL_SUM)
+    }
+#undef UCMX_TILE_CASE
+    UCMX_LAUNCH_CHECK("pool_blocks_tile_kernel");
+    return UCMX_OK;
+}
+
 }  // namespace
 }  // namespace ucmx
 
@@ -259,13 +415,33 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
     p.rep_index = rep_index;
     p.out_bf16 = (uint16_t*)out_bf16;
     p.out_f32 = out_f32;
-    p.rows_per_stage = (int32_t)(kStageBytes / (E64 * 2));
+    p.err = error_word();
+    if (!getenv("UCMX_POOL_NO_TILE")) {
+        PoolParams pt = p;
+        const int32_t rc = launch_pool_tile(pt, g, mode, (cudaStream_t)stream);
+        if (rc != UCMX_EUNSUPPORTED) return rc;
+    }
+    // With few blocks (a decode step pools one new block per request) a block's rows are cut into
+    // column pieces so that the work still covers the machine; each column is summed by one thread
+    // in token order either way, so results do not depend on the split.
+    const int sms = sm_count();
+    int cs = 1;
+    const int n_cg_row = p.E / 8;
+    while ((int64_t)n * cs < 4 * (int64_t)sms && cs < 8 && n_cg_row % (cs * 2) == 0 && n_cg_row / (cs * 2) >= 16) cs *= 2;
+    if (const char* e = getenv("UCMX_POOL_CS")) {  // tuning knob
+        const int v = atoi(e);
+        if (v >= 1 && v <= 8 && n_cg_row % v == 0) cs = v;
+    }
+    p.cs = cs;
+    p.cg_per_item = n_cg_row / cs;
+    const int64_t piece_bytes = (int64_t)p.cg_per_item * 16;
+    p.rows_per_stage = (int32_t)(kStageBytes / piece_bytes);
     if (p.rows_per_stage > p.T) p.rows_per_stage = p.T;
     p.chunks_per_block = (p.T + p.rows_per_stage - 1) / p.rows_per_stage;
-    p.dense = (g->token_stride == E64) ? 1 : 0;
+    p.dense = (g->token_stride == E64 && cs == 1) ? 1 : 0;
     p.err = error_word();
 
-    const int n_cg = p.E / 8;
+    const int n_cg = p.cg_per_item;
     int threads = ((n_cg + 31) / 32) * 32;
     int cgt = 1;
     while (threads > 256 && cgt < kMaxColGroupsPerThread) {
@@ -273,16 +449,21 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
         threads = (((n_cg + cgt - 1) / cgt + 31) / 32) * 32;
     }
     if (threads > 1024) return UCMX_EUNSUPPORTED;
-    const size_t smem = 128 + (size_t)kStages * kStageBytes;
-    const int ctas_per_sm = 3;
-    int grid = sm_count() * ctas_per_sm;
-    if (grid > n) grid = n;
+    // a CTA that owns a single work item needs no more stages than the item has chunks
+    p.stages = kStages;
+    if ((int64_t)n * cs <= (int64_t)sms * 3 && p.chunks_per_block < kStages) p.stages = p.chunks_per_block;
+    const size_t smem = 128 + (size_t)p.stages * kStageBytes;
+    int ctas_per_sm = (int)((size_t)(220 * 1024) / (smem + 1024));
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t grid = (int64_t)sms * ctas_per_sm;
+    if (grid > (int64_t)n * cs) grid = (int64_t)n * cs;
 
     cudaStream_t st = (cudaStream_t)stream;
     switch (mode) {
-        case UCMX_POOL_MEAN: return launch_pool<UCMX_POOL_MEAN>(p, threads, cgt, grid, smem, st);
-        case UCMX_POOL_MAX: return launch_pool<UCMX_POOL_MAX>(p, threads, cgt, grid, smem, st);
-        case UCMX_POOL_MIN: return launch_pool<UCMX_POOL_MIN>(p, threads, cgt, grid, smem, st);
-        default: return launch_pool<UCMX_POOL_SUM>(p, threads, cgt, grid, smem, st);
+        case UCMX_POOL_MEAN: return launch_pool<UCMX_POOL_MEAN>(p, threads, cgt, (int)grid, smem, st);
+        case UCMX_POOL_MAX: return launch_pool<UCMX_POOL_MAX>(p, threads, cgt, (int)grid, smem, st);
+        case UCMX_POOL_MIN: return launch_pool<UCMX_POOL_MIN>(p, threads, cgt, (int)grid, smem, st);
+        default: return launch_pool<UCMX_POOL_SUM>(p, threads, cgt, (int)grid, smem, st);
     }
 }

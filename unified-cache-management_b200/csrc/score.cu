@@ -3,7 +3,13 @@
 // score_dot: every candidate block contributes one table row (2 KiB of bf16 for 8 heads x 128)
 // that is read exactly once and dotted with its request's query, so the kernel is a gather-GEMV
 // bound by HBM (about 1 flop per byte); it runs on CUDA cores with 16-byte streaming loads, one
-// warp per row, the query held in registers.  Tensor cores would add nothing here.
+// warp per row and four rows in flight per warp, the query held in registers.  Tensor cores would
+// add nothing here.  The grid is one resident wave (a multiple of the SM count), each warp owning
+// a contiguous slice of the candidate list.  The per-KV-head query mean of the reference
+// (ucm/sparse/esa/esa.py:291-296) can be folded into the same kernel so that a decode step needs
+// no separate prologue launch.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ucmx {
@@ -11,6 +17,7 @@ namespace {
 
 constexpr int kScoreThreads = 256;
 constexpr int kMaxSmemOffsets = 2049;
+constexpr int kRowsInFlight = 4;
 
 // ------------------------------------------------------------------ query group mean
 
@@ -44,7 +51,10 @@ struct ScoreParams {
     const void* reps;
     const int32_t* offsets;
     const int32_t* slot_ids;
-    const float* q;
+    const float* q;          // fp32 [n_req, E] (already reduced per KV head), or NULL
+    const uint16_t* q_raw;   // bf16 [n_req, Hq, D] when the group mean is folded in
+    int64_t q_raw_stride;    // elements between requests in q_raw
+    int32_t Hq, D, round_bf16;
     float* out;
     int32_t n_req, total, E;
     float scale;
@@ -71,6 +81,65 @@ struct RowDot {
                 q[i * kPerPiece + v * 4 + 1] = f.y;
                 q[i * kPerPiece + v * 4 + 2] = f.z;
                 q[i * kPerPiece + v * 4 + 3] = f.w;
+            }
+        }
+    }
+    __device__ __forceinline__ void load_q_smem(const float* qrow, int lane)
+    {
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const float4* src = reinterpret_cast<const float4*>(qrow + (i * 32 + lane) * kPerPiece);
+#pragma unroll
+            for (int v = 0; v < kPerPiece / 4; ++v) {
+                const float4 f = src[v];
+                q[i * kPerPiece + v * 4 + 0] = f.x;
+                q[i * kPerPiece + v * 4 + 1] = f.y;
+                q[i * kPerPiece + v * 4 + 2] = f.z;
+                q[i * kPerPiece + v * 4 + 3] = f.w;
+            }
+        }
+    }
+    // q from the raw bf16 query [Hq, D]: mean over the head group in fp32 (heads in ascending
+    // order, times 1/group), optionally rounded to bf16 — the arithmetic of query_group_mean_kernel.
+    __device__ __noinline__ void load_q_raw(const uint16_t* __restrict__ qreq, int lane, int Hq, int Hkv, int D,
+                                               int round_bf16)
+    {
+        const int g = Hq >= Hkv ? Hq / Hkv : 1;
+        const int rep = Hq >= Hkv ? 1 : Hkv / Hq;
+        const float inv = 1.0f / (float)g;
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+#pragma unroll
+            for (int half = 0; half < kPerPiece / 4; ++half) {
+                // four consecutive elements e0..e0+3 of the flattened [Hkv, D] query
+                const int e0 = (i * 32 + lane) * kPerPiece + half * 4;
+                const int h = e0 / D, d = e0 - h * D;
+                const uint16_t* src = qreq + (int64_t)((h / rep) * g) * D + d;
+                uint2 w = __ldg(reinterpret_cast<const uint2*>(src));
+                float a0 = bf16lo(w.x), a1 = bf16hi(w.x), a2 = bf16lo(w.y), a3 = bf16hi(w.y);
+                for (int j = 1; j < g; ++j) {
+                    w = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * D));
+                    a0 += bf16lo(w.x);
+                    a1 += bf16hi(w.x);
+                    a2 += bf16lo(w.y);
+                    a3 += bf16hi(w.y);
+                }
+                if (Hq >= Hkv) {
+                    a0 *= inv;
+                    a1 *= inv;
+                    a2 *= inv;
+                    a3 *= inv;
+                    if (round_bf16) {
+                        a0 = bf16_round(a0);
+                        a1 = bf16_round(a1);
+                        a2 = bf16_round(a2);
+                        a3 = bf16_round(a3);
+                    }
+                }
+                q[i * kPerPiece + half * 4 + 0] = a0;
+                q[i * kPerPiece + half * 4 + 1] = a1;
+                q[i * kPerPiece + half * 4 + 2] = a2;
+                q[i * kPerPiece + half * 4 + 3] = a3;
             }
         }
     }
@@ -111,31 +180,118 @@ struct RowDot {
     }
 };
 
-template <int DT, int QN>
-__global__ void __launch_bounds__(kScoreThreads) score_dot_rows_kernel(ScoreParams p)
+template <int DT, int QN, bool FUSEQ>
+__global__ void __launch_bounds__(kScoreThreads, 2) score_dot_rows_kernel(ScoreParams p)
 {
     __shared__ int32_t s_off[kMaxSmemOffsets];
-    const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
-    if (off_in_smem) {
-        for (int i = threadIdx.x; i <= p.n_req; i += blockDim.x) s_off[i] = __ldg(p.offsets + i);
-        __syncthreads();
-    }
-    const int32_t* off = off_in_smem ? s_off : p.offsets;
-
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t W = (int64_t)gridDim.x * warps_per_cta;
     const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
     const int begin = (int)((int64_t)p.total * w / W);
     const int end = (int)((int64_t)p.total * (w + 1) / W);
-    if (begin >= end) return;
 
     using RD = RowDot<DT, QN>;
     RD rd;
     const size_t row_bytes = (size_t)p.E * (DT == UCMX_DT_BF16 ? 2 : 4);
     const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
 
-    int r = 0;
+    // Slot ids are held 32 rows at a time, one per lane (my_slot: rows [win, win+32); next_slot: the
+    // 32 after).  The first batch of row loads is issued before anything else in the kernel, so that
+    // HBM is already busy while the offsets and the queries are being staged.
+    auto load_slots = [&](int first) {
+        int v = -1;
+        if (first + lane < end) v = p.slot_ids ? __ldg(p.slot_ids + first + lane) : (first + lane);
+        return v;
+    };
+    int win = begin;
+    int my_slot = load_slots(begin);
+    int next_slot = load_slots(begin + 32);
+    int s[kRowsInFlight];
+    uint4 buf[kRowsInFlight][RD::kPieces];
+    auto issue = [&](int c) {
+#pragma unroll
+        for (int t = 0; t < kRowsInFlight; ++t) {
+            const int v = __shfl_sync(0xffffffffu, my_slot, (c + t - win) & 31);
+            s[t] = (c + t < end) ? v : -1;
+            if (s[t] >= 0) rd.load_row(base + (size_t)s[t] * row_bytes, lane, buf[t]);
+            else rd.zero_row(buf[t]);
+        }
+    };
+    issue(begin);
+
+    const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
+    if (off_in_smem) {
+        for (int i = threadIdx.x; i <= p.n_req; i += blockDim.x) s_off[i] = __ldg(p.offsets + i);
+        __syncthreads();
+    }
+    const int32_t* off = off_in_smem ? s_off : p.offsets;
+    const int Hkv = p.E / p.D;
+
+    // With the query mean folded in, the CTA first reduces the raw queries of the (at most
+    // kStagedReq) requests its slice starts in into shared memory, all threads at once; a warp that
+    // runs past them falls back to reducing its query on its own.
+    constexpr int kStagedReq = 2;
+    __shared__ __align__(16) float s_q[FUSEQ ? kStagedReq * QN * 32 : 4];
+    int r_cta = 0;
+    if (FUSEQ) {
+        const int cta_begin = (int)((int64_t)p.total * ((int64_t)blockIdx.x * warps_per_cta) / W);
+        {
+            int lo = 0, hi = p.n_req;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (off[mid] <= cta_begin) lo = mid; else hi = mid;
+            }
+            r_cta = lo;
+        }
+        const int g = p.Hq >= Hkv ? p.Hq / Hkv : 1;
+        const int rep = p.Hq >= Hkv ? 1 : Hkv / p.Hq;
+        const float inv = 1.0f / (float)g;
+        for (int idx = threadIdx.x; idx < kStagedReq * (p.E / 4); idx += blockDim.x) {
+            const int rr = idx / (p.E / 4);
+            const int e0 = (idx - rr * (p.E / 4)) * 4;
+            const int req = r_cta + rr;
+            if (req >= p.n_req) break;
+            const int h = e0 / p.D, d = e0 - h * p.D;
+            const uint16_t* src = p.q_raw + (int64_t)req * p.q_raw_stride + (int64_t)((h / rep) * g) * p.D + d;
+            uint2 w0 = __ldg(reinterpret_cast<const uint2*>(src));
+            float a0 = bf16lo(w0.x), a1 = bf16hi(w0.x), a2 = bf16lo(w0.y), a3 = bf16hi(w0.y);
+            if (g == 4) {
+                const uint2 w1 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)p.D));
+                const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)2 * p.D));
+                const uint2 w3 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)3 * p.D));
+                a0 = ((a0 + bf16lo(w1.x)) + bf16lo(w2.x)) + bf16lo(w3.x);
+                a1 = ((a1 + bf16hi(w1.x)) + bf16hi(w2.x)) + bf16hi(w3.x);
+                a2 = ((a2 + bf16lo(w1.y)) + bf16lo(w2.y)) + bf16lo(w3.y);
+                a3 = ((a3 + bf16hi(w1.y)) + bf16hi(w2.y)) + bf16hi(w3.y);
+            } else {
+                for (int j = 1; j < g; ++j) {
+                    const uint2 wj = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * p.D));
+                    a0 += bf16lo(wj.x);
+                    a1 += bf16hi(wj.x);
+                    a2 += bf16lo(wj.y);
+                    a3 += bf16hi(wj.y);
+                }
+            }
+            if (p.Hq >= Hkv) {
+                a0 *= inv;
+                a1 *= inv;
+                a2 *= inv;
+                a3 *= inv;
+                if (p.round_bf16) {
+                    a0 = bf16_round(a0);
+                    a1 = bf16_round(a1);
+                    a2 = bf16_round(a2);
+                    a3 = bf16_round(a3);
+                }
+            }
+            *reinterpret_cast<float4*>(&s_q[rr * p.E + e0]) = make_float4(a0, a1, a2, a3);
+        }
+        __syncthreads();
+    }
+    if (begin >= end) return;
+
+    int r;
     {
         int lo = 0, hi = p.n_req;
         while (hi - lo > 1) {
@@ -145,62 +301,62 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_rows_kernel(ScorePara
         r = lo;
     }
     int r_end = off[r + 1];
-    rd.load_q(p.q + (int64_t)r * p.E, lane);
 
-    for (int c0 = begin; c0 < end; c0 += 32) {
-        // the slots of up to 32 candidates, one per lane
-        const int nc = min(32, end - c0);
-        int my_slot = 0;
-        if (lane < nc) my_slot = p.slot_ids ? __ldg(p.slot_ids + c0 + lane) : (c0 + lane);
-        int j = 0;
-        for (; j + 1 < nc; j += 2) {
-            const int sa = __shfl_sync(0xffffffffu, my_slot, j);
-            const int sb = __shfl_sync(0xffffffffu, my_slot, j + 1);
-            uint4 a[RD::kPieces], b[RD::kPieces];
-            if (sa >= 0) rd.load_row(base + (size_t)sa * row_bytes, lane, a);
-            else rd.zero_row(a);
-            if (sb >= 0) rd.load_row(base + (size_t)sb * row_bytes, lane, b);
-            else rd.zero_row(b);
-            const int ca = c0 + j, cb = ca + 1;
-            while (ca >= r_end) {
-                ++r;
-                r_end = off[r + 1];
-                if (ca < r_end) rd.load_q(p.q + (int64_t)r * p.E, lane);
-            }
-            float va = rd.dot(a);
-            if (cb >= r_end) {
-                while (cb >= r_end) {
-                    ++r;
-                    r_end = off[r + 1];
-                }
-                rd.load_q(p.q + (int64_t)r * p.E, lane);
-            }
-            float vb = rd.dot(b);
+    auto fetch_q = [&](int req) {
+        if (FUSEQ) {
+            if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * p.E], lane);
+            else rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
+        } else {
+            rd.load_q(p.q + (int64_t)req * p.E, lane);
+        }
+    };
+    bool q_valid = false;
+
+    for (int c = begin; c < end; c += kRowsInFlight) {
+        float v[kRowsInFlight];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                va += __shfl_xor_sync(0xffffffffu, va, o);
-                vb += __shfl_xor_sync(0xffffffffu, vb, o);
-            }
-            if (lane == 0) {
-                p.out[ca] = sa < 0 ? -INFINITY : va * p.scale;
-                p.out[cb] = sb < 0 ? -INFINITY : vb * p.scale;
+        for (int t = 0; t < kRowsInFlight; ++t) {
+            v[t] = 0.0f;
+            const int row = c + t;
+            if (row < end) {
+                if (row >= r_end) {
+                    while (row >= r_end) {
+                        ++r;
+                        r_end = off[r + 1];
+                    }
+                    q_valid = false;
+                }
+                if (!q_valid) {
+                    fetch_q(r);
+                    q_valid = true;
+                }
+                v[t] = rd.dot(buf[t]);
             }
         }
-        if (j < nc) {
-            const int sa = __shfl_sync(0xffffffffu, my_slot, j);
-            uint4 a[RD::kPieces];
-            if (sa >= 0) rd.load_row(base + (size_t)sa * row_bytes, lane, a);
-            else rd.zero_row(a);
-            const int ca = c0 + j;
-            if (ca >= r_end) {
-                while (ca >= r_end) {
-                    ++r;
-                    r_end = off[r + 1];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int t = 0; t < kRowsInFlight; ++t) v[t] += __shfl_xor_sync(0xffffffffu, v[t], o);
+        }
+        if (lane < kRowsInFlight && c + lane < end) {
+            float mine = v[0];
+            int slot = s[0];
+#pragma unroll
+            for (int t = 1; t < kRowsInFlight; ++t)
+                if (lane == t) {
+                    mine = v[t];
+                    slot = s[t];
                 }
-                rd.load_q(p.q + (int64_t)r * p.E, lane);
+            p.out[c + lane] = slot < 0 ? -INFINITY : mine * p.scale;
+        }
+        const int next = c + kRowsInFlight;
+        if (next < end) {
+            if (next >= win + 32) {  // 32 is a multiple of the batch, so a batch never straddles windows
+                win += 32;
+                my_slot = next_slot;
+                next_slot = load_slots(win + 32);
             }
-            float va = warp_sum(rd.dot(a));
-            if (lane == 0) p.out[ca] = sa < 0 ? -INFINITY : va * p.scale;
+            issue(next);
         }
     }
 }
@@ -276,12 +432,12 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
     }
 }
 
-template <int DT>
+template <int DT, bool FUSEQ>
 int32_t launch_rows(const ScoreParams& p, int qn, int grid, cudaStream_t st)
 {
     switch (qn) {
 #define UCMX_ROWS_CASE(Q) \
-    case Q: score_dot_rows_kernel<DT, Q><<<grid, kScoreThreads, 0, st>>>(p); break;
+    case Q: score_dot_rows_kernel<DT, Q, FUSEQ><<<grid, kScoreThreads, 0, st>>>(p); break;
         UCMX_ROWS_CASE(8)
         UCMX_ROWS_CASE(16)
         UCMX_ROWS_CASE(32)
@@ -291,6 +447,29 @@ int32_t launch_rows(const ScoreParams& p, int qn, int grid, cudaStream_t st)
     }
     UCMX_LAUNCH_CHECK("score_dot_rows_kernel");
     return UCMX_OK;
+}
+
+bool rows_path_ok(int32_t reps_dtype, int32_t n_rep, int64_t E, int* qn)
+{
+    const int per_piece = reps_dtype == UCMX_DT_BF16 ? 8 : 4;
+    if (n_rep != 1 || E % (32 * per_piece) != 0) return false;
+    *qn = (int)(E / 32);
+    return *qn == 8 || *qn == 16 || *qn == 32 || *qn == 64;
+}
+
+int rows_grid(int32_t total)
+{
+    // one resident wave: two CTAs of 8 warps per SM; fewer when there is less than a row per warp
+    const int warps_per_cta = kScoreThreads / 32;
+    static const int per_sm = [] {
+        const char* e = getenv("UCMX_SCORE_CTAS_PER_SM");  // tuning knob; default = resident CTAs per SM
+        const int v = e ? atoi(e) : 0;
+        return v > 0 && v <= 64 ? v : 2;
+    }();
+    int64_t grid = (int64_t)sm_count() * per_sm;
+    const int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
+    if (grid > want) grid = want;
+    return (int)(grid < 1 ? 1 : grid);
 }
 
 }  // namespace
@@ -328,29 +507,68 @@ extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t 
     if (((uintptr_t)reps & 15) || ((uintptr_t)q & 15)) return UCMX_EPARAM;
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t E = (int64_t)n_kv_heads * head_dim;
-    const int per_piece = reps_dtype == UCMX_DT_BF16 ? 8 : 4;
-    const int sms = sm_count();
-
-    if (n_rep == 1 && E % (32 * per_piece) == 0) {
-        const int qn = (int)(E / 32);
-        if (qn == 8 || qn == 16 || qn == 32 || qn == 64) {
-            ScoreParams p{reps, req_offsets, slot_ids, q, out_scores, n_req, total, (int32_t)E, scale};
-            // aim at >= 2 candidates per warp, at most 8 resident CTAs per SM
-            const int warps_per_cta = kScoreThreads / 32;
-            int64_t want = ((int64_t)total + 2 * warps_per_cta - 1) / (2 * warps_per_cta);
-            int grid = (int)(want < 1 ? 1 : (want > (int64_t)sms * 8 ? (int64_t)sms * 8 : want));
-            if (reps_dtype == UCMX_DT_BF16) return launch_rows<UCMX_DT_BF16>(p, qn, grid, st);
-            return launch_rows<UCMX_DT_F32>(p, qn, grid, st);
-        }
+    int qn = 0;
+    if (rows_path_ok(reps_dtype, n_rep, E, &qn)) {
+        ScoreParams p{};
+        p.reps = reps;
+        p.offsets = req_offsets;
+        p.slot_ids = slot_ids;
+        p.q = q;
+        p.D = head_dim;
+        p.out = out_scores;
+        p.n_req = n_req;
+        p.total = total;
+        p.E = (int32_t)E;
+        p.scale = scale;
+        const int grid = rows_grid(total);
+        if (reps_dtype == UCMX_DT_BF16) return launch_rows<UCMX_DT_BF16, false>(p, qn, grid, st);
+        return launch_rows<UCMX_DT_F32, false>(p, qn, grid, st);
     }
     ScoreGenParams g{reps, req_offsets, slot_ids, q, out_scores, n_req, total, n_kv_heads, n_rep, head_dim, scale};
     const int warps_per_cta = kScoreThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
-    int grid = (int)(want > (int64_t)sms * 8 ? (int64_t)sms * 8 : want);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    int grid = (int)(want > cap ? cap : want);
     if (reps_dtype == UCMX_DT_BF16)
         score_dot_general_kernel<UCMX_DT_BF16><<<grid, kScoreThreads, 0, st>>>(g);
     else
         score_dot_general_kernel<UCMX_DT_F32><<<grid, kScoreThreads, 0, st>>>(g);
     UCMX_LAUNCH_CHECK("score_dot_general_kernel");
     return UCMX_OK;
+}
+
+extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t head_dim,
+                                        const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+                                        int32_t n_q_heads, int64_t query_stride, int32_t round_bf16, int32_t n_req,
+                                        int32_t total, float scale, float* out_scores, ucmx_stream_t stream)
+{
+    using namespace ucmx;
+    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req == 0 || total == 0) return UCMX_OK;
+    if (!reps || !req_offsets || !query || !out_scores) return UCMX_EPARAM;
+    if (reps_dtype != UCMX_DT_BF16 && reps_dtype != UCMX_DT_F32) return UCMX_EPARAM;
+    if (n_kv_heads < 1 || n_q_heads < 1 || head_dim < 8 || head_dim % 8) return UCMX_EPARAM;
+    if (n_q_heads >= n_kv_heads ? (n_q_heads % n_kv_heads) : (n_kv_heads % n_q_heads)) return UCMX_EPARAM;
+    if (query_stride < (int64_t)n_q_heads * head_dim || (query_stride % 4)) return UCMX_EPARAM;
+    if (((uintptr_t)reps & 15) || ((uintptr_t)query & 7)) return UCMX_EPARAM;
+    const int64_t E = (int64_t)n_kv_heads * head_dim;
+    int qn = 0;
+    if (!rows_path_ok(reps_dtype, 1, E, &qn)) return UCMX_EUNSUPPORTED;
+    ScoreParams p{};
+    p.reps = reps;
+    p.offsets = req_offsets;
+    p.slot_ids = slot_ids;
+    p.q_raw = (const uint16_t*)query;
+    p.q_raw_stride = query_stride;
+    p.Hq = n_q_heads;
+    p.D = head_dim;
+    p.round_bf16 = round_bf16;
+    p.out = out_scores;
+    p.n_req = n_req;
+    p.total = total;
+    p.E = (int32_t)E;
+    p.scale = scale;
+    const int grid = rows_grid(total);
+    if (reps_dtype == UCMX_DT_BF16) return launch_rows<UCMX_DT_BF16, true>(p, qn, grid, (cudaStream_t)stream);
+    return launch_rows<UCMX_DT_F32, true>(p, qn, grid, (cudaStream_t)stream);
 }

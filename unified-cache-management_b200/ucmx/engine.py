@@ -71,7 +71,7 @@ class DecodeRetrievalEngine:
         self.q_host: Optional[torch.Tensor] = None
         self.sel_host: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = self.L * (5 if with_kv_pool else 3)
+        self.launches_per_step = self.L * (4 if with_kv_pool else 2)
 
     # ---------------------------------------------------------------------------------- stages
     def make_queries(self) -> torch.Tensor:
@@ -88,9 +88,8 @@ class DecodeRetrievalEngine:
         ops.pool_blocks(self.kv_pool[0], self.block_table, out_slots=self.block_table, out_bf16=self.rep_tables[layer])
 
     def score_layer(self, layer: int) -> None:
-        ops.query_group_mean(self.q_dev[layer], self.H, out=self.qbar)
-        ops.score_dot(self.rep_tables[layer], self.offsets, self.qbar, total=self.batch.total,
-                      slot_ids=self.block_table, n_kv_heads=self.H, head_dim=self.D, out=self.scores)
+        ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
+                            slot_ids=self.block_table, n_kv_heads=self.H, out=self.scores)
         if self.score_reduce is not None:
             self.score_reduce(self.scores)
 

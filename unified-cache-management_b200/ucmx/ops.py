@@ -48,7 +48,7 @@ def kv_geometry(k_cache: torch.Tensor) -> N.KvGeometry:
     sb, st, sh, sd = k_cache.stride()
     if sd != 1 or sh != D:
         raise ValueError("heads and head_dim of the paged cache must be contiguous")
-    return N.KvGeometry(sb, st, T, H, D, 0)
+    return N.KvGeometry(sb, st, T, H, D, nb)
 
 
 def pool_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, *, mode: str = "mean",
@@ -115,6 +115,35 @@ def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *,
                               _ptr(_i32(slot_ids, "slot_ids")), _ptr(q), n_req, total, float(scale), _ptr(out),
                               _stream(reps))
     N.check("ucmx_score_dot", st, 1 if total and n_req else 0)
+    return out
+
+
+def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.Tensor, *, total: int,
+                    slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, round_bf16: bool = True,
+                    scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """score_dot with the per-KV-head query mean folded in: query is the raw bf16 [n_req, n_q_heads, head_dim].
+    Shapes the single-pass kernel does not cover go through query_group_mean + score_dot (two launches)."""
+    _need_cuda(reps, req_offsets, query, slot_ids, out)
+    if query.dim() != 3 or query.dtype != torch.bfloat16:
+        raise ValueError("query must be bf16 [n_req, n_q_heads, head_dim]")
+    n_req, Hq, D = query.shape
+    if n_req != req_offsets.numel() - 1:
+        raise ValueError("one query row per request")
+    if query.stride(2) != 1 or query.stride(1) != D:
+        query = query.contiguous()
+    dt = DT_BF16 if reps.dtype == torch.bfloat16 else DT_F32 if reps.dtype == torch.float32 else None
+    if dt is None or not reps.is_contiguous():
+        raise ValueError("reps must be contiguous bf16 or fp32")
+    if out is None:
+        out = torch.empty((total,), dtype=torch.float32, device=reps.device)
+    st = N.lib.ucmx_score_dot_query(_ptr(reps), dt, n_kv_heads, D, _ptr(_i32(req_offsets, "req_offsets")),
+                                    _ptr(_i32(slot_ids, "slot_ids")), _ptr(query), Hq, query.stride(0), int(round_bf16),
+                                    n_req, total, float(scale), _ptr(out), _stream(reps))
+    if st == N.EUNSUPPORTED:
+        qbar = query_group_mean(query, n_kv_heads, round_bf16=round_bf16)
+        return score_dot(reps, req_offsets, qbar, total=total, slot_ids=slot_ids, n_kv_heads=n_kv_heads, head_dim=D,
+                         scale=scale, out=out)
+    N.check("ucmx_score_dot_query", st, 1 if total and n_req else 0)
     return out
 
 
