@@ -9,6 +9,8 @@
 // ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:182-189) adds a bitonic sort of the k winners
 // in shared memory.  Scores were written by the scoring kernel a moment earlier and are re-read
 // from L2, so the passes cost latency, not HBM traffic.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ucmx {
@@ -63,7 +65,7 @@ __device__ __forceinline__ int block_excl_scan_flag(bool flag, int* s_warp, int&
 __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 {
     extern __shared__ __align__(16) unsigned long long s_sort[];  // score-descending order only
-    __shared__ uint32_t s_hist[256];
+    __shared__ uint32_t s_hist[4][256];  // one histogram per radix pass, cleared once
     __shared__ int s_warp[32];
     __shared__ uint32_t s_prefix;
     __shared__ int s_krem;
@@ -118,16 +120,16 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             s_prefix = 0;
             s_krem = kk;
         }
+        for (int i = tid; i < 4 * 256; i += blockDim.x) (&s_hist[0][0])[i] = 0;
+        __syncthreads();
         uint32_t mask = 0;
 #pragma unroll 1
         for (int pass = 0; pass < 4; ++pass) {
             const int shift = 24 - 8 * pass;
-            for (int i = tid; i < 256; i += blockDim.x) s_hist[i] = 0;
-            __syncthreads();
             const uint32_t prefix = s_prefix;
             for (int i = lo + tid; i < hi; i += blockDim.x) {
                 const uint32_t key = to_key(sc[i], is_float);
-                if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+                if ((key & mask) == prefix) atomicAdd(&s_hist[pass][(key >> shift) & 255u], 1u);
             }
             __syncthreads();
             if (tid < 32) {
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
                 uint32_t sum = 0;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    h[j] = s_hist[255 - 8 * tid - j];
+                    h[j] = s_hist[pass][255 - 8 * tid - j];
                     sum += h[j];
                 }
                 uint32_t incl = sum;
@@ -206,7 +208,21 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     const int cnt = min(out_base, cap);
     if (tid == 0) p.out_counts[r] = cnt;
 
-    if (desc && cnt > 0) {
+    if (desc && cnt > 0 && cnt <= 256) {
+        // few winners: every winner counts how many beat it (keys are unique), which is its place
+        __syncthreads();
+        unsigned long long mine = 0;
+        int rank = 0;
+        if (tid < cnt) {
+            mine = s_sort[tid];
+            for (int j = 0; j < cnt; ++j) rank += s_sort[j] > mine;
+        }
+        if (tid < cnt) {
+            const int i = (int)(~(uint32_t)(mine & 0xffffffffull));
+            p.out_idx[orow + rank] = p.id_map ? __ldg(p.id_map + base + i) : i;
+            if (p.out_scores) p.out_scores[orow + rank] = from_key((uint32_t)(mine >> 32), is_float);
+        }
+    } else if (desc && cnt > 0) {
         int P = 1;
         while (P < cnt) P <<= 1;
         for (int i = cnt + tid; i < P; i += blockDim.x) s_sort[i] = 0ull;
@@ -276,7 +292,15 @@ extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, con
     p.out_counts = out_counts;
     if (smem > 48 * 1024)
         UCMX_CUDA(cudaFuncSetAttribute(topk_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    topk_ragged_kernel<<<n_req, 1024, smem, (cudaStream_t)stream>>>(p);
+    // block size: enough threads for about two candidates each (the host does not know the ragged
+    // sizes, only the output width, so k is the hint), never fewer than the rank sort needs
+    int threads = 1024;
+    if (out_stride <= 64) threads = 512;
+    if (const char* e = getenv("UCMX_TOPK_THREADS")) {  // tuning knob
+        const int v = atoi(e);
+        if (v == 256 || v == 512 || v == 1024) threads = v;
+    }
+    topk_ragged_kernel<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("topk_ragged_kernel");
     return UCMX_OK;
 }
