@@ -203,12 +203,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=32, help=argparse.SUPPRESS)
+    ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--workload", default="decode64", choices=["decode64", "tp-long"],
+                    help="decode64: the 64-request ragged decode batch, data parallel over requests (default); "
+                         "tp-long: 8 requests of 1 048 576 tokens, KV heads split over the GPUs with an all-reduce of "
+                         "block scores before top-k")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profiler captures: 8 requests, 2 layers, 1 warm-up + 1 step, no host legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     n_req = 64
+    tp = args.workload == "tp-long"
+    if args.layers is None:
+        args.layers = 16 if tp else 32
     if args.profile_case:
         args.layers, args.steps, args.warmup, args.no_cpu_baseline, n_req = 2, 1, 1, True, 8
 
@@ -224,7 +231,8 @@ def main():
     import torch.distributed as dist
     from ucmx import _native
     from ucmx.engine import DecodeRetrievalEngine
-    from ucmx.workloads import LLAMA3_8B, ragged_decode_batch
+    from ucmx.parallel import ScoreAllReduce, head_range
+    from ucmx.workloads import LLAMA3_8B, QWEN2_72B_LIKE, fixed_batch, ragged_decode_batch
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
@@ -238,8 +246,17 @@ def main():
         if world > 1:
             dist.barrier(device_ids=[local_rank])
 
-    batch = ragged_decode_batch(seed=2002 + rank, n_req=n_req)
-    eng = DecodeRetrievalEngine(LLAMA3_8B, batch, dev, n_layers=args.layers, seed=1000 + rank)
+    if tp:
+        # every rank sees the same 8 requests and block tables and holds n_kv_heads/world of the heads
+        shape = QWEN2_72B_LIKE
+        batch = fixed_batch(8, 8192, 2048, seed=5005)
+        lo, hi = head_range(shape.n_kv_heads, rank, world)
+        eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank, heads_local=hi - lo,
+                                    score_reduce=ScoreAllReduce() if world > 1 else None)
+    else:
+        shape = LLAMA3_8B
+        batch = ragged_decode_batch(seed=2002 + rank, n_req=n_req)
+        eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank)
     eng.make_queries()
     torch.cuda.synchronize()
 
@@ -252,7 +269,8 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
-    prefill_gbs = batch.total * (LLAMA3_8B.slice_bytes + 2048) / prefill_ms / 1e6
+    row_bytes = eng.H * eng.D * 2
+    prefill_gbs = batch.total * (eng.T * row_bytes + row_bytes) / prefill_ms / 1e6
 
     if args.graph:
         eng.capture()
@@ -298,7 +316,9 @@ def main():
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
     tokens_per_step_all = eng.tokens_scored_per_step() * world   # same batch size on every rank (weak scaling)
-    if world > 1:
+    if tp:
+        tokens_per_step_all = eng.tokens_scored_per_step()       # one batch shared by all ranks (strong scaling)
+    elif world > 1:
         tt = torch.tensor([float(eng.tokens_scored_per_step())], dtype=torch.float64, device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.SUM)
         tokens_per_step_all = float(tt.item())
@@ -369,7 +389,7 @@ def main():
     }
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not tp:
         try:
             from oracle import oracle as orc
             if orc.have_ref():
@@ -388,9 +408,14 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(batch, extra={"cuda_graph": bool(args.graph), "layers": eng.L}),
+            "config": workload_config(batch, extra={"cuda_graph": bool(args.graph), "layers": eng.L}) if not tp else {
+                "workload": "long-context sharded retrieval: 8 requests x 1 048 576 tokens (8192 blocks each), Qwen2-72B-like "
+                            "KV (64q/8kv heads, head_dim 128), KV heads split over the GPUs, fp32 all-reduce of 65 536 block "
+                            "scores before top-k 2048, gather of the selected K,V head slices",
+                "layers": eng.L, "tp": world, "heads_per_rank": eng.H, "parallelism": f"tp{world} over KV heads",
+                "l2_policy": "inputs larger than L2 per step", "cuda_graph": bool(args.graph)},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_s * 1e3,
