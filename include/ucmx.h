@@ -256,6 +256,12 @@ int32_t ucmx_scatter_blocks(void* const* planes /* host */, int32_t n_planes,
 int32_t ucmx_copy_batch(void* const* dst_ptrs, const void* const* src_ptrs, int32_t number,
                         int64_t count, int32_t any_host_memory, ucmx_stream_t stream);
 
+/* One contiguous asynchronous copy in either direction (device or page-locked host memory on both
+ * ends): CudaDevice::H2DAsync / D2HAsync (ucm/store/device/cuda/cuda_device.cu:152-159).  Paired
+ * with a gather into (or scatter out of) a contiguous device staging area it moves a whole batch of
+ * block slices over the host link with one DMA instead of one per slice. */
+int32_t ucmx_memcpy_async(void* dst, const void* src, int64_t bytes, ucmx_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Pinned host ring — IBufferedDevice::GetBuffer (ucm/store/device/ibuffered_device.h:32-62):
  * one page-locked slab cut into n_slots slots of slot_bytes, handed out by index.

@@ -162,8 +162,17 @@ struct HamParams {
 
 constexpr int kHamThreads = 256;
 
+// carry-save adder on 32 bit columns at once: (h, l) = a + b + c
+__device__ __forceinline__ void csa(uint32_t& h, uint32_t& l, uint32_t a, uint32_t b, uint32_t c)
+{
+    const uint32_t u = a ^ b;
+    h = (a & b) | (u & c);
+    l = u ^ c;
+}
+
 // bits == 128 (one uint4 per code).  One warp per candidate block.
-__global__ void __launch_bounds__(kHamThreads) score_hamming_kernel(HamParams p)
+template <bool CROSS>
+__global__ void __launch_bounds__(kHamThreads, CROSS ? 2 : 4) score_hamming_kernel(HamParams p)
 {
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
@@ -184,7 +193,7 @@ __global__ void __launch_bounds__(kHamThreads) score_hamming_kernel(HamParams p)
         const uint4* qc = reinterpret_cast<const uint4*>(p.q_codes + (size_t)r * p.nq * 16);
         long long ham_total = 0;  // sum over pairs of popcount(q xor k)
         long long pairs = 0;
-        if (p.cross) {
+        if (CROSS) {
             // bit-sliced count of set query bits per position: c_b = P0 + 2 P1 + 4 P2 + 8 P3
             uint32_t P[4][4];
 #pragma unroll
@@ -211,6 +220,54 @@ __global__ void __launch_bounds__(kHamThreads) score_hamming_kernel(HamParams p)
                 }
             }
             int a0 = 0, a1 = 0, a2 = 0, a3 = 0, a4 = 0;
+            if ((pieces & 255) == 0) {
+                // Carry-save counting (Harley-Seal): the lane's key words of one word position are added
+                // bit-column-wise into binary counter planes with LOP3 full adders, eight words at a
+                // time, and popcounts are taken once per 32 words on the planes instead of five
+                // times per word; this keeps the all-pairs form bound by HBM rather than by the
+                // popcount pipe.  A lane sees pieces/32 words per position (a multiple of 8).
+                for (int base_pc = 0; base_pc < pieces; base_pc += 32 * 32) {
+                    uint32_t ones[4] = {0, 0, 0, 0}, twos[4] = {0, 0, 0, 0}, fours[4] = {0, 0, 0, 0};
+                    uint32_t eights[4] = {0, 0, 0, 0}, sixteens[4] = {0, 0, 0, 0}, thirtytwos[4] = {0, 0, 0, 0};
+                    const int groups = min(4, (pieces - base_pc) / 256);
+                    for (int grp = 0; grp < groups; ++grp) {
+                        uint4 k[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) k[j] = ld_stream16(row + base_pc + (grp * 8 + j) * 32 + lane);
+#pragma unroll
+                        for (int wd = 0; wd < 4; ++wd) {
+                            uint32_t x[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) x[j] = wd == 0 ? k[j].x : wd == 1 ? k[j].y : wd == 2 ? k[j].z : k[j].w;
+                            uint32_t twosA, twosB, foursA, foursB, e8;
+                            csa(twosA, ones[wd], ones[wd], x[0], x[1]);
+                            csa(twosB, ones[wd], ones[wd], x[2], x[3]);
+                            csa(foursA, twos[wd], twos[wd], twosA, twosB);
+                            csa(twosA, ones[wd], ones[wd], x[4], x[5]);
+                            csa(twosB, ones[wd], ones[wd], x[6], x[7]);
+                            csa(foursB, twos[wd], twos[wd], twosA, twosB);
+                            csa(e8, fours[wd], fours[wd], foursA, foursB);
+                            const uint32_t c16 = eights[wd] & e8;
+                            eights[wd] ^= e8;
+                            const uint32_t c32 = sixteens[wd] & c16;
+                            sixteens[wd] ^= c16;
+                            thirtytwos[wd] ^= c32;
+                        }
+                    }
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        const uint32_t plane[6] = {ones[wd], twos[wd], fours[wd], eights[wd], sixteens[wd], thirtytwos[wd]};
+#pragma unroll
+                        for (int l = 0; l < 6; ++l) {
+                            a0 += __popc(plane[l]) << l;
+                            a1 += __popc(plane[l] & P[0][wd]) << l;
+                            a2 += __popc(plane[l] & P[1][wd]) << l;
+                            a3 += __popc(plane[l] & P[2][wd]) << l;
+                            a4 += __popc(plane[l] & P[3][wd]) << l;
+                        }
+                    }
+                }
+            } else {
 #pragma unroll 4
             for (int pc = lane; pc < pieces; pc += 32) {
                 const uint4 k = ld_stream16(row + pc);
@@ -223,6 +280,7 @@ __global__ void __launch_bounds__(kHamThreads) score_hamming_kernel(HamParams p)
                     a3 += __popc(kw[wd] & P[2][wd]);
                     a4 += __popc(kw[wd] & P[3][wd]);
                 }
+            }
             }
             // sum_i popcount(q_i xor k) = C + nq*popc(k) - 2*sum_p 2^p popc(k & P_p)
             const long long weighted = (long long)a1 + 2ll * a2 + 4ll * a3 + 8ll * a4;
@@ -362,8 +420,10 @@ extern "C" int32_t ucmx_score_hamming(const uint8_t* codes, int32_t n_kv_heads, 
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
     const int64_t cap = (int64_t)sm_count() * 8;
     const int grid = (int)(want > cap ? cap : want);
-    if (bits == 128 && n_q_heads <= 15 && !((uintptr_t)q_codes & 15))
-        score_hamming_kernel<<<grid, kHamThreads, 0, (cudaStream_t)stream>>>(p);
+    if (bits == 128 && n_q_heads <= 15 && !((uintptr_t)q_codes & 15)) {
+        if (cross_head) score_hamming_kernel<true><<<grid, kHamThreads, 0, (cudaStream_t)stream>>>(p);
+        else score_hamming_kernel<false><<<grid, kHamThreads, 0, (cudaStream_t)stream>>>(p);
+    }
     else
         score_hamming_generic_kernel<<<grid, kHamThreads, 0, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("score_hamming_kernel");

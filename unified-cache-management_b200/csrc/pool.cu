@@ -54,8 +54,8 @@ __device__ __forceinline__ float pool_init()
 template <int MODE>
 __device__ __forceinline__ float pool_op(float a, float v)
 {
-    if (MODE == UCMX_POOL_MAX) return v > a ? v : a;
-    if (MODE == UCMX_POOL_MIN) return v < a ? v : a;
+    if (MODE == UCMX_POOL_MAX) return fmaxf(a, v);  // one FMNMX; inputs are finite bf16 values
+    if (MODE == UCMX_POOL_MIN) return fminf(a, v);
     return a + v;
 }
 

@@ -253,3 +253,12 @@ extern "C" int32_t ucmx_copy_batch(void* const* dst_ptrs, const void* const* src
     p.slice_bytes = count;
     return launch_xfer(p, any_host_memory != 0, (cudaStream_t)stream);
 }
+
+extern "C" int32_t ucmx_memcpy_async(void* dst, const void* src, int64_t bytes, ucmx_stream_t stream)
+{
+    if (bytes < 0) return UCMX_EPARAM;
+    if (bytes == 0) return UCMX_OK;
+    if (!dst || !src) return UCMX_EPARAM;
+    UCMX_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    return UCMX_OK;
+}

@@ -72,6 +72,7 @@ SIGNATURES = {
     "ucmx_gather_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
     "ucmx_scatter_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
     "ucmx_copy_batch": [_vp, _vp, _i32, _i64, _i32, _vp],
+    "ucmx_memcpy_async": [_vp, _vp, _i64, _vp],
     "ucmx_ring_create": [_sz, _sz, _pvp],
     "ucmx_ring_acquire": [_vp, _pvp, _pi32],
     "ucmx_ring_release": [_vp, _i32],

@@ -1,0 +1,149 @@
+"""Per-kernel throughput at the benchmark configurations' sizes (run: python -m ucmx.stage_bench [names]).
+
+Each kernel is timed alone with CUDA events over back-to-back launches that were queued while the
+GPU was busy (so host launch cost does not show), on inputs larger than L2 or rotated so that every
+launch reads cold data.  Prints one JSON object: microseconds per launch and GB/s of algorithmic
+bytes (what the kernel must read and write, not what the memory system moved).
+  hamming   config 3: 64-request ragged batch, 128-bit codes, 16 KiB per block, both head pairings
+  hash      config 3: sign-hash encoding of paged key blocks (exact FMA chain)
+  offload   config 4: gather 4096 blocks of K and V of one layer to pinned host memory and scatter
+            4096 back, direct (kernel writes host memory) and staged (device compaction + one DMA)
+  pool      config 1/2: pooling a whole pool, and the 64-block decode case
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import ops
+from .workloads import LLAMA3_8B, ragged_decode_batch
+
+
+def _time(fn, iters, reps=3):
+    best = float("inf")
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        torch.cuda._sleep(int(2e9 * 0.003))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) * 1e3 / iters)
+    return best
+
+
+def main(argv):
+    which = argv or ["hamming", "hash", "offload", "pool"]
+    dev = torch.device("cuda:0")
+    shape = LLAMA3_8B
+    batch = ragged_decode_batch(seed=3003)
+    g = torch.Generator(device=dev).manual_seed(3003)
+    off = torch.from_numpy(batch.offsets).to(dev)
+    table = torch.from_numpy(batch.block_table).to(dev)
+    out = {"blocks": batch.total}
+    T, H, D = shape.block_tokens, shape.n_kv_heads, shape.head_dim
+
+    if "hamming" in which:
+        n_tables = 3                                             # 3 x 547 MB rotate through L2
+        codes = [torch.randint(0, 256, (batch.n_slots, H, T, 16), generator=g, device=dev, dtype=torch.uint8)
+                 for _ in range(n_tables)]
+        qc = torch.randint(0, 256, (batch.n_req, H, 16), generator=g, device=dev, dtype=torch.uint8)
+        scores = torch.empty((batch.total,), dtype=torch.int32, device=dev)
+        nbytes = batch.total * (H * T * 16 + 8)
+        for name, cross in (("hamming_cross_head", True), ("hamming_matched_head", False)):
+            t = _time(lambda i: ops.score_hamming(codes[i % n_tables], off, qc, total=batch.total, slot_ids=table,
+                                                  cross_head=cross, out=scores), iters=6)
+            out[name] = {"us": t, "gbs": nbytes / t / 1e3}
+        del codes
+
+    if "hash" in which:
+        nb = 2048
+        k = torch.randn((nb, T, H, D), generator=g, device=dev).to(torch.bfloat16)
+        w = (torch.randn((D, 128), generator=g, device=dev) * 2).to(torch.bfloat16)
+        ids = torch.randperm(nb, generator=g, device=dev).to(torch.int32)
+        codes = torch.empty((nb, H, T, 16), dtype=torch.uint8, device=dev)
+        t = _time(lambda i: ops.hash_encode_blocks(k, ids, w, out=codes), iters=2)
+        flops = nb * T * H * 2.0 * D * 128
+        out["hash_encode_blocks"] = {"us": t, "gbs": nb * (T * H * D * 2 + T * H * 16) / t / 1e3, "tflops": flops / t / 1e6,
+                                     "blocks": nb}
+        del k, codes
+
+    if "offload" in which:
+        n_slots, n = 8192, 4096
+        kv = torch.empty((2, n_slots, T, H, D), dtype=torch.bfloat16, device=dev)
+        for p in range(2):
+            for s in range(0, n_slots, 1024):
+                kv[p, s:s + 1024].copy_(torch.randn((1024, T, H, D), generator=g, device=dev).to(torch.bfloat16))
+        perm = torch.randperm(n_slots, generator=g, device=dev).to(torch.int32)
+        src_ids, dst_ids = perm[:n].contiguous(), perm[n:].contiguous()
+        payload = n * 2 * shape.slice_bytes                      # 2 GiB
+        host = torch.empty(payload, dtype=torch.uint8).pin_memory()
+        stage = torch.empty(payload, dtype=torch.uint8, device=dev)
+        planes = [kv[0], kv[1]]
+        res = {}
+        res["gather_device_staging"] = _time(lambda i: ops.gather_blocks(planes, src_ids, stage), iters=4)
+        res["scatter_device_staging"] = _time(lambda i: ops.scatter_blocks(planes, dst_ids, stage), iters=4)
+        res["d2h_direct"] = _time(lambda i: ops.gather_blocks(planes, src_ids, host), iters=2, reps=2)
+        res["h2d_direct"] = _time(lambda i: ops.scatter_blocks(planes, dst_ids, host), iters=2, reps=2)
+
+        def d2h_staged(i):
+            ops.gather_blocks(planes, src_ids, stage)
+            host.copy_(stage, non_blocking=True)
+
+        def h2d_staged(i):
+            stage.copy_(host, non_blocking=True)
+            ops.scatter_blocks(planes, dst_ids, stage)
+
+        res["d2h_staged"] = _time(d2h_staged, iters=2, reps=2)
+        res["h2d_staged"] = _time(h2d_staged, iters=2, reps=2)
+        res["memcpy_d2h_pinned"] = _time(lambda i: host.copy_(stage, non_blocking=True), iters=2, reps=2)
+        res["memcpy_h2d_pinned"] = _time(lambda i: stage.copy_(host, non_blocking=True), iters=2, reps=2)
+
+        # what the reference does: one cudaMemcpyAsync per 256 KiB slice (dramstore_connector.py:129-132,161-164)
+        hv = host.view(n, 2, shape.slice_bytes)
+        ids_h = src_ids.cpu().tolist()
+        kvb = kv.view(torch.uint8).view(2, n_slots, shape.slice_bytes)
+
+        def per_block_d2h(i):
+            for j, b in enumerate(ids_h):
+                hv[j, 0].copy_(kvb[0, b], non_blocking=True)
+                hv[j, 1].copy_(kvb[1, b], non_blocking=True)
+
+        torch.cuda.synchronize()
+        a, bev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        per_block_d2h(0)
+        bev.record()
+        torch.cuda.synchronize()
+        res["per_block_memcpy_d2h"] = a.elapsed_time(bev) * 1e3
+        out["offload"] = {k2: {"us": v, "gbs_payload": payload / v / 1e3} for k2, v in res.items()}
+        out["offload"]["payload_bytes"] = payload
+        # round trip is bit exact
+        ops.gather_blocks(planes, src_ids, host)
+        ops.scatter_blocks(planes, dst_ids, host)
+        torch.cuda.synchronize()
+        out["offload"]["roundtrip_exact"] = bool(torch.equal(kv[:, dst_ids.long()], kv[:, src_ids.long()]))
+        del kv, stage, host
+
+    if "pool" in which:
+        nb = 8192                                                # 2 GiB of K
+        k = torch.empty((nb, T, H, D), dtype=torch.bfloat16, device=dev)
+        for s in range(0, nb, 1024):
+            k[s:s + 1024].copy_(torch.randn((1024, T, H, D), generator=g, device=dev).to(torch.bfloat16))
+        reps = torch.empty((nb, H, 1, D), dtype=torch.bfloat16, device=dev)
+        ids = torch.randperm(nb, generator=g, device=dev).to(torch.int32)
+        for mode in ("mean", "max"):
+            t = _time(lambda i: ops.pool_blocks(k, ids, mode=mode, out_slots=ids, out_bf16=reps), iters=4)
+            out[f"pool_{mode}_whole_pool"] = {"us": t, "gbs": nb * (shape.slice_bytes + 2048) / t / 1e3}
+        sets = [ids[i * 64:(i + 1) * 64].contiguous() for i in range(16)]
+        t = _time(lambda i: ops.pool_blocks(k, sets[i % 16], out_slots=sets[i % 16], out_bf16=reps), iters=16)
+        out["pool_mean_64_blocks"] = {"us": t, "gbs": 64 * (shape.slice_bytes + 2048) / t / 1e3}
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
