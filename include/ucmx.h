@@ -197,6 +197,30 @@ int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t*
                          void* out_scores, int32_t* out_counts, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Stage 3 -> 4 glue — resident-set remap (the "SparseKVManager block remap").
+ * Replaces: GSAPrefetchEngineC::GetHitAndMissBlock / RunPrefetchH2D / RunOneBsPrefetch / LoadKVToHBM
+ * (ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp:206-322) and ESA's delta logic
+ * (ucm/sparse/esa/esa.py:313-334).
+ *
+ * State, per request r (slots [slot_offsets[r], slot_offsets[r+1])): slot_phys[s] is the physical id
+ * of the s-th HBM block the request owns (ascending), slot_logical[s] the logical block it holds
+ * (-1 = none), slot_free[s] != 0 marks slots the previous round left on the free list.
+ * Selection, per request (entries [sel_offsets[r], sel_offsets[r+1]), of which only the first
+ * sel_counts[r] are used when sel_counts is given): ascending logical block ids (negative = skip).
+ * One round: a selected block that is resident keeps its slot; the others, in selection order, take
+ * the free-listed slots that are not hits now, in slot order; slot_logical is updated and the new
+ * free list is every slot that is neither a hit nor newly filled.
+ * Outputs, packed like sel: table[j] = physical id serving sel[j] (-1 if no slot was left);
+ * load_logical / load_phys = the (block to load -> HBM block) list, load_counts[r] entries from
+ * position sel_offsets[r].  max_logical bounds the logical ids, max_slots the slots of a request
+ * (both size the shared-memory lookup; (max_logical + 2*max_slots)*4 bytes must stay under 200 KiB). */
+int32_t ucmx_remap_resident(int32_t* slot_logical, uint8_t* slot_free, const int32_t* slot_phys,
+                            const int32_t* slot_offsets, const int32_t* sel, const int32_t* sel_offsets,
+                            const int32_t* sel_counts, int32_t n_req, int32_t max_logical,
+                            int32_t max_slots, int32_t* table, int32_t* load_logical, int32_t* load_phys,
+                            int32_t* load_counts, ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Score + top-k without any allocation.  (No counterpart in the reference: its retrieval runs on
  * host threads with std::vector scratch.)
  *

@@ -206,16 +206,18 @@ def scatter_blocks(planes, block_ids, slice_bytes, block_stride, staging):
                              _p(ids), C.c_int32(len(ids)), C.c_int64(slice_bytes), _p(st))
 
 
-def remap_resident(resident_logical, slot_ids, selected):
-    res = _c(resident_logical, np.int32).copy()
-    sl = _c(slot_ids, np.int32)
+def remap_resident(slot_logical, slot_free, slot_phys, selected):
+    """One round for one request. Returns (slot_logical', slot_free', table, load_logical, load_phys)."""
+    res = _c(slot_logical, np.int32).copy()
+    fr = _c(slot_free, np.uint8).copy()
+    sl = _c(slot_phys, np.int32)
     sel = _c(selected, np.int32)
-    sel_phys = np.empty(max(len(sel), 1), np.int32)
+    table = np.empty(max(len(sel), 1), np.int32)
     ll = np.empty(max(len(sel), 1), np.int32)
     lp = np.empty(max(len(sel), 1), np.int32)
-    n = lib().orc_remap_resident(_p(res), _p(sl), C.c_int32(len(sl)), _p(sel), C.c_int32(len(sel)),
-                                 _p(sel_phys), _p(ll), _p(lp))
-    return res, sel_phys[:len(sel)], ll[:n], lp[:n]
+    n = lib().orc_remap_resident(_p(res), _p(fr), _p(sl), C.c_int32(len(sl)), _p(sel), C.c_int32(len(sel)),
+                                 _p(table), _p(ll), _p(lp))
+    return res, fr, table[:len(sel)], ll[:n], lp[:n]
 
 
 def store_offset(block_tokens, heads_per_rank, head_dim, rank, tp_size, elem_bytes, layer, is_v,

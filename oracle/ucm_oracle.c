@@ -406,43 +406,52 @@ void orc_scatter_blocks(uint8_t *const *planes, int32_t n_planes, int64_t block_
  *
  * GSAPrefetchEngineC::GetHitAndMissBlock / RunPrefetchH2D / RunOneBsPrefetch /
  * LoadKVToHBM (ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp:206-322), for one
- * (request, layer):
- *   resident_logical[s] = logical block held by physical slot s of this
- *   request (-1 = holds nothing), slot_ids[s] = its physical block id.
- *   Selected logical blocks already resident are hits and stay where they are;
- *   the misses, in selection order, take the free slots (slots whose logical
- *   block is not selected) in ascending slot position.
- * Outputs: sel_phys[j] = physical block id serving selected[j] (or -1 when no
- * free slot was left), load_logical/load_phys = the (miss -> slot) load list,
- * resident_logical updated in place.  Returns the number of loads.
+ * (request, layer).  State: the request owns n_slots HBM blocks, slot s has
+ * physical id slot_phys[s] (ascending, the iteration order of the reference's
+ * std::map mBlocksMap) and holds logical block slot_logical[s] (-1 = nothing;
+ * together mBlocksMap/mDocsTables); slot_free[s] != 0 marks the slots on the
+ * free list the previous round left behind (mFreeBlock).
+ * Round: every selected logical block that is resident is a hit and stays
+ * (:216-227); the misses, in selection order, take the free-listed slots that
+ * are not hits now, in list order (:249-265), and the maps are updated
+ * (:313-322); the new free list is every slot that is neither hit nor newly
+ * filled (:298-307).  `selected` must be ascending (TopKImpl sorts its output),
+ * so that table[] is the block table in the reference's order (its
+ * std::map hitBlocksIdx iterates by logical index, :291-296).
+ * Outputs: table[j] = physical id serving selected[j] (-1 when no slot was
+ * left), load_logical/load_phys = the (miss -> block) load list; returns the
+ * number of loads.
  */
-int32_t orc_remap_resident(int32_t *resident_logical, const int32_t *slot_ids, int32_t n_slots,
-                           const int32_t *selected, int32_t n_sel, int32_t *sel_phys,
+int32_t orc_remap_resident(int32_t *slot_logical, uint8_t *slot_free, const int32_t *slot_phys,
+                           int32_t n_slots, const int32_t *selected, int32_t n_sel, int32_t *table,
                            int32_t *load_logical, int32_t *load_phys)
 {
-    uint8_t *keep = (uint8_t *)calloc((size_t)(n_slots > 0 ? n_slots : 1), 1);
+    uint8_t *hit = (uint8_t *)calloc((size_t)(n_slots > 0 ? n_slots : 1), 1);
     for (int32_t j = 0; j < n_sel; ++j) {
-        sel_phys[j] = -1;
+        table[j] = -1;
+        if (selected[j] < 0) continue;
         for (int32_t s = 0; s < n_slots; ++s)
-            if (resident_logical[s] == selected[j] && selected[j] >= 0) {
-                sel_phys[j] = slot_ids[s];
-                keep[s] = 1;
+            if (slot_logical[s] == selected[j]) {
+                table[j] = slot_phys[s];
+                hit[s] = 1;
                 break;
             }
     }
     int32_t n_load = 0, s = 0;
     for (int32_t j = 0; j < n_sel; ++j) {
-        if (sel_phys[j] != -1) continue;
-        while (s < n_slots && keep[s]) ++s;
+        if (table[j] != -1 || selected[j] < 0) continue;
+        while (s < n_slots && (!slot_free[s] || hit[s])) ++s;
         if (s >= n_slots) break;
-        keep[s] = 1;
-        resident_logical[s] = selected[j];
-        sel_phys[j] = slot_ids[s];
+        hit[s] = 1;
+        slot_logical[s] = selected[j];
+        table[j] = slot_phys[s];
         load_logical[n_load] = selected[j];
-        load_phys[n_load] = slot_ids[s];
+        load_phys[n_load] = slot_phys[s];
         ++n_load;
+        ++s;
     }
-    free(keep);
+    for (int32_t i = 0; i < n_slots; ++i) slot_free[i] = hit[i] ? 0 : 1;
+    free(hit);
     return n_load;
 }
 

@@ -310,3 +310,29 @@ def copy_batch(dst_ptrs: torch.Tensor, src_ptrs: torch.Tensor, count: int, *, an
     n = dst_ptrs.numel()
     st = N.lib.ucmx_copy_batch(_ptr(dst_ptrs), _ptr(src_ptrs), n, count, int(any_host_memory), _stream(dst_ptrs))
     N.check("ucmx_copy_batch", st, 1 if n and count else 0)
+
+
+def remap_resident(slot_logical: torch.Tensor, slot_free: torch.Tensor, slot_phys: torch.Tensor,
+                   slot_offsets: torch.Tensor, sel: torch.Tensor, sel_offsets: torch.Tensor, *, max_logical: int,
+                   max_slots: int, sel_counts: Optional[torch.Tensor] = None):
+    """One round of the resident-set remap for every request (state tensors are updated in place).
+
+    slot_logical int32, slot_free uint8, slot_phys int32: flat per-request state (CSR by slot_offsets);
+    sel: ascending selected logical blocks (CSR by sel_offsets).  Returns (table, load_logical, load_phys,
+    load_counts): table[j] = physical block serving sel[j]; the load lists are packed like sel."""
+    _need_cuda(slot_logical, slot_free, slot_phys, slot_offsets, sel, sel_offsets, sel_counts)
+    if slot_free.dtype != torch.uint8 or not slot_free.is_contiguous():
+        raise ValueError("slot_free must be contiguous uint8")
+    n_req = slot_offsets.numel() - 1
+    dev = sel.device
+    table = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+    load_logical = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+    load_phys = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+    load_counts = torch.zeros((n_req,), dtype=torch.int32, device=dev)
+    st = N.lib.ucmx_remap_resident(_ptr(_i32(slot_logical, "slot_logical")), _ptr(slot_free), _ptr(_i32(slot_phys, "slot_phys")),
+                                   _ptr(_i32(slot_offsets, "slot_offsets")), _ptr(_i32(sel, "sel")),
+                                   _ptr(_i32(sel_offsets, "sel_offsets")), _ptr(_i32(sel_counts, "sel_counts")), n_req,
+                                   max_logical, max_slots, _ptr(table), _ptr(load_logical), _ptr(load_phys),
+                                   _ptr(load_counts), _stream(sel))
+    N.check("ucmx_remap_resident", st, 1 if n_req else 0)
+    return table, load_logical, load_phys, load_counts
