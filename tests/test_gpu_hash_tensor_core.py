@@ -1,0 +1,69 @@
+"""The tensor-core (tcgen05) sign-hash encoder against the CPU checker and against the CUDA-core
+kernel: bit-exact, including vectors built so that projections cancel to (nearly) zero, where the
+sign is decided by the exact fused-multiply-add chain rather than by the tensor core."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev_bf16(u16):
+    return torch.from_numpy(np.ascontiguousarray(u16).view(np.int16)).to(DEV).view(torch.bfloat16)
+
+
+def test_paged_llama_shape_bit_exact(oracle):
+    from ucmx import ops
+    rng = np.random.default_rng(101)
+    w = H.randn_bf16(rng, (128, 128), 2.0)
+    k = H.randn_bf16(rng, (9, 128, 8, 128))
+    ids = np.array([8, 0, 3, 3, 5, 7], np.int32)
+    want = oracle.hash_encode(k[ids], w)                                   # [6, 128, 8, 16]
+    got = ops.hash_encode_blocks(dev_bf16(k), torch.from_numpy(ids).to(DEV), dev_bf16(w), head_major=False)
+    assert np.array_equal(got.cpu().numpy(), want)
+    slots = np.array([4, 2, 0, 1, 5, 3], np.int32)
+    out = torch.zeros((6, 8, 128, 16), dtype=torch.uint8, device=DEV)
+    ops.hash_encode_blocks(dev_bf16(k), torch.from_numpy(ids).to(DEV), dev_bf16(w), out_slots=torch.from_numpy(slots).to(DEV), out=out)
+    assert np.array_equal(out.cpu().numpy()[slots], want.transpose(0, 2, 1, 3))
+    from ucmx import _native
+    assert _native.device_error() == 0
+
+
+def test_cancelling_projections_take_the_exact_path(oracle):
+    from ucmx import ops
+    rng = np.random.default_rng(102)
+    n = 4096
+    x = H.bf16_to_f32(H.randn_bf16(rng, (n, 128)))
+    w = H.bf16_to_f32(H.randn_bf16(rng, (128, 128), 2.0))
+    # second half of every vector mirrors the first with opposite sign, and for half of the columns the
+    # weights repeat, so those projections cancel exactly in exact arithmetic
+    x[:, 64:] = -x[:, :64]
+    w[64:, ::2] = w[:64, ::2]
+    # a few rows with a tiny leftover so that the true sum is a small non-zero number
+    x[::7, 127] = H.bf16_to_f32(H.f32_to_bf16(x[::7, 127] * 1.0078125))
+    x16, w16 = H.f32_to_bf16(x), H.f32_to_bf16(w)
+    want = oracle.hash_encode(x16, w16)
+    got = ops.hash_encode(dev_bf16(x16), dev_bf16(w16)).cpu().numpy()
+    assert np.array_equal(got, want)
+    margins = oracle.hash_project(x16[:64], w16)
+    assert np.abs(margins[:, ::2]).max() < 0.25 < np.abs(margins[:, 1::2]).std()   # cancelling columns sit at rounding-noise level
+
+
+def test_tensor_core_and_cuda_core_kernels_agree_on_a_large_batch():
+    from ucmx import ops
+    g = torch.Generator(device=DEV).manual_seed(103)
+    x = torch.randn((1_000_003, 128), generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((128, 128), generator=g, device=DEV) * 2).to(torch.bfloat16)
+    a = ops.hash_encode(x, w)
+    os.environ["UCMX_HASH_NO_TC"] = "1"
+    try:
+        b = ops.hash_encode(x, w)
+    finally:
+        del os.environ["UCMX_HASH_NO_TC"]
+    assert torch.equal(a, b)
+    assert 0.45 < float(torch.tensor(np.unpackbits(a[:10000].cpu().numpy())).float().mean()) < 0.55

@@ -18,6 +18,11 @@ int32_t* error_word();  // device-visible int that bounded waits report into (NU
 int32_t cuda_status(const char* what, cudaError_t e);
 int sm_count();  // multiprocessors of the current device (cached)
 
+// tensor-core (tcgen05) sign-hash encoder; g == NULL: dense vectors, else paged blocks. UCMX_EUNSUPPORTED = not applicable
+int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucmx_kv_geometry* g, const int32_t* ids,
+                       const int32_t* out_slots, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
+                       int32_t head_major, uint8_t* out, cudaStream_t st);
+
 #define UCMX_CUDA(call)                                                  \
     do {                                                                 \
         cudaError_t e__ = (call);                                        \

@@ -1,0 +1,458 @@
+// Stage 1b on the 5th-generation tensor cores: sign-hash codes as a bf16 GEMM with an exactness net.
+//
+// The projection x[128] . W[128x128] of every key vector is a real GEMM (M = all token-heads of all
+// blocks, N = K = 128; about 120 flop per byte moved), so it belongs on tcgen05: 128-vector tiles of
+// the paged cache are brought in by tiled TMA loads (128-byte swizzle, the layout the MMA unit reads),
+// one elected thread issues eight tcgen05.mma (M128 N128 K16, bf16 in, fp32 accumulate in TMEM) per
+// tile, and four epilogue warps read the accumulator back with tcgen05.ld, take signs and pack bits.
+//
+// Codes must be bit-identical to the checker's definition - the sign of an fp32 fused-multiply-add
+// chain over d = 0..127 - while the tensor core adds in its own order.  Both sums differ from the
+// exact sum S by at most a few 2^-18 * sum|x_d w_d|, so wherever |acc| is clearly above that they
+// have the sign of S and agree.  The epilogue therefore trusts the tensor-core sign only when
+// |acc| > 2^-13 * |x| * |w_j| (Cauchy-Schwarz bounds sum|x_d w_d|; 2^-13 leaves a wide margin) and
+// recomputes the few remaining bits (about one per thousand for Gaussian data) with the exact chain
+// from the tile still sitting in shared memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ucmx {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kDim = 128;
+constexpr int kBits = 128;
+constexpr int kStagesA = 2;                       // with two CTAs per SM that is four tiles in flight per SM
+constexpr int kHalfBytes = kTileM * 128;          // one 64-element K half of a tile: 128 rows x 128 B
+constexpr int kTileBytes = 2 * kHalfBytes;        // 32 KiB
+constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr float kTau = 1.0f / 8192.0f;            // 2^-13
+constexpr int kFallbackSlots = 512;               // doubtful bits one warp pools per tile (about 5 are typical)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+struct TcParams {
+    const uint16_t* w;     // [128][128] bf16, row = d, column = bit
+    uint8_t* out;
+    int64_t n_vec;         // dense: number of vectors
+    int64_t n_tiles;
+    int32_t paged, H, T, head_major, tiles_per_block;
+    const int32_t* ids;
+    const int32_t* out_slots;
+    int32_t* err;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                     "r"(smem_u32(dst)), "l"(m), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, int c0, int c1, int c2, int c3, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+            "r"(smem_u32(dst)),
+        "l"(m), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                               // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                               // layout type: SWIZZLE_128B
+    return d;
+}
+// D fp32, A and B bf16, both K-major, N = 128, M = 128
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBits >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// byte offset of element (row, k) inside a [128 x 128] bf16 K-major tile stored as two swizzled halves
+__device__ __forceinline__ uint32_t sw_offset(int row, int k)
+{
+    const int half = k >> 6, c = (k & 63) >> 3;
+    return (uint32_t)(half * kHalfBytes + row * 128 + ((c ^ (row & 7)) << 4) + ((k & 7) << 1));
+}
+
+struct alignas(8) Barriers {
+    uint64_t full[kStagesA], empty[kStagesA], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    int32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;                                   // kStagesA tiles
+    unsigned char* sB = smem + kStagesA * kTileBytes;            // W^T as the B operand: row = bit, K = d
+    float* wnorm = reinterpret_cast<float*>(sB + kTileBytes);    // |w_j|
+    Barriers* bars = reinterpret_cast<Barriers*>(wnorm + kBits);
+    uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // 4 epilogue warps x kFallbackSlots
+    uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kFallbackSlots);
+    uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kFallbackSlots);   // max_j |w_j|
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- one-time set-up: barriers, the B operand (transposed and swizzled by hand), column norms, TMEM
+    if (tid == 0) {
+        for (int s = 0; s < kStagesA; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 128);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&bars->acc_full[a], 1);
+            mbar_init(&bars->acc_empty[a], 128);
+        }
+        bars->abort_flag = 0;
+        *wmax_bits = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    for (int i = tid; i < kDim * kBits; i += kThreads) {
+        const int d = i / kBits, j = i - d * kBits;              // W[d][j] -> B[row j][k d]
+        *reinterpret_cast<uint16_t*>(sB + sw_offset(j, d)) = __ldg(p.w + i);
+    }
+    if (tid < kBits) {
+        float s2 = 0.0f;
+        for (int d = 0; d < kDim; ++d) {
+            const float w = __uint_as_float((uint32_t)__ldg(p.w + d * kBits + tid) << 16);
+            s2 = fmaf(w, w, s2);
+        }
+        wnorm[tid] = sqrtf(s2) * 1.0001f;
+        atomicMax(wmax_bits, __float_as_uint(wnorm[tid]));   // non-negative floats order like their bit patterns
+    }
+    fence_proxy_async();            // the hand-written B tile must be visible to the MMA unit
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                     "r"(256)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + stride - 1) / stride : 0;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        for (int64_t it = 0; it < my_tiles; ++it) {
+            const int s = (int)(it % kStagesA);
+            const uint32_t par = (uint32_t)((it / kStagesA) & 1);
+            if (!mbar_wait(&bars->empty[s], par ^ 1u)) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 1);
+                break;
+            }
+            if (*(volatile int32_t*)&bars->abort_flag) break;
+            const int64_t tile = first + it * stride;
+            unsigned char* dst = sA + (size_t)s * kTileBytes;
+            mbar_expect_tx(&bars->full[s], kTileBytes);
+            if (p.paged) {
+                const int64_t blk = tile / p.tiles_per_block;
+                const int sub = (int)(tile - blk * p.tiles_per_block);
+                const int id = __ldg(p.ids + blk);
+                const int t0 = sub * (kTileM / p.H);
+                // a negative id reads outside the tensor: TMA fills zeros, the tile's codes are not stored
+                tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
+                tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
+            } else {
+                const int row0 = (int)(tile * kTileM);
+                tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
+                tma_load_2d(dst + kHalfBytes, &tmap, 64, row0, &bars->full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const uint32_t b_addr = smem_u32(sB);
+        for (int64_t it = 0; it < my_tiles; ++it) {
+            const int s = (int)(it % kStagesA), a = (int)(it & 1);
+            if (!mbar_wait(&bars->full[s], (uint32_t)((it / kStagesA) & 1)) ||
+                !mbar_wait(&bars->acc_empty[a], (uint32_t)(((it >> 1) & 1) ^ 1))) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 1);
+                break;
+            }
+            if (*(volatile int32_t*)&bars->abort_flag) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileBytes);
+#pragma unroll
+            for (int k = 0; k < kDim / 16; ++k) {
+                const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
+                umma_bf16(tmem_base + (uint32_t)a * kBits, smem_desc_sw128(a_addr + koff), smem_desc_sw128(b_addr + koff),
+                          k > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->acc_full[a]);   // arrives when the eight MMAs above have completed
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue: signs, margin test, exact fallback
+        const int q = warp & 3;                  // the TMEM lane quarter this warp may read
+        const int m = q * 32 + lane;             // tile row = vector
+        for (int64_t it = 0; it < my_tiles; ++it) {
+            const int s = (int)(it % kStagesA), a = (int)(it & 1);
+            if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it >> 1) & 1))) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 1);
+                break;
+            }
+            if (*(volatile int32_t*)&bars->abort_flag) break;
+            tc_fence_after();
+            (void)mbar_wait(&bars->full[s], (uint32_t)((it / kStagesA) & 1));  // already complete: acquires the TMA-written tile
+            const unsigned char* xa = sA + (size_t)s * kTileBytes;
+            // |x|^2 of this row (order of the additions does not matter for a bound)
+            float x2 = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xa + sw_offset(m, c * 8));
+                const float e[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y), bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x2 = fmaf(e[i], e[i], x2);
+            }
+            // one threshold for the whole row: |acc| <= tau |x| max_j|w_j| (a little wider than per column, no table look-up)
+            const uint32_t thr_bits = __float_as_uint(kTau * sqrtf(x2) * 1.0001f * __uint_as_float(*wmax_bits));
+            uint32_t code[4], doubt[4];
+#pragma unroll
+            for (int cw = 0; cw < 4; ++cw) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kBits + cw * 32), v);
+                uint32_t bits = 0, unsure = 0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    // sign from the sign bit (a zero sum is below the threshold and is settled exactly below);
+                    // magnitudes compare as integers
+                    bits |= ((~v[j]) >> 31) << j;
+                    unsure |= ((v[j] & 0x7fffffffu) <= thr_bits ? 1u : 0u) << j;
+                }
+                code[cw] = bits;
+                doubt[cw] = unsure;
+            }
+            // the accumulator is read: hand it back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(&bars->acc_empty[a]);
+            // Exact recomputation of the doubtful bits: the fp32 FMA chain over d, in order.  The chain
+            // of one bit cannot be split, but different bits can go to different lanes: the warp pools
+            // its (row, column) pairs in shared memory and deals them out, so a tile with a handful of
+            // doubtful bits costs one chain's latency instead of one per bit of the unluckiest lane.
+            {
+                const int mine = __popc(doubt[0]) + __popc(doubt[1]) + __popc(doubt[2]) + __popc(doubt[3]);
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const int total = __shfl_sync(0xffffffffu, incl, 31);
+                if (total > 0) {
+                    uint16_t* list = fb_list + (warp - 2) * kFallbackSlots;
+                    uint8_t* res = fb_res + (warp - 2) * kFallbackSlots;
+                    int pos = incl - mine;
+#pragma unroll
+                    for (int cw = 0; cw < 4; ++cw) {
+                        uint32_t pend = doubt[cw];
+                        while (pend) {
+                            const int j = __ffs(pend) - 1;
+                            pend &= pend - 1;
+                            if (pos < kFallbackSlots) list[pos] = (uint16_t)((m << 7) | (cw * 32 + j));
+                            ++pos;
+                        }
+                    }
+                    __syncwarp();
+                    const int pooled = min(total, kFallbackSlots);
+                    for (int e = lane; e < pooled; e += 32) {
+                        const int row = list[e] >> 7, col = list[e] & 127;
+                        float acc = 0.0f;
+#pragma unroll 4
+                        for (int c = 0; c < 16; ++c) {
+                            const uint4 xv = *reinterpret_cast<const uint4*>(xa + sw_offset(row, c * 8));
+                            const uint4 wv = *reinterpret_cast<const uint4*>(sB + sw_offset(col, c * 8));
+                            acc = fmaf(bf16lo(xv.x), bf16lo(wv.x), acc);
+                            acc = fmaf(bf16hi(xv.x), bf16hi(wv.x), acc);
+                            acc = fmaf(bf16lo(xv.y), bf16lo(wv.y), acc);
+                            acc = fmaf(bf16hi(xv.y), bf16hi(wv.y), acc);
+                            acc = fmaf(bf16lo(xv.z), bf16lo(wv.z), acc);
+                            acc = fmaf(bf16hi(xv.z), bf16hi(wv.z), acc);
+                            acc = fmaf(bf16lo(xv.w), bf16lo(wv.w), acc);
+                            acc = fmaf(bf16hi(xv.w), bf16hi(wv.w), acc);
+                        }
+                        res[e] = acc > 0.0f ? 1 : 0;
+                    }
+                    __syncwarp();
+                    pos = incl - mine;
+#pragma unroll
+                    for (int cw = 0; cw < 4; ++cw) {
+                        uint32_t pend = doubt[cw];
+                        while (pend) {
+                            const int j = __ffs(pend) - 1;
+                            pend &= pend - 1;
+                            uint32_t bit;
+                            if (pos < kFallbackSlots) {
+                                bit = res[pos];
+                            } else {
+                                // more doubtful bits than the pool holds (degenerate inputs): the owner does its own
+                                const int col = cw * 32 + j;
+                                float acc = 0.0f;
+                                for (int d = 0; d < kDim; ++d) {
+                                    const float xv = __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t*>(xa + sw_offset(m, d)) << 16);
+                                    const float wv = __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t*>(sB + sw_offset(col, d)) << 16);
+                                    acc = fmaf(xv, wv, acc);
+                                }
+                                bit = acc > 0.0f ? 1u : 0u;
+                            }
+                            ++pos;
+                            code[cw] = (code[cw] & ~(1u << j)) | (bit << j);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            // this row's share of the tile is consumed: release the stage to the producer
+            mbar_arrive(&bars->empty[s]);
+            // store 16 bytes of code
+            const int64_t tile = first + it * stride;
+            int64_t orow = -1;
+            if (p.paged) {
+                const int64_t blk = tile / p.tiles_per_block;
+                const int sub = (int)(tile - blk * p.tiles_per_block);
+                const int id = __ldg(p.ids + blk);
+                const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
+                const int t = sub * (kTileM / p.H) + m / p.H, h = m % p.H;
+                if (id >= 0 && slot >= 0)
+                    orow = p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
+            } else {
+                const int64_t v = tile * kTileM + m;
+                if (v < p.n_vec) orow = v;
+            }
+            if (orow >= 0) *reinterpret_cast<uint4*>(p.out + orow * 16) = make_uint4(code[0], code[1], code[2], code[3]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+    }
+}
+
+}  // namespace
+
+// Returns UCMX_EUNSUPPORTED when the tensor-core path does not apply; the caller then runs the
+// CUDA-core kernel, which produces the same codes.
+int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucmx_kv_geometry* g, const int32_t* ids,
+                       const int32_t* out_slots, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
+                       int32_t head_major, uint8_t* out, cudaStream_t st)
+{
+    EncodeTiledFn enc = encode_fn();
+    if (!enc || dim != kDim || bits != kBits || ((uintptr_t)out & 15) || ((uintptr_t)x & 15)) return UCMX_EUNSUPPORTED;
+    TcParams p{};
+    p.w = (const uint16_t*)w;
+    p.out = out;
+    p.err = error_word();
+    alignas(64) CUtensorMap tmap;
+    CUresult r;
+    if (g) {
+        const int H = g->n_kv_heads, T = g->block_tokens;
+        if (g->head_dim != kDim || g->reserved <= 0 || H < 1 || H > kTileM || kTileM % H || T % (kTileM / H)) return UCMX_EUNSUPPORTED;
+        if (kTileM / H > 256 || (g->token_stride % 8) || (g->block_stride % 8)) return UCMX_EUNSUPPORTED;
+        const cuuint64_t dims[4] = {(cuuint64_t)kDim, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)g->reserved};
+        const cuuint64_t strides[3] = {(cuuint64_t)kDim * 2, (cuuint64_t)g->token_stride * 2, (cuuint64_t)g->block_stride * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)H, (cuuint32_t)(kTileM / H), 1};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        p.paged = 1;
+        p.H = H;
+        p.T = T;
+        p.head_major = head_major;
+        p.tiles_per_block = T * H / kTileM;
+        p.ids = ids;
+        p.out_slots = out_slots;
+        p.n_tiles = (int64_t)n_blocks * p.tiles_per_block;
+    } else {
+        if (x_stride % 8 || n_vec < 1 || n_vec > 0x7fffffffll) return UCMX_EUNSUPPORTED;
+        const cuuint64_t dims[2] = {(cuuint64_t)kDim, (cuuint64_t)n_vec};
+        const cuuint64_t strides[1] = {(cuuint64_t)x_stride * 2};
+        const cuuint32_t box[2] = {64, kTileM};
+        const cuuint32_t es[2] = {1, 1};
+        r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        p.n_vec = n_vec;
+        p.n_tiles = (n_vec + kTileM - 1) / kTileM;
+    }
+    if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
+    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kFallbackSlots * 3 + 128;
+    UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid = (int64_t)sm_count() * 2;
+    if (grid > p.n_tiles) grid = p.n_tiles;
+    hash_encode_tc_kernel<<<(unsigned)grid, kThreads, smem, st>>>(tmap, p);
+    UCMX_LAUNCH_CHECK("hash_encode_tc_kernel");
+    return UCMX_OK;
+}
+
+}  // namespace ucmx
