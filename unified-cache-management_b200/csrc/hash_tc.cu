@@ -170,15 +170,23 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         mbar_init_fence();
     }
     __syncthreads();
-    for (int i = tid; i < kDim * kBits; i += kThreads) {
-        const int d = i / kBits, j = i - d * kBits;              // W[d][j] -> B[row j][k d]
-        *reinterpret_cast<uint16_t*>(sB + sw_offset(j, d)) = __ldg(p.w + i);
+    for (int i = tid; i < kDim * kBits / 8; i += kThreads) {
+        const int d = i / (kBits / 8), j0 = (i - d * (kBits / 8)) * 8;   // eight bits j0..j0+7 of row d: W[d][j] -> B[row j][k d]
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
+        const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            *reinterpret_cast<uint16_t*>(sB + sw_offset(j0 + t, d)) = (uint16_t)(e[t >> 1] >> ((t & 1) * 16));
     }
+    __syncthreads();
     if (tid < kBits) {
         float s2 = 0.0f;
-        for (int d = 0; d < kDim; ++d) {
-            const float w = __uint_as_float((uint32_t)__ldg(p.w + d * kBits + tid) << 16);
-            s2 = fmaf(w, w, s2);
+#pragma unroll 4
+        for (int c = 0; c < 16; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(sB + sw_offset(tid, c * 8));
+            const float e[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y), bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) s2 = fmaf(e[t], e[t], s2);
         }
         wnorm[tid] = sqrtf(s2) * 1.0001f;
         atomicMax(wmax_bits, __float_as_uint(wnorm[tid]));   // non-negative floats order like their bit patterns
