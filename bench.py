@@ -208,6 +208,9 @@ def main():
                     help="decode64: the 64-request ragged decode batch, data parallel over requests (default); "
                          "tp-long: 8 requests of 1 048 576 tokens, KV heads split over the GPUs with an all-reduce of "
                          "block scores before top-k")
+    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer"],
+                    help="tp-long only: how partial block scores are summed over ranks - a NCCL all-reduce between the "
+                         "scoring and top-k kernels, or peer-memory loads inside the top-k kernel")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profiler captures: 8 requests, 2 layers, 1 warm-up + 1 step, no host legs")
     args = ap.parse_args()
@@ -231,7 +234,7 @@ def main():
     import torch.distributed as dist
     from ucmx import _native
     from ucmx.engine import DecodeRetrievalEngine
-    from ucmx.parallel import ScoreAllReduce, head_range
+    from ucmx.parallel import PeerScoreExchange, ScoreAllReduce, head_range
     from ucmx.workloads import LLAMA3_8B, QWEN2_72B_LIKE, fixed_batch, ragged_decode_batch
 
     if not torch.cuda.is_available():
@@ -251,8 +254,10 @@ def main():
         shape = QWEN2_72B_LIKE
         batch = fixed_batch(8, 8192, 2048, seed=5005)
         lo, hi = head_range(shape.n_kv_heads, rank, world)
+        peer = PeerScoreExchange.create(batch.total, dev) if (world > 1 and args.allreduce == "peer") else None
         eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank, heads_local=hi - lo,
-                                    score_reduce=ScoreAllReduce() if world > 1 else None)
+                                    score_reduce=ScoreAllReduce() if (world > 1 and peer is None) else None,
+                                    peer_exchange=peer)
     else:
         shape = LLAMA3_8B
         batch = ragged_decode_batch(seed=2002 + rank, n_req=n_req)
@@ -414,7 +419,7 @@ def main():
                 "workload": "long-context sharded retrieval: 8 requests x 1 048 576 tokens (8192 blocks each), Qwen2-72B-like "
                             "KV (64q/8kv heads, head_dim 128), KV heads split over the GPUs, fp32 all-reduce of 65 536 block "
                             "scores before top-k 2048, gather of the selected K,V head slices",
-                "layers": eng.L, "tp": world, "heads_per_rank": eng.H, "parallelism": f"tp{world} over KV heads",
+                "layers": eng.L, "tp": world, "heads_per_rank": eng.H, "parallelism": f"tp{world} over KV heads", "allreduce": args.allreduce if world > 1 else "none",
                 "l2_policy": "inputs larger than L2 per step", "cuda_graph": bool(args.graph)},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},

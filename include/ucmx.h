@@ -197,6 +197,36 @@ int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t*
                          void* out_scores, int32_t* out_counts, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel retrieval: exchange of partial block scores over peer memory, fused into top-k.
+ * (No counterpart in the reference, which has no cross-rank exchange: under tensor parallelism its
+ * ranks select independently over their own KV heads, ucm/sparse/esa/esa.py:196-198.)
+ *
+ * Every rank owns an exchange buffer that all ranks can address (peer-mapped, e.g. torch symmetric
+ * memory): bytes [0,128) hold one uint32 flag per rank, partial scores live further up.  A round:
+ *   1. each rank scores its own KV heads into its buffer at parts_offset_bytes (ucmx_score_dot* with
+ *      out_scores pointing there);
+ *   2. ucmx_peer_signal, next on the same stream, publishes `epoch` into flag[my_rank] of every
+ *      rank's buffer (release at system scope: the scores written before are visible to whoever
+ *      sees the flag);
+ *   3. ucmx_topk_ragged_peer_sum waits until all `world` flags in its own buffer have reached
+ *      `epoch`, adds the partial scores of all ranks in rank order (peer loads over NVLink; the
+ *      same order everywhere, so every rank gets bit-identical sums and selections), writes them
+ *      to summed_scores and selects as ucmx_topk_ragged does.
+ * peer_bases is a DEVICE array of `world` buffer base addresses.  Use increasing epochs and alternate
+ * parts_offset_bytes between two halves from round to round, so that a rank never overwrites scores a
+ * slower peer may still be reading.  The wait is bounded: if a peer never signals, code 4 is
+ * recorded (ucmx_device_error) and the kernel goes on with what it has instead of hanging. */
+int32_t ucmx_peer_signal(void* const* peer_bases, int32_t world, int32_t my_rank, uint32_t epoch,
+                         ucmx_stream_t stream);
+int32_t ucmx_topk_ragged_peer_sum(void* const* peer_bases, int32_t world, int32_t my_rank,
+                                  int64_t parts_offset_bytes, uint32_t epoch, float* summed_scores,
+                                  const int32_t* req_offsets, const int32_t* k_per_req, int32_t n_req,
+                                  int32_t start_win, int32_t end_win, int32_t window_mode, int32_t order,
+                                  const int32_t* id_map, int32_t out_stride, const int32_t* out_offsets,
+                                  int32_t* out_idx, float* out_scores, int32_t* out_counts,
+                                  ucmx_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Stage 3 -> 4 glue — resident-set remap (the "SparseKVManager block remap").
  * Replaces: GSAPrefetchEngineC::GetHitAndMissBlock / RunPrefetchH2D / RunOneBsPrefetch / LoadKVToHBM
  * (ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp:206-322) and ESA's delta logic

@@ -28,7 +28,23 @@ struct TopkParams {
     int32_t* out_idx;
     uint32_t* out_scores;
     int32_t* out_counts;
+    // tensor-parallel score exchange folded into the prologue (NULL / 0 on a single rank)
+    const unsigned char* const* peer_bases;  // base of every rank's exchange buffer, peer-mapped
+    int32_t world, my_rank;
+    int64_t parts_offset;                    // byte offset of this round's partial scores inside a buffer
+    uint32_t epoch;                          // value every rank's flag must have reached
+    float* sum_out;                          // where the summed scores go (local), then read as `scores`
+    int32_t* err;
 };
+
+constexpr uint32_t kPeerSpinLimit = 1u << 21;
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ uint32_t to_key(uint32_t bits, bool is_float)
 {
@@ -76,7 +92,37 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     const int n = __ldg(p.offsets + r + 1) - base;
     const int k = __ldg(p.k_per_req + r);
     const bool is_float = p.is_float != 0;
-    const uint32_t* sc = p.scores + base;
+    if (p.peer_bases) {
+        // One-shot all-reduce fused into the selection: every rank scored its own KV heads into its
+        // exchange buffer and then raised its flag on every peer; wait (bounded) for all flags, then
+        // add the partial scores of this request straight out of the peers' memory, in rank order, so
+        // that every rank computes bit-identical sums and therefore identical selections.
+        if (tid < p.world) {
+            const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.peer_bases[p.my_rank]) + tid;
+            bool ok = false;
+            for (uint32_t it = 0; it < kPeerSpinLimit; ++it) {
+                if ((int32_t)(ld_acquire_sys(flag) - p.epoch) >= 0) {
+                    ok = true;
+                    break;
+                }
+                __nanosleep(64);
+            }
+            if (!ok) {
+                if (p.err) atomicExch(p.err, 4);   // a peer never signalled: sums below are incomplete
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < n; i += blockDim.x) {
+            float acc = 0.0f;
+            for (int rk = 0; rk < p.world; ++rk) {
+                const float* part = reinterpret_cast<const float*>(p.peer_bases[rk] + p.parts_offset);
+                acc += __ldcv(part + base + i);
+            }
+            p.sum_out[base + i] = acc;
+        }
+        __syncthreads();
+    }
+    const uint32_t* sc = (p.peer_bases ? reinterpret_cast<const uint32_t*>(p.sum_out) : p.scores) + base;
     const int64_t orow = p.out_offsets ? (int64_t)__ldg(p.out_offsets + r) : (int64_t)r * p.out_stride;
     const int cap = p.out_offsets ? min(__ldg(p.out_offsets + r + 1) - (int)orow, p.out_stride) : p.out_stride;
 
@@ -255,13 +301,15 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 }  // namespace
 }  // namespace ucmx
 
-extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
+namespace ucmx {
+static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
                                     const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
                                     int32_t window_mode, int32_t order, const int32_t* id_map, int32_t out_stride,
                                     const int32_t* out_offsets, int32_t* out_idx, void* out_scores,
-                                    int32_t* out_counts, ucmx_stream_t stream)
+                                    int32_t* out_counts, const unsigned char* const* peer_bases, int32_t world,
+                                    int32_t my_rank, int64_t parts_offset, uint32_t epoch, float* sum_out,
+                                    ucmx_stream_t stream)
 {
-    using namespace ucmx;
     if (n_req < 0) return UCMX_EPARAM;
     if (n_req == 0) return UCMX_OK;
     if (!scores || !req_offsets || !k_per_req || !out_idx || !out_counts) return UCMX_EPARAM;
@@ -290,6 +338,13 @@ extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, con
     p.out_idx = out_idx;
     p.out_scores = (uint32_t*)out_scores;
     p.out_counts = out_counts;
+    p.peer_bases = peer_bases;
+    p.world = world;
+    p.my_rank = my_rank;
+    p.parts_offset = parts_offset;
+    p.epoch = epoch;
+    p.sum_out = sum_out;
+    p.err = peer_bases ? error_word() : nullptr;
     if (smem > 48 * 1024)
         UCMX_CUDA(cudaFuncSetAttribute(topk_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // block size: enough threads for about two candidates each (the host does not know the ragged
@@ -303,4 +358,57 @@ extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, con
     topk_ragged_kernel<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("topk_ragged_kernel");
     return UCMX_OK;
+}
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
+                                    const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
+                                    int32_t window_mode, int32_t order, const int32_t* id_map, int32_t out_stride,
+                                    const int32_t* out_offsets, int32_t* out_idx, void* out_scores,
+                                    int32_t* out_counts, ucmx_stream_t stream)
+{
+    return ucmx::topk_launch(scores, score_dtype, req_offsets, k_per_req, n_req, start_win, end_win, window_mode, order,
+                             id_map, out_stride, out_offsets, out_idx, out_scores, out_counts, nullptr, 1, 0, 0, 0, nullptr,
+                             stream);
+}
+
+namespace ucmx {
+namespace {
+__global__ void peer_signal_kernel(unsigned char* const* peer_bases, int world, int my_rank, uint32_t epoch)
+{
+    // everything this rank wrote before (its partial scores) must be visible to a peer that sees the flag
+    __threadfence_system();
+    const int r = threadIdx.x;
+    if (r < world) {
+        uint32_t* flag = reinterpret_cast<uint32_t*>(peer_bases[r]) + my_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+    }
+}
+}  // namespace
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_peer_signal(void* const* peer_bases, int32_t world, int32_t my_rank, uint32_t epoch,
+                                    ucmx_stream_t stream)
+{
+    if (!peer_bases || world < 1 || world > 32 || my_rank < 0 || my_rank >= world) return UCMX_EPARAM;
+    ucmx::peer_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned char* const*)peer_bases, world, my_rank, epoch);
+    UCMX_LAUNCH_CHECK("peer_signal_kernel");
+    return UCMX_OK;
+}
+
+extern "C" int32_t ucmx_topk_ragged_peer_sum(void* const* peer_bases, int32_t world, int32_t my_rank,
+                                             int64_t parts_offset_bytes, uint32_t epoch, float* summed_scores,
+                                             const int32_t* req_offsets, const int32_t* k_per_req, int32_t n_req,
+                                             int32_t start_win, int32_t end_win, int32_t window_mode, int32_t order,
+                                             const int32_t* id_map, int32_t out_stride, const int32_t* out_offsets,
+                                             int32_t* out_idx, float* out_scores, int32_t* out_counts,
+                                             ucmx_stream_t stream)
+{
+    if (!peer_bases || !summed_scores || world < 1 || world > 32 || my_rank < 0 || my_rank >= world ||
+        parts_offset_bytes < 128 || (parts_offset_bytes & 15))
+        return UCMX_EPARAM;
+    return ucmx::topk_launch(summed_scores, UCMX_DT_F32, req_offsets, k_per_req, n_req, start_win, end_win, window_mode,
+                             order, id_map, out_stride, out_offsets, out_idx, out_scores, out_counts,
+                             (const unsigned char* const*)peer_bases, world, my_rank, parts_offset_bytes, epoch,
+                             summed_scores, stream);
 }

@@ -9,13 +9,14 @@
 // full.  The mapped-host kernel uses plain 16-byte loads/stores like the reference's
 // H2DKernel/D2HKernel (ucm/store/device/cuda/cuda_device.cu:47-69) but with a grid sized to the
 // device instead of a fixed 32x256.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ucmx {
 
 namespace {
 
-constexpr int kXferStages = 4;
 constexpr int kMaxPlanes = 8;
 
 struct XferParams {
@@ -179,14 +180,29 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
         UCMX_LAUNCH_CHECK("xfer_plain_kernel");
         return UCMX_OK;
     }
-    p.chunk_bytes = 16384;
+    // tuning knobs (read once): chunk size, ring depth, CTAs per SM
+    static const int k_chunk = [] { const char* e = getenv("UCMX_XFER_CHUNK"); const int v = e ? atoi(e) : 0; return (v >= 1024 && v <= 65536 && v % 16 == 0) ? v : 8192; }();
+    static const int k_stages = [] { const char* e = getenv("UCMX_XFER_STAGES"); const int v = e ? atoi(e) : 0; return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8 || v == 12 || v == 16) ? v : 8; }();
+    static const int k_per_sm = [] { const char* e = getenv("UCMX_XFER_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 16) ? v : 3; }();
+    p.chunk_bytes = k_chunk;
     if (p.slice_bytes < p.chunk_bytes) p.chunk_bytes = (int32_t)p.slice_bytes;
     p.chunks_per_slice = (int32_t)((p.slice_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
     p.items = p.n * (p.mode == 0 ? p.n_planes : 1) * p.chunks_per_slice;
-    const size_t smem = 128 + (size_t)kXferStages * p.chunk_bytes;
-    auto kern = xfer_bulk_kernel<kXferStages>;
+    const size_t smem = 128 + (size_t)k_stages * p.chunk_bytes;
+    if (smem > 220 * 1024) return UCMX_EUNSUPPORTED;
+    void (*kern)(XferParams) = xfer_bulk_kernel<8>;
+    switch (k_stages) {
+        case 4: kern = xfer_bulk_kernel<4>; break;
+        case 2: kern = xfer_bulk_kernel<2>; break;
+        case 3: kern = xfer_bulk_kernel<3>; break;
+        case 6: kern = xfer_bulk_kernel<6>; break;
+        case 12: kern = xfer_bulk_kernel<12>; break;
+        case 16: kern = xfer_bulk_kernel<16>; break;
+        default: break;
+    }
     UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int ctas_per_sm = 3;
+    int ctas_per_sm = k_per_sm;
+    while (ctas_per_sm > 1 && (size_t)ctas_per_sm * (smem + 1024) > 227 * 1024) --ctas_per_sm;
     int64_t grid = (int64_t)sms * ctas_per_sm;
     if (grid > p.items) grid = p.items;
     kern<<<(unsigned)grid, 32, smem, st>>>(p);

@@ -66,6 +66,9 @@ SIGNATURES = {
     "ucmx_score_dot_query": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp],
     "ucmx_score_hamming": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "ucmx_topk_ragged": [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
+    "ucmx_peer_signal": [_vp, _i32, _i32, C.c_uint32, _vp],
+    "ucmx_topk_ragged_peer_sum": [_vp, _i32, _i32, _i64, C.c_uint32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32,
+                                  _vp, _vp, _vp, _vp, _vp],
     "ucmx_remap_resident": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "ucmx_retrieve_topk_noalloc": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i32, _i32, _i32,
                                    _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],

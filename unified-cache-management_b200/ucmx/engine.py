@@ -23,16 +23,19 @@ from .workloads import KvShape, RaggedBatch
 class DecodeRetrievalEngine:
     def __init__(self, shape: KvShape, batch: RaggedBatch, device: torch.device, *, n_layers: Optional[int] = None,
                  with_kv_pool: bool = True, heads_local: Optional[int] = None, seed: int = 0,
-                 score_reduce=None):
+                 score_reduce=None, peer_exchange=None):
         """heads_local: KV heads held by this rank under tensor parallelism (default: all).
         score_reduce: callable applied in place to the fp32 score vector between scoring and top-k
-        (the tensor-parallel all-reduce); None on a single rank."""
+        (the tensor-parallel all-reduce); None on a single rank.
+        peer_exchange: a parallel.PeerScoreExchange; partial scores then go into peer-mapped memory and are
+        summed inside the top-k kernel instead of by score_reduce."""
         self.shape, self.batch, self.device = shape, batch, device
         self.L = n_layers if n_layers is not None else shape.n_layers
         self.H = heads_local if heads_local is not None else shape.n_kv_heads
         self.Hq = shape.n_q_heads * self.H // shape.n_kv_heads
         self.D, self.T = shape.head_dim, shape.block_tokens
         self.score_reduce = score_reduce
+        self.peer_exchange = peer_exchange
         i32 = dict(dtype=torch.int32, device=device)
         self.offsets = torch.from_numpy(batch.offsets).to(device)
         self.k_per_req = torch.from_numpy(batch.k_per_req).to(device)
@@ -88,12 +91,20 @@ class DecodeRetrievalEngine:
         ops.pool_blocks(self.kv_pool[0], self.block_table, out_slots=self.block_table, out_bf16=self.rep_tables[layer])
 
     def score_layer(self, layer: int) -> None:
+        out = self.scores if self.peer_exchange is None else self.peer_exchange.begin_round()
         ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
-                            slot_ids=self.block_table, n_kv_heads=self.H, out=self.scores)
-        if self.score_reduce is not None:
+                            slot_ids=self.block_table, n_kv_heads=self.H, out=out)
+        if self.peer_exchange is not None:
+            self.peer_exchange.signal()
+        elif self.score_reduce is not None:
             self.score_reduce(self.scores)
 
     def topk_layer(self, layer: int) -> None:
+        if self.peer_exchange is not None:
+            self.peer_exchange.topk(self.offsets, self.k_per_req, out_stride=self.out_stride, order=ops.ORDER_SCORE_DESC,
+                                    id_map=self.block_table, out_offsets=self.k_offsets, out_idx=self.sel_ids[layer],
+                                    out_scores=self.sel_scores[layer], out_counts=self.sel_counts[layer])
+            return
         ops.topk_ragged(self.scores, self.offsets, self.k_per_req, out_stride=self.out_stride,
                         order=ops.ORDER_SCORE_DESC, id_map=self.block_table, out_offsets=self.k_offsets,
                         out_idx=self.sel_ids[layer], out_scores=self.sel_scores[layer],
