@@ -78,6 +78,7 @@ __device__ __forceinline__ int block_excl_scan_flag(bool flag, int* s_warp, int&
     return before + in_warp;
 }
 
+template <bool PEER>
 __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 {
     extern __shared__ __align__(16) unsigned long long s_sort[];  // score-descending order only
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     const int n = __ldg(p.offsets + r + 1) - base;
     const int k = __ldg(p.k_per_req + r);
     const bool is_float = p.is_float != 0;
-    if (p.peer_bases) {
+    if (PEER) {
         // One-shot all-reduce fused into the selection: every rank scored its own KV heads into its
         // exchange buffer and then raised its flag on every peer; wait (bounded) for all flags, then
         // add the partial scores of this request straight out of the peers' memory, in rank order, so
@@ -112,17 +113,39 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             }
         }
         __syncthreads();
-        for (int i = tid; i < n; i += blockDim.x) {
-            float acc = 0.0f;
-            for (int rk = 0; rk < p.world; ++rk) {
-                const float* part = reinterpret_cast<const float*>(p.peer_bases[rk] + p.parts_offset);
-                acc += __ldcv(part + base + i);
+        // The loads cross NVLink, so latency is what matters: up to eight ranks x eight elements per
+        // thread are requested before the first one is used (L1 is bypassed: the data is a peer's).
+        constexpr int kU = 4, kW = 8;
+        for (int i0 = tid; i0 < n; i0 += blockDim.x * kU) {
+            float acc[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) acc[u] = 0.0f;
+            for (int r0 = 0; r0 < p.world; r0 += kW) {
+                float v[kW][kU];
+#pragma unroll
+                for (int w = 0; w < kW; ++w) {
+                    const bool live = r0 + w < p.world;
+                    const float* part = reinterpret_cast<const float*>(p.peer_bases[live ? r0 + w : p.my_rank] + p.parts_offset);
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const int i = i0 + u * blockDim.x;
+                        v[w][u] = (live && i < n) ? __ldcg(part + base + i) : 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int w = 0; w < kW; ++w)
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) acc[u] += v[w][u];   // rank order: the same sum on every rank
             }
-            p.sum_out[base + i] = acc;
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i < n) p.sum_out[base + i] = acc[u];
+            }
         }
         __syncthreads();
     }
-    const uint32_t* sc = (p.peer_bases ? reinterpret_cast<const uint32_t*>(p.sum_out) : p.scores) + base;
+    const uint32_t* sc = (PEER ? reinterpret_cast<const uint32_t*>(p.sum_out) : p.scores) + base;
     const int64_t orow = p.out_offsets ? (int64_t)__ldg(p.out_offsets + r) : (int64_t)r * p.out_stride;
     const int cap = p.out_offsets ? min(__ldg(p.out_offsets + r + 1) - (int)orow, p.out_stride) : p.out_stride;
 
@@ -345,8 +368,8 @@ static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_
     p.epoch = epoch;
     p.sum_out = sum_out;
     p.err = peer_bases ? error_word() : nullptr;
-    if (smem > 48 * 1024)
-        UCMX_CUDA(cudaFuncSetAttribute(topk_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    void (*kern)(TopkParams) = peer_bases ? topk_ragged_kernel<true> : topk_ragged_kernel<false>;
+    if (smem > 48 * 1024) UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // block size: enough threads for about two candidates each (the host does not know the ragged
     // sizes, only the output width, so k is the hint), never fewer than the rank sort needs
     int threads = 1024;
@@ -355,7 +378,7 @@ static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_
         const int v = atoi(e);
         if (v == 256 || v == 512 || v == 1024) threads = v;
     }
-    topk_ragged_kernel<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
+    kern<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("topk_ragged_kernel");
     return UCMX_OK;
 }
