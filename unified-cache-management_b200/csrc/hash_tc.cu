@@ -271,31 +271,55 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             tc_fence_after();
             (void)mbar_wait(&bars->full[s], (uint32_t)((it / kStagesA) & 1));  // already complete: acquires the TMA-written tile
             const unsigned char* xa = sA + (size_t)s * kTileBytes;
-            // |x|^2 of this row (order of the additions does not matter for a bound)
+            // An upper bound on |x|^2 of this row, cheaply: packed bf16 multiply-adds into eight pairs of
+            // partial sums of eight terms each (a bf16 running sum of k non-negative terms is low by at
+            // most k * 2^-8 relative, covered by the 1.05 below), added up in fp32.
             float x2 = 0.0f;
+            {
+                __nv_bfloat162 part[8];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const uint4 v = *reinterpret_cast<const uint4*>(xa + sw_offset(m, c * 8));
-                const float e[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y), bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+                for (int g = 0; g < 8; ++g) part[g] = __floats2bfloat162_rn(0.0f, 0.0f);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x2 = fmaf(e[i], e[i], x2);
+                for (int c = 0; c < 16; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xa + sw_offset(m, c * 8));
+                    const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&e[i]);
+                        part[(c * 4 + i) & 7] = __hfma2(h, h, part[(c * 4 + i) & 7]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < 8; ++g) x2 += __low2float(part[g]) + __high2float(part[g]);
             }
             // one threshold for the whole row: |acc| <= tau |x| max_j|w_j| (a little wider than per column, no table look-up)
-            const uint32_t thr_bits = __float_as_uint(kTau * sqrtf(x2) * 1.0001f * __uint_as_float(*wmax_bits));
+            const float thr = kTau * sqrtf(x2 * 1.05f) * 1.0001f * __uint_as_float(*wmax_bits);
             uint32_t code[4], doubt[4];
 #pragma unroll
             for (int cw = 0; cw < 4; ++cw) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kBits + cw * 32), v);
-                uint32_t bits = 0, unsure = 0;
+                // Sign bits: shift each accumulator's sign into a word, highest column first (one funnel
+                // shift per value).  A set sign bit means "not positive"; an exact zero has a clear sign bit
+                // but is below any threshold, so it is settled by the exact chain like every doubtful bit.
+                uint32_t neg = 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    // sign from the sign bit (a zero sum is below the threshold and is settled exactly below);
-                    // magnitudes compare as integers
-                    bits |= ((~v[j]) >> 31) << j;
-                    unsure |= ((v[j] & 0x7fffffffu) <= thr_bits ? 1u : 0u) << j;
+                for (int j = 31; j >= 0; --j) neg = __funnelshift_l(v[j], neg, 1);
+                // Smallest magnitude of each group of eight columns (one min per value); only groups that
+                // dip under the threshold are looked at column by column.
+                uint32_t unsure = 0;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    float mn = fabsf(__uint_as_float(v[g8 * 8]));
+#pragma unroll
+                    for (int j = 1; j < 8; ++j) mn = fminf(mn, fabsf(__uint_as_float(v[g8 * 8 + j])));
+                    if (mn <= thr) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            unsure |= (fabsf(__uint_as_float(v[g8 * 8 + j])) <= thr ? 1u : 0u) << (g8 * 8 + j);
+                    }
                 }
-                code[cw] = bits;
+                code[cw] = ~neg;
                 doubt[cw] = unsure;
             }
             // the accumulator is read: hand it back to the MMA warp
