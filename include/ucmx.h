@@ -29,6 +29,7 @@ extern "C" {
 #define UCMX_EPARAM (-50000)
 #define UCMX_EOOM (-50001)
 #define UCMX_EOSERROR (-50002)
+#define UCMX_EDUPLICATE (-50003)
 #define UCMX_ENOOBJ (-50005)
 #define UCMX_EUNSUPPORTED (-50008)
 
@@ -369,6 +370,49 @@ int32_t ucmx_retrieval_result_shape(ucmx_retrieval* r, int32_t req_id, int32_t* 
 int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, int32_t* host_indices,
                                   float* host_scores);
 int32_t ucmx_retrieval_destroy(ucmx_retrieval* r);
+
+/* ---------------------------------------------------------------- file-per-block store data plane
+ * Replaces UC::NFSStore (ucm/store/nfsstore/cc/api/nfsstore.h:34-91) for block files and slice
+ * transfer: SpaceManager::NewBlock/CommitBlock/LookupBlock (nfsstore/cc/domain/space/space_manager.cc:57-134),
+ * the shard layout data/<first 8 id bytes, %016x>/<next 8 id bytes, %016x>.dat with ".act" (or temp/...)
+ * until commit (space_shard_layout.cc:51-126, space_shard_temp_layout.cc:29-54), task submit/wait/check
+ * (ucm/store/task/task_manager.cc:28-104) and PosixQueue::S2D/D2S/S2H/H2S (trans/posix_queue.cc:98-138).
+ * Block ids are byte strings of at least 16 bytes; the first 16 name the file.  The storage backend of
+ * a block is backends[std::hash<std::string>(id) % n], as in the reference (same C++ runtime).
+ * Hotness tracking (utime touches on lookup) is not part of this data plane. */
+typedef struct ucmx_fstore ucmx_fstore;
+#define UCMX_FSTORE_DUMP 0
+#define UCMX_FSTORE_LOAD 1
+#define UCMX_FSTORE_HOST 0
+#define UCMX_FSTORE_DEVICE 1
+/* backends: ':'-separated directories (the first gets data/ [and temp/] created, the others must hold
+ * them already).  transfer_enable = 0 builds a store that only manages block files (scheduler role).
+ * device_id < 0: host-memory transfers only.  io_size: bytes per staging slot (262144 in the
+ * reference); slots_per_worker (0 = 16) page-locked slots for each of worker_number (0 = 8) threads;
+ * timeout_ms (0 = 30000) bounds ucmx_fstore_wait. */
+int32_t ucmx_fstore_create(const char* backends, size_t block_size, int32_t temp_dump_dir,
+                           int32_t transfer_enable, int32_t device_id, size_t io_size,
+                           size_t slots_per_worker, size_t worker_number, size_t timeout_ms,
+                           ucmx_fstore** out);
+int32_t ucmx_fstore_destroy(ucmx_fstore* store);
+/* path of the block's file: activated != 0 = while being written, 0 = committed */
+int32_t ucmx_fstore_path(const ucmx_fstore* store, const char* id, size_t id_len, int32_t activated,
+                         char* out, size_t capacity);
+/* creates the block's file at block_size bytes; UCMX_EDUPLICATE if it exists committed or in progress */
+int32_t ucmx_fstore_alloc(ucmx_fstore* store, const char* id, size_t id_len);
+int32_t ucmx_fstore_lookup(const ucmx_fstore* store, const char* id, size_t id_len, int32_t* found);
+/* success != 0: publish (rename to .dat), UCMX_ENOOBJ if nothing was in progress; 0: discard */
+int32_t ucmx_fstore_commit(ucmx_fstore* store, const char* id, size_t id_len, int32_t success);
+/* n slices: bytes [offsets[i], offsets[i]+lengths[i]) of block ids[i]'s file <-> addresses[i] (host
+ * or device memory by `location`).  Dumps write the in-progress file, loads read the committed one.
+ * Returns at once with a task id (> 0); the caller's buffers stay borrowed until wait returns. */
+int32_t ucmx_fstore_submit(ucmx_fstore* store, int32_t type, int32_t location, const char* const* ids,
+                           const size_t* id_lens, const size_t* offsets, const uintptr_t* addresses,
+                           const size_t* lengths, size_t n, size_t* task_id);
+/* 0 when every slice moved; UCMX_ERROR if any failed or the timeout passed (the call still returns
+ * only after the workers have let go of the buffers); UCMX_ENOOBJ for an unknown or already waited id */
+int32_t ucmx_fstore_wait(ucmx_fstore* store, size_t task_id);
+int32_t ucmx_fstore_check(ucmx_fstore* store, size_t task_id, int32_t* finished);
 
 #ifdef __cplusplus
 }

@@ -246,6 +246,65 @@ def ref_retrieval_backend():
     return mod
 
 
+_nfs = None
+
+
+def have_nfs_ref() -> bool:
+    return os.path.exists(os.path.join(_REF_DIR, "libnfs_ref.so"))
+
+
+def ref_nfs() -> C.CDLL:
+    """The reference's NFS-store space manager and file helpers (space_manager.cc,
+    space_shard_layout.cc, space_shard_temp_layout.cc, file.cc, posix_file.cc) behind nfs_ref_shim.cpp."""
+    global _nfs
+    if _nfs is None:
+        L = C.CDLL(os.path.join(_REF_DIR, "libnfs_ref.so"))
+        L.nfsref_create.restype = C.c_void_p
+        L.nfsref_create.argtypes = [C.c_char_p, C.c_size_t, C.c_int, C.POINTER(C.c_int)]
+        L.nfsref_destroy.argtypes = [C.c_void_p]
+        L.nfsref_new_block.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        L.nfsref_lookup_block.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        L.nfsref_commit_block.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t, C.c_int]
+        L.nfsref_data_path.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t, C.c_int, C.c_char_p, C.c_size_t]
+        L.nfsref_write.argtypes = [C.c_char_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int]
+        L.nfsref_read.argtypes = [C.c_char_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int]
+        _nfs = L
+    return _nfs
+
+
+class RefSpaceManager:
+    """Thin object over ref_nfs(): the reference's SpaceManager on a set of backend directories."""
+
+    def __init__(self, backends: str, block_size: int, temp_dir: bool = False):
+        st = C.c_int(0)
+        self.h = ref_nfs().nfsref_create(backends.encode(), block_size, int(temp_dir), C.byref(st))
+        self.status = st.value
+        if not self.h:
+            raise RuntimeError(f"reference SpaceManager::Setup failed with {st.value}")
+
+    def new_block(self, bid: bytes) -> int:
+        return ref_nfs().nfsref_new_block(self.h, bid, len(bid))
+
+    def commit(self, bid: bytes, success: bool = True) -> int:
+        return ref_nfs().nfsref_commit_block(self.h, bid, len(bid), int(success))
+
+    def lookup(self, bid: bytes) -> bool:
+        return bool(ref_nfs().nfsref_lookup_block(self.h, bid, len(bid)))
+
+    def path(self, bid: bytes, activated: bool) -> str:
+        buf = C.create_string_buffer(4096)
+        ref_nfs().nfsref_data_path(self.h, bid, len(bid), int(activated), buf, 4096)
+        return buf.value.decode()
+
+    @staticmethod
+    def write(path: str, offset: int, data: np.ndarray, direct: bool = False) -> int:
+        return ref_nfs().nfsref_write(path.encode(), offset, data.nbytes, data.ctypes.data, int(direct))
+
+    @staticmethod
+    def read(path: str, offset: int, out: np.ndarray, direct: bool = False) -> int:
+        return ref_nfs().nfsref_read(path.encode(), offset, out.nbytes, out.ctypes.data, int(direct))
+
+
 _gsa = None
 
 

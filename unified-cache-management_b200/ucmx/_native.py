@@ -16,6 +16,7 @@ ERROR = -1
 EPARAM = -50000
 EOOM = -50001
 EOSERROR = -50002
+EDUPLICATE = -50003
 ENOOBJ = -50005
 EUNSUPPORTED = -50008
 
@@ -25,7 +26,7 @@ WIN_NONE, WIN_FORCE, WIN_EXCLUDE = 0, 1, 2
 ORDER_SCORE_DESC, ORDER_INDEX_ASC = 0, 1
 
 _STATUS_NAMES = {
-    OK: "OK", ERROR: "ERROR", EPARAM: "EPARAM", EOOM: "EOOM", EOSERROR: "EOSERROR",
+    OK: "OK", ERROR: "ERROR", EPARAM: "EPARAM", EOOM: "EOOM", EOSERROR: "EOSERROR", EDUPLICATE: "EDUPLICATE",
     ENOOBJ: "ENOOBJ", EUNSUPPORTED: "EUNSUPPORTED",
 }
 
@@ -96,6 +97,16 @@ SIGNATURES = {
     "ucmx_retrieval_result_shape": [_vp, _i32, _pi32, _pi32],
     "ucmx_retrieval_get_result": [_vp, _i32, _vp, _vp],
     "ucmx_retrieval_destroy": [_vp],
+    "ucmx_fstore_create": [C.c_char_p, _sz, _i32, _i32, _i32, _sz, _sz, _sz, _sz, _pvp],
+    "ucmx_fstore_destroy": [_vp],
+    "ucmx_fstore_path": [_vp, C.c_char_p, _sz, _i32, C.c_char_p, _sz],
+    "ucmx_fstore_alloc": [_vp, C.c_char_p, _sz],
+    "ucmx_fstore_lookup": [_vp, C.c_char_p, _sz, _pi32],
+    "ucmx_fstore_commit": [_vp, C.c_char_p, _sz, _i32],
+    "ucmx_fstore_submit": [_vp, _i32, _i32, C.POINTER(C.c_char_p), C.POINTER(_sz), C.POINTER(_sz),
+                           C.POINTER(C.c_size_t), C.POINTER(_sz), _sz, C.POINTER(_sz)],
+    "ucmx_fstore_wait": [_vp, _sz],
+    "ucmx_fstore_check": [_vp, _sz, _pi32],
 }
 _RESTYPES = {"ucmx_last_error": C.c_char_p}
 

@@ -9,6 +9,9 @@ bytes (what the kernel must read and write, not what the memory system moved).
   offload   config 4: gather 4096 blocks of K and V of one layer to pinned host memory and scatter
             4096 back, direct (kernel writes host memory) and staged (device compaction + one DMA)
   pool      config 1/2: pooling a whole pool, and the 64-block decode case
+  filestore (only when named) file-per-block store: dump 256 blocks x 16 K/V layer slices of 256 KiB (1 GiB) from
+            HBM to block files under $UCMX_STORE_DIR (default: the temp dir) and load them back; wall-clock GB/s,
+            bounded by that directory's file system; also with one slice per launch (the reference's granularity)
 """
 from __future__ import annotations
 
@@ -142,6 +145,47 @@ def main(argv):
         sets = [ids[i * 64:(i + 1) * 64].contiguous() for i in range(16)]
         t = _time(lambda i: ops.pool_blocks(k, sets[i % 16], out_slots=sets[i % 16], out_bf16=reps), iters=16)
         out["pool_mean_64_blocks"] = {"us": t, "gbs": 64 * (shape.slice_bytes + 2048) / t / 1e3}
+    if "filestore" in which:
+        import os
+        import shutil
+        import tempfile
+        import time
+
+        import numpy as np
+
+        from .store.nfsstore import UcmNfsStore
+        nblk, nsl = 256, 16
+        sl = shape.slice_bytes
+        cache = torch.empty((nblk * nsl, sl), dtype=torch.uint8, device=dev)
+        cache.random_(0, 256, generator=g)
+        back = torch.zeros_like(cache)
+        rng = np.random.default_rng(4004)
+        ids = [rng.integers(1, 256, size=32, dtype=np.uint8).tobytes() for _ in range(nblk)]
+        bl = [b for b in ids for _ in range(nsl)]
+        offs = [j * sl for _ in ids for j in range(nsl)]
+        res = {"bytes": nblk * nsl * sl}
+        for name, slots in (("grouped", 16), ("one_slice_per_launch", 2)):
+            root = tempfile.mkdtemp(dir=os.environ.get("UCMX_STORE_DIR"))
+            try:
+                store = UcmNfsStore({"storage_backends": root, "kv_block_size": nsl * sl, "role": "worker", "device": 0,
+                                     "io_size": sl, "buffer_number": slots, "stream_number": 8})
+                store.create(ids)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                st_d = store.wait(store.dump(bl, offs, list(cache)))
+                t1 = time.perf_counter()
+                store.commit(ids, True)
+                t2 = time.perf_counter()
+                st_l = store.wait(store.load(bl, offs, list(back)))
+                t3 = time.perf_counter()
+                torch.cuda.synchronize()
+                res[name] = {"dump_gbs": res["bytes"] / (t1 - t0) / 1e9, "load_gbs": res["bytes"] / (t3 - t2) / 1e9,
+                             "status": [st_d, st_l], "exact": bool(torch.equal(back, cache))}
+                back.zero_()
+                store.close()
+            finally:
+                shutil.rmtree(root, ignore_errors=True)
+        out["filestore"] = res
     print(json.dumps(out))
 
 

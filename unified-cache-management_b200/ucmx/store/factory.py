@@ -28,3 +28,4 @@ class UcmConnectorFactory:
 
 
 UcmConnectorFactory.register_connector("UcmDramStore", "ucmx.store.dramstore", "UcmDramStore")
+UcmConnectorFactory.register_connector("UcmNfsStore", "ucmx.store.nfsstore", "UcmNfsStore")
