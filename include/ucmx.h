@@ -414,6 +414,37 @@ int32_t ucmx_fstore_submit(ucmx_fstore* store, int32_t type, int32_t location, c
 int32_t ucmx_fstore_wait(ucmx_fstore* store, size_t task_id);
 int32_t ucmx_fstore_check(ucmx_fstore* store, size_t task_id, int32_t* finished);
 
+/* ---------------------------------------------------------------- KVStar softmax-vote retrieval
+ * Replaces kvstar_retrieve.AsyncRetrieveByCPU -> KVStar::Execute
+ * (ucm/sparse/kvstar/retrieve/core/domain/retrieve_task/simd_compute_kernel.cpp:635-764, called from
+ * ucm/sparse/kvstar/multistep.py:240-262) and extract_block_repre (multistep.py:279-316).
+ *
+ * ucmx_kvstar_block_repre: per block, keep d_pruned channels of every head (pruned_index: device int64
+ * [H][d_pruned], or NULL to keep all) and average every `merge` consecutive tokens; result is IEEE half
+ * [slot][T/merge][H][d_pruned] at out_slots[i] (or i).  The mean is rounded to bf16 first (the
+ * reference averages in the cache's dtype), then converted to half.
+ *
+ * ucmx_kvstar_scores: for each request r, query rows q[q_offsets[r] .. q_offsets[r+1]) ([token][Hq][d_orig]
+ * half, at most max_q_tokens tokens) vote on the request's candidate blocks (CSR req_offsets over slot_ids
+ * into the representation table; slot_ids NULL = candidates are table rows 0..total-1):
+ *   out[c] = sum over query rows of sum over the block's M positions of softmax_over_all_positions(q . k).
+ * pruned_index: device int64 [n_req][H][d_pruned] (channels of d_orig), or NULL when d_pruned == d_orig.
+ * Dot products are not scaled (as in the reference).  Follow with ucmx_topk_ragged on `out`.
+ * workspace: device scratch of ucmx_kvstar_workspace_bytes(...) bytes, 16-byte aligned.
+ * Shapes with H*d_pruned % 64 == 0, d_pruned % 16 == 0, M % 32 == 0, max_q_tokens*Hq/H <= 128 run on the
+ * tensor cores (tcgen05); all others on a CUDA-core kernel with the same results to rounding. */
+int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_geometry* geom, const int32_t* block_ids,
+                                const int32_t* out_slots, int32_t n, const int64_t* pruned_index,
+                                int32_t d_pruned, int32_t merge, void* reps_f16, ucmx_stream_t stream);
+size_t ucmx_kvstar_workspace_bytes(int32_t total_blocks, int32_t n_req, int32_t max_q_tokens,
+                                   int32_t n_q_heads, int32_t n_kv_heads);
+int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int32_t M, int32_t n_kv_heads,
+                           int32_t d_pruned, const int32_t* req_offsets, const int32_t* slot_ids,
+                           int32_t n_req, int32_t total, const void* q_f16, const int32_t* q_offsets,
+                           int32_t max_q_tokens, int32_t n_q_heads, int32_t d_orig,
+                           const int64_t* pruned_index, void* workspace, size_t workspace_bytes,
+                           float* out_scores, ucmx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

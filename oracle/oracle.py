@@ -228,6 +228,51 @@ def store_offset(block_tokens, heads_per_rank, head_dim, rank, tp_size, elem_byt
                                       C.c_int32(int(is_mla))))
 
 
+# ------------------------------------------------------------------------- KVStar
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+def kvstar_block_repre(k_bf16, ids, pruned, merge):
+    """k_bf16: uint16 bf16 bits [num_blocks, T, H, D]; pruned: int64 [H, d_pruned] or None.
+    Returns half bits [n, T/merge, H, d_pruned]."""
+    k = _c(k_bf16, np.uint16)
+    nb, T, H, D = k.shape
+    ids = _c(ids, np.int32)
+    pr = _c(pruned, np.int64)
+    dp = D if pr is None else pr.shape[1]
+    out = np.empty((len(ids), T // merge, H, dp), np.uint16)
+    lib().orc_kvstar_block_repre(k.ctypes.data_as(C.c_void_p), C.c_int64(T * H * D), C.c_int64(H * D), C.c_int32(T),
+                                 C.c_int32(H), C.c_int32(D), ids.ctypes.data_as(C.c_void_p), C.c_int32(len(ids)),
+                                 None if pr is None else pr.ctypes.data_as(C.c_void_p), C.c_int32(dp), C.c_int32(merge),
+                                 out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def kvstar_scores(q_f16, reps_f16, pruned=None):
+    """q_f16: half bits [x, Hq, d_orig]; reps_f16: half bits [n, M, H, d_pruned]. Returns float32 [n]."""
+    q = _c(q_f16, np.uint16)
+    r = _c(reps_f16, np.uint16)
+    pr = _c(pruned, np.int64)
+    x, Hq, d_orig = q.shape
+    n, M, H, dp = r.shape
+    scratch = np.empty(x * Hq * n * M, np.float32)
+    out = np.empty(n, np.float32)
+    lib().orc_kvstar_scores(q.ctypes.data_as(C.c_void_p), C.c_int32(x), C.c_int32(Hq), C.c_int32(d_orig),
+                            r.ctypes.data_as(C.c_void_p), C.c_int32(n), C.c_int32(M), C.c_int32(H), C.c_int32(dp),
+                            None if pr is None else pr.ctypes.data_as(C.c_void_p), scratch.ctypes.data_as(C.c_void_p),
+                            out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def kvstar_topk(scores, k):
+    s = _c(scores, np.float32)
+    out = np.empty(max(min(k, len(s)), 0), np.int64)
+    cnt = lib().orc_kvstar_topk(s.ctypes.data_as(C.c_void_p), C.c_int32(len(s)), C.c_int32(k), out.ctypes.data_as(C.c_void_p))
+    return out[:cnt]
+
+
 # ------------------------------------------------------- the compiled reference
 
 def have_ref() -> bool:
@@ -303,6 +348,34 @@ class RefSpaceManager:
     @staticmethod
     def read(path: str, offset: int, out: np.ndarray, direct: bool = False) -> int:
         return ref_nfs().nfsref_read(path.encode(), offset, out.nbytes, out.ctypes.data, int(direct))
+
+
+def have_kvstar_ref() -> bool:
+    return all(os.path.exists(os.path.join(_REF_DIR, f)) for f in ("libkvstar_ref.so", "libkvstar_ref_scalar.so"))
+
+
+_kvstar = {}
+
+
+def ref_kvstar_topk(q_f16, reps_f16, pruned, topk, scalar=False):
+    """KVStar::Execute of the reference (simd_compute_kernel.cpp) on one request: the selected block
+    indices, in the order the reference returns them (scalar build: best first; AVX2 build: any order)."""
+    name = "libkvstar_ref_scalar.so" if scalar else "libkvstar_ref.so"
+    if name not in _kvstar:
+        _kvstar[name] = C.CDLL(os.path.join(_REF_DIR, name))
+    q = _c(q_f16, np.uint16)
+    r = _c(reps_f16, np.uint16)
+    pr = _c(pruned, np.int64)
+    x, Hq, d_orig = q.shape
+    n, M, H, dp = r.shape
+    out = np.empty(max(topk, 1), np.int64)
+    cnt = _kvstar[name].kvstar_ref_execute(q.ctypes.data_as(C.c_void_p), C.c_int64(x), C.c_int64(Hq), C.c_int64(d_orig),
+                                           r.ctypes.data_as(C.c_void_p), C.c_int64(n), C.c_int64(M), C.c_int64(H),
+                                           C.c_int64(dp), None if pr is None else pr.ctypes.data_as(C.c_void_p),
+                                           C.c_int(topk), out.ctypes.data_as(C.c_void_p))
+    if cnt < 0:
+        raise RuntimeError("the reference kernel threw")
+    return out[:cnt]
 
 
 _gsa = None

@@ -467,3 +467,136 @@ int64_t orc_store_offset(int32_t block_tokens, int32_t heads_per_rank, int32_t h
     int64_t k_off = is_mla ? layer_sz * layer : layer_sz * layer + layer_sz / tp_size * rank;
     return is_v ? k_off + k_sz : k_off;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * KVStar: multi-query softmax-vote retrieval.
+ * ------------------------------------------------------------------------------------------ */
+
+/* IEEE half -> float, every class of value (the reference's scalar path has the same table-free
+ * conversion, ucm/sparse/kvstar/retrieve/core/domain/retrieve_task/simd_compute_kernel.cpp:773-813;
+ * its AVX2 path uses vcvtph2ps, which is this function in hardware). */
+static inline float f16_to_f32(uint16_t h)
+{
+    uint32_t s = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 0x1fu, m = h & 0x3ffu, bits;
+    if (e == 0) {
+        if (m == 0) {
+            bits = s;
+        } else {
+            int sh = 0;
+            while (!(m & 0x400u)) { m <<= 1; ++sh; }
+            bits = s | ((uint32_t)(127 - 15 - sh + 1) << 23) | ((m & 0x3ffu) << 13);
+        }
+    } else if (e == 31) {
+        bits = s | 0x7f800000u | (m << 13);
+    } else {
+        bits = s | ((e + 112u) << 23) | (m << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* float -> IEEE half, round to nearest even (what torch's .to(float16) does) */
+static inline uint16_t f32_to_f16(float f)
+{
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t s = (x >> 16) & 0x8000u, a = x & 0x7fffffffu;
+    if (a >= 0x7f800000u) return (uint16_t)(s | 0x7c00u | ((a > 0x7f800000u) ? 0x200u : 0));
+    if (a >= 0x477ff000u) return (uint16_t)(s | 0x7c00u);              /* rounds to infinity */
+    if (a < 0x33000001u) return (uint16_t)s;                           /* below half the smallest subnormal */
+    int32_t e = (int32_t)(a >> 23) - 127;
+    uint32_t m = (a & 0x7fffffu) | 0x800000u;
+    int shift = e < -14 ? (13 + (-14 - e)) : 13;
+    uint32_t half = m >> shift, rem = m & ((1u << shift) - 1u), mid = 1u << (shift - 1);
+    if (rem > mid || (rem == mid && (half & 1u))) ++half;
+    if (e < -14) return (uint16_t)(s | half);                         /* subnormal (may carry into the normal range) */
+    return (uint16_t)(s | (((uint32_t)(e + 15) << 10) + (half - 0x400u)));
+}
+
+uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
+float orc_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
+/* Block representations (extract_block_repre, ucm/sparse/kvstar/multistep.py:279-316, and the cast
+ * of :495-499): keep the d_pruned listed channels of every head, average each run of `merge`
+ * consecutive tokens in the cache's dtype (fp32 sum in token order times the fp32 reciprocal, rounded
+ * to bf16, which is how torch reduces a bf16 tensor on the GPU), then cast to half.
+ * k: bf16 bits, element (block, token, head, d) at block*block_stride + token*token_stride + head*D + d.
+ * out: half bits [n][T/merge][H][d_pruned].  pruned == NULL keeps all D channels (d_pruned == D). */
+void orc_kvstar_block_repre(const uint16_t *k, int64_t block_stride, int64_t token_stride,
+                            int32_t T, int32_t H, int32_t D, const int32_t *ids, int32_t n,
+                            const int64_t *pruned, int32_t d_pruned, int32_t merge, uint16_t *out)
+{
+    const int32_t M = T / merge;
+    const float inv = 1.0f / (float)merge;
+    for (int32_t i = 0; i < n; ++i)
+        for (int32_t m = 0; m < M; ++m)
+            for (int32_t h = 0; h < H; ++h)
+                for (int32_t dp = 0; dp < d_pruned; ++dp) {
+                    const int64_t d = pruned ? pruned[(int64_t)h * d_pruned + dp] : dp;
+                    float acc = 0.0f;
+                    for (int32_t c = 0; c < merge; ++c)
+                        acc += bf16_to_f32(k[(int64_t)ids[i] * block_stride + (int64_t)(m * merge + c) * token_stride + (int64_t)h * D + d]);
+                    out[(((int64_t)i * M + m) * H + h) * d_pruned + dp] = f32_to_f16(bf16_to_f32(f32_to_bf16(acc * inv)));
+                }
+}
+
+/* Vote scores of one request (the scalar path of KVStar::Execute, simd_compute_kernel.cpp:816-960,
+ * stopping before its top-k): raw dot products of every query row (x tokens x Hq heads) with the
+ * representations of its KV head over all S = n*M positions, a softmax over S per row, and per
+ * block the sum of its M probabilities over all rows.  q: half [x][Hq][d_orig]; reps: half
+ * [n][M][H][d_pruned]; pruned: [H][d_pruned] channel indices into d_orig or NULL; out: float [n].
+ * scratch: x*Hq*n*M floats. */
+void orc_kvstar_scores(const uint16_t *q, int32_t x, int32_t Hq, int32_t d_orig, const uint16_t *reps,
+                       int32_t n, int32_t M, int32_t H, int32_t d_pruned, const int64_t *pruned,
+                       float *scratch, float *out)
+{
+    const int32_t g = Hq / H;
+    const int64_t S = (int64_t)n * M;
+    for (int32_t t = 0; t < x; ++t)
+        for (int32_t h = 0; h < H; ++h)
+            for (int32_t gg = 0; gg < g; ++gg) {
+                const int32_t head = h * g + gg;
+                const uint16_t *qv = q + ((int64_t)t * Hq + head) * d_orig;
+                float *row = scratch + ((int64_t)t * Hq + head) * S;
+                for (int64_t s = 0; s < S; ++s) {
+                    const uint16_t *kv = reps + (s * H + h) * d_pruned;
+                    float score = 0.0f;
+                    for (int32_t d = 0; d < d_pruned; ++d) {
+                        const int64_t dq = pruned ? pruned[(int64_t)h * d_pruned + d] : d;
+                        score += f16_to_f32(qv[dq]) * f16_to_f32(kv[d]);
+                    }
+                    row[s] = score;
+                }
+            }
+    for (int64_t r = 0; r < (int64_t)x * Hq; ++r) {
+        float *row = scratch + r * S;
+        float mx = row[0], sum = 0.0f;
+        for (int64_t s = 1; s < S; ++s)
+            if (row[s] > mx) mx = row[s];
+        for (int64_t s = 0; s < S; ++s) {
+            row[s] = expf(row[s] - mx);
+            sum += row[s];
+        }
+        if (sum > 1e-9f)
+            for (int64_t s = 0; s < S; ++s) row[s] /= sum;
+    }
+    for (int32_t b = 0; b < n; ++b) out[b] = 0.0f;
+    for (int64_t r = 0; r < (int64_t)x * Hq; ++r)
+        for (int64_t s = 0; s < S; ++s) out[s / M] += scratch[r * S + s];
+}
+
+/* The k highest-voted blocks, best first; equal scores go to the lower index here (the reference's
+ * heap and nth_element variants leave the order of ties, and of the result, unspecified:
+ * simd_compute_kernel.cpp:748-755,962-979).  Returns the count written. */
+int32_t orc_kvstar_topk(const float *scores, int32_t n, int32_t k, int64_t *out)
+{
+    if (k > n) k = n;
+    if (k <= 0) return 0;
+    orc_pair *p = (orc_pair *)malloc((size_t)n * sizeof(orc_pair));
+    for (int32_t i = 0; i < n; ++i) { p[i].s = scores[i]; p[i].i = i; }
+    qsort(p, (size_t)n, sizeof(orc_pair), cmp_desc_stable);
+    for (int32_t i = 0; i < k; ++i) out[i] = p[i].i;
+    free(p);
+    return k;
+}

@@ -68,3 +68,36 @@ def case_hash(seed=1005):
     q = randn_bf16(rng, (1, 8, 128))                # one decode token, 8 (group-mean) heads
     keys = randn_bf16(rng, (7, 16, 8, 128))         # 7 blocks of 16 tokens, 8 kv heads
     return w, q, keys
+
+
+def f32_to_f16_bits(x):
+    return np.ascontiguousarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+KVSTAR_CASES = {
+    # name: (seed, x tokens, Hq, H, d_orig, d_pruned, M positions per block, n blocks, top-k)
+    "llama": (6001, 8, 32, 8, 128, 32, 64, 96, 24),          # tensor-core shape: 4 heads per instruction, 2 groups
+    "qwen": (6002, 8, 64, 8, 128, 32, 64, 80, 20),           # 8-way groups: 2 heads per instruction, 4 groups
+    "short_group": (6003, 5, 32, 8, 128, 32, 32, 70, 18),    # 20 query rows per head padded to 32
+    "odd": (6004, 3, 6, 2, 40, 24, 10, 37, 9),               # a shape only the CUDA-core kernel takes
+    "unpruned": (6005, 2, 8, 4, 64, 64, 32, 41, 10),         # no channel list: d_pruned == d_orig
+}
+
+
+def case_kvstar(name):
+    """Query group (half bits [x, Hq, d]), block representations (half bits [n, M, H, d_pruned]) and the
+    kept-channel list (int64 [H, d_pruned] or None) of one KVStar retrieval."""
+    seed, x, Hq, H, D, dp, M, n, k = KVSTAR_CASES[name]
+    rng = np.random.default_rng(seed)
+    q = f32_to_f16_bits(rng.standard_normal((x, Hq, D), dtype=np.float32))
+    reps = f32_to_f16_bits(rng.standard_normal((n, M, H, dp), dtype=np.float32) * np.float32(0.6))
+    pruned = None if dp == D else np.stack([rng.permutation(D)[:dp] for _ in range(H)]).astype(np.int64)
+    return q, reps, pruned, k
+
+
+def case_kvstar_repre(seed=6101, merge=2, dp=32):
+    rng = np.random.default_rng(seed + merge)
+    k = randn_bf16(rng, (7, 128, 8, 128))
+    ids = rng.permutation(7)[:5].astype(np.int32)
+    pruned = np.stack([rng.permutation(128)[:dp] for _ in range(8)]).astype(np.int64)
+    return k, ids, pruned

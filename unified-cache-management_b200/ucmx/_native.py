@@ -107,8 +107,12 @@ SIGNATURES = {
                            C.POINTER(C.c_size_t), C.POINTER(_sz), _sz, C.POINTER(_sz)],
     "ucmx_fstore_wait": [_vp, _sz],
     "ucmx_fstore_check": [_vp, _sz, _pi32],
+    "ucmx_kvstar_block_repre": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp],
+    "ucmx_kvstar_workspace_bytes": [_i32, _i32, _i32, _i32, _i32],
+    "ucmx_kvstar_scores": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz,
+                           _vp, _vp],
 }
-_RESTYPES = {"ucmx_last_error": C.c_char_p}
+_RESTYPES = {"ucmx_last_error": C.c_char_p, "ucmx_kvstar_workspace_bytes": C.c_size_t}
 
 
 def _load() -> C.CDLL:

@@ -336,3 +336,69 @@ def remap_resident(slot_logical: torch.Tensor, slot_free: torch.Tensor, slot_phy
                                    _ptr(load_counts), _stream(sel))
     N.check("ucmx_remap_resident", st, 1 if n_req else 0)
     return table, load_logical, load_phys, load_counts
+
+
+def kvstar_block_repre(k_cache: torch.Tensor, block_ids: torch.Tensor, *, merge: int = 1,
+                       pruned_index: Optional[torch.Tensor] = None, out_slots: Optional[torch.Tensor] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """KVStar block representations: fp16 [slot, T/merge, H, d_pruned] from a bf16 paged cache.
+
+    pruned_index: int64 [H, d_pruned] channels to keep per head (None keeps all)."""
+    _need_cuda(k_cache, block_ids, pruned_index, out_slots, out)
+    g = kv_geometry(k_cache)
+    ids = _i32(block_ids, "block_ids")
+    n = ids.numel()
+    if pruned_index is not None:
+        if pruned_index.dtype != torch.int64 or not pruned_index.is_contiguous() or pruned_index.shape[0] != g.n_kv_heads:
+            raise ValueError("pruned_index must be contiguous int64 [n_kv_heads, d_pruned]")
+        dp = pruned_index.shape[1]
+    else:
+        dp = g.head_dim
+    if g.block_tokens % merge:
+        raise ValueError("block_tokens must be a multiple of merge")
+    M = g.block_tokens // merge
+    if out is None:
+        out = torch.empty((n, M, g.n_kv_heads, dp), dtype=torch.float16, device=k_cache.device)
+    if out.dtype != torch.float16 or not out.is_contiguous() or tuple(out.shape[1:]) != (M, g.n_kv_heads, dp):
+        raise ValueError("out must be contiguous fp16 [n_slots, T/merge, n_kv_heads, d_pruned]")
+    st = N.lib.ucmx_kvstar_block_repre(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+                                       _ptr(pruned_index), dp, merge, _ptr(out), _stream(k_cache))
+    N.check("ucmx_kvstar_block_repre", st, 1 if n else 0)
+    return out
+
+
+def kvstar_workspace_bytes(total: int, n_req: int, max_q_tokens: int, n_q_heads: int, n_kv_heads: int) -> int:
+    return int(N.lib.ucmx_kvstar_workspace_bytes(total, n_req, max_q_tokens, n_q_heads, n_kv_heads))
+
+
+def kvstar_scores(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, q_offsets: torch.Tensor, *,
+                  total: int, max_q_tokens: int, slot_ids: Optional[torch.Tensor] = None,
+                  pruned_index: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """KVStar softmax votes of every candidate block.
+
+    reps fp16 [n_slots, M, H, d_pruned]; q fp16 [sum of query tokens, Hq, d_orig]; q_offsets int32 [n_req+1];
+    req_offsets int32 [n_req+1] over slot_ids (or over table rows); pruned_index int64 [n_req, H, d_pruned]."""
+    _need_cuda(reps, req_offsets, q, q_offsets, slot_ids, pruned_index, workspace, out)
+    if reps.dim() != 4 or reps.dtype != torch.float16 or not reps.is_contiguous():
+        raise ValueError("reps must be contiguous fp16 [n_slots, M, n_kv_heads, d_pruned]")
+    if q.dim() != 3 or q.dtype != torch.float16 or not q.is_contiguous():
+        raise ValueError("q must be contiguous fp16 [tokens, n_q_heads, head_dim]")
+    n_slots, M, H, dp = reps.shape
+    n_req = req_offsets.numel() - 1
+    if q_offsets.numel() != n_req + 1:
+        raise ValueError("q_offsets and req_offsets describe different numbers of requests")
+    if pruned_index is not None and (pruned_index.dtype != torch.int64 or not pruned_index.is_contiguous()
+                                     or tuple(pruned_index.shape) != (n_req, H, dp)):
+        raise ValueError("pruned_index must be contiguous int64 [n_req, n_kv_heads, d_pruned]")
+    need = kvstar_workspace_bytes(total, n_req, max_q_tokens, q.shape[1], H)
+    if workspace is None:
+        workspace = torch.empty((need,), dtype=torch.uint8, device=reps.device)
+    if out is None:
+        out = torch.empty((total,), dtype=torch.float32, device=reps.device)
+    st = N.lib.ucmx_kvstar_scores(_ptr(reps), n_slots, M, H, dp, _ptr(_i32(req_offsets, "req_offsets")),
+                                  _ptr(_i32(slot_ids, "slot_ids")), n_req, total, _ptr(q), _ptr(_i32(q_offsets, "q_offsets")),
+                                  max_q_tokens, q.shape[1], q.shape[2], _ptr(pruned_index), _ptr(workspace),
+                                  workspace.numel() * workspace.element_size(), _ptr(out), _stream(reps))
+    N.check("ucmx_kvstar_scores", st, 3 if total and n_req else 0)
+    return out

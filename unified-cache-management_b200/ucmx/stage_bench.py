@@ -9,6 +9,9 @@ bytes (what the kernel must read and write, not what the memory system moved).
   offload   config 4: gather 4096 blocks of K and V of one layer to pinned host memory and scatter
             4096 back, direct (kernel writes host memory) and staged (device compaction + one DMA)
   pool      config 1/2: pooling a whole pool, and the 64-block decode case
+  kvstar    (only when named) KVStar softmax-vote scoring of the 64-request ragged batch: 8 query tokens x 32 heads per
+            request against fp16 representations [64 positions, 8 heads, 32 kept channels] per block (32 KiB); the
+            tensor-core kernel, the row statistics and the vote kernel timed together, and the CUDA-core kernel beside it
   filestore (only when named) file-per-block store: dump 256 blocks x 16 K/V layer slices of 256 KiB (1 GiB) from
             HBM to block files under $UCMX_STORE_DIR (default: the temp dir) and load them back; wall-clock GB/s,
             bounded by that directory's file system; also with one slice per launch (the reference's granularity)
@@ -145,6 +148,41 @@ def main(argv):
         sets = [ids[i * 64:(i + 1) * 64].contiguous() for i in range(16)]
         t = _time(lambda i: ops.pool_blocks(k, sets[i % 16], out_slots=sets[i % 16], out_bf16=reps), iters=16)
         out["pool_mean_64_blocks"] = {"us": t, "gbs": 64 * (shape.slice_bytes + 2048) / t / 1e3}
+    if "kvstar" in which:
+        import os
+        Mp, dp, xq, Hq = 64, 32, 8, shape.n_q_heads
+        nb = batch.total
+        reps = torch.empty((nb, Mp, H, dp), dtype=torch.float16, device=dev)
+        for s in range(0, nb, 2048):
+            e = min(nb, s + 2048)
+            reps[s:e].copy_((torch.randn((e - s, Mp, H, dp), generator=g, device=dev) * 0.6).to(torch.float16))
+        nreq = batch.n_req
+        q = torch.randn((nreq * xq, Hq, D), generator=g, device=dev).to(torch.float16)
+        qoff = (torch.arange(nreq + 1, device=dev) * xq).to(torch.int32)
+        pr = torch.stack([torch.stack([torch.randperm(D, generator=g, device=dev)[:dp] for _ in range(H)])
+                          for _ in range(nreq)]).contiguous()
+        ws = torch.empty((ops.kvstar_workspace_bytes(nb, nreq, xq, Hq, H),), dtype=torch.uint8, device=dev)
+        votes = torch.empty((nb,), dtype=torch.float32, device=dev)
+
+        def run(i):
+            ops.kvstar_scores(reps, off, q, qoff, total=nb, max_q_tokens=xq, slot_ids=table, pruned_index=pr,
+                              workspace=ws, out=votes)
+        t = _time(run, iters=4)
+        nbytes = nb * (Mp * H * dp * 2 + 4)
+        flops = 2.0 * xq * Hq * dp * Mp * nb
+        res = {"us": t, "gbs": nbytes / t / 1e3, "tflops_useful": flops / t / 1e6, "exps_per_us": xq * Hq * Mp * nb / t}
+        ref_votes = votes.clone()
+        os.environ["UCMX_KVSTAR_NO_TC"] = "1"
+        try:
+            t2 = _time(run, iters=1, reps=1)
+        finally:
+            os.environ.pop("UCMX_KVSTAR_NO_TC", None)
+        torch.cuda.synchronize()
+        res["cuda_core_us"] = t2
+        res["max_rel_diff_between_kernels"] = float(((votes - ref_votes).abs() / ref_votes.abs().clamp_min(1e-6)).max())
+        out["kvstar"] = res
+        del reps, ws
+
     if "filestore" in which:
         import os
         import shutil
