@@ -8,10 +8,11 @@
 // This is the one scoring variant that is a real GEMM (x*Hq rows against S columns, half precision),
 // so the dot products run on tcgen05.  The softmax needs the maximum and the sum over all S, which
 // no single CTA sees; it is therefore split:
-//   pass 1 (one tile = one block of M positions): per query row, the block-local maximum m and
-//           p = sum_s exp(score_s - m), 8 bytes per (block, row) instead of M scores;
+//   pass 1 (one tile = one block of M positions): per query row, the block-local maximum m (kept in
+//           units of log2, m = max * log2 e) and p = sum_s 2^(score_s * log2 e - m), 8 bytes per
+//           (block, row) instead of M scores;
 //   pass 2a (per request and row): the global maximum and normaliser from the (m, p) pairs;
-//   pass 2b (per block): votes = sum_rows p * exp(m - m_row) / Z_row.
+//   pass 2b (per block): votes = sum_rows p * 2^(m - m_row) / Z_row.
 // The representations are read exactly once; the (m, p) pairs add about 6 % traffic.
 //
 // Tensor-core mapping of pass 1: accumulator rows (TMEM lanes) are query rows and columns are the M
@@ -33,7 +34,7 @@ namespace {
 
 constexpr int kRows = 128;              // accumulator rows per instruction (TMEM lanes)
 constexpr int kChunkA = kRows * 128;    // one 64-element K chunk of the A operand: 128 rows x 128 B
-constexpr int kTcThreads = 192;         // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kTcThreads = 320;         // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5 and 6-9: two epilogue sets
 constexpr float kLog2e = 1.4426950408889634f;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -72,6 +73,7 @@ struct KsParams {
     int32_t hpg, G, cpg;        // heads per MMA group, groups, 64-element K chunks per group
     uint32_t idesc;
     int32_t stages, tile_bytes;
+    int32_t n_acc;              // accumulator sets in tensor memory (2 or 4)
 };
 
 __device__ __forceinline__ float ex2(float x)
@@ -120,7 +122,10 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+// tcgen05.ld split into issue and wait, so that one load can be in flight while the previous one is
+// consumed.  The wait names the registers as read-write operands: nothing that uses them may be
+// scheduled before it.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -131,11 +136,82 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                   "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]),
+                   "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]),
+                   "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
+}
+
+// 64 consecutive columns of this warp's 32 lanes, valid on return
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
+        "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]),
+          "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]),
+          "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]),
+          "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]),
+          "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+        : "r"(taddr)
+        : "memory");
+}
+
+// One MMA of the fully specialised issue sequence (64 positions per block, 64-element K chunks):
+// operand offsets are immediates, so each instruction costs three integer adds.
+template <int I, int CPG>
+__device__ __forceinline__ void umma_f16_step(uint32_t d_base, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc)
+{
+    constexpr int c = I >> 2, k4 = I & 3, g = c / CPG, kc = c % CPG;
+    constexpr int a_off = (c * kChunkA + k4 * 32) >> 4, b_off = (c * 64 * 128 + k4 * 32) >> 4, d_off = g * 64;
+    constexpr int acc = (kc | k4) ? 1 : 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b32 ta, tb, td;\n\t.reg .b64 da, db;\n\t"
+        "add.u32 ta, %1, %5;\n\t"
+        "add.u32 tb, %2, %6;\n\t"
+        "add.u32 td, %0, %7;\n\t"
+        "mov.b64 da, {ta, %3};\n\t"
+        "mov.b64 db, {tb, %3};\n\t"
+        "setp.ne.b32 p, %8, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %4, p;\n\t}" ::"r"(d_base),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(a_off), "n"(b_off), "n"(d_off), "n"(acc)
+        : "memory");
+}
+template <int CPG>
+__device__ __forceinline__ void umma_f16_block16(uint32_t d_base, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc)
+{
+    umma_f16_step<0, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<1, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<2, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<3, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<4, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<5, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<6, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<7, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<8, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<9, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<10, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<11, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<12, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<13, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<14, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<15, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
 }
 
 struct alignas(8) KsBarriers {
-    uint64_t full[8], empty[8], acc_full[2], acc_empty[2], a_ready;
+    uint64_t full[8], empty[8], acc_full[4], acc_empty[4], a_ready;
     uint32_t tmem_base;
     int32_t abort_flag;
 };
@@ -181,6 +257,8 @@ __device__ void build_a_operand(unsigned char* sA, const KsParams& p, int req, i
 }
 
 // ------------------------------------------------------------------------------ pass 1, tensor cores
+template <int NM>   // 64-element K chunks per head group (1 or 2) of the specialised shape: 64 positions per block and
+                    // heads * d_pruned == 256, whose 16 instructions per block are issued with immediate offsets; else 0
 __global__ void __launch_bounds__(kTcThreads, 1)
 kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
 {
@@ -196,15 +274,15 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
     const int t1 = (int)((int64_t)p.total * (blockIdx.x + 1) / gridDim.x);
     const int my_tiles = t1 - t0;
     const int acc_cols = p.G * p.M;                                      // TMEM columns of one accumulator set
-    const uint32_t tmem_cols = acc_cols * 2 <= 32 ? 32u : acc_cols * 2 <= 64 ? 64u : acc_cols * 2 <= 128 ? 128u
-                               : acc_cols * 2 <= 256 ? 256u : 512u;
+    const int want_cols = acc_cols * p.n_acc;
+    const uint32_t tmem_cols = want_cols <= 32 ? 32u : want_cols <= 64 ? 64u : want_cols <= 128 ? 128u : want_cols <= 256 ? 256u : 512u;
 
     if (tid == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&bars->full[s], 1);
             mbar_init(&bars->empty[s], 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < 4; ++a) {
             mbar_init(&bars->acc_full[a], 1);
             mbar_init(&bars->acc_empty[a], 128);
         }
@@ -230,17 +308,18 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------------ TMA producer
-        for (int it = 0; it < my_tiles; ++it) {
-            const int s = it % p.stages;
-            const uint32_t par = (uint32_t)((it / p.stages) & 1);
+        int s = 0;
+        uint32_t par = 0;
+        int slot_next = my_tiles > 0 ? (p.slot_ids ? __ldg(p.slot_ids + t0) : t0) : 0;
+        for (int it = 0; it < my_tiles; ++it, s = (s + 1 == p.stages ? 0 : s + 1), par ^= (s == 0 ? 1u : 0u)) {
+            const int slot = slot_next;
+            if (it + 1 < my_tiles) slot_next = p.slot_ids ? __ldg(p.slot_ids + t0 + it + 1) : t0 + it + 1;   // in flight during the wait
             if (!mbar_wait(&bars->empty[s], par ^ 1u)) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 5);
                 break;
             }
             if (*(volatile int32_t*)&bars->abort_flag) break;
-            const int t = t0 + it;
-            const int slot = p.slot_ids ? __ldg(p.slot_ids + t) : t;
             unsigned char* dst = sB + (size_t)s * p.tile_bytes;
             mbar_expect_tx(&bars->full[s], (uint32_t)p.tile_bytes);
             // a negative slot reads outside the tensor: TMA fills zeros, the epilogue marks the block empty
@@ -248,12 +327,23 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
+        // One thread issues every instruction, and an M128 N64 K16 instruction occupies the tensor core for
+        // far less time than a lone thread needs for a few dozen dependent instructions; whatever this
+        // loop executes between two MMAs is therefore tensor-core idle time.  For the common shape the
+        // sixteen instructions of a block are issued from immediates (umma_f16_block16), stage and
+        // accumulator indices are counters, and there is a single commit per block.
         const uint32_t a_addr = smem_u32(sA);
         int req = my_tiles > 0 ? find_request(p.offsets, p.n_req, t0) : 0;
         int req_end = my_tiles > 0 ? __ldg(p.offsets + req + 1) : 0;
         uint32_t a_gen = 0;
+        const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(0) >> 32);
+        const uint32_t a_lo = (uint32_t)smem_desc_sw128(a_addr);
+        const uint32_t idesc = p.idesc;
+        const int stages = p.stages, n_acc = p.n_acc, tile_bytes = p.tile_bytes;
+        const uint32_t sB_addr = smem_u32(sB);
+        int s = 0, a = 0;
+        uint32_t full_par = 0, acc_par = 1;
         for (int it = 0; it < my_tiles; ++it) {
-            const int s = it % p.stages, a = it & 1;
             const int t = t0 + it;
             bool ok = true;
             if (t >= req_end) {
@@ -265,46 +355,78 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
                 ok = mbar_wait(&bars->a_ready, a_gen & 1u);
                 ++a_gen;
             }
-            if (!ok || !mbar_wait(&bars->full[s], (uint32_t)((it / p.stages) & 1)) ||
-                !mbar_wait(&bars->acc_empty[a], (uint32_t)(((it >> 1) & 1) ^ 1))) {
+            if (ok) ok = mbar_wait(&bars->full[s], full_par);
+            if (!ok || !mbar_wait(&bars->acc_empty[a], acc_par)) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 5);
                 break;
             }
-            if (*(volatile int32_t*)&bars->abort_flag) break;
             tc_fence_after();
-            const uint32_t b_addr = smem_u32(sB + (size_t)s * p.tile_bytes);
-            for (int g = 0; g < p.G; ++g) {
-                const uint32_t d_addr = tmem_base + (uint32_t)(a * acc_cols + g * p.M);
-                for (int kc = 0; kc < p.cpg; ++kc) {
-                    const int c = g * p.cpg + kc;
+            const uint32_t b_addr = sB_addr + (uint32_t)(s * tile_bytes);
+            const uint32_t d_base = tmem_base + (uint32_t)(a * acc_cols);
+            if constexpr (NM > 0) {
+                umma_f16_block16<NM>(d_base, a_lo, (uint32_t)smem_desc_sw128(b_addr), desc_hi, idesc);
+            } else {
+                for (int g = 0; g < p.G; ++g)
+                    for (int kc = 0; kc < p.cpg; ++kc) {
+                        const int c = g * p.cpg + kc;
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        umma_f16(d_addr, smem_desc_sw128(a_addr + (uint32_t)(c * kChunkA + k4 * 32)),
-                                 smem_desc_sw128(b_addr + (uint32_t)(c * chunk_b + k4 * 32)), p.idesc, (kc | k4) ? 1u : 0u);
-                }
+                        for (int k4 = 0; k4 < 4; ++k4)
+                            umma_f16(d_base + (uint32_t)(g * p.M), smem_desc_sw128(a_addr + (uint32_t)(c * kChunkA + k4 * 32)),
+                                     smem_desc_sw128(b_addr + (uint32_t)(c * chunk_b + k4 * 32)), idesc, (kc | k4) ? 1u : 0u);
+                    }
             }
-            umma_commit(&bars->empty[s]);      // the tile's shared memory is free once these MMAs have read it
+            // one commit per block: the epilogue set that receives it passes the "shared memory is free" half
+            // of the news on to the producer
             umma_commit(&bars->acc_full[a]);
+            if (++s == stages) {
+                s = 0;
+                full_par ^= 1u;
+            }
+            if (++a == n_acc) {
+                a = 0;
+                acc_par ^= 1u;
+            }
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue: block-local softmax pieces
+        // Two sets of four warps take alternate blocks, so each scheduler holds two epilogue warps and
+        // one can compute while the other waits for tensor memory.  With four accumulator sets the MMA
+        // warp runs two blocks ahead of each epilogue set, which then never waits for the tensor core.
+        const int set = (warp - 2) >> 2;
         const int qd = warp & 3;                 // the TMEM lane quarter this warp may read
         const int row = qd * 32 + lane;
         const int hl = row / p.Rp, j = row - hl * p.Rp;
-        int req = my_tiles > 0 ? find_request(p.offsets, p.n_req, t0) : 0;
-        int req_end = my_tiles > 0 ? __ldg(p.offsets + req + 1) : 0;
-        int nrows = my_tiles > 0 ? (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq : 0;
-        for (int it = 0; it < my_tiles; ++it) {
-            const int a = it & 1;
+        int req = 0, req_end = 0, nrows = 0;
+        if (my_tiles > 0) {
+            req = find_request(p.offsets, p.n_req, t0);
+            req_end = __ldg(p.offsets + req + 1);
+            nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
+        }
+        const int cpm = p.M >> 5;                // 32-column chunks per group
+        const int n_loads = p.G * 2 * cpm;       // per group: one sweep for the maximum, one for the exponentials
+        int sfree = set % p.stages;               // stage of this set's current block
+        for (int it = set; it < my_tiles; it += 2) {
+            const int a = it % p.n_acc;
             const int t = t0 + it;
-            if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it >> 1) & 1))) {
+            const int slot = p.slot_ids ? __ldg(p.slot_ids + t) : t;   // needed only at the end: in flight during the wait
+            if (t >= req_end) {
+                while (t >= req_end) {
+                    ++req;
+                    req_end = __ldg(p.offsets + req + 1);
+                }
+                nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
+            }
+            if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it / p.n_acc) & 1))) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 5);
                 break;
             }
             if (*(volatile int32_t*)&bars->abort_flag) break;
             tc_fence_after();
+            if (qd == 0 && lane == 0) mbar_arrive(&bars->empty[sfree]);   // the MMAs have read the block's shared memory
+            sfree += 2;
+            while (sfree >= p.stages) sfree -= p.stages;
             // every MMA issued so far has completed.  If the next block belongs to another request, its
             // A operand is built now, before this block's exponentials, so the tensor core is not kept waiting
             if (it + 1 < my_tiles && t + 1 >= req_end) {
@@ -317,45 +439,102 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
                 fence_proxy_async();
                 mbar_arrive(&bars->a_ready);
             }
-            const int slot = p.slot_ids ? __ldg(p.slot_ids + t) : t;
             const bool live = hl < p.hpg && j < nrows;
-            for (int g = 0; g < p.G; ++g) {
-                const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(a * acc_cols + g * p.M);
-                float mx = -INFINITY;
-                for (int c = 0; c < p.M; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+            const uint32_t tbase = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(a * acc_cols);
+            float2* orow = p.part + (int64_t)t * p.Rtot + hl * p.Rp + j;
+            // The loads of one block form a sequence (group, sweep, chunk); the next one is in flight
+            // while the current one is consumed.
+            float mx = -INFINITY, mb = 0.0f, s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+            // load i of the sequence: group i / (2*cpm), sweep (i / cpm) & 1, chunk i % cpm (counters, no divisions)
+            int ag = 0, ar = 0;                  // position of the next load to issue
+            auto next_address = [&]() {
+                const int c = ar >= cpm ? ar - cpm : ar;
+                const uint32_t adr = tbase + (uint32_t)(ag * p.M + c * 32);
+                if (++ar == 2 * cpm) {
+                    ar = 0;
+                    ++ag;
                 }
-                float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-                for (int c = 0; c < p.M; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c, v);
+                return adr;
+            };
+            int cg = 0, cr = 0;                  // position of the next load to consume
+            auto consume = [&](const uint32_t (&v)[32]) {
+                if (cr < cpm) {
+                    float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        s0 += ex2((__uint_as_float(v[i]) - mx) * kLog2e);
-                        s1 += ex2((__uint_as_float(v[i + 1]) - mx) * kLog2e);
-                        s2 += ex2((__uint_as_float(v[i + 2]) - mx) * kLog2e);
-                        s3 += ex2((__uint_as_float(v[i + 3]) - mx) * kLog2e);
+                    for (int e = 0; e < 32; e += 4) {
+                        m0 = fmaxf(m0, __uint_as_float(v[e]));
+                        m1 = fmaxf(m1, __uint_as_float(v[e + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(v[e + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(v[e + 3]));
+                    }
+                    mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                    if (cr == cpm - 1) mb = mx * kLog2e;        // the block maximum, in units of log2
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        s0 += ex2(fmaf(__uint_as_float(v[e]), kLog2e, -mb));
+                        s1 += ex2(fmaf(__uint_as_float(v[e + 1]), kLog2e, -mb));
+                        s2 += ex2(fmaf(__uint_as_float(v[e + 2]), kLog2e, -mb));
+                        s3 += ex2(fmaf(__uint_as_float(v[e + 3]), kLog2e, -mb));
                     }
                 }
-                if (live) {
-                    const int h = g * p.hpg + hl;
-                    float2 o = make_float2(mx, (s0 + s1) + (s2 + s3));
-                    if (slot < 0) o = make_float2(-INFINITY, 0.0f);
-                    p.part[(int64_t)t * p.Rtot + h * p.Rp + j] = o;
+                if (++cr == 2 * cpm) {
+                    if (live) {
+                        float2 o = make_float2(mb, (s0 + s1) + (s2 + s3));
+                        if (slot < 0) o = make_float2(-INFINITY, 0.0f);
+                        orow[cg * p.hpg * p.Rp] = o;
+                    }
+                    mx = -INFINITY;
+                    s0 = s1 = s2 = s3 = 0.0f;
+                    cr = 0;
+                    ++cg;
                 }
+            };
+            if (p.M == 64) {
+                // one block of one group fits in registers: a single read of tensor memory serves both the
+                // maximum and the exponentials
+                for (int g = 0; g < p.G; ++g) {
+                    uint32_t v[64];
+                    tmem_ld64(tbase + (uint32_t)(g * 64), v);
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int e = 0; e < 64; e += 4) {
+                        m0 = fmaxf(m0, __uint_as_float(v[e]));
+                        m1 = fmaxf(m1, __uint_as_float(v[e + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(v[e + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(v[e + 3]));
+                    }
+                    const float nb = -(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * kLog2e);
+                    float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 64; e += 4) {
+                        q0 += ex2(fmaf(__uint_as_float(v[e]), kLog2e, nb));
+                        q1 += ex2(fmaf(__uint_as_float(v[e + 1]), kLog2e, nb));
+                        q2 += ex2(fmaf(__uint_as_float(v[e + 2]), kLog2e, nb));
+                        q3 += ex2(fmaf(__uint_as_float(v[e + 3]), kLog2e, nb));
+                    }
+                    if (live) {
+                        float2 o = make_float2(-nb, (q0 + q1) + (q2 + q3));
+                        if (slot < 0) o = make_float2(-INFINITY, 0.0f);
+                        orow[g * p.hpg * p.Rp] = o;
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&bars->acc_empty[a]);
+                continue;
+            }
+            uint32_t va[32], vb[32];
+            tmem_ld32_issue(next_address(), va);
+            for (int i = 0; i < n_loads; i += 2) {
+                tmem_ld_wait(va);
+                tmem_ld32_issue(next_address(), vb);
+                consume(va);
+                tmem_ld_wait(vb);
+                if (i + 2 < n_loads) tmem_ld32_issue(next_address(), va);
+                consume(vb);
             }
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[a]);
-            if (t + 1 >= req_end && it + 1 < my_tiles) {
-                while (t + 1 >= req_end) {
-                    ++req;
-                    req_end = __ldg(p.offsets + req + 1);
-                }
-                nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
-            }
         }
     }
 
@@ -403,9 +582,9 @@ kvstar_partial_generic_kernel(KsParams p)
                         acc = fmaf(__half2float(__ushort_as_half(qb)), __half2float(__ushort_as_half(kv[d])), acc);
                     }
                     if (pass == 0) mx = fmaxf(mx, acc);
-                    else sum += ex2((acc - mx) * kLog2e);
+                    else sum += ex2(fmaf(acc, kLog2e, -mx * kLog2e));
                 }
-                if (pass == 1) o = make_float2(mx, sum);
+                if (pass == 1) o = make_float2(mx * kLog2e, sum);
             }
         }
         p.part[(int64_t)t * p.Rtot + h * p.Rp + xq * p.gq + gg] = o;
@@ -426,14 +605,22 @@ kvstar_stats_kernel(KsParams p)
     const bool live = rowid < p.Rtot && (rowid % p.Rp) < nrows;
     float m = -INFINITY, z = 0.0f;
     if (live) {
-        for (int b = b0 + warp; b < b1; b += 8) {
-            const float2 v = __ldcg(p.part + (int64_t)b * p.Rtot + rowid);
-            if (v.x > m) {
-                z = z * ex2((m - v.x) * kLog2e) + v.y;     // m == -inf: z is 0 and ex2(-inf) is 0
-                m = v.x;
-            } else if (v.x > -INFINITY) {
-                z += v.y * ex2((v.x - m) * kLog2e);
-            }
+        // eight independent loads per step, then one branch-free merge: the loop is bound by memory
+        // latency, so the loads must not wait for the running pair
+        for (int b = b0 + warp * 8; b < b1; b += 64) {
+            float2 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = b + u < b1 ? __ldcg(p.part + (int64_t)(b + u) * p.Rtot + rowid) : make_float2(-INFINITY, 0.0f);
+            float mn = m;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) mn = fmaxf(mn, v[u].x);
+            const float ms = mn == -INFINITY ? 0.0f : mn;      // keeps (-inf) - (-inf) out of the exponent
+            float acc = z * ex2(m - ms);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += v[u].y * ex2(v[u].x - ms);
+            z = acc;
+            m = mn;
         }
     }
     sm[warp][lane] = make_float2(m, z);
@@ -443,7 +630,7 @@ kvstar_stats_kernel(KsParams p)
         for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sm[w][lane].x);
         float zz = 0.0f;
         for (int w = 0; w < 8; ++w)
-            if (sm[w][lane].x > -INFINITY) zz += sm[w][lane].y * ex2((sm[w][lane].x - mm) * kLog2e);
+            if (sm[w][lane].x > -INFINITY) zz += sm[w][lane].y * ex2(sm[w][lane].x - mm);
         p.stats[(int64_t)req * p.Rtot + rowid] = make_float2(mm, zz > 0.0f ? 1.0f / zz : 0.0f);
     }
 }
@@ -453,19 +640,46 @@ kvstar_stats_kernel(KsParams p)
 __global__ void __launch_bounds__(256)
 kvstar_vote_kernel(KsParams p)
 {
+    __shared__ int s_off[1025], s_q[1025];
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const bool cached = p.n_req <= 1024;       // request boundaries and query counts, searched in shared memory
+    if (cached)
+        for (int i = threadIdx.x; i <= p.n_req; i += blockDim.x) {
+            s_off[i] = __ldg(p.offsets + i);
+            s_q[i] = __ldg(p.q_offsets + i);
+        }
+    __syncthreads();
     if (t >= p.total) return;
-    const int req = find_request(p.offsets, p.n_req, t);
-    const int nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
+    int req, nrows;
+    if (cached) {
+        int lo = 0, hi = p.n_req;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= t) lo = mid; else hi = mid;
+        }
+        req = lo;
+        nrows = (s_q[req + 1] - s_q[req]) * p.gq;
+    } else {
+        req = find_request(p.offsets, p.n_req, t);
+        nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
+    }
     const float2* pp = p.part + (int64_t)t * p.Rtot;
     const float2* st = p.stats + (int64_t)req * p.Rtot;
     float acc = 0.0f;
-    for (int r = lane; r < p.Rtot; r += 32) {
-        if ((r % p.Rp) >= nrows) continue;
-        const float2 v = __ldcg(pp + r);
-        const float2 s = __ldcg(st + r);
-        if (v.x > -INFINITY) acc += v.y * ex2((v.x - s.x) * kLog2e) * s.y;
+    for (int r0 = lane; r0 < p.Rtot; r0 += 256) {
+        // eight independent pairs of loads before the first use
+        float2 v[8], sr[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int r = r0 + u * 32;
+            const bool on = r < p.Rtot && (r % p.Rp) < nrows;
+            v[u] = on ? __ldcg(pp + r) : make_float2(-INFINITY, 0.0f);
+            sr[u] = on ? __ldcg(st + r) : make_float2(0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (v[u].x > -INFINITY) acc += v[u].y * ex2(v[u].x - sr[u].x) * sr[u].y;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -622,6 +836,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
         p.G = H / p.hpg;
         p.cpg = p.hpg * d_pruned / 64;
         tc = p.G * M <= 256;                         // two accumulator sets must fit the 512 TMEM columns
+        p.n_acc = p.G * M <= 128 ? 4 : 2;
     }
     if (tc) {
         p.idesc = (1u << 4) | ((uint32_t)(M >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);   // D fp32, A and B half, K-major
@@ -642,10 +857,12 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
                                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r == CUDA_SUCCESS) {
                 const size_t smem = 1024 + a_bytes + (size_t)p.stages * p.tile_bytes + sizeof(KsBarriers) + 64;
-                UCMX_CUDA(cudaFuncSetAttribute(kvstar_partial_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                 int grid = sm_count();
                 if (grid > total) grid = total;
-                kvstar_partial_tc_kernel<<<grid, kTcThreads, smem, st>>>(tmap, p);
+                const bool special = M == 64 && C == 256 && (p.cpg == 1 || p.cpg == 2);
+                auto kern = !special ? kvstar_partial_tc_kernel<0> : p.cpg == 1 ? kvstar_partial_tc_kernel<1> : kvstar_partial_tc_kernel<2>;
+                UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                kern<<<grid, kTcThreads, smem, st>>>(tmap, p);
                 UCMX_LAUNCH_CHECK("kvstar_partial_tc_kernel");
             } else {
                 tc = false;
