@@ -129,3 +129,26 @@ def test_block_representations_bit_exact(oracle, merge):
     want = oracle.kvstar_block_repre(k, ids, None, merge)
     got = table[slots.long()].cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
     np.testing.assert_array_equal(got, want)
+
+
+def test_kvstar_retrieve_module_interface(oracle):
+    """The call sequence of ucm/sparse/kvstar/multistep.py: submit, wait, read the result."""
+    from ucmx import kvstar as kvstar_retrieve
+    q, reps, pruned, k = H.case_kvstar("llama")
+    tq = torch.from_numpy(q.view(np.int16).copy()).view(torch.float16)            # host tensors, as the reference passes
+    tr = torch.from_numpy(reps.view(np.int16).copy()).view(torch.float16)
+    tid = kvstar_retrieve.AsyncRetrieveByCPU(tq, tr, torch.from_numpy(pruned), k, 7, kvstar_retrieve.CPU)
+    assert kvstar_retrieve.Wait(tid) == 0
+    res = kvstar_retrieve.GetTaskResult(tid)
+    assert res["status"] == "SUCCESS" and len(res["data"]) == k
+    np.testing.assert_array_equal(np.sort(res["data"]), G["llama_avx2"])
+    # best first, like the reference's scalar build
+    np.testing.assert_array_equal(res["data"], G["llama_rank"][:k])
+    assert kvstar_retrieve.GetTaskResult(10 ** 9) is None
+    tid0 = kvstar_retrieve.AsyncRetrieveByCPU(tq, tr, torch.from_numpy(pruned), 0)
+    kvstar_retrieve.Wait(tid0)
+    assert kvstar_retrieve.GetTaskResult(tid0)["data"] == []
+    with pytest.raises(RuntimeError, match="3D"):
+        kvstar_retrieve.AsyncRetrieveByCPU(tq[0], tr, None, k)
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        kvstar_retrieve.AsyncRetrieveByCPU(tq, tr, torch.from_numpy(pruned[:, :8].copy()), k)
