@@ -39,8 +39,10 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes per launch of the dominant kernel (xfer_bulk_kernel gathering one layer's selected K and
-# V blocks) read from an ncu capture; see profiles/.  None until a capture has been summarised.
-NCU_GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# V blocks) over its algorithmic bytes, from a one-pass ncu capture of this benchmark at full size
+# (profiles/xfer_bulk_gather_full_size_traffic.md): reads 955.28 MB = the payload, writes 895.5 MB (the
+# last ~57 MB are still dirty in L2 when the kernel ends), against 2 x 955.25 MB.
+NCU_GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.969
 
 
 def env_int(name, default):
