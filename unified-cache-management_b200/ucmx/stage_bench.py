@@ -12,6 +12,9 @@ bytes (what the kernel must read and write, not what the memory system moved).
   kvstar    (only when named) KVStar softmax-vote scoring of the 64-request ragged batch: 8 query tokens x 32 heads per
             request against fp16 representations [64 positions, 8 heads, 32 kept channels] per block (32 KiB); the
             tensor-core kernel, the row statistics and the vote kernel timed together, and the CUDA-core kernel beside it
+  connector (only when named) prefix-cache dump and load of 256 blocks x 32 layers (4 GiB) through the host-memory store:
+            this connector's one address table per layer against the reference's call pattern (one dump per block,
+            layer and K/V with a tensor view; one K and one V load per request and layer); wall-clock GB/s
   filestore (only when named) file-per-block store: dump 256 blocks x 16 K/V layer slices of 256 KiB (1 GiB) from
             HBM to block files under $UCMX_STORE_DIR (default: the temp dir) and load them back; wall-clock GB/s,
             bounded by that directory's file system; also with one slice per launch (the reference's granularity)
@@ -182,6 +185,75 @@ def main(argv):
         res["max_rel_diff_between_kernels"] = float(((votes - ref_votes).abs() / ref_votes.abs().clamp_min(1e-6)).max())
         out["kvstar"] = res
         del reps, ws
+
+    if "connector" in which:
+        import time
+        import types
+
+        from .connector import ReqMeta, UCConnectorV1Metadata, UnifiedCacheConnectorV1
+        Lc, nbc, nblk = 32, 320, 256
+        mc = types.SimpleNamespace(dtype=torch.bfloat16, is_deepseek_mla=False, get_num_layers=lambda pc: Lc,
+                                   get_num_kv_heads=lambda pc: H, get_head_size=lambda: D)
+        cfg = types.SimpleNamespace(
+            model_config=mc, parallel_config=types.SimpleNamespace(tensor_parallel_size=1),
+            cache_config=types.SimpleNamespace(block_size=T),
+            kv_transfer_config=types.SimpleNamespace(kv_role="kv_both", kv_connector_extra_config={
+                "ucm_connector_name": "UcmDramStore", "ucm_connector_config": {"max_cache_size": 5 << 30}}))
+        kvc = {f"model.layers.{l}.attn": torch.empty((2, nbc, T, H, D), dtype=torch.bfloat16, device=dev).normal_(generator=g)
+               for l in range(Lc)}
+        hs = [f"{i:032x}" for i in range(nblk)]
+        ids = torch.randperm(nbc, generator=g, device=dev)[:nblk].tolist()
+        reqs = [ReqMeta(f"r{r}", dump_blocks=list(zip(hs[r * 32:(r + 1) * 32], ids[r * 32:(r + 1) * 32]))) for r in range(8)]
+        nbytes = nblk * Lc * 2 * shape.slice_bytes
+        res = {"bytes": nbytes}
+        for name in ("table_per_layer", "reference_call_pattern"):
+            conn = UnifiedCacheConnectorV1(cfg, "worker", rank=0)
+            conn.register_kv_caches(kvc)
+            conn.bind_connector_metadata(UCConnectorV1Metadata(reqs))
+            conn.connector._ensure_slab()           # page-locking 5 GiB is a one-time cost of the store, not of a dump
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if name == "table_per_layer":
+                for lname, layer in kvc.items():
+                    conn.save_kv_layer(lname, layer)
+                ok = conn.wait_for_save()
+            else:
+                tasks = []
+                for lname, layer in kvc.items():
+                    for r in reqs:
+                        tensors, offsets = conn.get_tensor_and_offset_layerwise([b[1] for b in r.dump_blocks], layer, lname)
+                        torch.cuda.current_stream().synchronize()
+                        for bid, o, tns in zip([b[0] for b in r.dump_blocks] * 2, offsets, tensors):
+                            tasks.append(conn.connector.dump([bid], [o], [tns]))
+                ok = all(conn.connector.wait(tk) == 0 for tk in tasks)
+            t1 = time.perf_counter()
+            conn.connector.commit(hs, True)
+            # load everything back into other slots
+            dst = torch.randperm(nbc, generator=g, device=dev)[:nblk].tolist()
+            lreqs = [ReqMeta(f"l{r}", load_blocks=list(zip(hs[r * 32:(r + 1) * 32], dst[r * 32:(r + 1) * 32]))) for r in range(8)]
+            conn.bind_connector_metadata(UCConnectorV1Metadata(lreqs))
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            if name == "table_per_layer":
+                conn.start_load_kv()
+                for lname in kvc:
+                    conn.wait_for_layer_load(lname)
+            else:
+                tasks = []
+                for r in lreqs:
+                    for lname, layer in kvc.items():
+                        tensors, offsets = conn.get_tensor_and_offset_layerwise([b[1] for b in r.load_blocks], layer, lname)
+                        n = len(r.load_blocks)
+                        tasks.append(conn.connector.load([b[0] for b in r.load_blocks], offsets[:n], tensors[:n]))
+                        tasks.append(conn.connector.load([b[0] for b in r.load_blocks], offsets[n:], tensors[n:]))
+                assert all(conn.connector.wait(tk) == 0 for tk in tasks)
+            torch.cuda.synchronize()
+            t3 = time.perf_counter()
+            res[name] = {"dump_ms": (t1 - t0) * 1e3, "dump_gbs": nbytes / (t1 - t0) / 1e9, "load_ms": (t3 - t2) * 1e3,
+                         "load_gbs": nbytes / (t3 - t2) / 1e9, "ok": bool(ok)}
+            conn.connector.close()
+        out["connector"] = res
+        del kvc
 
     if "filestore" in which:
         import os
