@@ -67,3 +67,40 @@ def test_tensor_core_and_cuda_core_kernels_agree_on_a_large_batch():
         del os.environ["UCMX_HASH_NO_TC"]
     assert torch.equal(a, b)
     assert 0.45 < float(torch.tensor(np.unpackbits(a[:10000].cpu().numpy())).float().mean()) < 0.55
+
+
+def test_zero_and_tiny_vectors(oracle):
+    """Rows of zeros (every projection is exactly zero: all bits 0), rows whose squares underflow, and enough
+    of them in one tile to overflow the fixer warp's queue."""
+    from ucmx import ops
+    rng = np.random.default_rng(104)
+    n = 128 * 20
+    x = H.bf16_to_f32(H.randn_bf16(rng, (n, 128)))
+    x[5:300] = 0.0
+    x[300:420] *= 1e-24
+    x[420:500] *= 1e-36
+    x[1000, :64] = 0.0
+    w16 = H.randn_bf16(rng, (128, 128), 2.0)
+    x16 = H.f32_to_bf16(x)
+    want = oracle.hash_encode(x16, w16)
+    got = ops.hash_encode(dev_bf16(x16), dev_bf16(w16)).cpu().numpy()
+    assert np.array_equal(got, want)
+    assert not want[5:300].any()
+
+
+def test_repeated_runs_are_identical():
+    """The code words settled by the fixer warp and those stored by the epilogue never overlap: a dozen runs of a
+    batch large enough to keep every SM busy give the same bytes as the CUDA-core kernel."""
+    from ucmx import ops
+    g = torch.Generator(device=DEV).manual_seed(105)
+    x = torch.randn((400_000, 128), generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((128, 128), generator=g, device=DEV) * 2).to(torch.bfloat16)
+    os.environ["UCMX_HASH_NO_TC"] = "1"
+    try:
+        ref = ops.hash_encode(x, w)
+    finally:
+        del os.environ["UCMX_HASH_NO_TC"]
+    for rep in range(12):
+        got = ops.hash_encode(x, w)
+        bad = (got.view(torch.int32) != ref.view(torch.int32)).nonzero()
+        assert bad.numel() == 0, f"run {rep}: {bad.shape[0]} words differ, first (row, word): {bad[:8].tolist()}"

@@ -11,8 +11,10 @@
 // exact sum S by at most a few 2^-18 * sum|x_d w_d|, so wherever |acc| is clearly above that they
 // have the sign of S and agree.  The epilogue therefore trusts the tensor-core sign only when
 // |acc| > 2^-13 * |x| * |w_j| (Cauchy-Schwarz bounds sum|x_d w_d|; 2^-13 leaves a wide margin) and
-// recomputes the few remaining bits (about one per thousand for Gaussian data) with the exact chain
-// from the tile still sitting in shared memory.
+// hands the few remaining bits (about one per thousand for Gaussian data) to a fixer warp, which runs
+// the exact chain from the tile still sitting in shared memory and patches the stored code.  A chain is
+// 128 dependent multiply-adds: run by the epilogue warps themselves it cost a quarter of the kernel's
+// time (plus as much again for pooling the work); on a warp of its own it overlaps with everything else.
 #include <cuda.h>
 
 #include <mutex>
@@ -28,9 +30,10 @@ constexpr int kBits = 128;
 constexpr int kStagesA = 2;                       // with two CTAs per SM that is four tiles in flight per SM
 constexpr int kHalfBytes = kTileM * 128;          // one 64-element K half of a tile: 128 rows x 128 B
 constexpr int kTileBytes = 2 * kHalfBytes;        // 32 KiB
-constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kThreads = 192;                     // warp 0: exact-chain fixer, warp 1: TMA + MMA issue and TMEM owner, warps 2-5: epilogue
 constexpr float kTau = 1.0f / 8192.0f;            // 2^-13
-constexpr int kFallbackSlots = 512;               // doubtful bits one warp pools per tile (about 5 are typical)
+constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
+constexpr int kFixSlots = 256;                    // code words with doubtful bits the fixer warp takes per tile (about 20 are typical)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -134,11 +137,41 @@ __device__ __forceinline__ uint32_t sw_offset(int row, int k)
     return (uint32_t)(half * kHalfBytes + row * 128 + ((c ^ (row & 7)) << 4) + ((k & 7) << 1));
 }
 
+// output row of tile row m, or -1 when that vector's code is not stored
+__device__ __forceinline__ int64_t out_row_of(const TcParams& p, int64_t tile, int m)
+{
+    if (p.paged) {
+        const int64_t blk = tile / p.tiles_per_block;
+        const int sub = (int)(tile - blk * p.tiles_per_block);
+        const int id = __ldg(p.ids + blk);
+        const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
+        const int t = sub * (kTileM / p.H) + m / p.H, h = m % p.H;
+        if (id < 0 || slot < 0) return -1;
+        return p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
+    }
+    const int64_t v = tile * kTileM + m;
+    return v < p.n_vec ? v : -1;
+}
+
 struct alignas(8) Barriers {
-    uint64_t full[kStagesA], empty[kStagesA], acc_full[2], acc_empty[2];
+    uint64_t full[kStagesA], empty[kStagesA], acc_full[2], acc_empty[2], fix_ready[kStagesA];
     uint32_t tmem_base;
     int32_t abort_flag;
+    uint32_t fix_n[kStagesA];   // code words queued for the fixer, per stage
 };
+
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity)   // one non-blocking poll
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
@@ -152,6 +185,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // 4 epilogue warps x kFallbackSlots
     uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kFallbackSlots);
     uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kFallbackSlots);   // max_j |w_j|
+    uint4* fixq = reinterpret_cast<uint4*>(wmax_bits + 4);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -159,7 +193,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     if (tid == 0) {
         for (int s = 0; s < kStagesA; ++s) {
             mbar_init(&bars->full[s], 1);
-            mbar_init(&bars->empty[s], 128);
+            mbar_init(&bars->empty[s], 1);          // the fixer lets a stage go
+            mbar_init(&bars->fix_ready[s], 128);    // every epilogue thread has queued its doubtful words and stored the others
+            bars->fix_n[s] = 0;
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&bars->acc_full[a], 1);
@@ -206,55 +242,155 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     const int64_t first = blockIdx.x, stride = gridDim.x;
     const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + stride - 1) / stride : 0;
 
-    if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------------ TMA producer
+    if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ TMA and MMA issue, one thread
+        // Both jobs are a few instructions per tile.  The thread polls without blocking: whichever of "a
+        // stage is free -> load the next tile" and "a tile has landed and an accumulator is free -> issue
+        // its MMAs" is possible is done; neither ever waits for the other.
+        const uint32_t b_addr = smem_u32(sB);
+        int64_t ld = 0, mm = 0;
+        uint32_t idle = 0;
+        while (mm < my_tiles) {
+            bool progress = false;
+            if (ld < my_tiles) {
+                const int s = (int)(ld % kStagesA);
+                if (mbar_test(&bars->empty[s], (uint32_t)(((ld / kStagesA) & 1) ^ 1))) {
+                    const int64_t tile = first + ld * stride;
+                    unsigned char* dst = sA + (size_t)s * kTileBytes;
+                    mbar_expect_tx(&bars->full[s], kTileBytes);
+                    if (p.paged) {
+                        const int64_t blk = tile / p.tiles_per_block;
+                        const int sub = (int)(tile - blk * p.tiles_per_block);
+                        const int id = __ldg(p.ids + blk);
+                        const int t0 = sub * (kTileM / p.H);
+                        // a negative id reads outside the tensor: TMA fills zeros, the tile's codes are not stored
+                        tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
+                        tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
+                    } else {
+                        const int row0 = (int)(tile * kTileM);
+                        tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
+                        tma_load_2d(dst + kHalfBytes, &tmap, 64, row0, &bars->full[s]);
+                    }
+                    ++ld;
+                    progress = true;
+                }
+            }
+            if (mm < ld) {
+                const int s = (int)(mm % kStagesA), a = (int)(mm & 1);
+                if (mbar_test(&bars->full[s], (uint32_t)((mm / kStagesA) & 1)) &&
+                    mbar_test(&bars->acc_empty[a], (uint32_t)(((mm >> 1) & 1) ^ 1))) {
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileBytes);
+#pragma unroll
+                    for (int k = 0; k < kDim / 16; ++k) {
+                        const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
+                        umma_bf16(tmem_base + (uint32_t)a * kBits, smem_desc_sw128(a_addr + koff), smem_desc_sw128(b_addr + koff),
+                                  k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&bars->acc_full[a]);   // arrives when the eight MMAs above have completed
+                    ++mm;
+                    progress = true;
+                }
+            }
+            if (progress) {
+                idle = 0;
+            } else if (++idle > (1u << 24) || *(volatile int32_t*)&bars->abort_flag) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 1);
+                break;
+            }
+        }
+    } else if (warp == 0) {
+        // ------------------------------------------------------------------ fixer: exact chains for the queued bits
+        // The fp32 FMA chain over d, in order, from the tile and the weights in shared memory; one lane per
+        // queued code word (usually one doubtful bit in it).  The lane settles the bits and stores the word.
+        // The stage is held until the vector is in registers, and with two stages that delay goes straight
+        // into the load of the tile after next: what does not depend on the queue (where the tile's codes
+        // go) is worked out while waiting.
         for (int64_t it = 0; it < my_tiles; ++it) {
             const int s = (int)(it % kStagesA);
             const uint32_t par = (uint32_t)((it / kStagesA) & 1);
-            if (!mbar_wait(&bars->empty[s], par ^ 1u)) {
-                bars->abort_flag = 1;
-                if (p.err) atomicExch(p.err, 1);
-                break;
-            }
-            if (*(volatile int32_t*)&bars->abort_flag) break;
             const int64_t tile = first + it * stride;
-            unsigned char* dst = sA + (size_t)s * kTileBytes;
-            mbar_expect_tx(&bars->full[s], kTileBytes);
+            int64_t blk = 0, slot = 0;
+            int sub = 0, id = 0;
             if (p.paged) {
-                const int64_t blk = tile / p.tiles_per_block;
-                const int sub = (int)(tile - blk * p.tiles_per_block);
-                const int id = __ldg(p.ids + blk);
-                const int t0 = sub * (kTileM / p.H);
-                // a negative id reads outside the tensor: TMA fills zeros, the tile's codes are not stored
-                tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
-                tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
-            } else {
-                const int row0 = (int)(tile * kTileM);
-                tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
-                tma_load_2d(dst + kHalfBytes, &tmap, 64, row0, &bars->full[s]);
+                blk = tile / p.tiles_per_block;
+                sub = (int)(tile - blk * p.tiles_per_block);
+                id = __ldg(p.ids + blk);
+                slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
             }
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------------ MMA issuer
-        const uint32_t b_addr = smem_u32(sB);
-        for (int64_t it = 0; it < my_tiles; ++it) {
-            const int s = (int)(it % kStagesA), a = (int)(it & 1);
-            if (!mbar_wait(&bars->full[s], (uint32_t)((it / kStagesA) & 1)) ||
-                !mbar_wait(&bars->acc_empty[a], (uint32_t)(((it >> 1) & 1) ^ 1))) {
+            if (!mbar_wait(&bars->fix_ready[s], par)) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 1);
                 break;
             }
             if (*(volatile int32_t*)&bars->abort_flag) break;
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileBytes);
-#pragma unroll
-            for (int k = 0; k < kDim / 16; ++k) {
-                const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
-                umma_bf16(tmem_base + (uint32_t)a * kBits, smem_desc_sw128(a_addr + koff), smem_desc_sw128(b_addr + koff),
-                          k > 0 ? 1u : 0u);
+            (void)mbar_wait(&bars->full[s], par);              // already complete: acquires the TMA-written tile
+            const int n = (int)min(*(volatile uint32_t*)&bars->fix_n[s], (uint32_t)kFixSlots);
+            const unsigned char* xa = sA + (size_t)s * kTileBytes;
+            const uint4* q = fixq + s * kFixSlots;
+            // Passes of 32 queued words.  Once the vectors of the last pass are in registers nothing here needs
+            // the tile any more (the weights stay in shared memory), so the stage is released before the chains run.
+            const int passes = (n + 31) >> 5;
+            if (passes == 0) {
+                __syncwarp();                                  // every lane has read the count before it is reset
+                if (lane == 0) {
+                    bars->fix_n[s] = 0;
+                    mbar_arrive(&bars->empty[s]);
+                }
             }
-            umma_commit(&bars->acc_full[a]);   // arrives when the eight MMAs above have completed
+            for (int ps = 0; ps < passes; ++ps) {
+                const int e = ps * 32 + lane;
+                const uint4 ent = e < n ? q[e] : make_uint4(0xffffffffu, 0u, 0u, 0u);   // x = ~0: nothing here
+                const bool live = ent.x != 0xffffffffu;
+                const int row = (int)(ent.x & 127u), cw = (int)((ent.x >> 8) & 3u);
+                uint4 xv[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) xv[c] = *reinterpret_cast<const uint4*>(xa + sw_offset(row, c * 8));
+                if (ps == passes - 1) {
+                    // The loads must have delivered before the stage goes.  Only an instruction that reads the
+                    // registers makes a lane wait for them, so every lane folds its vector into one word and the
+                    // warp votes on it (the vote is also the point where the lanes meet).
+                    uint32_t fold = 0;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) fold ^= xv[c].x ^ xv[c].y ^ xv[c].z ^ xv[c].w;
+                    const unsigned seen = __ballot_sync(0xffffffffu, fold != 0x9e3779b9u);
+                    if (lane == 0 && seen != 0xdeadbeefu) {
+                        bars->fix_n[s] = 0;
+                        mbar_arrive(&bars->empty[s]);          // the stage may be loaded again
+                    }
+                }
+                if (!live) continue;
+                uint32_t word = ent.z, pend = ent.y;
+                while (pend) {
+                    const int j = __ffs(pend) - 1;
+                    pend &= pend - 1;
+                    const int col = cw * 32 + j;
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const uint4 wv = *reinterpret_cast<const uint4*>(sB + sw_offset(col, c * 8));
+                        acc = fmaf(bf16lo(xv[c].x), bf16lo(wv.x), acc);
+                        acc = fmaf(bf16hi(xv[c].x), bf16hi(wv.x), acc);
+                        acc = fmaf(bf16lo(xv[c].y), bf16lo(wv.y), acc);
+                        acc = fmaf(bf16hi(xv[c].y), bf16hi(wv.y), acc);
+                        acc = fmaf(bf16lo(xv[c].z), bf16lo(wv.z), acc);
+                        acc = fmaf(bf16hi(xv[c].z), bf16hi(wv.z), acc);
+                        acc = fmaf(bf16lo(xv[c].w), bf16lo(wv.w), acc);
+                        acc = fmaf(bf16hi(xv[c].w), bf16hi(wv.w), acc);
+                    }
+                    word = (word & ~(1u << j)) | ((acc > 0.0f ? 1u : 0u) << j);
+                }
+                int64_t orow;
+                if (p.paged) {
+                    const int t = sub * (kTileM / p.H) + row / p.H, h = row % p.H;
+                    orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
+                } else {
+                    const int64_t v = tile * kTileM + row;
+                    orow = v < p.n_vec ? v : -1;
+                }
+                if (orow >= 0) reinterpret_cast<uint32_t*>(p.out + orow * 16)[cw] = word;
+            }
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue: signs, margin test, exact fallback
@@ -293,7 +429,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 for (int g = 0; g < 8; ++g) x2 += __low2float(part[g]) + __high2float(part[g]);
             }
             // one threshold for the whole row: |acc| <= tau |x| max_j|w_j| (a little wider than per column, no table look-up)
-            const float thr = kTau * sqrtf(x2 * 1.05f) * 1.0001f * __uint_as_float(*wmax_bits);
+            // a row so small that its squares underflow in bf16 gets no trusted bits at all (threshold = infinity)
+            const float thr = x2 >= 1e-30f ? kTau * sqrtf(x2 * 1.05f) * 1.0001f * __uint_as_float(*wmax_bits) : INFINITY;
             uint32_t code[4], doubt[4];
 #pragma unroll
             for (int cw = 0; cw < 4; ++cw) {
@@ -329,7 +466,38 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             // of one bit cannot be split, but different bits can go to different lanes: the warp pools
             // its (row, column) pairs in shared memory and deals them out, so a tile with a handful of
             // doubtful bits costs one chain's latency instead of one per bit of the unluckiest lane.
+            // A 32-bit word of the code that holds doubtful bits is not stored here: it goes, with the mask of
+            // those bits, to the fixer, which stores it once they are settled.  Every word thus has one writer.
+            bool queued = false;
             {
+                const int wmine = (doubt[0] != 0) + (doubt[1] != 0) + (doubt[2] != 0) + (doubt[3] != 0);
+                int wincl = wmine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, wincl, o);
+                    if (lane >= o) wincl += v;
+                }
+                const int wtotal = __shfl_sync(0xffffffffu, wincl, 31);
+                if (wtotal > 0) {
+                    // one reservation per warp in the stage's queue
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(&bars->fix_n[s], (uint32_t)wtotal);
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    uint4* q = fixq + s * kFixSlots;
+                    if (base + (uint32_t)wtotal > (uint32_t)kFixSlots) {
+                        // no room: what the reservation covers below the capacity is marked empty and this warp
+                        // settles its bits itself (below)
+                        for (uint32_t e = base + (uint32_t)lane; e < (uint32_t)kFixSlots; e += 32) q[e] = make_uint4(0xffffffffu, 0u, 0u, 0u);
+                    } else {
+                        queued = true;
+                        uint32_t pos = base + (uint32_t)(wincl - wmine);
+#pragma unroll
+                        for (int cw = 0; cw < 4; ++cw)
+                            if (doubt[cw]) q[pos++] = make_uint4((uint32_t)m | ((uint32_t)cw << 8), doubt[cw], code[cw], 0u);
+                    }
+                }
+            }
+            if (!queued) {
                 const int mine = __popc(doubt[0]) + __popc(doubt[1]) + __popc(doubt[2]) + __popc(doubt[3]);
                 int incl = mine;
 #pragma unroll
@@ -401,24 +569,20 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     __syncwarp();
                 }
             }
-            // this row's share of the tile is consumed: release the stage to the producer
-            mbar_arrive(&bars->empty[s]);
-            // store 16 bytes of code
-            const int64_t tile = first + it * stride;
-            int64_t orow = -1;
-            if (p.paged) {
-                const int64_t blk = tile / p.tiles_per_block;
-                const int sub = (int)(tile - blk * p.tiles_per_block);
-                const int id = __ldg(p.ids + blk);
-                const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
-                const int t = sub * (kTileM / p.H) + m / p.H, h = m % p.H;
-                if (id >= 0 && slot >= 0)
-                    orow = p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
-            } else {
-                const int64_t v = tile * kTileM + m;
-                if (v < p.n_vec) orow = v;
+            // store the settled words of the code, then tell the fixer, which releases the stage when it has
+            // what it needs of the tile
+            const int64_t orow = out_row_of(p, first + it * stride, m);
+            if (orow >= 0) {
+                if (queued && (doubt[0] | doubt[1] | doubt[2] | doubt[3])) {
+                    uint32_t* o32 = reinterpret_cast<uint32_t*>(p.out + orow * 16);
+#pragma unroll
+                    for (int cw = 0; cw < 4; ++cw)
+                        if (!doubt[cw]) o32[cw] = code[cw];
+                } else {
+                    *reinterpret_cast<uint4*>(p.out + orow * 16) = make_uint4(code[0], code[1], code[2], code[3]);
+                }
             }
-            if (orow >= 0) *reinterpret_cast<uint4*>(p.out + orow * 16) = make_uint4(code[0], code[1], code[2], code[3]);
+            mbar_arrive(&bars->fix_ready[s]);
         }
     }
 
@@ -478,7 +642,7 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.n_tiles = (n_vec + kTileM - 1) / kTileM;
     }
     if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
-    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kFallbackSlots * 3 + 128;
+    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
     UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = (int64_t)sm_count() * 2;
     if (grid > p.n_tiles) grid = p.n_tiles;
