@@ -181,6 +181,69 @@ def run_reference(args, rank: int):
     print(json.dumps(base))
 
 
+def run_offload(args, rank, world, local_rank, dev, barrier):
+    """Configuration 4: per step and GPU, gather 4096 randomly chosen K and V blocks of one layer (2 GiB) into
+    pinned host memory and scatter 4096 blocks back into randomly chosen free slots.  Device side: one
+    compaction kernel per direction; host link: one DMA per direction.  Weak scaling (every GPU moves its own)."""
+    import torch
+    import torch.distributed as dist
+    from ucmx import _native, ops
+    from ucmx.workloads import LLAMA3_8B as shape
+    g = torch.Generator(device=dev).manual_seed(4004 + rank)
+    n_slots, n = 8192, 4096
+    T, H, D = shape.block_tokens, shape.n_kv_heads, shape.head_dim
+    kv = torch.empty((2, n_slots, T, H, D), dtype=torch.bfloat16, device=dev)
+    for p in range(2):
+        for s in range(0, n_slots, 1024):
+            kv[p, s:s + 1024].copy_(torch.randn((1024, T, H, D), generator=g, device=dev).to(torch.bfloat16))
+    perm = torch.randperm(n_slots, generator=g, device=dev).to(torch.int32)
+    src_ids, dst_ids = perm[:n].contiguous(), perm[n:].contiguous()
+    payload = n * 2 * shape.slice_bytes
+    host = torch.empty(payload, dtype=torch.uint8).pin_memory()
+    stage = torch.empty(payload, dtype=torch.uint8, device=dev)
+    planes = [kv[0], kv[1]]
+
+    def step():
+        ops.gather_blocks(planes, src_ids, stage)
+        host.copy_(stage, non_blocking=True)
+        stage.copy_(host, non_blocking=True)
+        ops.scatter_blocks(planes, dst_ids, stage)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    launches_before = _native.launch_count
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    exact = bool(torch.equal(kv[:, dst_ids.long()], kv[:, src_ids.long()]))
+    if rank == 0:
+        gbs = 2.0 * payload * world * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "kv_block_offload_bytes_per_s", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "KV block offload: per GPU and step 4096 random K+V blocks of one Llama-3-8B layer (2 GiB) "
+                                   "gathered to pinned host memory and 4096 scattered back into free slots",
+                       "payload_bytes_per_direction_per_gpu": payload, "route": "device compaction + one DMA per direction"},
+            "per_gpu_gbs_each_direction": payload * args.steps / (ms * 1e-3) / 1e9 * 2 / 2, "roundtrip_exact": exact,
+            "gpu_launches": _native.launch_count - launches_before, "clocks": clocks}))
+
+
 def workload_config(batch, extra=None):
     cfg = {
         "workload": "ESA batched decode, 64 requests, ctx U[8192,131072] tokens, Llama-3-8B KV (32q/8kv heads, "
@@ -206,10 +269,11 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
-    ap.add_argument("--workload", default="decode64", choices=["decode64", "tp-long"],
+    ap.add_argument("--workload", default="decode64", choices=["decode64", "tp-long", "offload"],
                     help="decode64: the 64-request ragged decode batch, data parallel over requests (default); "
                          "tp-long: 8 requests of 1 048 576 tokens, KV heads split over the GPUs with an all-reduce of "
-                         "block scores before top-k")
+                         "block scores before top-k; offload: every GPU moves 4096 random K+V blocks of one layer (2 GiB) to "
+                         "pinned host memory and 4096 back into free slots per step")
     ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer"],
                     help="tp-long only: how partial block scores are summed over ranks - a NCCL all-reduce between the "
                          "scoring and top-k kernels, or peer-memory loads inside the top-k kernel")
@@ -250,6 +314,12 @@ def main():
     def barrier():
         if world > 1:
             dist.barrier(device_ids=[local_rank])
+
+    if args.workload == "offload":
+        run_offload(args, rank, world, local_rank, dev, barrier)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     if tp:
         # every rank sees the same 8 requests and block tables and holds n_kv_heads/world of the heads

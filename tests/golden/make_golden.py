@@ -1,5 +1,5 @@
 """Regenerates tests/golden/golden.npz from the reference itself (run in a container that has the
-UCM checkout at $UCM_REFERENCE, default /root/reference, and oracle/_ref built by `make -C oracle ref`).
+UCM checkout at $UCM_REFERENCE and oracle/_ref built by `make -C oracle ref`).
 
 Outputs only are stored; the inputs are re-created from seeds by tests/helpers.py.
 Sources of each vector:

@@ -22,28 +22,32 @@ def half(bits):
     return torch.from_numpy(bits.view(np.int16).copy()).view(torch.float16).cuda()
 
 
-def run_single(q, reps, pruned, no_tc=False):
+MODES = {"tensor_core": None, "one_block_tiles": "UCMX_KVSTAR_ONE_BLOCK_TILES", "cuda_core": "UCMX_KVSTAR_NO_TC"}
+
+
+def run_single(q, reps, pruned, mode="tensor_core"):
     n = reps.shape[0]
     off = torch.tensor([0, n], dtype=torch.int32, device="cuda")
     qoff = torch.tensor([0, q.shape[0]], dtype=torch.int32, device="cuda")
     pr = None if pruned is None else torch.from_numpy(pruned).cuda().unsqueeze(0).contiguous()
-    if no_tc:
-        os.environ["UCMX_KVSTAR_NO_TC"] = "1"
+    if MODES[mode]:
+        os.environ[MODES[mode]] = "1"
     try:
         out = ops.kvstar_scores(half(reps), off, half(q), qoff, total=n, max_q_tokens=q.shape[0], pruned_index=pr)
     finally:
-        os.environ.pop("UCMX_KVSTAR_NO_TC", None)
+        if MODES[mode]:
+            os.environ.pop(MODES[mode], None)
     torch.cuda.synchronize()
     assert N.device_error() == 0
     return out.cpu().numpy()
 
 
-@pytest.mark.parametrize("no_tc", [False, True])
+@pytest.mark.parametrize("mode", sorted(MODES))
 @pytest.mark.parametrize("name", sorted(H.KVSTAR_CASES))
-def test_votes_and_selection_match(oracle, name, no_tc):
+def test_votes_and_selection_match(oracle, name, mode):
     q, reps, pruned, k = H.case_kvstar(name)
     want = oracle.kvstar_scores(q, reps, pruned)
-    got = run_single(q, reps, pruned, no_tc)
+    got = run_single(q, reps, pruned, mode)
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=1e-6)
     srt = np.sort(want)[::-1]
     assert srt[k - 1] - srt[k] > 4 * RTOL * srt[k - 1], "the seeded case must not sit on a tie"
@@ -83,15 +87,16 @@ def test_ragged_batch_with_slots_and_per_request_channels(oracle):
     pruned = np.stack([np.stack([rng.permutation(D)[:dp] for _ in range(Hk)]) for _ in xs]).astype(np.int64)
     off = np.concatenate([[0], np.cumsum(n_blocks)]).astype(np.int32)
     qoff = np.concatenate([[0], np.cumsum(xs)]).astype(np.int32)
-    for no_tc in (False, True):
-        if no_tc:
-            os.environ["UCMX_KVSTAR_NO_TC"] = "1"
+    for mode in sorted(MODES):
+        if MODES[mode]:
+            os.environ[MODES[mode]] = "1"
         try:
             got = ops.kvstar_scores(half(table), torch.from_numpy(off).cuda(), half(q), torch.from_numpy(qoff).cuda(),
                                     total=int(off[-1]), max_q_tokens=8, slot_ids=torch.from_numpy(slots).cuda(),
                                     pruned_index=torch.from_numpy(pruned).cuda()).cpu().numpy()
         finally:
-            os.environ.pop("UCMX_KVSTAR_NO_TC", None)
+            if MODES[mode]:
+                os.environ.pop(MODES[mode], None)
         assert N.device_error() == 0
         for r in range(len(xs)):
             want = oracle.kvstar_scores(q[qoff[r]:qoff[r + 1]], table[slots[off[r]:off[r + 1]]], pruned[r])

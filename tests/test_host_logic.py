@@ -109,3 +109,22 @@ def test_workloads_are_seeded_and_in_range():
     assert a.n_req == 64 and a.blocks_per_req.min() >= 64 and a.blocks_per_req.max() <= 1024
     assert (a.k_per_req == np.maximum(16, np.ceil(0.05 * a.blocks_per_req - 1e-9))).all()
     assert sorted(a.block_table.tolist()) == list(range(a.total))
+
+
+def test_kvstar_module_rejects_bad_shapes_like_the_reference():
+    """The shape checks of KVStar::Execute (simd_compute_kernel.cpp:637-666) come before any device work."""
+    import torch
+    from ucmx import kvstar
+    q = torch.zeros((8, 32, 128), dtype=torch.float16)
+    reps = torch.zeros((10, 64, 8, 32), dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="Query shape must be 3D"):
+        kvstar.AsyncRetrieveByCPU(q[0], reps, None, 4)
+    with pytest.raises(RuntimeError, match="BlockRep shape must be 4D"):
+        kvstar.AsyncRetrieveByCPU(q, reps[0], None, 4)
+    with pytest.raises(RuntimeError, match="divisible"):
+        kvstar.AsyncRetrieveByCPU(q[:, :30], reps, None, 4)
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        kvstar.AsyncRetrieveByCPU(q, reps, torch.zeros((8, 16), dtype=torch.int64), 4)
+    with pytest.raises(RuntimeError, match="Dimension mismatch"):
+        kvstar.AsyncRetrieveByCPU(q, reps, None, 4)
+    assert kvstar.GetTaskResult(123456) is None and kvstar.Wait(123456) == -1 and kvstar.Setup() == 0

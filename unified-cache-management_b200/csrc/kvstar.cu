@@ -171,11 +171,11 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64])
 
 // One MMA of the fully specialised issue sequence (64 positions per block, 64-element K chunks):
 // operand offsets are immediates, so each instruction costs three integer adds.
-template <int I, int CPG>
+template <int I, int CPG, int POS = 64>   // POS: positions (B rows, accumulator columns) per instruction
 __device__ __forceinline__ void umma_f16_step(uint32_t d_base, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc)
 {
     constexpr int c = I >> 2, k4 = I & 3, g = c / CPG, kc = c % CPG;
-    constexpr int a_off = (c * kChunkA + k4 * 32) >> 4, b_off = (c * 64 * 128 + k4 * 32) >> 4, d_off = g * 64;
+    constexpr int a_off = (c * kChunkA + k4 * 32) >> 4, b_off = (c * POS * 128 + k4 * 32) >> 4, d_off = g * POS;
     constexpr int acc = (kc | k4) ? 1 : 0;
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b32 ta, tb, td;\n\t.reg .b64 da, db;\n\t"
@@ -189,25 +189,25 @@ __device__ __forceinline__ void umma_f16_step(uint32_t d_base, uint32_t a_lo, ui
         "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(a_off), "n"(b_off), "n"(d_off), "n"(acc)
         : "memory");
 }
-template <int CPG>
+template <int CPG, int POS = 64>
 __device__ __forceinline__ void umma_f16_block16(uint32_t d_base, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc)
 {
-    umma_f16_step<0, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<1, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<2, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<3, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<4, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<5, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<6, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<7, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<8, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<9, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<10, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<11, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<12, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<13, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<14, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
-    umma_f16_step<15, CPG>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<0, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<1, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<2, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<3, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<4, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<5, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<6, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<7, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<8, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<9, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<10, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<11, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<12, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<13, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<14, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
+    umma_f16_step<15, CPG, POS>(d_base, a_lo, b_lo, desc_hi, idesc);
 }
 
 struct alignas(8) KsBarriers {
@@ -546,6 +546,202 @@ kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
     }
 }
 
+// ------------------------------------------------------------------------------ pass 1, two blocks per instruction
+// The same pipeline for the common shape (64 positions per block, heads * d_pruned == 256, two head
+// groups), with consecutive candidate blocks of one request taken in pairs: an M128 N128 K16 instruction
+// costs hardly more than an N64 one, so the sixteen instructions of a tile now cover two blocks, and the
+// MMA-issuing thread - the serial resource of the one-block kernel - has half the work per block.  A pair
+// never spans two requests (they have different A operands); a request's odd block is a tile of one.
+// Two stages of 64 KiB, two accumulator sets of 2 x 128 columns.
+constexpr int kPairStage = 65536;
+__global__ void __launch_bounds__(kTcThreads, 1)
+kvstar_partial_pair_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;                                  // 4 chunks of 16 KiB
+    unsigned char* sB = sA + 4 * kChunkA;                      // 2 stages: chunk c at c*16 KiB, second block 8 KiB further
+    KsBarriers* bars = reinterpret_cast<KsBarriers*>(sB + 2 * kPairStage);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = (int)((int64_t)p.total * blockIdx.x / gridDim.x);
+    const int t1 = (int)((int64_t)p.total * (blockIdx.x + 1) / gridDim.x);
+    if (tid == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+            mbar_init(&bars->acc_full[s], 1);
+            mbar_init(&bars->acc_empty[s], 128);
+        }
+        mbar_init(&bars->a_ready, 128);
+        bars->abort_flag = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (t1 > t0 && tid < kRows) build_a_operand(sA, p, find_request(p.offsets, p.n_req, t0), tid);
+    fence_proxy_async();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    // every role walks the same tiling: (first block t, blocks in the tile nb, request, its end)
+    int req = 0, req_end = 0;
+    if (t1 > t0) {
+        req = find_request(p.offsets, p.n_req, t0);
+        req_end = __ldg(p.offsets + req + 1);
+    }
+    auto enter = [&](int t) {          // request of block t (t is never inside an empty request's range)
+        bool changed = false;
+        while (t >= req_end) {
+            ++req;
+            req_end = __ldg(p.offsets + req + 1);
+            changed = true;
+        }
+        return changed;
+    };
+    auto blocks_of = [&](int t) { return (t + 1 < req_end && t + 1 < t1) ? 2 : 1; };
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        int it = 0;
+        for (int t = t0; t < t1; ++it) {
+            enter(t);
+            const int nb = blocks_of(t);
+            const int s = it & 1;
+            int slot[2];
+            for (int h = 0; h < nb; ++h) slot[h] = p.slot_ids ? __ldg(p.slot_ids + t + h) : t + h;   // in flight during the wait
+            if (!mbar_wait(&bars->empty[s], (uint32_t)(((it >> 1) & 1) ^ 1))) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 5);
+                break;
+            }
+            if (*(volatile int32_t*)&bars->abort_flag) break;
+            unsigned char* dst = sB + (size_t)s * kPairStage;
+            mbar_expect_tx(&bars->full[s], (uint32_t)(nb * 32768));
+            for (int h = 0; h < nb; ++h)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tma_load_2d(dst + c * 16384 + h * 8192, &tmap, c * 64, slot[h] * 64, &bars->full[s]);
+            t += nb;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const uint32_t a_lo = (uint32_t)smem_desc_sw128(smem_u32(sA));
+        const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(0) >> 32);
+        const uint32_t idesc2 = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+        const uint32_t idesc1 = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+        const uint32_t sB_addr = smem_u32(sB);
+        uint32_t a_gen = 0;
+        int it = 0;
+        for (int t = t0; t < t1; ++it) {
+            bool ok = true;
+            if (enter(t)) {            // first block of another request: the epilogue warps have to rebuild the A operand first
+                ok = mbar_wait(&bars->a_ready, a_gen & 1u);
+                ++a_gen;
+            }
+            const int nb = blocks_of(t);
+            const int s = it & 1;
+            const uint32_t par = (uint32_t)((it >> 1) & 1);
+            if (!ok || !mbar_wait(&bars->full[s], par) || !mbar_wait(&bars->acc_empty[s], par ^ 1u)) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 5);
+                break;
+            }
+            tc_fence_after();
+            umma_f16_block16<2, 128>(tmem_base + (uint32_t)(s * 256), a_lo, (uint32_t)smem_desc_sw128(sB_addr + (uint32_t)(s * kPairStage)),
+                                     desc_hi, nb == 2 ? idesc2 : idesc1);
+            umma_commit(&bars->acc_full[s]);
+            t += nb;
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue (two sets, alternate tiles)
+        const int set = (warp - 2) >> 2;
+        const int qd = warp & 3;
+        const int row = qd * 32 + lane;
+        const int hl = row / p.Rp, j = row - hl * p.Rp;
+        int nrows = t1 > t0 ? (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq : 0;
+        int it = 0;
+        for (int t = t0; t < t1; ++it) {
+            if (enter(t)) nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
+            const int nb = blocks_of(t);
+            if ((it & 1) != set) {
+                t += nb;
+                continue;
+            }
+            const int s = it & 1;                               // == set: stage and accumulator set of this tile
+            int slot[2];
+            for (int h = 0; h < nb; ++h) slot[h] = p.slot_ids ? __ldg(p.slot_ids + t + h) : t + h;
+            if (!mbar_wait(&bars->acc_full[s], (uint32_t)((it >> 1) & 1))) {
+                bars->abort_flag = 1;
+                if (p.err) atomicExch(p.err, 5);
+                break;
+            }
+            if (*(volatile int32_t*)&bars->abort_flag) break;
+            tc_fence_after();
+            if (qd == 0 && lane == 0) mbar_arrive(&bars->empty[s]);   // the MMAs have read the tile's shared memory
+            // every MMA issued so far has completed: if the next tile starts another request, build its A operand now
+            const int tn = t + nb;
+            if (tn < t1 && tn >= req_end) {
+                int nreq = req, nend = req_end;
+                while (tn >= nend) {
+                    ++nreq;
+                    nend = __ldg(p.offsets + nreq + 1);
+                }
+                build_a_operand(sA, p, nreq, row);
+                fence_proxy_async();
+                mbar_arrive(&bars->a_ready);
+            }
+            const bool live = hl < p.hpg && j < nrows;
+            const uint32_t tbase = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(s * 256);
+            for (int h = 0; h < nb; ++h) {
+                float2* orow = p.part + (int64_t)(t + h) * p.Rtot + hl * p.Rp + j;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t v[64];
+                    tmem_ld64(tbase + (uint32_t)(g * 128 + h * 64), v);
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int e = 0; e < 64; e += 4) {
+                        m0 = fmaxf(m0, __uint_as_float(v[e]));
+                        m1 = fmaxf(m1, __uint_as_float(v[e + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(v[e + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(v[e + 3]));
+                    }
+                    const float nbias = -(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * kLog2e);
+                    float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 64; e += 4) {
+                        q0 += ex2(fmaf(__uint_as_float(v[e]), kLog2e, nbias));
+                        q1 += ex2(fmaf(__uint_as_float(v[e + 1]), kLog2e, nbias));
+                        q2 += ex2(fmaf(__uint_as_float(v[e + 2]), kLog2e, nbias));
+                        q3 += ex2(fmaf(__uint_as_float(v[e + 3]), kLog2e, nbias));
+                    }
+                    if (live) {
+                        float2 o = make_float2(-nbias, (q0 + q1) + (q2 + q3));
+                        if (slot[h] < 0) o = make_float2(-INFINITY, 0.0f);
+                        orow[g * p.hpg * p.Rp] = o;
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars->acc_empty[s]);
+            t += nb;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------ pass 1, CUDA cores
 // Any shape: one CTA per candidate block, the block's representations in shared memory, one thread
 // per query row at a time; dot products as fp32 fused multiply-adds in channel order.
@@ -875,6 +1071,15 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
                 const size_t smem = 1024 + a_bytes + (size_t)p.stages * p.tile_bytes + sizeof(KsBarriers) + 64;
                 int grid = sm_count();
                 if (grid > total) grid = total;
+                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_ONE_BLOCK_TILES") == nullptr) {
+                    const size_t psmem = 1024 + 4 * (size_t)kChunkA + 2 * (size_t)kPairStage + sizeof(KsBarriers) + 64;
+                    UCMX_CUDA(cudaFuncSetAttribute(kvstar_partial_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
+                    int pgrid = sm_count();
+                    if (pgrid > total) pgrid = total;
+                    kvstar_partial_pair_kernel<<<pgrid, kTcThreads, psmem, st>>>(tmap, p);
+                    UCMX_LAUNCH_CHECK("kvstar_partial_pair_kernel");
+                    goto pass2;
+                }
                 const bool special = M == 64 && C == 256 && (p.cpg == 1 || p.cpg == 2);
                 auto kern = !special ? kvstar_partial_tc_kernel<0> : p.cpg == 1 ? kvstar_partial_tc_kernel<1> : kvstar_partial_tc_kernel<2>;
                 UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -899,6 +1104,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
         kvstar_partial_generic_kernel<<<total, 256, smem, st>>>(p);
         UCMX_LAUNCH_CHECK("kvstar_partial_generic_kernel");
     }
+pass2:
     kvstar_stats_kernel<<<dim3((p.Rtot + 31) / 32, n_req), 256, 0, st>>>(p);
     UCMX_LAUNCH_CHECK("kvstar_stats_kernel");
     kvstar_vote_kernel<<<(total + 8 * kVoteBlocks - 1) / (8 * kVoteBlocks), 256, 0, st>>>(p);
