@@ -1071,7 +1071,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
                 const size_t smem = 1024 + a_bytes + (size_t)p.stages * p.tile_bytes + sizeof(KsBarriers) + 64;
                 int grid = sm_count();
                 if (grid > total) grid = total;
-                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_ONE_BLOCK_TILES") == nullptr) {
+                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_PAIR_TILES") != nullptr) {
                     const size_t psmem = 1024 + 4 * (size_t)kChunkA + 2 * (size_t)kPairStage + sizeof(KsBarriers) + 64;
                     UCMX_CUDA(cudaFuncSetAttribute(kvstar_partial_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
                     int pgrid = sm_count();
