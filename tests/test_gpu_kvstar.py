@@ -22,7 +22,7 @@ def half(bits):
     return torch.from_numpy(bits.view(np.int16).copy()).view(torch.float16).cuda()
 
 
-MODES = {"tensor_core": None, "pair_tiles": "UCMX_KVSTAR_PAIR_TILES", "cuda_core": "UCMX_KVSTAR_NO_TC"}
+MODES = {"tensor_core": None, "one_block_tiles": "UCMX_KVSTAR_ONE_BLOCK_TILES", "cuda_core": "UCMX_KVSTAR_NO_TC"}
 
 
 def run_single(q, reps, pruned, mode="tensor_core"):

@@ -832,14 +832,13 @@ kvstar_stats_kernel(KsParams p)
 }
 
 // ------------------------------------------------------------------------------ pass 2b: votes
-// one warp per four candidate blocks, all of their loads issued before the first use
-constexpr int kVoteBlocks = 4;
+// one warp per candidate block
 __global__ void __launch_bounds__(256)
 kvstar_vote_kernel(KsParams p)
 {
     __shared__ int s_off[1025], s_q[1025];
     const int lane = threadIdx.x & 31;
-    const int tb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * kVoteBlocks;
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
     const bool cached = p.n_req <= 1024;       // request boundaries and query counts, searched in shared memory
     if (cached)
         for (int i = threadIdx.x; i <= p.n_req; i += blockDim.x) {
@@ -847,55 +846,40 @@ kvstar_vote_kernel(KsParams p)
             s_q[i] = __ldg(p.q_offsets + i);
         }
     __syncthreads();
-    if (tb >= p.total) return;
-    int req[kVoteBlocks], nrows[kVoteBlocks];
-#pragma unroll
-    for (int k = 0; k < kVoteBlocks; ++k) {
-        const int t = min(tb + k, p.total - 1);
-        if (cached) {
-            int lo = 0, hi = p.n_req;
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (s_off[mid] <= t) lo = mid; else hi = mid;
-            }
-            req[k] = lo;
-            nrows[k] = (s_q[lo + 1] - s_q[lo]) * p.gq;
-        } else {
-            req[k] = find_request(p.offsets, p.n_req, t);
-            nrows[k] = (__ldg(p.q_offsets + req[k] + 1) - __ldg(p.q_offsets + req[k])) * p.gq;
+    if (t >= p.total) return;
+    int req, nrows;
+    if (cached) {
+        int lo = 0, hi = p.n_req;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= t) lo = mid; else hi = mid;
         }
+        req = lo;
+        nrows = (s_q[req + 1] - s_q[req]) * p.gq;
+    } else {
+        req = find_request(p.offsets, p.n_req, t);
+        nrows = (__ldg(p.q_offsets + req + 1) - __ldg(p.q_offsets + req)) * p.gq;
     }
-    float acc[kVoteBlocks];
+    const float2* pp = p.part + (int64_t)t * p.Rtot;
+    const float2* st = p.stats + (int64_t)req * p.Rtot;
+    float acc = 0.0f;
+    for (int r0 = lane; r0 < p.Rtot; r0 += 256) {
+        // eight independent pairs of loads before the first use
+        float2 v[8], sr[8];
 #pragma unroll
-    for (int k = 0; k < kVoteBlocks; ++k) acc[k] = 0.0f;
-    for (int r0 = lane; r0 < p.Rtot; r0 += 128) {
-        float2 v[kVoteBlocks][4], sr[kVoteBlocks][4];
-#pragma unroll
-        for (int k = 0; k < kVoteBlocks; ++k) {
-            const int t = min(tb + k, p.total - 1);
-            const float2* pp = p.part + (int64_t)t * p.Rtot;
-            const float2* st = p.stats + (int64_t)req[k] * p.Rtot;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int r = r0 + u * 32;
-                const bool on = r < p.Rtot && (r % p.Rp) < nrows[k];
-                v[k][u] = on ? __ldcg(pp + r) : make_float2(-INFINITY, 0.0f);
-                sr[k][u] = on ? __ldcg(st + r) : make_float2(0.0f, 0.0f);
-            }
+        for (int u = 0; u < 8; ++u) {
+            const int r = r0 + u * 32;
+            const bool on = r < p.Rtot && (r % p.Rp) < nrows;
+            v[u] = on ? __ldcg(pp + r) : make_float2(-INFINITY, 0.0f);
+            sr[u] = on ? __ldcg(st + r) : make_float2(0.0f, 0.0f);
         }
 #pragma unroll
-        for (int k = 0; k < kVoteBlocks; ++k)
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (v[k][u].x > -INFINITY) acc[k] += v[k][u].y * ex2(v[k][u].x - sr[k][u].x) * sr[k][u].y;
+        for (int u = 0; u < 8; ++u)
+            if (v[u].x > -INFINITY) acc += v[u].y * ex2(v[u].x - sr[u].x) * sr[u].y;
     }
 #pragma unroll
-    for (int k = 0; k < kVoteBlocks; ++k) {
-        float a = acc[k];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (lane == 0 && tb + k < p.total) p.out[tb + k] = a;
-    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) p.out[t] = acc;
 }
 
 // ------------------------------------------------------------------------------ block representations
@@ -1071,7 +1055,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
                 const size_t smem = 1024 + a_bytes + (size_t)p.stages * p.tile_bytes + sizeof(KsBarriers) + 64;
                 int grid = sm_count();
                 if (grid > total) grid = total;
-                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_PAIR_TILES") != nullptr) {
+                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_ONE_BLOCK_TILES") == nullptr) {
                     const size_t psmem = 1024 + 4 * (size_t)kChunkA + 2 * (size_t)kPairStage + sizeof(KsBarriers) + 64;
                     UCMX_CUDA(cudaFuncSetAttribute(kvstar_partial_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
                     int pgrid = sm_count();
@@ -1107,7 +1091,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
 pass2:
     kvstar_stats_kernel<<<dim3((p.Rtot + 31) / 32, n_req), 256, 0, st>>>(p);
     UCMX_LAUNCH_CHECK("kvstar_stats_kernel");
-    kvstar_vote_kernel<<<(total + 8 * kVoteBlocks - 1) / (8 * kVoteBlocks), 256, 0, st>>>(p);
+    kvstar_vote_kernel<<<(total + 7) / 8, 256, 0, st>>>(p);
     UCMX_LAUNCH_CHECK("kvstar_vote_kernel");
     return UCMX_OK;
 }

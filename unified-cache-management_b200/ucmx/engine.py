@@ -150,16 +150,34 @@ class DecodeRetrievalEngine:
         self.q_host.copy_(self.q_dev)
         self.sel_host = torch.empty(self.sel_ids.shape, dtype=torch.int32).pin_memory()
         self.cnt_host = torch.empty(self.sel_counts.shape, dtype=torch.int32).pin_memory()
+        self._copy_stream = torch.cuda.Stream(device=self.device)
+        self._q_ready = [torch.cuda.Event() for _ in range(self.L)]
+        self._layer_done = [torch.cuda.Event() for _ in range(self.L)]
 
     def step_host(self) -> torch.Tensor:
         """End to end with host buffers: each layer's queries come from pinned host memory and its
-        selected block ids and counts go back to pinned host memory; returns after a final sync."""
+        selected block ids and counts go back to pinned host memory; returns after a final sync.
+
+        The copies run on their own stream: layer l's kernels wait for the event of their own queries
+        only, and its results leave while layer l+1 computes, so the host link works beside the kernels
+        instead of between them."""
+        main = torch.cuda.current_stream(self.device)
+        cs = self._copy_stream
+        cs.wait_stream(main)                               # earlier work on the buffers has finished
+        with torch.cuda.stream(cs):
+            for l in range(self.L):
+                self.q_dev[l].copy_(self.q_host[l], non_blocking=True)
+                self._q_ready[l].record(cs)
         for l in range(self.L):
-            self.q_dev[l].copy_(self.q_host[l], non_blocking=True)
+            main.wait_event(self._q_ready[l])
             self.layer_step(l)
-            self.sel_host[l].copy_(self.sel_ids[l], non_blocking=True)
-            self.cnt_host[l].copy_(self.sel_counts[l], non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+            self._layer_done[l].record(main)
+            with torch.cuda.stream(cs):
+                cs.wait_event(self._layer_done[l])
+                self.sel_host[l].copy_(self.sel_ids[l], non_blocking=True)
+                self.cnt_host[l].copy_(self.sel_counts[l], non_blocking=True)
+        main.wait_stream(cs)
+        main.synchronize()
         return self.sel_host
 
     @property
