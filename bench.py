@@ -189,6 +189,8 @@ def run_offload(args, rank, world, local_rank, dev, barrier):
     import torch.distributed as dist
     from ucmx import _native, ops
     from ucmx.workloads import LLAMA3_8B as shape
+    from ucmx.store.numa import bind_to_device_node
+    numa_node = None if os.environ.get("UCMX_NO_NUMA_BIND") else bind_to_device_node(local_rank)   # before page-locking
     g = torch.Generator(device=dev).manual_seed(4004 + rank)
     n_slots, n = 8192, 4096
     T, H, D = shape.block_tokens, shape.n_kv_heads, shape.head_dim
@@ -239,7 +241,7 @@ def run_offload(args, rank, world, local_rank, dev, barrier):
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": "KV block offload: per GPU and step 4096 random K+V blocks of one Llama-3-8B layer (2 GiB) "
                                    "gathered to pinned host memory and 4096 scattered back into free slots",
-                       "payload_bytes_per_direction_per_gpu": payload, "route": "device compaction + one DMA per direction"},
+                       "payload_bytes_per_direction_per_gpu": payload, "route": "device compaction + one DMA per direction", "numa_node_of_rank0": numa_node},
             "per_gpu_gbs_each_direction": payload * args.steps / (ms * 1e-3) / 1e9 * 2 / 2, "roundtrip_exact": exact,
             "gpu_launches": _native.launch_count - launches_before, "clocks": clocks}))
 

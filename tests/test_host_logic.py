@@ -128,3 +128,18 @@ def test_kvstar_module_rejects_bad_shapes_like_the_reference():
     with pytest.raises(RuntimeError, match="Dimension mismatch"):
         kvstar.AsyncRetrieveByCPU(q, reps, None, 4)
     assert kvstar.GetTaskResult(123456) is None and kvstar.Wait(123456) == -1 and kvstar.Setup() == 0
+
+
+def test_numa_helpers_read_sysfs_layout(tmp_path):
+    from ucmx.store import numa
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("16-19,48,50-51\n")
+    assert numa.device_numa_node("0000:1B:00.0", str(tmp_path)) == 1
+    assert numa.node_cpus(1, str(tmp_path)) == [16, 17, 18, 19, 48, 50, 51]
+    assert numa.device_numa_node("0000:ff:00.0", str(tmp_path)) is None and numa.node_cpus(7, str(tmp_path)) == []
+    (dev / "numa_node").write_text("-1\n")
+    assert numa.device_numa_node("0000:1b:00.0", str(tmp_path)) is None
