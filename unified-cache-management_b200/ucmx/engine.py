@@ -74,13 +74,27 @@ class DecodeRetrievalEngine:
         self.q_host: Optional[torch.Tensor] = None
         self.sel_host: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = self.L * (4 if with_kv_pool else 2)
+        self.launches_per_step = self.L * (3 if with_kv_pool else 2) + (1 if with_kv_pool else 0)
+        self._pool_all = None
 
     # ---------------------------------------------------------------------------------- stages
     def make_queries(self) -> torch.Tensor:
         q = torch.randn((self.L, self.batch.n_req, self.Hq, self.D), generator=self.gen, device=self.device)
         self.q_dev.copy_(q.to(torch.bfloat16))
         return self.q_dev
+
+    def pool_all_layers(self) -> None:
+        """Representatives of the blocks that filled up since the last step, for every layer, in one launch: the
+        rows go to slot `layer * n_slots + block id` of the stacked tables.  (Blocks fill between steps, so this
+        need not wait for the layers to come round one by one.)"""
+        if self._pool_all is None:
+            ns = self.batch.n_slots
+            ids = self.new_block_ids.repeat(self.L).contiguous()
+            slots = (torch.arange(self.L, device=self.device, dtype=torch.int64)[:, None] * ns
+                     + self.new_block_ids.long()[None, :]).reshape(-1).to(torch.int32).contiguous()
+            self._pool_all = (ids, slots, self.rep_tables.view(self.L * ns, self.H, 1, self.D))
+        ids, slots, table = self._pool_all
+        ops.pool_blocks(self.kv_pool[0], ids, out_slots=slots, out_bf16=table)
 
     def pool_layer(self, layer: int) -> None:
         ops.pool_blocks(self.kv_pool[0], self.new_block_ids, out_slots=self.new_block_ids,
@@ -114,8 +128,7 @@ class DecodeRetrievalEngine:
         ops.gather_blocks([self.kv_pool[0], self.kv_pool[1]], self.sel_ids[layer], self.staging)
 
     def layer_step(self, layer: int) -> None:
-        if self.kv_pool is not None:
-            self.pool_layer(layer)
+        """Score, select and gather one layer (pooling of new blocks is done for all layers at the start of a step)."""
         self.score_layer(layer)
         self.topk_layer(layer)
         if self.kv_pool is not None:
@@ -127,6 +140,8 @@ class DecodeRetrievalEngine:
         if self.graph is not None:
             self.graph.replay()
             return
+        if self.kv_pool is not None:
+            self.pool_all_layers()
         for l in range(self.L):
             self.layer_step(l)
 
@@ -135,12 +150,16 @@ class DecodeRetrievalEngine:
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
+            if self.kv_pool is not None:
+                self.pool_all_layers()
             for l in range(min(self.L, 2)):
                 self.layer_step(l)          # warm up lazily initialised state outside capture
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
+            if self.kv_pool is not None:
+                self.pool_all_layers()
             for l in range(self.L):
                 self.layer_step(l)
         self.graph = graph
@@ -168,6 +187,8 @@ class DecodeRetrievalEngine:
             for l in range(self.L):
                 self.q_dev[l].copy_(self.q_host[l], non_blocking=True)
                 self._q_ready[l].record(cs)
+        if self.kv_pool is not None:
+            self.pool_all_layers()
         for l in range(self.L):
             main.wait_event(self._q_ready[l])
             self.layer_step(l)
