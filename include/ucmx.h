@@ -135,6 +135,19 @@ int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
                        const float* q, int32_t n_req, int32_t total, float scale, float* out_scores,
                        ucmx_stream_t stream);
 
+/* GSA's device-side weights (cal_topk, ucm/sparse/gsa/gsa.py:386-412): weight of a block = mean over the
+ * QUERY heads of max over the block's n_rep representatives of dot(query head, representative of its KV
+ * head); no softmax scale (the reference computes one and does not apply it).  query is raw bf16
+ * [n_req, n_q_heads, head_dim], query_stride elements between requests; the table is bf16
+ * [slot, n_kv_heads, n_rep, head_dim].  include_mask / exclude_mask: one byte per candidate (device), or
+ * NULL; a set include byte gives +inf, a set exclude byte -inf (exclude wins), as masked_fill_ does there.
+ * n_q_heads / n_kv_heads must be a power of two <= 32.  Computed in fp32. */
+int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                             const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+                             int32_t n_q_heads, int64_t query_stride, int32_t n_req, int32_t total,
+                             const uint8_t* include_mask, const uint8_t* exclude_mask,
+                             float* out_scores, ucmx_stream_t stream);
+
 /* Stages 2-prologue and 2a in one launch: `query` is the raw bf16 decode query [n_req, n_q_heads,
  * head_dim] (query_stride elements between requests); the per-KV-head mean of
  * ucmx_query_group_mean (same arithmetic, same round_bf16 switch) is taken inside the scoring

@@ -228,6 +228,24 @@ def store_offset(block_tokens, heads_per_rank, head_dim, rank, tp_size, elem_byt
                                       C.c_int32(int(is_mla))))
 
 
+def score_dot_gsa_heads(reps_f32, req_offsets, slot_ids, q_bf16, include_mask=None, exclude_mask=None):
+    """GSA's device-side weights: mean over query heads of the per-head maximum over a block's representatives.
+    reps_f32 [n_slots, H, n_rep, D] fp32; q_bf16 uint16 bits [n_req, Hq, D]."""
+    reps = _c(reps_f32, np.float32)
+    off = _c(req_offsets, np.int32)
+    ids = _c(slot_ids, np.int32)
+    q = _c(q_bf16, np.uint16)
+    inc = _c(include_mask, np.uint8)
+    exc = _c(exclude_mask, np.uint8)
+    n_slots, H, n_rep, D = reps.shape
+    n_req, Hq, _ = q.shape
+    out = np.empty(int(off[-1]), np.float32)
+    vp = lambda a: None if a is None else a.ctypes.data_as(C.c_void_p)
+    lib().orc_score_dot_gsa_heads(vp(reps), C.c_int32(H), C.c_int32(n_rep), C.c_int32(D), vp(off), vp(ids), C.c_int32(n_req),
+                                  vp(q), C.c_int32(Hq), vp(inc), vp(exc), vp(out))
+    return out
+
+
 # ------------------------------------------------------------------------- KVStar
 
 def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:

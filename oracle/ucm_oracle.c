@@ -600,3 +600,43 @@ int32_t orc_kvstar_topk(const float *scores, int32_t n, int32_t k, int64_t *out)
     free(p);
     return k;
 }
+
+/* GSA's on-device scoring variant (cal_topk, ucm/sparse/gsa/gsa.py:386-412): every query head is dotted
+ * with the representatives of its KV head, the maximum over a block's n_rep representatives is taken
+ * per QUERY head, and the block's weight is the mean over query heads; blocks flagged in include_mask
+ * weigh +inf, those in exclude_mask -inf (exclude wins: it is applied last).  No softmax scale is applied
+ * (the reference computes one and leaves it unused).  Computed in fp32 here; the reference's tensors are
+ * in the model dtype, so its own result carries bf16 rounding on top.
+ * q: bf16 bits [n_req][Hq][D]; reps: fp32 [n_slots][H][n_rep][D]; masks: one byte per candidate or NULL. */
+void orc_score_dot_gsa_heads(const float *reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                             const int32_t *req_offsets, const int32_t *slot_ids, int32_t n_req,
+                             const uint16_t *q, int32_t n_q_heads, const uint8_t *include_mask,
+                             const uint8_t *exclude_mask, float *out)
+{
+    const int32_t g = n_q_heads / n_kv_heads;
+    for (int32_t r = 0; r < n_req; ++r)
+        for (int32_t c = req_offsets[r]; c < req_offsets[r + 1]; ++c) {
+            const int32_t slot = slot_ids ? slot_ids[c] : c;
+            float acc = 0.0f;
+            if (slot < 0) {
+                out[c] = -INFINITY;
+                continue;
+            }
+            for (int32_t i = 0; i < n_q_heads; ++i) {
+                const int32_t h = i / g;
+                const uint16_t *qv = q + ((int64_t)r * n_q_heads + i) * head_dim;
+                float best = -INFINITY;
+                for (int32_t m = 0; m < n_rep; ++m) {
+                    const float *kv = reps + (((int64_t)slot * n_kv_heads + h) * n_rep + m) * head_dim;
+                    float dot = 0.0f;
+                    for (int32_t d = 0; d < head_dim; ++d) dot += bf16_to_f32(qv[d]) * kv[d];
+                    if (dot > best) best = dot;
+                }
+                acc += best;
+            }
+            float w = acc / (float)n_q_heads;
+            if (include_mask && include_mask[c]) w = INFINITY;
+            if (exclude_mask && exclude_mask[c]) w = -INFINITY;
+            out[c] = w;
+        }
+}

@@ -101,3 +101,22 @@ def case_kvstar_repre(seed=6101, merge=2, dp=32):
     ids = rng.permutation(7)[:5].astype(np.int32)
     pruned = np.stack([rng.permutation(128)[:dp] for _ in range(8)]).astype(np.int64)
     return k, ids, pruned
+
+
+def case_gsa_heads(seed=7001):
+    """GSA device-side scoring: 3 requests over a shared table with 3 representatives per block and head."""
+    rng = np.random.default_rng(seed)
+    H, Hq, D, R, n_slots = 8, 32, 128, 3, 90
+    reps = randn_bf16(rng, (n_slots, H, R, D), 0.3)
+    q = randn_bf16(rng, (3, Hq, D))
+    counts = [40, 7, 33]
+    off = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    ids = rng.permutation(n_slots)[:off[-1]].astype(np.int32)
+    inc = np.zeros(off[-1], np.uint8)
+    exc = np.zeros(off[-1], np.uint8)
+    for a, b in zip(off[:-1], off[1:]):
+        inc[a:a + 2] = 1          # the first blocks are always kept
+        inc[b - 1] = 1            # and the newest one
+        exc[a + 4] = 1
+    exc[off[1] - 1] = 1           # flagged both ways: exclude wins
+    return reps, q, off, ids, inc, exc

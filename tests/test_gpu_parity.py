@@ -433,3 +433,42 @@ def test_full_size_properties(ops):
     ops.scatter_blocks([k2, v2], sel, staging)
     assert torch.equal(k2[sel.long()], k[sel.long()]) and torch.equal(v2[sel.long()], v[sel.long()])
     assert int(k2.view(torch.int16).ne(0).any(dim=(1, 2, 3)).sum()) == 512
+
+
+# ---------------------------------------------------------------- GSA device-side weights (per query head)
+
+def test_score_dot_heads_matches_checker_and_reference(ops, oracle):
+    reps, q, off, ids, inc, exc = H.case_gsa_heads()
+    dev = "cuda:0"
+    t = lambda a: torch.from_numpy(a).to(dev)
+    bf = lambda u: torch.from_numpy(u.view(np.int16).copy()).to(dev).view(torch.bfloat16)
+    got = ops.score_dot_heads(bf(reps), t(off), bf(q), total=int(off[-1]), slot_ids=t(ids), include_mask=t(inc),
+                              exclude_mask=t(exc)).cpu().numpy()
+    want = oracle.score_dot_gsa_heads(H.bf16_to_f32(reps), off, ids, q, inc, exc)
+    fin = np.isfinite(want)
+    assert np.array_equal(np.isposinf(got), np.isposinf(want)) and np.array_equal(np.isneginf(got), np.isneginf(want))
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)
+    ref = np.load(os.path.join(os.path.dirname(__file__), "golden", "gsa_heads.npz"))["weights"]   # the reference, in bf16
+    assert np.all(np.abs(got[fin] - ref[fin]) <= 8e-3 * np.maximum(np.abs(got[fin]), 0.5))
+    # with one representative per block the weights rank blocks like the group-mean dot product does
+    one = ops.score_dot_heads(bf(reps[:, :, :1].copy()), t(off), bf(q), total=int(off[-1]), slot_ids=t(ids)).cpu().numpy()
+    esa = ops.score_dot_query(bf(reps[:, :, :1].copy()), t(off), bf(q), total=int(off[-1]), slot_ids=t(ids), n_kv_heads=8).cpu().numpy()
+    np.testing.assert_allclose(one * 8, esa, rtol=0, atol=0.06)      # esa rounds the group mean of q to bf16 (values ~ +-10)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,R", [(8, 8, 128, 2), (64, 8, 128, 1), (4, 2, 64, 5), (32, 1, 32, 3)])
+def test_score_dot_heads_shapes(ops, oracle, Hq, Hkv, D, R):
+    rng = np.random.default_rng(Hq * 131 + R)
+    n_slots = 50
+    reps = H.randn_bf16(rng, (n_slots, Hkv, R, D), 0.5)
+    q = H.randn_bf16(rng, (2, Hq, D))
+    off = np.array([0, 19, 50], np.int32)
+    ids = rng.permutation(n_slots).astype(np.int32)
+    ids[3] = -1
+    dev = "cuda:0"
+    bf = lambda u: torch.from_numpy(u.view(np.int16).copy()).to(dev).view(torch.bfloat16)
+    got = ops.score_dot_heads(bf(reps), torch.from_numpy(off).to(dev), bf(q), total=50, slot_ids=torch.from_numpy(ids).to(dev)).cpu().numpy()
+    want = oracle.score_dot_gsa_heads(H.bf16_to_f32(reps), off, ids, q)
+    assert np.isneginf(got[3]) and np.isneginf(want[3])
+    fin = np.isfinite(want)
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)

@@ -139,3 +139,15 @@ def test_gather_scatter_roundtrip(oracle):
     dst = np.array([1, 5, 3], np.int32)
     oracle.scatter_blocks([k2, v2], dst, 4096, 4096, st)
     assert np.array_equal(k2[dst], kp[ids]) and np.array_equal(v2[dst], vp[ids])
+
+
+def test_gsa_device_weights_match_reference_expression(oracle):
+    """The reference evaluates cal_topk in bf16 (two roundings: the dot products and the mean), the checker in
+    fp32: agreement to 8e-3 relative, identical +inf / -inf pattern."""
+    reps, q, off, ids, inc, exc = H.case_gsa_heads()
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "gsa_heads.npz"))["weights"]
+    got = oracle.score_dot_gsa_heads(H.bf16_to_f32(reps), off, ids, q, inc, exc)
+    assert np.array_equal(np.isposinf(got), np.isposinf(want)) and np.array_equal(np.isneginf(got), np.isneginf(want))
+    fin = np.isfinite(want)
+    assert np.all(np.abs(got[fin] - want[fin]) <= 8e-3 * np.maximum(np.abs(got[fin]), 0.5))
+    assert np.isneginf(got[off[1] - 1])          # flagged both ways: excluded

@@ -537,6 +537,123 @@ extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t 
     return UCMX_OK;
 }
 
+namespace ucmx {
+namespace {
+// ---------------------------------------------------------------------------------------------
+// GSA's device-side weights (cal_topk, ucm/sparse/gsa/gsa.py:386-412): per QUERY head the largest dot
+// product with the block's n_rep representatives of its KV head, averaged over query heads; include
+// and exclude masks turn into +inf / -inf (exclude last).  One warp per candidate.  The warp is cut into
+// g = Hq/H lane groups, one per query head of the KV head at hand, so the representative row is read once
+// per (head, representative) - as a broadcast - and the reduction is a short one inside the group.
+struct ScoreHeadsParams {
+    const void* reps;           // [slot][H][R][D] bf16
+    const int32_t* offsets;
+    const int32_t* slot_ids;
+    const uint16_t* q;          // bf16 [n_req][Hq][D], q_stride elements between requests
+    const uint8_t* include_mask;
+    const uint8_t* exclude_mask;
+    float* out;
+    int64_t q_stride;
+    int32_t n_req, total, H, Hq, R, D;
+};
+
+__global__ void __launch_bounds__(kScoreThreads) score_dot_heads_kernel(ScoreHeadsParams p)
+{
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int64_t W = (int64_t)gridDim.x * warps_per_cta;
+    const int64_t w0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int g = p.Hq / p.H;                  // query heads per KV head: 1, 2, 4, ... 32
+    const int lanes_per_head = 32 / g;
+    const int gi = lane / lanes_per_head;      // which query head of the group this lane works for
+    const int li = lane - gi * lanes_per_head;
+    const int pieces = p.D / 4;                // 8-byte pieces of a row
+    const uint16_t* reps = reinterpret_cast<const uint16_t*>(p.reps);
+    const float inv = 1.0f / (float)p.Hq;
+
+    for (int64_t c = w0; c < p.total; c += W) {
+        const int r = find_request(p.offsets, p.n_req, (int)c);
+        const int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        if (slot < 0) {
+            if (lane == 0) p.out[c] = -INFINITY;
+            continue;
+        }
+        const uint16_t* row = reps + (size_t)slot * p.H * p.R * p.D;
+        const uint16_t* qr = p.q + (int64_t)r * p.q_stride;
+        float total = 0.0f;                    // lane li == 0 of each group: sum over KV heads of its query head's maximum
+        for (int h = 0; h < p.H; ++h) {
+            const uint16_t* qv = qr + (size_t)(h * g + gi) * p.D;
+            float best = -INFINITY;
+            for (int j = 0; j < p.R; ++j) {
+                const uint16_t* kv = row + ((size_t)h * p.R + j) * p.D;
+                float acc = 0.0f;
+                for (int pc = li; pc < pieces; pc += lanes_per_head) {
+                    const uint2 kw = __ldg(reinterpret_cast<const uint2*>(kv) + pc);
+                    const uint2 qw = __ldg(reinterpret_cast<const uint2*>(qv) + pc);
+                    acc = fmaf(bf16lo(qw.x), bf16lo(kw.x), acc);
+                    acc = fmaf(bf16hi(qw.x), bf16hi(kw.x), acc);
+                    acc = fmaf(bf16lo(qw.y), bf16lo(kw.y), acc);
+                    acc = fmaf(bf16hi(qw.y), bf16hi(kw.y), acc);
+                }
+                for (int o = lanes_per_head >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                best = fmaxf(best, acc);
+            }
+            total += best;
+        }
+        // one value per lane group (every lane of a group holds it): add the groups up
+        for (int o = lanes_per_head; o < 32; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane == 0) {
+            float w = total * inv;
+            if (p.include_mask && __ldg(p.include_mask + c)) w = INFINITY;
+            if (p.exclude_mask && __ldg(p.exclude_mask + c)) w = -INFINITY;
+            p.out[c] = w;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                                        const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+                                        int32_t n_q_heads, int64_t query_stride, int32_t n_req, int32_t total,
+                                        const uint8_t* include_mask, const uint8_t* exclude_mask, float* out_scores,
+                                        ucmx_stream_t stream)
+{
+    using namespace ucmx;
+    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req == 0 || total == 0) return UCMX_OK;
+    if (!reps || !req_offsets || !query || !out_scores) return UCMX_EPARAM;
+    if (n_kv_heads < 1 || n_rep < 1 || head_dim < 4 || (head_dim & 3) || n_q_heads < n_kv_heads || n_q_heads % n_kv_heads) return UCMX_EPARAM;
+    const int g = n_q_heads / n_kv_heads;
+    if (g > 32 || (g & (g - 1))) {
+        set_last_text("score_dot_heads: query heads per KV head must be a power of two up to 32");
+        return UCMX_EUNSUPPORTED;
+    }
+    if (query_stride < (int64_t)n_q_heads * head_dim || (query_stride & 3) || ((uintptr_t)reps & 7) || ((uintptr_t)query & 7)) return UCMX_EPARAM;
+    ScoreHeadsParams p{};
+    p.reps = reps;
+    p.offsets = req_offsets;
+    p.slot_ids = slot_ids;
+    p.q = (const uint16_t*)query;
+    p.include_mask = include_mask;
+    p.exclude_mask = exclude_mask;
+    p.out = out_scores;
+    p.q_stride = query_stride;
+    p.n_req = n_req;
+    p.total = total;
+    p.H = n_kv_heads;
+    p.Hq = n_q_heads;
+    p.R = n_rep;
+    p.D = head_dim;
+    const int warps_per_cta = kScoreThreads / 32;
+    int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    score_dot_heads_kernel<<<(int)(want > cap ? cap : want), kScoreThreads, 0, (cudaStream_t)stream>>>(p);
+    UCMX_LAUNCH_CHECK("score_dot_heads_kernel");
+    return UCMX_OK;
+}
+
 extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t head_dim,
                                         const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
                                         int32_t n_q_heads, int64_t query_stride, int32_t round_bf16, int32_t n_req,

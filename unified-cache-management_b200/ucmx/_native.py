@@ -65,6 +65,7 @@ SIGNATURES = {
     "ucmx_query_group_mean": [_vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp],
     "ucmx_score_dot": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "ucmx_score_dot_query": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp],
+    "ucmx_score_dot_heads": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp],
     "ucmx_score_hamming": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "ucmx_topk_ragged": [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "ucmx_peer_signal": [_vp, _i32, _i32, C.c_uint32, _vp],

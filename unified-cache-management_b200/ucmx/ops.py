@@ -147,6 +147,30 @@ def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.
     return out
 
 
+def score_dot_heads(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.Tensor, *, total: int,
+                    slot_ids: Optional[torch.Tensor] = None, include_mask: Optional[torch.Tensor] = None,
+                    exclude_mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """GSA's device-side block weights: mean over query heads of the per-head maximum over a block's
+    representatives.  reps bf16 [n_slots, H, n_rep, D]; query bf16 [n_req, Hq, D]; masks uint8 [total]."""
+    _need_cuda(reps, req_offsets, query, slot_ids, include_mask, exclude_mask, out)
+    if reps.dim() != 4 or reps.dtype != torch.bfloat16 or not reps.is_contiguous():
+        raise ValueError("reps must be contiguous bf16 [n_slots, n_kv_heads, n_rep, head_dim]")
+    if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1 or query.stride(1) != query.shape[2]:
+        raise ValueError("query must be bf16 [n_req, n_q_heads, head_dim] with contiguous heads")
+    for m in (include_mask, exclude_mask):
+        if m is not None and (m.dtype != torch.uint8 or not m.is_contiguous() or m.numel() != total):
+            raise ValueError("masks must be contiguous uint8 [total]")
+    n_slots, H, R, D = reps.shape
+    n_req = req_offsets.numel() - 1
+    if out is None:
+        out = torch.empty((total,), dtype=torch.float32, device=reps.device)
+    st = N.lib.ucmx_score_dot_heads(_ptr(reps), H, R, D, _ptr(_i32(req_offsets, "req_offsets")), _ptr(_i32(slot_ids, "slot_ids")),
+                                    _ptr(query), query.shape[1], query.stride(0), n_req, total, _ptr(include_mask),
+                                    _ptr(exclude_mask), _ptr(out), _stream(reps))
+    N.check("ucmx_score_dot_heads", st, 1 if total and n_req else 0)
+    return out
+
+
 def score_hamming(codes: torch.Tensor, req_offsets: torch.Tensor, q_codes: torch.Tensor, *, total: int,
                   slot_ids: Optional[torch.Tensor] = None, cross_head: bool = True,
                   out: Optional[torch.Tensor] = None) -> torch.Tensor:

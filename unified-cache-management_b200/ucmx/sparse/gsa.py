@@ -58,6 +58,10 @@ class GSA(UcmSparseBase):
         self.n_rep = int(cfg.get("max_norm_num", 1))
         self.start_window = int(cfg.get("start_window", 1))      # TopkBlockSelector defaults (select_topk_block.h:20)
         self.end_window = int(cfg.get("end_window", 2))
+        # "offload": the CPU library's weights, sum over KV heads of the max over representatives against the
+        # group-mean query (select_topk_block.cpp:53-76); "device": the weights of the reference's on-GPU
+        # path, mean over query heads of each head's max (gsa.py:386-412).  They rank alike with one representative.
+        self.score_variant = str(cfg.get("score_variant", "offload"))
         self.kv_caches: Dict[str, torch.Tensor] = {}
         self.kpre: List[Optional[torch.Tensor]] = [None] * self.n_layers
         self.pooled: List[set] = [set() for _ in range(self.n_layers)]
@@ -111,9 +115,13 @@ class GSA(UcmSparseBase):
         phys = np.concatenate([np.asarray(b, np.int32) for b in md.block_ids]) if len(counts) else np.zeros(0, np.int32)
         d_off, d_phys = self._i32(off, dev), self._i32(phys, dev)
         rows = torch.from_numpy(np.asarray(md.query_rows, np.int64)).to(dev)
-        qbar = ops.query_group_mean(query.index_select(0, rows), self.num_kv_heads, round_bf16=False)
-        scores = ops.score_dot(self._table(layer, k_cache), d_off, qbar, total=int(off[-1]), slot_ids=d_phys,
-                               n_kv_heads=self.num_kv_heads, head_dim=self.head_size, n_rep=self.n_rep)
+        if self.score_variant == "device":
+            scores = ops.score_dot_heads(self._table(layer, k_cache), d_off, query.index_select(0, rows).contiguous(),
+                                         total=int(off[-1]), slot_ids=d_phys)
+        else:
+            qbar = ops.query_group_mean(query.index_select(0, rows), self.num_kv_heads, round_bf16=False)
+            scores = ops.score_dot(self._table(layer, k_cache), d_off, qbar, total=int(off[-1]), slot_ids=d_phys,
+                                   n_kv_heads=self.num_kv_heads, head_dim=self.head_size, n_rep=self.n_rep)
         width = int(max(1, ks.max() if len(ks) else 1, ))
         width = max(width, int(counts.max()) if len(counts) else 1) if (counts <= ks).any() else width
         table, _, cnt = ops.topk_ragged(scores, d_off, self._i32(ks, dev), out_stride=width, start_win=self.start_window,
