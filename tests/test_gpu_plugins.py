@@ -1,5 +1,5 @@
 """The reference-facing layers on the GPU: the DRAM store (mirrors the cases of the reference's
-test/test_ucm_dram.py), HashEncoder, and the ESA / KvComp / GSA plug-ins driven through the
+test/test_ucm_dram.py), HashEncoder, and the ESA / KvComp / GSA / KVStar plug-ins driven through the
 UcmSparseBase hooks by a miniature model runner, each checked against the CPU checker."""
 import os
 from types import SimpleNamespace
@@ -274,6 +274,88 @@ def test_kvcomp_hooks_select_and_load(oracle):
             # the windows were restored from the copies taken at the end of prefill
             assert torch.equal(run.kv[l][0][decode_blocks[r][0]], dev_bf16(run.kv_host[l][0][prefill_blocks[r][0]]))
             assert torch.equal(run.kv[l][1][decode_blocks[r][-1]], dev_bf16(run.kv_host[l][1][prefill_blocks[r][-1]]))
+    store.close()
+
+
+def test_kvstar_multistep_hooks_vote_and_load(oracle):
+    """Prefill builds pruned fp16 representations and the first query group; decode step 1 loads the blocks
+    that group votes for, and the next stride's group (decode queries 1..8) decides at step 9."""
+    from ucmx.sparse.base import UcmSparseRole
+    from ucmx.sparse.factory import UcmSparseFactory
+    from ucmx.sparse.kvstar import KVStarMultiStep, KVStarMultiStepSparseMetaData, ReqMeta, block_hash
+    from ucmx.store.dramstore import UcmDramStore
+
+    slice_bytes = T * HKV * D * 2
+    store = UcmDramStore({"role": "worker", "max_cache_size": 512 * slice_bytes, "kv_block_size": slice_bytes, "device": DEV})
+    cfg = {"retrieval_stride": 8, "sparse_ratio": 0.25, "blk_repre_dim_prune_ratio": 0.25, "blk_repre_inner_token_merge": 2}
+    ks = UcmSparseFactory.create_sparse_method(make_config("KVStarMultiStep", cfg, store), UcmSparseRole.WORKER)
+    assert isinstance(ks, KVStarMultiStep) and ks.d_pruned == D // 4
+    run = Runner(ks, seed=84)
+    rng = run.rng
+    n_tok = {"A": 12 * T, "B": 30 * T + 5}
+    n_full = {"A": 12, "B": 30}
+    prefill_blocks = {"A": list(range(0, 12)), "B": list(range(12, 43))}           # B ends in a partial block
+    starts = {"A": 0, "B": n_tok["A"]}
+    metas = [ReqMeta(r, i, n_tok[r], 0, n_tok[r], 0, 0, prefill_blocks[r], starts[r], n_tok[r]) for i, r in enumerate(n_tok)]
+    q_pre = [H.randn_bf16(rng, (n_tok["A"] + n_tok["B"], HQ, D)) for _ in range(LAYERS)]
+    run.step(metas, [dev_bf16(q) for q in q_pre], KVStarMultiStepSparseMetaData())
+
+    pruned, reps = {}, {}
+    for l in range(LAYERS):
+        for r in n_tok:
+            k = H.bf16_to_f32(run.kv_host[l][0][prefill_blocks[r][: n_full[r]]]).reshape(-1, HKV, D)
+            want_channels = np.argsort(-np.abs(k).astype(np.float64).mean(0), axis=-1)[:, : D // 4]
+            pr = ks.req_states[r].pruned[l].cpu().numpy()
+            assert [set(a) for a in pr] == [set(a) for a in want_channels]
+            pruned[l, r] = pr
+            want = oracle.kvstar_block_repre(run.kv_host[l][0], np.asarray(prefill_blocks[r][: n_full[r]], np.int32), pr, 2)
+            got = ks.tables[l][torch.tensor(ks.req_states[r].slots, device=DEV)].view(torch.int16).cpu().numpy().view(np.uint16)
+            assert np.array_equal(got, want)
+            reps[l, r] = want
+            assert f"{block_hash(r, n_full[r] - 1)}_0" in store.slot_of
+
+    def half_bits(q_u16):
+        return H.f32_to_f16_bits(H.bf16_to_f32(q_u16))
+
+    def check(l, r, group_u16, targets):
+        mid = reps[l, r][1: n_full[r] - 2]
+        s = oracle.kvstar_scores(half_bits(group_u16), mid, pruned[l, r])
+        k = len(targets)
+        best = np.sort(s)[::-1][:k]
+        srcs = []
+        for dst in targets:
+            hit = [j for j in range(len(mid)) if torch.equal(run.kv[l][0][dst], dev_bf16(run.kv_host[l][0][prefill_blocks[r][1 + j]]))]
+            assert len(hit) == 1
+            assert torch.equal(run.kv[l][1][dst], dev_bf16(run.kv_host[l][1][prefill_blocks[r][1 + hit[0]]]))
+            srcs.append(hit[0])
+        assert len(set(srcs)) == k
+        np.testing.assert_allclose(s[srcs], best, rtol=2e-3)           # the k largest votes, in descending order
+
+    k_mid = {"A": 3, "B": 7}                                                       # ceil(9 / 4), ceil(27 / 4)
+    decode_blocks = {"A": list(range(50, 50 + 1 + 3 + 2)), "B": list(range(60, 60 + 1 + 7 + 3))}
+    for l in range(LAYERS):
+        for r in n_tok:
+            run.kv[l][:, decode_blocks[r]] = 0
+    q_dec = {}
+    for step in range(1, 10):
+        metas = [ReqMeta(r, i, n_tok[r], step, 1, n_tok[r] + step - 1, 0, decode_blocks[r], i, 1) for i, r in enumerate(n_tok)]
+        q_dec[step] = [H.randn_bf16(rng, (2, HQ, D)) for _ in range(LAYERS)]
+        if step == 9:
+            for l in range(LAYERS):
+                for r in n_tok:
+                    run.kv[l][:, decode_blocks[r][1: 1 + k_mid[r]]] = 0
+        run.step(metas, [dev_bf16(q) for q in q_dec[step]], KVStarMultiStepSparseMetaData())
+        for l in range(LAYERS):
+            for i, r in enumerate(n_tok):
+                targets = decode_blocks[r][1: 1 + k_mid[r]]
+                if step == 1:
+                    check(l, r, q_pre[l][starts[r] + n_tok[r] - 8: starts[r] + n_tok[r]], targets)
+                    assert torch.equal(run.kv[l][0][decode_blocks[r][0]], dev_bf16(run.kv_host[l][0][prefill_blocks[r][0]]))
+                    assert torch.equal(run.kv[l][1][decode_blocks[r][-1]], dev_bf16(run.kv_host[l][1][prefill_blocks[r][-1]]))
+                if step == 9:
+                    check(l, r, np.stack([q_dec[t][l][i] for t in range(1, 9)]), targets)
+    ks.request_finished_in_worker("A")
+    assert "A" not in ks.req_states and len(ks.pool.allocated) == n_full["B"]
     store.close()
 
 

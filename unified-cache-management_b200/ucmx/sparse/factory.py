@@ -34,3 +34,4 @@ class UcmSparseFactory:
 UcmSparseFactory.register_sparse_method("ESA", "ucmx.sparse.esa", "ESA")
 UcmSparseFactory.register_sparse_method("KvComp", "ucmx.sparse.kvcomp", "KvComp")
 UcmSparseFactory.register_sparse_method("GSA", "ucmx.sparse.gsa", "GSA")
+UcmSparseFactory.register_sparse_method("KVStarMultiStep", "ucmx.sparse.kvstar", "KVStarMultiStep")
