@@ -309,6 +309,71 @@ def ref_retrieval_backend():
     return mod
 
 
+def have_prefetch_ref() -> bool:
+    return os.path.isdir(_REF_DIR) and any(f.startswith("gsa_prefetch") for f in os.listdir(_REF_DIR))
+
+
+def ref_gsa_prefetch():
+    """The reference's GSA prefetch engine (ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp + pybinds.cpp), compiled
+    unmodified into its own Python module."""
+    import torch  # noqa: F401  (the module links against libtorch)
+    if "gsa_prefetch" in sys.modules:
+        return sys.modules["gsa_prefetch"]
+    name = [f for f in os.listdir(_REF_DIR) if f.startswith("gsa_prefetch")][0]
+    spec = importlib.util.spec_from_file_location("gsa_prefetch", os.path.join(_REF_DIR, name))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["gsa_prefetch"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def ref_prefetch_rounds(n_layers, block_table, owned_idx, free_idx, rounds, req_id=7, bs_index=1, idx_dtype="int32"):
+    """Runs the reference engine for one request through several selection rounds, the way
+    ucm/sparse/gsa/prefetch/prefetch_engine.py drives it (:88-94 construction, :329-379 first state, :203-233 a round).
+
+    block_table[i]: physical block of logical block i; owned_idx: the logical blocks resident at the start
+    (set_blocks_map's selectIndex); free_idx: those of them whose blocks start on the free list, in list order;
+    rounds: list of integer arrays [n_layers, k] - the selected logical blocks of every layer.
+    Returns one dict per round with, per layer: the block table the engine wrote, its load list (blocks, logical
+    indices of all misses), the free list it left behind and its block -> logical map."""
+    import time
+
+    import torch
+    mod = ref_gsa_prefetch()
+    max_bs, max_len = bs_index + 2, len(block_table) + 4
+    free_block = torch.zeros((n_layers, max_bs, max_len), dtype=torch.int32)
+    free_len = torch.zeros((n_layers, max_bs), dtype=torch.int32)
+    tables = [torch.zeros((n_layers, max_bs, max_len), dtype=torch.int32) for _ in range(2)]
+    table_len = [torch.zeros((n_layers, max_bs), dtype=torch.int32) for _ in range(2)]
+    eng = mod.GSAPrefetchEngineC(free_block, tables[0], free_len, table_len[0], False)
+    eng.set_blocks_map(req_id, [int(b) for b in block_table], [int(i) for i in owned_idx])
+    free_block[:, bs_index, : len(free_idx)] = torch.tensor([int(block_table[i]) for i in free_idx], dtype=torch.int32)
+    free_len[:, bs_index] = len(free_idx)
+    out = []
+    for step, sel in enumerate(rounds):
+        sel = np.asarray(sel)
+        k = sel.shape[1]
+        buf = torch.zeros((n_layers, 1, max_len), dtype=getattr(torch, idx_dtype))
+        buf[:, 0, :k] = torch.from_numpy(sel.astype(np.int64))
+        t, tl = tables[step % 2], table_len[step % 2]            # the caller alternates two tables (:205-214)
+        eng.set_blocks_table_info(t, tl, buf, step)
+        eng.run_async_prefetch_bs([req_id], [k], [bs_index], 0)
+        deadline = time.time() + 30
+        while not eng.get_prefetch_status():
+            if time.time() > deadline:
+                raise RuntimeError("reference prefetch engine did not finish")
+            time.sleep(0.001)
+        loads, misses, bmap = eng.obtain_load_blocks(), eng.obtain_miss_idxs(), eng.obtain_blocks_map()
+        out.append({
+            "table": [t[l, bs_index, : int(tl[l, bs_index])].tolist() for l in range(n_layers)],
+            "load_blocks": [list(loads[0][l]) for l in range(n_layers)],
+            "miss_idx": [list(misses[0][l]) for l in range(n_layers)],
+            "free": [free_block[l, bs_index, : int(free_len[l, bs_index])].tolist() for l in range(n_layers)],
+            "blocks_map": [{int(b): int(i) for b, i in bmap[req_id][l].items()} for l in range(n_layers)],
+        })
+    return out
+
+
 _nfs = None
 
 

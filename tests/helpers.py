@@ -120,3 +120,61 @@ def case_gsa_heads(seed=7001):
         exc[a + 4] = 1
     exc[off[1] - 1] = 1           # flagged both ways: exclude wins
     return reps, q, off, ids, inc, exc
+
+
+# ---------------------------------------------------------------- resident-set remap scenarios
+REMAP_SCENARIOS = {
+    # name: (seed, layers, logical blocks, resident at start, on the free list at start, selected per round, rounds,
+    #        ascending selections, index dtype)
+    "steady": (7101, 3, 64, 24, 6, 16, 6, True, "int32"),
+    "free_list_runs_out": (7102, 2, 48, 12, 2, 10, 4, True, "int32"),        # more misses than free blocks
+    "all_hits_then_all_misses": (7103, 2, 40, 10, 4, 6, 3, True, "int64"),
+    "unsorted_selection": (7104, 2, 64, 20, 8, 12, 5, False, "int64"),
+    "one_block": (7105, 1, 8, 1, 1, 1, 4, True, "int32"),
+}
+
+
+def remap_scenario(name):
+    """Seeded inputs of one life cycle of a request in the prefetch engine.  The blocks on the initial free list
+    are given in ascending physical order - the order every later free list has."""
+    seed, L, n_logical, n_owned, n_free, k, n_rounds, ascending, idx_dtype = REMAP_SCENARIOS[name]
+    rng = np.random.default_rng(seed)
+    block_table = [int(x) for x in rng.permutation(4 * n_logical)[:n_logical] + 1]
+    owned = sorted(int(x) for x in rng.permutation(n_logical)[:n_owned])
+    free_idx = sorted((int(x) for x in rng.permutation(owned)[:n_free]), key=lambda i: block_table[i])
+    rounds = []
+    for r in range(n_rounds):
+        sel = np.stack([rng.permutation(n_logical)[:k] for _ in range(L)])
+        if name == "all_hits_then_all_misses":
+            held = [i for i in owned if i not in free_idx]
+            sel = np.stack([np.asarray(held[:k]) if r == 0 else
+                            np.asarray([i for i in range(n_logical) if i not in owned][r * k: (r + 1) * k]) for _ in range(L)])
+        if ascending:
+            sel = np.sort(sel, axis=1)
+        rounds.append(sel.astype(np.int64))
+    return {"n_layers": L, "block_table": block_table, "owned_idx": owned, "free_idx": free_idx, "rounds": rounds,
+            "idx_dtype": idx_dtype}
+
+
+def remap_replay(oracle, sc):
+    """The scenario through the CPU checker, in the shape oracle.ref_prefetch_rounds returns."""
+    bt = sc["block_table"]
+    order = sorted(sc["owned_idx"], key=lambda i: bt[i])
+    phys = np.asarray([bt[i] for i in order], np.int32)
+    out = []
+    logical = [np.asarray(order, np.int32) for _ in range(sc["n_layers"])]
+    free = [np.asarray([1 if i in sc["free_idx"] else 0 for i in order], np.uint8) for _ in range(sc["n_layers"])]
+    for sel in sc["rounds"]:
+        res = {"table": [], "load_blocks": [], "miss_idx": [], "free": [], "blocks_map": []}
+        for l in range(sc["n_layers"]):
+            before = set(int(x) for x in logical[l])
+            logical[l], free[l], table, ll, lp = oracle.remap_resident(logical[l], free[l], phys, sel[l].astype(np.int32))
+            pairs = sorted((int(s), int(t)) for s, t in zip(sel[l], table) if t >= 0)      # the engine lists by logical index
+            res["table"].append([t for _, t in pairs])
+            res["load_blocks"].append([int(x) for x in lp])
+            assert [int(x) for x in ll] == [int(s) for s in sel[l] if int(s) not in before][: len(ll)]
+            res["miss_idx"].append([int(s) for s in sel[l] if int(s) not in before])
+            res["free"].append([int(p) for p, f in zip(phys, free[l]) if f])
+            res["blocks_map"].append({int(p): int(x) for p, x in zip(phys, logical[l])})
+        out.append(res)
+    return out

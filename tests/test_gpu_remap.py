@@ -89,3 +89,36 @@ def test_remap_feeds_the_block_transfer(oracle):
     t, s = table.cpu().numpy(), sel.cpu().numpy().reshape(-1)
     for j in range(20):
         assert np.array_equal(got[t[j]], store[s[j]])
+
+
+@pytest.mark.parametrize("name", list(H.REMAP_SCENARIOS))
+def test_remap_replays_recorded_prefetch_engine(name):
+    """The device kernel against recorded runs of the reference's GSAPrefetchEngineC itself
+    (tests/golden/remap_rounds.json): every layer of a scenario is one entry of a single ragged launch."""
+    import json
+    import os
+
+    from ucmx import ops
+    with open(os.path.join(os.path.dirname(__file__), "golden", "remap_rounds.json")) as f:
+        recorded = {c["name"]: c["rounds"] for c in json.load(f)}[name]
+    sc = H.remap_scenario(name)
+    L, bt = sc["n_layers"], sc["block_table"]
+    order = sorted(sc["owned_idx"], key=lambda i: bt[i])
+    phys = np.asarray([bt[i] for i in order], np.int32)
+    ns = len(order)
+    d_logical = dev(np.tile(np.asarray(order, np.int32), L))
+    d_free = dev(np.tile(np.asarray([1 if i in sc["free_idx"] else 0 for i in order], np.uint8), L), np.uint8)
+    d_phys, d_slot_off = dev(np.tile(phys, L)), dev(np.arange(L + 1) * ns)
+    for sel, want in zip(sc["rounds"], recorded):
+        k = sel.shape[1]
+        table, ll, lp, lc = ops.remap_resident(d_logical, d_free, d_phys, d_slot_off, dev(sel.reshape(-1)), dev(np.arange(L + 1) * k),
+                                               max_logical=len(bt), max_slots=ns)
+        table, ll, lp, lc = table.cpu().numpy(), ll.cpu().numpy(), lp.cpu().numpy(), lc.cpu().numpy()
+        logical, free = d_logical.cpu().numpy().reshape(L, ns), d_free.cpu().numpy().reshape(L, ns)
+        for l in range(L):
+            pairs = sorted((int(s), int(t)) for s, t in zip(sel[l], table[l * k:(l + 1) * k]) if t >= 0)
+            assert [t for _, t in pairs] == want["table"][l]
+            assert lp[l * k: l * k + lc[l]].tolist() == want["load_blocks"][l]
+            assert ll[l * k: l * k + lc[l]].tolist() == want["miss_idx"][l][: lc[l]]
+            assert [int(p) for p, f in zip(phys, free[l]) if f] == want["free"][l]
+            assert {str(int(p)): int(x) for p, x in zip(phys, logical[l])} == want["blocks_map"][l]

@@ -151,3 +151,46 @@ def test_gsa_device_weights_match_reference_expression(oracle):
     fin = np.isfinite(want)
     assert np.all(np.abs(got[fin] - want[fin]) <= 8e-3 * np.maximum(np.abs(got[fin]), 0.5))
     assert np.isneginf(got[off[1] - 1])          # flagged both ways: excluded
+
+
+def _same_rounds(mine, ref):
+    assert len(mine) == len(ref)
+    for a, b in zip(mine, ref):
+        maps = [{int(k): int(v) for k, v in m.items()} for m in b["blocks_map"]]
+        assert a["table"] == b["table"]                 # block table, in logical order
+        assert a["load_blocks"] == b["load_blocks"]     # blocks taken from the free list, in miss order
+        assert a["miss_idx"] == b["miss_idx"]
+        assert a["free"] == b["free"]                   # the free list left behind
+        assert a["blocks_map"] == maps
+
+
+@pytest.mark.parametrize("name", list(H.REMAP_SCENARIOS))
+def test_remap_matches_recorded_prefetch_engine(oracle, name):
+    """Recorded runs of the reference's GSAPrefetchEngineC (kvcache_pre.cpp compiled unmodified): tables, load
+    lists, free lists and block maps of every layer after every round, all identical."""
+    import json
+    with open(os.path.join(os.path.dirname(__file__), "golden", "remap_rounds.json")) as f:
+        recorded = {c["name"]: c["rounds"] for c in json.load(f)}
+    _same_rounds(H.remap_replay(oracle, H.remap_scenario(name)), recorded[name])
+
+
+def test_remap_matches_live_prefetch_engine(oracle):
+    """Random life cycles against the compiled reference itself, when it has been built here."""
+    if not oracle.have_prefetch_ref():
+        pytest.skip("the reference prefetch engine is not built")
+    rng = np.random.default_rng(7200)
+    for it in range(25):
+        n_logical = int(rng.integers(4, 80))
+        n_owned = int(rng.integers(1, n_logical))
+        block_table = [int(x) for x in rng.permutation(3 * n_logical)[:n_logical] + 1]
+        owned = sorted(int(x) for x in rng.permutation(n_logical)[:n_owned])
+        n_free = int(rng.integers(0, n_owned + 1))
+        free_idx = sorted((int(x) for x in rng.permutation(owned)[:n_free]), key=lambda i: block_table[i])
+        k = int(rng.integers(1, n_logical + 1))
+        L = int(rng.integers(1, 4))
+        rounds = [np.stack([np.sort(rng.permutation(n_logical)[:k]) if it % 2 else rng.permutation(n_logical)[:k]
+                            for _ in range(L)]).astype(np.int64) for _ in range(int(rng.integers(1, 6)))]
+        sc = {"n_layers": L, "block_table": block_table, "owned_idx": owned, "free_idx": free_idx, "rounds": rounds,
+              "idx_dtype": "int32" if it % 3 else "int64"}
+        ref = oracle.ref_prefetch_rounds(L, block_table, owned, free_idx, rounds, req_id=it, idx_dtype=sc["idx_dtype"])
+        _same_rounds(H.remap_replay(oracle, sc), ref)
