@@ -177,7 +177,9 @@ __global__ void __launch_bounds__(kThreads, 2)
 hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
 {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // rounded up to 1 KiB (the swizzle's period) by pointer arithmetic on the shared array, so that every pointer
+    // derived from it is known to be a shared-memory pointer and its loads and stores are shared-memory instructions
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* sA = smem;                                   // kStagesA tiles
     unsigned char* sB = smem + kStagesA * kTileBytes;            // W^T as the B operand: row = bit, K = d
     float* wnorm = reinterpret_cast<float*>(sB + kTileBytes);    // |w_j|

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 kvstar_partial_tc_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
 {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     unsigned char* sA = smem;                                            // G*cpg chunks of 16 KiB
     unsigned char* sB = sA + (size_t)p.G * p.cpg * kChunkA;              // stages of tile_bytes
     KsBarriers* bars = reinterpret_cast<KsBarriers*>(sB + (size_t)p.stages * p.tile_bytes);
@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 kvstar_partial_pair_kernel(const __grid_constant__ CUtensorMap tmap, KsParams p)
 {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     unsigned char* sA = smem;                                  // 4 chunks of 16 KiB
     unsigned char* sB = sA + 4 * kChunkA;                      // 2 stages: chunk c at c*16 KiB, second block 8 KiB further
     KsBarriers* bars = reinterpret_cast<KsBarriers*>(sB + 2 * kPairStage);
