@@ -58,24 +58,40 @@ __device__ __forceinline__ uint32_t from_key(uint32_t key, bool is_float)
     return (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
 }
 
-// exclusive prefix sum of a 0/1 flag over the thread block, in thread order; returns the prefix
-// and leaves the block total in `total`.  s_warp needs 32 ints.  Two barriers.
-__device__ __forceinline__ int block_excl_scan_flag(bool flag, int* s_warp, int& total)
+// exclusive prefix sums of two small counts over the thread block, in thread order (one pass, two barriers);
+// the block totals come back in tot_a / tot_b.  s_warp needs 64 ints.
+__device__ __forceinline__ void block_excl_scan_pair(int a, int b, int* s_warp, int& before_a, int& before_b, int& tot_a, int& tot_b)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-    const unsigned b = __ballot_sync(0xffffffffu, flag);
-    const int in_warp = __popc(b & ((1u << lane) - 1u));
-    if (lane == 0) s_warp[warp] = __popc(b);
-    __syncthreads();
-    int before = 0, tot = 0;
-    for (int w = 0; w < nwarp; ++w) {
-        const int v = s_warp[w];
-        if (w < warp) before += v;
-        tot += v;
+    int ia = a, ib = b;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int va = __shfl_up_sync(0xffffffffu, ia, o), vb = __shfl_up_sync(0xffffffffu, ib, o);
+        if (lane >= o) {
+            ia += va;
+            ib += vb;
+        }
+    }
+    if (lane == 31) {
+        s_warp[warp] = ia;
+        s_warp[32 + warp] = ib;
     }
     __syncthreads();
-    total = tot;
-    return before + in_warp;
+    int ba = 0, bb = 0, ta = 0, tb = 0;
+    for (int w = 0; w < nwarp; ++w) {
+        const int va = s_warp[w], vb = s_warp[32 + w];
+        if (w < warp) {
+            ba += va;
+            bb += vb;
+        }
+        ta += va;
+        tb += vb;
+    }
+    __syncthreads();
+    before_a = ba + ia - a;
+    before_b = bb + ib - b;
+    tot_a = ta;
+    tot_b = tb;
 }
 
 template <bool PEER>
@@ -83,7 +99,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 {
     extern __shared__ __align__(16) unsigned long long s_sort[];  // score-descending order only
     __shared__ uint32_t s_hist[4][256];  // one histogram per radix pass, cleared once
-    __shared__ int s_warp[32];
+    __shared__ int s_warp[64];
     __shared__ uint32_t s_prefix;
     __shared__ int s_krem;
 
@@ -196,6 +212,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
         for (int pass = 0; pass < 4; ++pass) {
             const int shift = 24 - 8 * pass;
             const uint32_t prefix = s_prefix;
+            // (plain shared-memory adds: aggregating equal buckets within a warp by votes or match was measured slower)
             for (int i = lo + tid; i < hi; i += blockDim.x) {
                 const uint32_t key = to_key(sc[i], is_float);
                 if ((key & mask) == prefix) atomicAdd(&s_hist[pass][(key >> shift) & 255u], 1u);
@@ -238,42 +255,57 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
         need = s_krem;
     }
 
-    // ordered compaction over all positions
+    // Ordered compaction over all positions.  Every thread owns a contiguous run of positions, counts what it will
+    // surely take (forced windows, keys above the threshold) and its keys equal to the threshold; one scan of the two
+    // counts over the block gives each run its first output place (ties go to the lowest positions: of the equal keys
+    // before a run, the first `need` are taken), then the run is written out in order.
     const bool desc = p.order == UCMX_ORDER_SCORE_DESC;
-    int out_base = 0, eq_base = 0;
-    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
-        const int i = c0 + tid;
-        bool forced = false, gt = false, eq = false;
-        uint32_t key = 0;
-        if (i < n) {
-            forced = (i < fstart) || (i >= n - fend);
-            const bool in_range = i >= lo && i < hi;
-            if (in_range || forced) key = to_key(sc[i], is_float);
-            if (in_range && kk > 0) {
-                if (all) gt = true;
-                else {
-                    gt = key > T;
-                    eq = key == T;
+    const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int i_begin = min(tid * per, n), i_end = min(i_begin + per, n);
+    const bool ranged = kk > 0;
+    int sure = 0, ties = 0;
+    for (int i = i_begin; i < i_end; ++i) {
+        const bool forced = (i < fstart) || (i >= n - fend);
+        if (forced) {
+            ++sure;
+        } else if (ranged && i >= lo && i < hi) {
+            if (all) {
+                ++sure;
+            } else {
+                const uint32_t key = to_key(sc[i], is_float);
+                sure += key > T;
+                ties += key == T;
+            }
+        }
+    }
+    int sure_before, ties_before, sure_total, ties_total;
+    block_excl_scan_pair(sure, ties, s_warp, sure_before, ties_before, sure_total, ties_total);
+    int pos = sure_before + min(ties_before, need);
+    int tie_rank = ties_before;
+    for (int i = i_begin; i < i_end; ++i) {
+        const bool forced = (i < fstart) || (i >= n - fend);
+        const bool in_range = i >= lo && i < hi;
+        if (!forced && !(ranged && in_range)) continue;
+        const uint32_t key = to_key(sc[i], is_float);
+        bool take = forced;
+        if (!forced) {
+            if (all) take = true;
+            else if (key > T) take = true;
+            else if (key == T) take = tie_rank++ < need;
+        }
+        if (take) {
+            if (pos < cap) {
+                if (desc) {
+                    s_sort[pos] = ((unsigned long long)key << 32) | (unsigned long long)(~(uint32_t)i);
+                } else {
+                    p.out_idx[orow + pos] = p.id_map ? __ldg(p.id_map + base + i) : i;
+                    if (p.out_scores) p.out_scores[orow + pos] = from_key(key, is_float);
                 }
             }
+            ++pos;
         }
-        int eq_total = 0;
-        int eq_rank = 0;
-        if (!all && kk > 0) eq_rank = eq_base + block_excl_scan_flag(eq, s_warp, eq_total);
-        const bool take = forced || gt || (eq && eq_rank < need);
-        int take_total = 0;
-        const int pos = out_base + block_excl_scan_flag(take, s_warp, take_total);
-        if (take && pos < cap) {
-            if (desc) {
-                s_sort[pos] = ((unsigned long long)key << 32) | (unsigned long long)(~(uint32_t)i);
-            } else {
-                p.out_idx[orow + pos] = p.id_map ? __ldg(p.id_map + base + i) : i;
-                if (p.out_scores) p.out_scores[orow + pos] = from_key(key, is_float);
-            }
-        }
-        out_base += take_total;
-        eq_base += eq_total;
     }
+    const int out_base = sure_total + min(ties_total, need);
     const int cnt = min(out_base, cap);
     if (tid == 0) p.out_counts[r] = cnt;
 
@@ -296,22 +328,27 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
         while (P < cnt) P <<= 1;
         for (int i = cnt + tid; i < P; i += blockDim.x) s_sort[i] = 0ull;
         __syncthreads();
+        // Bitonic network, one thread per compare-exchange: pair t of a stage with distance j is the elements
+        // (t / j) * 2j + t % j and j further up.  For j <= 32 the 32 pairs of a warp lie in 64 consecutive elements
+        // that no other warp touches, so between two such stages the warp alone has to meet; the block meets only
+        // around the stages that reach further.
         for (int k2 = 2; k2 <= P; k2 <<= 1) {
             for (int j = k2 >> 1; j > 0; j >>= 1) {
-                for (int i = tid; i < P; i += blockDim.x) {
-                    const int ixj = i ^ j;
-                    if (ixj > i) {
-                        const unsigned long long a = s_sort[i], b = s_sort[ixj];
-                        const bool up = (i & k2) == 0;  // descending overall
-                        if (up ? (a < b) : (a > b)) {
-                            s_sort[i] = b;
-                            s_sort[ixj] = a;
-                        }
+                for (int t = tid; t < (P >> 1); t += blockDim.x) {
+                    const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1)), ixj = i | j;
+                    const unsigned long long a = s_sort[i], b = s_sort[ixj];
+                    const bool up = (i & k2) == 0;  // descending overall
+                    if (up ? (a < b) : (a > b)) {
+                        s_sort[i] = b;
+                        s_sort[ixj] = a;
                     }
                 }
-                __syncthreads();
+                const int j_next = j > 1 ? (j >> 1) : k2;          // first distance of the next merge is k2
+                if (j > 32 || j_next > 32) __syncthreads();
+                else __syncwarp();
             }
         }
+        __syncthreads();
         for (int j = tid; j < cnt; j += blockDim.x) {
             const unsigned long long v = s_sort[j];
             const int i = (int)(~(uint32_t)(v & 0xffffffffull));
