@@ -269,6 +269,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
+    ap.add_argument("--no-e2e-graph", action="store_true", help="end-to-end step launched call by call instead of replayed from its CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
     ap.add_argument("--workload", default="decode64", choices=["decode64", "tp-long", "offload"],
@@ -439,6 +440,8 @@ def main():
     e2e_s = float("nan")
     if not args.profile_case:
         eng.alloc_host()
+        if not tp and not args.no_e2e_graph:
+            eng.capture_host()                 # copies and kernels of both streams in one graph; step_host() replays it
         for _ in range(2):
             eng.step_host()
         barrier()
@@ -503,7 +506,8 @@ def main():
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_s * 1e3,
-                    "h2d_bytes_per_step": eng.h2d_bytes_per_step, "d2h_bytes_per_step": eng.d2h_bytes_per_step},
+                    "h2d_bytes_per_step": eng.h2d_bytes_per_step, "d2h_bytes_per_step": eng.d2h_bytes_per_step,
+                    "cuda_graph": eng.host_graph is not None},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "cpu_baseline": cpu_baseline,

@@ -74,6 +74,7 @@ class DecodeRetrievalEngine:
         self.q_host: Optional[torch.Tensor] = None
         self.sel_host: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.host_graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = self.L * (3 if with_kv_pool else 2) + (1 if with_kv_pool else 0)
         self._pool_all = None
 
@@ -173,14 +174,10 @@ class DecodeRetrievalEngine:
         self._q_ready = [torch.cuda.Event() for _ in range(self.L)]
         self._layer_done = [torch.cuda.Event() for _ in range(self.L)]
 
-    def step_host(self) -> torch.Tensor:
-        """End to end with host buffers: each layer's queries come from pinned host memory and its
-        selected block ids and counts go back to pinned host memory; returns after a final sync.
-
-        The copies run on their own stream: layer l's kernels wait for the event of their own queries
-        only, and its results leave while layer l+1 computes, so the host link works beside the kernels
-        instead of between them."""
-        main = torch.cuda.current_stream(self.device)
+    def _enqueue_host_step(self, main: torch.cuda.Stream) -> None:
+        """The end-to-end step as stream work, without the final wait: the copies run on their own stream; layer
+        l's kernels wait for the event of their own queries only, and its results leave while layer l+1 computes,
+        so the host link works beside the kernels instead of between them."""
         cs = self._copy_stream
         cs.wait_stream(main)                               # earlier work on the buffers has finished
         with torch.cuda.stream(cs):
@@ -198,6 +195,28 @@ class DecodeRetrievalEngine:
                 self.sel_host[l].copy_(self.sel_ids[l], non_blocking=True)
                 self.cnt_host[l].copy_(self.sel_counts[l], non_blocking=True)
         main.wait_stream(cs)
+
+    def capture_host(self) -> None:
+        """Record the end-to-end step - host-to-device copies, kernels, device-to-host copies, on both streams -
+        into one CUDA graph; step_host() then replays it.  The pinned host buffers are part of the graph, so the
+        caller keeps writing queries into q_host and reading selections from sel_host / cnt_host."""
+        if self.score_reduce is not None or self.peer_exchange is not None:
+            raise RuntimeError("the captured end-to-end step covers the single-rank path only")
+        for _ in range(2):                                 # lazily initialised state is set up outside capture
+            self.step_host()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._enqueue_host_step(torch.cuda.current_stream(self.device))
+        self.host_graph = graph
+
+    def step_host(self) -> torch.Tensor:
+        """End to end with host buffers: each layer's queries come from pinned host memory and its
+        selected block ids and counts go back to pinned host memory; returns after a final sync."""
+        main = torch.cuda.current_stream(self.device)
+        if self.host_graph is not None:
+            self.host_graph.replay()
+        else:
+            self._enqueue_host_step(main)
         main.synchronize()
         return self.sel_host
 
