@@ -1,6 +1,6 @@
 """Benchmark of the decode-step sparse-KV retrieval path (pool -> score -> top-k -> gather).
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--graph]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-graph]
 
 Workload (default): 64 decode requests with context lengths uniform in [8192, 131072] tokens
 (seeded, rounded up to 128-token blocks), Llama-3-8B KV shapes (32 query heads, 8 KV heads,
@@ -268,7 +268,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step call by call instead of replaying its CUDA graph")
     ap.add_argument("--no-e2e-graph", action="store_true", help="end-to-end step launched call by call instead of replayed from its CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
@@ -352,16 +352,28 @@ def main():
     row_bytes = eng.H * eng.D * 2
     prefill_gbs = batch.total * (eng.T * row_bytes + row_bytes) / prefill_ms / 1e6
 
-    if args.graph:
+    # The step is replayed from a CUDA graph unless --no-graph (or a tensor-parallel run, whose exchange is driven
+    # from the host).  The gather launches are timed by events around them.  An event record costs about 6 us of
+    # stream time, call by call and as a graph node alike, so in graph mode the last of the K timed steps replays
+    # a second graph that has an event pair around each of its gathers and the other K-1 replay the plain one;
+    # call by call, every fourth gather launch of every step carries a pair.
+    use_graph = not args.no_graph and not tp and not args.profile_case
+    timed_graph = None
+    if use_graph:
+        gev = [(torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True))
+               for _ in range(eng.L)]
+        timed_graph = eng.capture(gather_events=gev)
         eng.capture()
+        timed_graph.replay()
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()
 
     # ---- timed region: K steps, device-resident inputs; the gather launches carry their own events
-    n_gather = args.steps * eng.L
-    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_gather)] \
-        if not args.graph else []
+    every = 1 if args.profile_case else 4
+    if not use_graph:
+        gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(args.steps * ((eng.L + every - 1) // every))]
     sampler = ClockSampler(local_rank)
     launches_before = _native.launch_count
     barrier()
@@ -369,9 +381,10 @@ def main():
     sampler.start()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
-    if args.graph:
-        for _ in range(args.steps):
+    if use_graph:
+        for _ in range(args.steps - 1):
             eng.step()
+        timed_graph.replay()
     else:
         gi = 0
         for _ in range(args.steps):
@@ -379,16 +392,19 @@ def main():
             for l in range(eng.L):
                 eng.score_layer(l)
                 eng.topk_layer(l)
-                a, b = gev[gi]
-                gi += 1
-                a.record()
-                eng.gather_layer(l)
-                b.record()
+                if l % every == 0:
+                    a, b = gev[gi]
+                    gi += 1
+                    a.record()
+                    eng.gather_layer(l)
+                    b.record()
+                else:
+                    eng.gather_layer(l)
     t_end.record()
     torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    launches = (_native.launch_count - launches_before) if not args.graph else eng.launches_per_step * args.steps
+    launches = (_native.launch_count - launches_before) if not use_graph else eng.launches_per_step * args.steps
     elapsed_ms = t_start.elapsed_time(t_end)
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
@@ -467,7 +483,7 @@ def main():
         roofline = {"kernel": "xfer_bulk_kernel (gather of selected K,V blocks, one layer)", "bound": "hbm",
                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": traffic, "algorithmic_bytes_per_launch": eng.bytes_gather_layer(),
-                    "avg_launch_us": gather_avg_ms * 1e3}
+                    "avg_launch_us": gather_avg_ms * 1e3, "launches_timed": len(gather_ms)}
     stage_gbs = {
         "score": eng.bytes_score_layer() / (stages_us["score"] * 1e-6) / 1e9,
         "gather": eng.bytes_gather_layer() / (stages_us["gather"] * 1e-6) / 1e9,
@@ -497,12 +513,12 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(batch, extra={"cuda_graph": bool(args.graph), "layers": eng.L}) if not tp else {
+            "config": workload_config(batch, extra={"cuda_graph": use_graph, "layers": eng.L}) if not tp else {
                 "workload": "long-context sharded retrieval: 8 requests x 1 048 576 tokens (8192 blocks each), Qwen2-72B-like "
                             "KV (64q/8kv heads, head_dim 128), KV heads split over the GPUs, fp32 all-reduce of 65 536 block "
                             "scores before top-k 2048, gather of the selected K,V head slices",
                 "layers": eng.L, "tp": world, "heads_per_rank": eng.H, "parallelism": f"tp{world} over KV heads", "allreduce": args.allreduce if world > 1 else "none",
-                "l2_policy": "inputs larger than L2 per step", "cuda_graph": bool(args.graph)},
+                "l2_policy": "inputs larger than L2 per step", "cuda_graph": use_graph},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_s * 1e3,

@@ -128,12 +128,17 @@ class DecodeRetrievalEngine:
     def gather_layer(self, layer: int) -> None:
         ops.gather_blocks([self.kv_pool[0], self.kv_pool[1]], self.sel_ids[layer], self.staging)
 
-    def layer_step(self, layer: int) -> None:
-        """Score, select and gather one layer (pooling of new blocks is done for all layers at the start of a step)."""
+    def layer_step(self, layer: int, gather_events=None) -> None:
+        """Score, select and gather one layer (pooling of new blocks is done for all layers at the start of a step).
+        gather_events: an optional (before, after) pair of CUDA events recorded around the gather launch."""
         self.score_layer(layer)
         self.topk_layer(layer)
         if self.kv_pool is not None:
+            if gather_events is not None:
+                gather_events[0].record()
             self.gather_layer(layer)
+            if gather_events is not None:
+                gather_events[1].record()
 
     # ------------------------------------------------------------------------------------ steps
     def step(self) -> None:
@@ -146,8 +151,13 @@ class DecodeRetrievalEngine:
         for l in range(self.L):
             self.layer_step(l)
 
-    def capture(self) -> None:
-        """Record the whole step once into a CUDA graph; later steps replay it (one launch)."""
+    def capture(self, gather_events=None) -> torch.cuda.CUDAGraph:
+        """Record the whole step once into a CUDA graph and return it.  Without events the graph also becomes the
+        one step() replays.
+        gather_events: optional list of one (before, after) pair of events per layer, created with
+        torch.cuda.Event(enable_timing=True, external=True); they become event-record nodes of the graph, so after
+        a replay they hold the times of that replay's gather launches.  (Such nodes cost about 6 us each, which
+        is why the instrumented graph is a separate one.)"""
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
@@ -162,8 +172,10 @@ class DecodeRetrievalEngine:
             if self.kv_pool is not None:
                 self.pool_all_layers()
             for l in range(self.L):
-                self.layer_step(l)
-        self.graph = graph
+                self.layer_step(l, None if gather_events is None else gather_events[l])
+        if gather_events is None:
+            self.graph = graph
+        return graph
 
     def alloc_host(self) -> None:
         self.q_host = torch.empty(self.q_dev.shape, dtype=torch.bfloat16).pin_memory()
