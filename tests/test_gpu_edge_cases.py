@@ -129,3 +129,38 @@ def test_argument_errors_are_status_codes():
     # the context is still healthy
     assert ops.pool_blocks(k, dev_i32([1, 2])).shape == (2, 2, 1, 64)
     assert N.device_error() == 0
+
+
+def test_topk_ties_cut_inside_a_threads_run(oracle):
+    """A few distinct score values over requests far larger than the thread block: every thread owns a run of
+    positions, the threshold value occurs thousands of times and only its first few positions may be taken."""
+    from ucmx import ops
+    rng = np.random.default_rng(123)
+    counts = [7000, 1025, 4096, 33]
+    off = H.ragged_offsets(counts)
+    s = rng.choice(np.array([-1.5, 0.0, 0.25, 0.25, 3.0], np.float32), int(off[-1])).astype(np.float32)
+    d_s = torch.from_numpy(s).to(DEV)
+    for ks in ([300, 200, 2048, 7], [6999, 1, 4095, 33], [129, 1024, 257, 0]):
+        k = np.asarray(ks, np.int32)
+        idx, sc, cnt = ops.topk_ragged(d_s, dev_i32(off), dev_i32(k), out_stride=7000 if max(ks) > 2048 else 2048,
+                                       order=ops.ORDER_INDEX_ASC)
+        idx, sc, cnt = idx.cpu().numpy(), sc.cpu().numpy(), cnt.cpu().numpy()
+        for r, n in enumerate(counts):
+            seg = s[off[r]:off[r + 1]]
+            want, _ = oracle.topk_esa(seg, int(k[r]))
+            want = np.sort(want)
+            assert cnt[r] == len(want) and np.array_equal(idx[r, :cnt[r]], want), (ks, r)
+            assert np.array_equal(sc[r, :cnt[r]], seg[want])
+        if max(ks) <= 8192:
+            idx, _, cnt = ops.topk_ragged(d_s, dev_i32(off), dev_i32(k), out_stride=max(max(ks), 1), want_scores=False)
+            idx, cnt = idx.cpu().numpy(), cnt.cpu().numpy()
+            for r in range(len(counts)):
+                want, _ = oracle.topk_esa(s[off[r]:off[r + 1]], int(k[r]))
+                assert np.array_equal(idx[r, :cnt[r]], want), (ks, r, "score order")
+        # forced windows on top (GSA)
+        idx, _, cnt = ops.topk_ragged(d_s, dev_i32(off), dev_i32(k), out_stride=7000, start_win=3, end_win=5,
+                                      window_mode=ops.WIN_FORCE, order=ops.ORDER_INDEX_ASC, want_scores=False)
+        idx, cnt = idx.cpu().numpy(), cnt.cpu().numpy()
+        for r in range(len(counts)):
+            want = oracle.topk_gsa(s[off[r]:off[r + 1]], int(k[r]), 3, 5, cap=7000)
+            assert cnt[r] == len(want) and np.array_equal(idx[r, :cnt[r]], want), (ks, r, "windows")
