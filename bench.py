@@ -253,7 +253,7 @@ def workload_config(batch, extra=None):
         "n_req": int(batch.n_req), "blocks_total_per_layer": int(batch.total), "selected_per_layer": int(batch.total_k),
         "layers": 32, "stages": "pool(64 new blocks of each of the 32 layers, one launch per step) + per layer score+topk+gather(K,V of selected)",
         "l2_policy": "inputs larger than L2: 2.3 GB of representatives and an 18 GB K/V pool are cycled per step",
-        "parallelism": "dp over requests",
+        "parallelism": "dp over requests: every GPU serves 64 requests of these lengths over its own block table and data",
     }
     if extra:
         cfg.update(extra)
@@ -335,7 +335,9 @@ def main():
                                     peer_exchange=peer)
     else:
         shape = LLAMA3_8B
-        batch = ragged_decode_batch(seed=2002 + rank, n_req=n_req)
+        # weak scaling: every rank serves requests of the same lengths (the same work per GPU) over its own block
+        # table, keys and queries
+        batch = ragged_decode_batch(seed=2002, n_req=n_req, table_seed=None if rank == 0 else 7007 + rank)
         eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank)
     eng.make_queries()
     torch.cuda.synchronize()

@@ -64,9 +64,11 @@ def _prefix(v: np.ndarray) -> np.ndarray:
 
 
 def ragged_decode_batch(seed: int = 2002, n_req: int = 64, min_ctx: int = 8192, max_ctx: int = 131072,
-                        block_tokens: int = 128, ratio: float = 0.05, min_k: int = 16) -> RaggedBatch:
+                        block_tokens: int = 128, ratio: float = 0.05, min_k: int = 16, table_seed=None) -> RaggedBatch:
     """Requests with context lengths uniform in [min_ctx, max_ctx], rounded up to whole blocks; a paged
-    pool with exactly one slot per block and a randomly permuted block table; k = max(min_k, ceil(ratio*n))."""
+    pool with exactly one slot per block and a randomly permuted block table; k = max(min_k, ceil(ratio*n)).
+    table_seed: a separate seed for the block table, so that several ranks can hold batches of the same request
+    lengths (the same amount of work) over different tables."""
     rng = np.random.default_rng(seed)
     ctx = rng.integers(min_ctx, max_ctx + 1, n_req)
     blocks = ((ctx + block_tokens - 1) // block_tokens).astype(np.int32)
@@ -74,7 +76,7 @@ def ragged_decode_batch(seed: int = 2002, n_req: int = 64, min_ctx: int = 8192, 
     k = np.maximum(min_k, np.ceil(ratio * blocks - 1e-9)).astype(np.int32)
     k = np.minimum(k, blocks)
     total = int(offsets[-1])
-    table = rng.permutation(total).astype(np.int32)
+    table = (rng if table_seed is None else np.random.default_rng(table_seed)).permutation(total).astype(np.int32)
     return RaggedBatch(blocks, offsets, k, _prefix(k), table, total)
 
 
