@@ -77,10 +77,16 @@ __device__ __forceinline__ void resolve(const XferParams& p, int64_t item, const
 }
 
 // Device <-> device: bulk async copies through a shared-memory ring, one driving thread per CTA.
+// The driving thread is the only instruction stream, so what it does per chunk is kept short: the work item is
+// resolved once (at load time; destination and size wait in shared memory for the store), with 32-bit arithmetic
+// when the item count allows, and the block id of the next chunk is requested one chunk ahead, so that its
+// latency (an L2 access once the id list outgrows what L1 keeps beside the ring) is not waited for.
 template <int STAGES>
 __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
 {
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ unsigned char* s_dst[STAGES];
+    __shared__ uint32_t s_bytes[STAGES];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     unsigned char* ring = smem + 128;
     if (threadIdx.x != 0) return;
@@ -92,13 +98,50 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
     const int64_t first = blockIdx.x;
     if (first >= p.items) return;
     const int64_t my_count = (p.items - first + G - 1) / G;
+    const bool ids_mode = p.mode == 0;
+    const bool small = p.items < 0x7fffffffll;      // every index fits 32 bits
+
+    // block index (into p.ids) of work item `item`
+    auto block_of = [&](int64_t item) -> int64_t {
+        if (small) return (int64_t)(((uint32_t)item / (uint32_t)p.chunks_per_slice) / (uint32_t)p.n_planes);
+        return (item / p.chunks_per_slice) / p.n_planes;
+    };
+    int32_t id_ahead = ids_mode ? __ldg(p.ids + block_of(first)) : 0;      // id of the next item to be loaded
 
     auto load = [&](int64_t j) {
-        const unsigned char* src;
-        unsigned char* dst;
-        uint32_t bytes;
-        resolve(p, first + j * G, src, dst, bytes);
+        const int64_t item = first + j * G;
         const int s = (int)(j % STAGES);
+        const unsigned char* src = nullptr;
+        unsigned char* dst = nullptr;
+        uint32_t bytes = 0;
+        if (ids_mode) {
+            const int32_t id = id_ahead;
+            if (j + 1 < my_count) id_ahead = __ldg(p.ids + block_of(item + G));   // used by the next call
+            int64_t slice;
+            int32_t c;
+            if (small) {
+                const uint32_t sl = (uint32_t)item / (uint32_t)p.chunks_per_slice;
+                c = (int32_t)((uint32_t)item - sl * (uint32_t)p.chunks_per_slice);
+                slice = sl;
+            } else {
+                slice = item / p.chunks_per_slice;
+                c = (int32_t)(item - slice * p.chunks_per_slice);
+            }
+            const int64_t off = (int64_t)c * p.chunk_bytes;
+            const int64_t left = p.slice_bytes - off;
+            if (id >= 0) {
+                bytes = (uint32_t)(left < p.chunk_bytes ? left : p.chunk_bytes);
+                const int32_t pl = small ? (int32_t)((uint32_t)slice % (uint32_t)p.n_planes) : (int32_t)(slice % p.n_planes);
+                unsigned char* paged = p.planes[pl] + (int64_t)id * p.block_stride + off;
+                unsigned char* stag = p.staging + slice * p.slice_bytes + off;
+                src = p.to_staging ? paged : stag;
+                dst = p.to_staging ? stag : paged;
+            }
+        } else {
+            resolve(p, item, src, dst, bytes);
+        }
+        s_dst[s] = dst;
+        s_bytes[s] = bytes;
         mbar_expect_tx(&full[s], bytes);
         if (bytes) bulk_g2s(ring + (size_t)s * p.chunk_bytes, src, bytes, &full[s]);
     };
@@ -115,11 +158,8 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
             if (p.err) atomicExch(p.err, 1);
             break;
         }
-        const unsigned char* src;
-        unsigned char* dst;
-        uint32_t bytes;
-        resolve(p, first + j * G, src, dst, bytes);
-        if (bytes) bulk_s2g(dst, ring + (size_t)s * p.chunk_bytes, bytes);
+        const uint32_t bytes = s_bytes[s];
+        if (bytes) bulk_s2g(s_dst[s], ring + (size_t)s * p.chunk_bytes, bytes);
         bulk_commit();
         // refill the stage whose store was committed one group ago
         if (j >= 1 && j - 1 + STAGES < my_count) {
@@ -180,10 +220,17 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
         UCMX_LAUNCH_CHECK("xfer_plain_kernel");
         return UCMX_OK;
     }
-    // tuning knobs (read once): chunk size, ring depth, CTAs per SM
+    // tuning knobs (read once): chunk size, ring depth, CTAs per SM.  Measured defaults: the same 24 chunks of 8 KiB
+    // in flight per SM either way, as two CTAs with rings of twelve for slices of 128 KiB and more (256 KiB: 6.7 TB/s
+    // against 6.0) and as three CTAs with rings of eight for smaller ones (32 KiB: 6.5 TB/s against 6.1; 64 KiB:
+    // 6.7 against 6.4).
     static const int k_chunk = [] { const char* e = getenv("UCMX_XFER_CHUNK"); const int v = e ? atoi(e) : 0; return (v >= 1024 && v <= 65536 && v % 16 == 0) ? v : 8192; }();
-    static const int k_stages = [] { const char* e = getenv("UCMX_XFER_STAGES"); const int v = e ? atoi(e) : 0; return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8 || v == 12 || v == 16) ? v : 8; }();
-    static const int k_per_sm = [] { const char* e = getenv("UCMX_XFER_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 16) ? v : 3; }();
+    static const int env_stages = [] { const char* e = getenv("UCMX_XFER_STAGES"); const int v = e ? atoi(e) : 0; return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8 || v == 12 || v == 16) ? v : 0; }();
+    static const int env_per_sm = [] { const char* e = getenv("UCMX_XFER_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 16) ? v : 0; }();
+    static const int64_t k_large = [] { const char* e = getenv("UCMX_XFER_LARGE_SLICE"); const long long v = e ? atoll(e) : 0; return v > 0 ? (int64_t)v : (int64_t)131072; }();
+    const bool large = p.slice_bytes >= k_large;
+    const int k_stages = env_stages ? env_stages : (large ? 12 : 8);
+    const int k_per_sm = env_per_sm ? env_per_sm : (large ? 2 : 3);
     p.chunk_bytes = k_chunk;
     if (p.slice_bytes < p.chunk_bytes) p.chunk_bytes = (int32_t)p.slice_bytes;
     p.chunks_per_slice = (int32_t)((p.slice_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
