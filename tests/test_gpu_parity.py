@@ -144,6 +144,35 @@ def test_score_dot_ragged(ops, oracle, dtype):
     np.testing.assert_allclose(got1, ref1, **_score_tol(ref1))
 
 
+@pytest.mark.parametrize("dtype,Hkv,D", [("bf16", 1, 128), ("bf16", 1, 64), ("bf16", 2, 16), ("f32", 1, 64), ("f32", 2, 16), ("bf16", 1, 16)])
+def test_score_dot_narrow_rows(ops, oracle, dtype, Hkv, D):
+    """Rows of 32 to 256 bytes (one KV head per rank under head parallelism): several rows per warp, empty requests,
+    empty table entries, a range that does not divide by the rows in flight."""
+    rng = np.random.default_rng(23)
+    n_slots, E = 3001, Hkv * D
+    reps16 = H.randn_bf16(rng, (n_slots, E), 0.09)
+    reps32 = H.bf16_to_f32(reps16)
+    counts = [0, 64, 0, 0, 4099, 1, 33, 3000, 0, 131, 7]
+    off = H.ragged_offsets(counts)
+    total = int(off[-1])
+    slots = rng.integers(0, n_slots, total).astype(np.int32)
+    slots[[0, 63, 64, 4000, total - 1]] = -1
+    q = H.bf16_to_f32(H.randn_bf16(rng, (len(counts), E)))
+    table = dev_bf16(reps16) if dtype == "bf16" else torch.from_numpy(reps32).to(DEV)
+    got = ops.score_dot(table, dev_i32(off), torch.from_numpy(q).to(DEV), total=total, slot_ids=dev_i32(slots),
+                        n_kv_heads=Hkv, head_dim=D, scale=0.5).cpu().numpy()
+    ok = slots >= 0
+    ref = 0.5 * oracle.score_dot_esa(reps32, off, np.maximum(slots, 0), q)
+    np.testing.assert_allclose(got[ok], ref[ok], **_score_tol(ref))
+    assert np.isneginf(got[~ok]).all()
+    # identity slots, one request, a total that is not a multiple of anything
+    off1 = np.array([0, n_slots], np.int32)
+    got1 = ops.score_dot(table, dev_i32(off1), torch.from_numpy(q[1:2]).to(DEV), total=n_slots, n_kv_heads=Hkv,
+                         head_dim=D).cpu().numpy()
+    ref1 = oracle.score_dot_esa(reps32, off1, None, q[1:2])
+    np.testing.assert_allclose(got1, ref1, **_score_tol(ref1))
+
+
 @pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (8, 8, 128), (2, 4, 64), (64, 8, 128)])
 def test_score_dot_query_fused_equals_two_step(ops, oracle, Hq, Hkv, D):
     """The fused prologue takes the same mean, in the same order, as ucmx_query_group_mean: the scores

@@ -472,6 +472,90 @@ int rows_grid(int32_t total)
     return (int)(grid < 1 ? 1 : grid);
 }
 
+// Narrow rows, one representative per head: a row of 32 to 256 bytes (for instance one KV head of 128 bf16
+// channels, which is what a rank holds under eight-way head parallelism) is too short for a warp.  Here a group of
+// LPR lanes owns a row, a warp covers 32 / LPR rows with one load instruction and keeps four such instructions in
+// flight; every lane walks the request boundaries for its own rows (they only grow) and takes its eight (bf16) or
+// four (fp32) query elements from the L1-resident query.
+template <int DT, int LPR>
+__global__ void __launch_bounds__(kScoreThreads) score_dot_narrow_kernel(ScoreGenParams p)
+{
+    constexpr int kRows = 32 / LPR;          // rows per load instruction of a warp
+    constexpr int kU = 4;                    // load instructions in flight
+    constexpr int kPer = (DT == UCMX_DT_BF16) ? 8 : 4;
+    const int lane = threadIdx.x & 31, sub = lane / LPR, pc = lane % LPR;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int64_t W = (int64_t)gridDim.x * warps_per_cta;
+    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int begin = (int)((int64_t)p.total * w / W);
+    const int end = (int)((int64_t)p.total * (w + 1) / W);
+    if (begin >= end) return;
+    const int E = p.H * p.D;
+    const size_t row_bytes = (size_t)E * (DT == UCMX_DT_BF16 ? 2 : 4);
+    const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
+    int r = find_request(p.offsets, p.n_req, begin);
+    int r_end = __ldg(p.offsets + r + 1);
+    for (int c = begin; c < end; c += kRows * kU) {
+        uint4 v[kU];
+        int slot[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int row = c + u * kRows + sub;
+            slot[u] = -2;                    // -2: past the end, -1: an empty entry of the table
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (row < end) {
+                slot[u] = p.slot_ids ? __ldg(p.slot_ids + row) : row;
+                if (slot[u] >= 0) v[u] = ld_stream16(base + (size_t)slot[u] * row_bytes + (size_t)pc * 16);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int row = c + u * kRows + sub;
+            float acc = 0.0f;
+            if (slot[u] >= 0) {
+                while (row >= r_end) {
+                    ++r;
+                    r_end = __ldg(p.offsets + r + 1);
+                }
+                const float4* qq = reinterpret_cast<const float4*>(p.q + (int64_t)r * E + pc * kPer);
+                const float4 q0 = __ldg(qq);
+                if (DT == UCMX_DT_BF16) {
+                    const float4 q1 = __ldg(qq + 1);
+                    acc = fmaf(q0.x, bf16lo(v[u].x), acc);
+                    acc = fmaf(q0.y, bf16hi(v[u].x), acc);
+                    acc = fmaf(q0.z, bf16lo(v[u].y), acc);
+                    acc = fmaf(q0.w, bf16hi(v[u].y), acc);
+                    acc = fmaf(q1.x, bf16lo(v[u].z), acc);
+                    acc = fmaf(q1.y, bf16hi(v[u].z), acc);
+                    acc = fmaf(q1.z, bf16lo(v[u].w), acc);
+                    acc = fmaf(q1.w, bf16hi(v[u].w), acc);
+                } else {
+                    acc = fmaf(q0.x, __uint_as_float(v[u].x), acc);
+                    acc = fmaf(q0.y, __uint_as_float(v[u].y), acc);
+                    acc = fmaf(q0.z, __uint_as_float(v[u].z), acc);
+                    acc = fmaf(q0.w, __uint_as_float(v[u].w), acc);
+                }
+            }
+#pragma unroll
+            for (int o = LPR >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (pc == 0 && slot[u] != -2) p.out[row] = slot[u] >= 0 ? acc * p.scale : -INFINITY;
+        }
+    }
+}
+
+template <int DT>
+bool launch_narrow(const ScoreGenParams& g, int64_t row_bytes, cudaStream_t st)
+{
+    const int grid = rows_grid(g.total);
+    switch (row_bytes) {
+        case 256: score_dot_narrow_kernel<DT, 16><<<grid, kScoreThreads, 0, st>>>(g); return true;
+        case 128: score_dot_narrow_kernel<DT, 8><<<grid, kScoreThreads, 0, st>>>(g); return true;
+        case 64: score_dot_narrow_kernel<DT, 4><<<grid, kScoreThreads, 0, st>>>(g); return true;
+        case 32: score_dot_narrow_kernel<DT, 2><<<grid, kScoreThreads, 0, st>>>(g); return true;
+        default: return false;
+    }
+}
+
 }  // namespace
 }  // namespace ucmx
 
@@ -525,6 +609,15 @@ extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t 
         return launch_rows<UCMX_DT_F32, false>(p, qn, grid, st);
     }
     ScoreGenParams g{reps, req_offsets, slot_ids, q, out_scores, n_req, total, n_kv_heads, n_rep, head_dim, scale};
+    static const bool no_narrow = getenv("UCMX_SCORE_NO_NARROW") != nullptr;   // comparison knob: the one-row-per-warp kernel for every shape
+    if (n_rep == 1 && !no_narrow) {
+        const int64_t row_bytes = E * (reps_dtype == UCMX_DT_BF16 ? 2 : 4);
+        const bool done = reps_dtype == UCMX_DT_BF16 ? launch_narrow<UCMX_DT_BF16>(g, row_bytes, st) : launch_narrow<UCMX_DT_F32>(g, row_bytes, st);
+        if (done) {
+            UCMX_LAUNCH_CHECK("score_dot_narrow_kernel");
+            return UCMX_OK;
+        }
+    }
     const int warps_per_cta = kScoreThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
     const int64_t cap = (int64_t)sm_count() * 8;
