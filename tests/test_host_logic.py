@@ -109,6 +109,10 @@ def test_workloads_are_seeded_and_in_range():
     assert a.n_req == 64 and a.blocks_per_req.min() >= 64 and a.blocks_per_req.max() <= 1024
     assert (a.k_per_req == np.maximum(16, np.ceil(0.05 * a.blocks_per_req - 1e-9))).all()
     assert sorted(a.block_table.tolist()) == list(range(a.total))
+    # the same request lengths over another block table: what every rank of a request-parallel run holds
+    c = ragged_decode_batch(seed=2002, table_seed=7008)
+    assert np.array_equal(a.blocks_per_req, c.blocks_per_req) and np.array_equal(a.k_per_req, c.k_per_req)
+    assert not np.array_equal(a.block_table, c.block_table) and sorted(c.block_table.tolist()) == list(range(a.total))
 
 
 def test_kvstar_module_rejects_bad_shapes_like_the_reference():
@@ -143,3 +147,27 @@ def test_numa_helpers_read_sysfs_layout(tmp_path):
     assert numa.device_numa_node("0000:ff:00.0", str(tmp_path)) is None and numa.node_cpus(7, str(tmp_path)) == []
     (dev / "numa_node").write_text("-1\n")
     assert numa.device_numa_node("0000:1b:00.0", str(tmp_path)) is None
+
+
+def test_kvstar_multistep_registered_and_slot_estimate():
+    """The fourth sparse method of the reference's factory (ucm/sparse/factory.py:47-52) and its scheduler-side
+    slot estimate (multistep.py:775-814): prefill is not sparsified; in decode the middle of the prompt shrinks to
+    ceil(ratio * middle blocks) while the init window, the local window and everything after the prompt stay."""
+    from types import SimpleNamespace as NS
+
+    from ucmx.sparse.base import INVALID_SLOT, UcmSparseRole
+    from ucmx.sparse.factory import UcmSparseFactory
+    from ucmx.sparse.kvstar import KVStarMultiStep
+    agent = UcmSparseFactory.create_sparse_method(cfg("KVStarMultiStep", {"sparse_ratio": 0.25}), UcmSparseRole.SCHEDULER)
+    assert isinstance(agent, KVStarMultiStep)
+    bs = agent.block_size
+    assert agent.d_pruned == round(agent.head_size * 0.25) and agent.stride == 5 and agent.merge == 2
+    assert agent.estimate_num_slots_sparsed(NS(num_output_tokens=0, num_prompt_tokens=40 * bs, num_tokens=40 * bs)) == INVALID_SLOT
+    # 40 full prompt blocks: 1 + 2 stay, ceil(37 / 4) = 10 of the middle are kept -> 13 blocks, plus the decode tail
+    req = NS(num_output_tokens=3, num_prompt_tokens=40 * bs, num_tokens=40 * bs + 3)
+    assert agent.estimate_num_slots_sparsed(req) == 13 * bs + 3
+    req = NS(num_output_tokens=bs, num_prompt_tokens=40 * bs, num_tokens=41 * bs)
+    assert agent.estimate_num_slots_sparsed(req) == 14 * bs
+    # a prompt no longer than the windows is left alone
+    req = NS(num_output_tokens=1, num_prompt_tokens=2 * bs, num_tokens=2 * bs + 1)
+    assert agent.estimate_num_slots_sparsed(req) == 2 * bs + 1
