@@ -54,8 +54,11 @@ int32_t ucmx_compiled_arch(void);
 /* Text of the last CUDA error this thread's calls met ("" if none). Host. */
 const char* ucmx_last_error(void);
 /* Kernels never spin without limit: a wait on an asynchronous copy that does not complete gives
- * up and records a code here (1 = a bulk copy did not land, 2 = a misaligned pointer pair was
- * skipped) instead of hanging the device.  Reads the code (0 = none) and optionally clears it. */
+ * up and records a code here instead of hanging the device, and an id that points outside the
+ * table or cache it indexes is skipped and recorded instead of dereferenced:
+ *   1 = a bulk copy did not land, 2 = a misaligned pointer pair was skipped, 3 = a slot or block id
+ *   was outside its table (the entry was treated as empty), 4 = a tensor-parallel peer never
+ *   delivered its scores.  Reads the code (0 = none) and optionally clears it. */
 int32_t ucmx_device_error(int32_t* code, int32_t clear);
 
 /* ---------------------------------------------------------------------------------------------
@@ -130,9 +133,20 @@ int32_t ucmx_query_group_mean(const void* q, int32_t n_tok, int32_t n_q_heads, i
 #define UCMX_DT_BF16 0
 #define UCMX_DT_F32 1
 #define UCMX_DT_I32 2
-int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t n_rep,
-                       int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
-                       const float* q, int32_t n_req, int32_t total, float scale, float* out_scores,
+/* Tensor-parallel ranks pass `exchange` (host pointer; NULL on a single rank): the kernel then also
+ * delivers its partial scores to every rank, see "Tensor-parallel retrieval" below; out_scores may
+ * be NULL in that case.  n_slots is the number of rows of the table: a slot id at or beyond it is
+ * treated as an empty entry (-inf) and reported through ucmx_device_error (code 3), never read. */
+typedef struct ucmx_peer_exchange {
+    void* const* bases; /* DEVICE array of `world` exchange-buffer addresses, in rank order */
+    int32_t world;
+    int32_t my_rank;
+    int64_t n_scores;   /* scores a rank's part of the inbox holds (>= total of every call) */
+} ucmx_peer_exchange;
+int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads,
+                       int32_t n_rep, int32_t head_dim, const int32_t* req_offsets,
+                       const int32_t* slot_ids, const float* q, int32_t n_req, int32_t total,
+                       float scale, float* out_scores, const ucmx_peer_exchange* exchange /* host */,
                        ucmx_stream_t stream);
 
 /* GSA's device-side weights (cal_topk, ucm/sparse/gsa/gsa.py:386-412): weight of a block = mean over the
@@ -142,8 +156,8 @@ int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
  * [slot, n_kv_heads, n_rep, head_dim].  include_mask / exclude_mask: one byte per candidate (device), or
  * NULL; a set include byte gives +inf, a set exclude byte -inf (exclude wins), as masked_fill_ does there.
  * n_q_heads / n_kv_heads must be a power of two <= 32.  Computed in fp32. */
-int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
-                             const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+int32_t ucmx_score_dot_heads(const void* reps, int64_t n_slots, int32_t n_kv_heads, int32_t n_rep,
+                             int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
                              int32_t n_q_heads, int64_t query_stride, int32_t n_req, int32_t total,
                              const uint8_t* include_mask, const uint8_t* exclude_mask,
                              float* out_scores, ucmx_stream_t stream);
@@ -154,10 +168,12 @@ int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, int32_t n_rep
  * kernel.  n_rep is 1.  Returns UCMX_EUNSUPPORTED for shapes the single-pass kernel does not cover
  * (n_kv_heads*head_dim not a multiple of 256 for bf16 tables / 128 for fp32 tables, or above 2048);
  * use the two calls above then. */
-int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t head_dim,
-                             const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
-                             int32_t n_q_heads, int64_t query_stride, int32_t round_bf16, int32_t n_req,
-                             int32_t total, float scale, float* out_scores, ucmx_stream_t stream);
+int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads,
+                             int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
+                             const void* query, int32_t n_q_heads, int64_t query_stride,
+                             int32_t round_bf16, int32_t n_req, int32_t total, float scale,
+                             float* out_scores, const ucmx_peer_exchange* exchange /* host */,
+                             ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Stage 2b — Hamming-similarity scores on packed hash codes (integer exact).
@@ -211,34 +227,35 @@ int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, const int32_t*
                          void* out_scores, int32_t* out_counts, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Tensor-parallel retrieval: exchange of partial block scores over peer memory, fused into top-k.
- * (No counterpart in the reference, which has no cross-rank exchange: under tensor parallelism its
- * ranks select independently over their own KV heads, ucm/sparse/esa/esa.py:196-198.)
+ * Tensor-parallel retrieval: the all-reduce of partial block scores, fused into the scoring and
+ * top-k kernels over peer memory.  (No counterpart in the reference, which has no cross-rank
+ * exchange: under tensor parallelism its ranks select independently over their own KV heads,
+ * ucm/sparse/esa/esa.py:196-198.)
  *
- * Every rank owns an exchange buffer that all ranks can address (peer-mapped, e.g. torch symmetric
- * memory): bytes [0,128) hold one uint32 flag per rank, partial scores live further up.  A round:
- *   1. each rank scores its own KV heads into its buffer at parts_offset_bytes (ucmx_score_dot* with
- *      out_scores pointing there);
- *   2. ucmx_peer_signal, next on the same stream, publishes `epoch` into flag[my_rank] of every
- *      rank's buffer (release at system scope: the scores written before are visible to whoever
- *      sees the flag);
- *   3. ucmx_topk_ragged_peer_sum waits until all `world` flags in its own buffer have reached
- *      `epoch`, adds the partial scores of all ranks in rank order (peer loads over NVLink; the
- *      same order everywhere, so every rank gets bit-identical sums and selections), writes them
- *      to summed_scores and selects as ucmx_topk_ragged does.
- * peer_bases is a DEVICE array of `world` buffer base addresses.  Use increasing epochs and alternate
- * parts_offset_bytes between two halves from round to round, so that a rank never overwrites scores a
- * slower peer may still be reading.  The wait is bounded: if a peer never signals, code 4 is
- * recorded (ucmx_device_error) and the kernel goes on with what it has instead of hanging. */
-int32_t ucmx_peer_signal(void* const* peer_bases, int32_t world, int32_t my_rank, uint32_t epoch,
-                         ucmx_stream_t stream);
-int32_t ucmx_topk_ragged_peer_sum(void* const* peer_bases, int32_t world, int32_t my_rank,
-                                  int64_t parts_offset_bytes, uint32_t epoch, float* summed_scores,
+ * Every rank owns an exchange buffer of ucmx_peer_exchange_bytes(world, n_scores) bytes that all
+ * ranks can address (peer-mapped, e.g. torch symmetric memory), zeroed once before its first use:
+ * a 256-byte header (one flag per rank, this rank's arrival and round counters) and an inbox of
+ * two halves x world parts of partial scores.  A round:
+ *   1. ucmx_score_dot / ucmx_score_dot_query with `exchange` set: the rank scores its own KV heads
+ *      and stores every score into inbox[round & 1][my_rank] of EVERY rank (plain peer stores); the
+ *      kernel's last thread block then publishes the round number into flag[my_rank] of every rank
+ *      (release at system scope: the scores stored before are visible to whoever sees the flag).
+ *   2. ucmx_topk_ragged_peer_sum, next on the same stream: waits until all `world` flags of its own
+ *      buffer have reached the round, adds the parts in rank order (local loads; the same order
+ *      everywhere, so every rank gets bit-identical sums and selections), writes the sums to
+ *      summed_scores and selects as ucmx_topk_ragged does.
+ * The round number lives in the buffer and advances by itself, so the two launches can be captured
+ * in a CUDA graph and replayed; the halves alternate, so a fast rank never overwrites scores a
+ * slower peer may still be reading.  Every rank must run the same sequence of rounds.  The wait is
+ * bounded: if a peer never delivers, code 4 is recorded (ucmx_device_error) and the kernel goes on
+ * with what it has instead of hanging.  No multicast and no remote loads are involved. */
+size_t ucmx_peer_exchange_bytes(int32_t world, int64_t n_scores);
+int32_t ucmx_topk_ragged_peer_sum(const ucmx_peer_exchange* exchange /* host */, float* summed_scores,
                                   const int32_t* req_offsets, const int32_t* k_per_req, int32_t n_req,
-                                  int32_t start_win, int32_t end_win, int32_t window_mode, int32_t order,
-                                  const int32_t* id_map, int32_t out_stride, const int32_t* out_offsets,
-                                  int32_t* out_idx, float* out_scores, int32_t* out_counts,
-                                  ucmx_stream_t stream);
+                                  int32_t total, int32_t start_win, int32_t end_win, int32_t window_mode,
+                                  int32_t order, const int32_t* id_map, int32_t out_stride,
+                                  const int32_t* out_offsets, int32_t* out_idx, float* out_scores,
+                                  int32_t* out_counts, ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Stage 3 -> 4 glue — resident-set remap (the "SparseKVManager block remap").
@@ -256,13 +273,31 @@ int32_t ucmx_topk_ragged_peer_sum(void* const* peer_bases, int32_t world, int32_
  * free list is every slot that is neither a hit nor newly filled.
  * Outputs, packed like sel: table[j] = physical id serving sel[j] (-1 if no slot was left);
  * load_logical / load_phys = the (block to load -> HBM block) list, load_counts[r] entries from
- * position sel_offsets[r].  max_logical bounds the logical ids, max_slots the slots of a request
- * (both size the shared-memory lookup; (max_logical + 2*max_slots)*4 bytes must stay under 200 KiB). */
+ * position sel_offsets[r]; the entries behind them, up to sel_offsets[r+1], are set to -1, so the
+ * lists of all requests can go to ucmx_move_blocks as one array.  max_logical bounds the logical
+ * ids, max_slots the slots of a request (both size the shared-memory lookup; (max_logical +
+ * 2*max_slots)*4 bytes must stay under 200 KiB; a request with more slots than max_slots is
+ * refused: nothing loaded, table -1, code 3 for ucmx_device_error).
+ * moves (optional, host pointer): also write ONE list of block moves for all requests, ready for
+ * ucmx_move_blocks, when the blocks' home is a paged pool in HBM: for every block to load,
+ * move_src = src_map[src_map_offsets[r] + logical block] (e.g. the request's row of the block
+ * table; src_map_offsets NULL: every request starts at 0) and move_dst = the HBM block it goes to.
+ * Requests append their entries at move_count[0] (atomically, so the order of requests in the list
+ * is arbitrary); move_count is two int32 in device memory, both 0 before the call -
+ * ucmx_move_blocks(..., n_device = move_count, ...) consumes the list and zeroes them again. */
+typedef struct ucmx_remap_moves {
+    const int32_t* src_map;
+    const int32_t* src_map_offsets;
+    int32_t* move_src;
+    int32_t* move_dst;
+    int32_t* move_count;
+} ucmx_remap_moves;
 int32_t ucmx_remap_resident(int32_t* slot_logical, uint8_t* slot_free, const int32_t* slot_phys,
                             const int32_t* slot_offsets, const int32_t* sel, const int32_t* sel_offsets,
                             const int32_t* sel_counts, int32_t n_req, int32_t max_logical,
                             int32_t max_slots, int32_t* table, int32_t* load_logical, int32_t* load_phys,
-                            int32_t* load_counts, ucmx_stream_t stream);
+                            int32_t* load_counts, const ucmx_remap_moves* moves /* host */,
+                            ucmx_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Score + top-k without any allocation.  (No counterpart in the reference: its retrieval runs on
@@ -279,15 +314,19 @@ int32_t ucmx_remap_resident(int32_t* slot_logical, uint8_t* slot_free, const int
  *  - total must not exceed ucmx_noalloc_max_candidates() (1 048 576 candidates, a 4 MiB array that
  *    every GPU which loads the library holds until the process exits); larger batches are
  *    rejected with UCMX_EUNSUPPORTED and a message in ucmx_last_error().
- *  - The first call on each device looks up the array's device address (the device of `stream`
- *    must be current); make that first call before starting any stream capture.
+ *  - Every call needs the device of `stream` to be the current device.  The first call on each
+ *    device also looks up the array's device address; make that first call before starting any
+ *    stream capture.
+ *  - Out-of-range slot ids are skipped (scored -inf) as everywhere else, but not recorded for
+ *    ucmx_device_error: the word that call reads is allocated on first use.
  *  - All calls on a device share the one array and it keeps the last call's scores.  Calls are
  *    safe back to back on one stream; two calls that may overlap on the GPU (different streams
  *    without an ordering between them) race on it and must be serialised by the caller.
  *  - Only out_idx / out_scores / out_counts are results; the scores of unselected candidates are
  *    not returned. */
-int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
-                                   int32_t n_rep, int32_t head_dim, const int32_t* req_offsets,
+int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dtype, int64_t n_slots,
+                                   int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                                   const int32_t* req_offsets,
                                    const int32_t* slot_ids, const float* q, int32_t n_req,
                                    int32_t total, float scale, const int32_t* k_per_req,
                                    int32_t start_win, int32_t end_win, int32_t window_mode,
@@ -303,21 +342,38 @@ int32_t ucmx_noalloc_max_candidates(void);
  * (ucm/store/nfsstore/tsf_task/posix_queue.cc:98-124) and CudaDevice::H2DBatchSync/D2HBatchSync with
  * H2DKernel/D2HKernel (ucm/store/device/cuda/cuda_device.cu:47-81,180-211).
  *
- * planes: host array of n_planes (<= 8) base pointers (K cache, V cache, ... of one layer).
+ * planes: host array of n_planes (<= 8) base pointers (K cache, V cache, ... of one layer), each
+ * holding n_blocks blocks.
  * For i in [0,n), p in [0,n_planes): slice_bytes bytes at planes[p] + block_ids[i]*block_stride_bytes
  * are copied to (gather) or from (scatter) staging + (i*n_planes + p)*slice_bytes.  block_ids is a
- * device array; negative ids are skipped.  staging may be device memory or page-locked host memory
+ * device array; negative ids are skipped, and so is an id at or beyond n_blocks, which is also
+ * recorded for ucmx_device_error (code 3) - it is never turned into an address.  staging may be device memory or page-locked host memory
  * mapped into the device's address space (direct zero-copy transfer); pass staging_is_host != 0 in
  * the latter case so that plain loads/stores are used instead of bulk async copies.
  * slice_bytes, block_stride_bytes and all pointers must be multiples of 16. */
 int32_t ucmx_gather_blocks(const void* const* planes /* host */, int32_t n_planes,
-                           int64_t block_stride_bytes, const int32_t* block_ids, int32_t n,
-                           int64_t slice_bytes, void* staging, int32_t staging_is_host,
+                           int64_t block_stride_bytes, int64_t n_blocks, const int32_t* block_ids,
+                           int32_t n, int64_t slice_bytes, void* staging, int32_t staging_is_host,
                            ucmx_stream_t stream);
 int32_t ucmx_scatter_blocks(void* const* planes /* host */, int32_t n_planes,
-                            int64_t block_stride_bytes, const int32_t* block_ids, int32_t n,
-                            int64_t slice_bytes, const void* staging, int32_t staging_is_host,
-                            ucmx_stream_t stream);
+                            int64_t block_stride_bytes, int64_t n_blocks, const int32_t* block_ids,
+                            int32_t n, int64_t slice_bytes, const void* staging,
+                            int32_t staging_is_host, ucmx_stream_t stream);
+/* Block to block inside device memory: for i in [0,n), p in [0,n_planes): the slice of block
+ * src_ids[i] of src_planes[p] goes to block dst_ids[i] of dst_planes[p]; an entry with a negative
+ * id on either side is skipped, an id beyond its cache is skipped and recorded (code 3).  This is
+ * the delta load of a decode step (ESA wait_retrieval_and_start_load, ucm/sparse/esa/esa.py:313-338;
+ * GSAPrefetchEngineC::RunPrefetchH2D, ucm/sparse/gsa/prefetch/src/kvcache_pre.cpp:240-272) when
+ * the blocks' home is HBM: the move list of ucmx_remap_resident goes in as it is.
+ * n_device (optional, device memory, two int32): when given, only the first min(n, n_device[0])
+ * entries are moved - the length of a list that was built on the device - and the kernel sets both
+ * words back to 0 when it is done (n_device[1] is its scratch; both must be 0 before the list is
+ * built).  n then only bounds the launch. */
+int32_t ucmx_move_blocks(const void* const* src_planes /* host */, void* const* dst_planes /* host */,
+                         int32_t n_planes, int64_t src_block_stride_bytes, int64_t n_src_blocks,
+                         const int32_t* src_ids, int64_t dst_block_stride_bytes, int64_t n_dst_blocks,
+                         const int32_t* dst_ids, int32_t n, const int32_t* n_device, int64_t slice_bytes,
+                         ucmx_stream_t stream);
 /* Pointer-pair form, the signature of IDevice::H2DBatchSync / D2HBatchSync
  * (ucm/store/device/idevice.h:48-51) minus the blocking allocation: dst_ptrs/src_ptrs are DEVICE
  * arrays of `number` addresses, `count` bytes each (multiple of 16). Asynchronous on stream. */
@@ -360,8 +416,14 @@ int32_t ucmx_task_destroy(ucmx_task* task);
  * of `dim` fp32 values; submit(query[b,dim], topk, indexes[b,max_idx] with -1 padding) -> request
  * id; poll / wait / get_result(indices int32[b,topk], scores fp32[b,topk]).
  * Here the table lives on the device (kept as bf16 when table_dtype == UCMX_DT_BF16, which is
- * lossless for bf16-rounded representatives, else fp32) and a request is a stream-ordered
- * score + top-k on a private stream instead of a job for a thread pool.
+ * lossless for bf16-rounded representatives, else fp32) and requests are served by a stream-ordered
+ * score + top-k on a private stream instead of jobs for a thread pool.  Submits are coalesced: a
+ * submit stores its query rows and index lists in page-locked memory and returns; everything
+ * submitted since the last launch goes to the GPU as ONE ragged batch when any of those requests
+ * is polled, waited for or collected, when ucmx_retrieval_flush is called, or when 2048 query rows
+ * (or 4 Mi candidates) have piled up.  ESA's pattern - one submit per request of the decode batch,
+ * then one wait per request (ucm/sparse/esa/esa.py:286-339) - thus costs one launch per layer.
+ * submit refuses (UCMX_EPARAM) an index below -1 or at or beyond n_items.
  * Pointers named host_* are host memory; get_result copies min(topk, n_allowed) entries per row and
  * pads the rest of the row with -1 / -inf, then forgets the request (as the reference does). */
 typedef struct ucmx_retrieval ucmx_retrieval;
@@ -376,6 +438,8 @@ int32_t ucmx_retrieval_table(ucmx_retrieval* r, void** table, int32_t* table_dty
 int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_query, int32_t batch,
                               int32_t query_dim, int32_t topk, const int32_t* host_indexes,
                               int32_t max_idx, int32_t* req_id);
+int32_t ucmx_retrieval_flush(ucmx_retrieval* r); /* launch what has been submitted so far */
+int32_t ucmx_retrieval_launches(ucmx_retrieval* r, int64_t* kernels); /* kernels launched so far */
 int32_t ucmx_retrieval_poll(ucmx_retrieval* r, int32_t req_id, int32_t* ready);
 int32_t ucmx_retrieval_wait(ucmx_retrieval* r, int32_t req_id);
 int32_t ucmx_retrieval_result_shape(ucmx_retrieval* r, int32_t req_id, int32_t* batch,
@@ -449,6 +513,10 @@ int32_t ucmx_fstore_check(ucmx_fstore* store, size_t task_id, int32_t* finished)
 int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_geometry* geom, const int32_t* block_ids,
                                 const int32_t* out_slots, int32_t n, const int64_t* pruned_index,
                                 int32_t d_pruned, int32_t merge, void* reps_f16, ucmx_stream_t stream);
+/* Which kernel ucmx_kvstar_scores runs for a shape: 0 = CUDA cores, 1 = tensor cores with one block per tile,
+ * 2 = tensor cores with two blocks per instruction (host-side arithmetic only, nothing is launched). */
+int32_t ucmx_kvstar_kernel_choice(int32_t n_slots, int32_t M, int32_t n_kv_heads, int32_t d_pruned,
+                                  int32_t max_q_tokens, int32_t n_q_heads);
 size_t ucmx_kvstar_workspace_bytes(int32_t total_blocks, int32_t n_req, int32_t max_q_tokens,
                                    int32_t n_q_heads, int32_t n_kv_heads);
 int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int32_t M, int32_t n_kv_heads,

@@ -54,19 +54,16 @@ def test_cancelling_projections_take_the_exact_path(oracle):
     assert np.abs(margins[:, ::2]).max() < 0.25 < np.abs(margins[:, 1::2]).std()   # cancelling columns sit at rounding-noise level
 
 
-def test_tensor_core_and_cuda_core_kernels_agree_on_a_large_batch():
+def test_large_batch_matches_the_checker(oracle):
+    """A batch large enough to keep every SM busy for many tiles, a size that is no multiple of the tile, against
+    the CPU checker's FMA chain bit for bit."""
     from ucmx import ops
-    g = torch.Generator(device=DEV).manual_seed(103)
-    x = torch.randn((1_000_003, 128), generator=g, device=DEV).to(torch.bfloat16)
-    w = (torch.randn((128, 128), generator=g, device=DEV) * 2).to(torch.bfloat16)
-    a = ops.hash_encode(x, w)
-    os.environ["UCMX_HASH_NO_TC"] = "1"
-    try:
-        b = ops.hash_encode(x, w)
-    finally:
-        del os.environ["UCMX_HASH_NO_TC"]
-    assert torch.equal(a, b)
-    assert 0.45 < float(torch.tensor(np.unpackbits(a[:10000].cpu().numpy())).float().mean()) < 0.55
+    rng = np.random.default_rng(103)
+    x16 = H.randn_bf16(rng, (200_003, 128))
+    w16 = H.randn_bf16(rng, (128, 128), 2.0)
+    got = ops.hash_encode(dev_bf16(x16), dev_bf16(w16)).cpu().numpy()
+    assert np.array_equal(got, oracle.hash_encode(x16, w16))
+    assert 0.45 < float(np.unpackbits(got[:10000]).mean()) < 0.55
 
 
 def test_zero_and_tiny_vectors(oracle):
@@ -88,18 +85,15 @@ def test_zero_and_tiny_vectors(oracle):
     assert not want[5:300].any()
 
 
-def test_repeated_runs_are_identical():
+def test_repeated_runs_are_identical(oracle):
     """The code words settled by the fixer warp and those stored by the epilogue never overlap: a dozen runs of a
-    batch large enough to keep every SM busy give the same bytes as the CUDA-core kernel."""
+    batch large enough to keep every SM busy give the same bytes, and those are the checker's."""
     from ucmx import ops
-    g = torch.Generator(device=DEV).manual_seed(105)
-    x = torch.randn((400_000, 128), generator=g, device=DEV).to(torch.bfloat16)
-    w = (torch.randn((128, 128), generator=g, device=DEV) * 2).to(torch.bfloat16)
-    os.environ["UCMX_HASH_NO_TC"] = "1"
-    try:
-        ref = ops.hash_encode(x, w)
-    finally:
-        del os.environ["UCMX_HASH_NO_TC"]
+    rng = np.random.default_rng(105)
+    x16 = H.randn_bf16(rng, (150_000, 128))
+    w16 = H.randn_bf16(rng, (128, 128), 2.0)
+    x, w = dev_bf16(x16), dev_bf16(w16)
+    ref = torch.from_numpy(oracle.hash_encode(x16, w16)).to(DEV)
     for rep in range(12):
         got = ops.hash_encode(x, w)
         bad = (got.view(torch.int32) != ref.view(torch.int32)).nonzero()

@@ -22,32 +22,28 @@ def half(bits):
     return torch.from_numpy(bits.view(np.int16).copy()).view(torch.float16).cuda()
 
 
-MODES = {"tensor_core": None, "one_block_tiles": "UCMX_KVSTAR_ONE_BLOCK_TILES", "cuda_core": "UCMX_KVSTAR_NO_TC"}
-
-
-def run_single(q, reps, pruned, mode="tensor_core"):
+def run_single(q, reps, pruned):
     n = reps.shape[0]
     off = torch.tensor([0, n], dtype=torch.int32, device="cuda")
     qoff = torch.tensor([0, q.shape[0]], dtype=torch.int32, device="cuda")
     pr = None if pruned is None else torch.from_numpy(pruned).cuda().unsqueeze(0).contiguous()
-    if MODES[mode]:
-        os.environ[MODES[mode]] = "1"
-    try:
-        out = ops.kvstar_scores(half(reps), off, half(q), qoff, total=n, max_q_tokens=q.shape[0], pruned_index=pr)
-    finally:
-        if MODES[mode]:
-            os.environ.pop(MODES[mode], None)
+    out = ops.kvstar_scores(half(reps), off, half(q), qoff, total=n, max_q_tokens=q.shape[0], pruned_index=pr)
     torch.cuda.synchronize()
     assert N.device_error() == 0
     return out.cpu().numpy()
 
 
-@pytest.mark.parametrize("mode", sorted(MODES))
+def kernel_choice(q, reps):
+    """0 = CUDA cores, 1 = tensor cores one block per tile, 2 = tensor cores two blocks per instruction."""
+    n, M, Hk, dp = reps.shape
+    return N.lib.ucmx_kvstar_kernel_choice(n, M, Hk, dp, q.shape[0], q.shape[1])
+
+
 @pytest.mark.parametrize("name", sorted(H.KVSTAR_CASES))
-def test_votes_and_selection_match(oracle, name, mode):
+def test_votes_and_selection_match(oracle, name):
     q, reps, pruned, k = H.case_kvstar(name)
     want = oracle.kvstar_scores(q, reps, pruned)
-    got = run_single(q, reps, pruned, mode)
+    got = run_single(q, reps, pruned)
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=1e-6)
     srt = np.sort(want)[::-1]
     assert srt[k - 1] - srt[k] > 4 * RTOL * srt[k - 1], "the seeded case must not sit on a tie"
@@ -60,17 +56,19 @@ def test_votes_and_selection_match(oracle, name, mode):
     np.testing.assert_array_equal(np.sort(sel), np.sort(G[name + "_rank"][:k]))
 
 
-def test_benchmark_shapes_take_the_tensor_core_kernel():
-    os.environ["UCMX_KVSTAR_REQUIRE_TC"] = "1"
-    try:
-        for name in ("llama", "qwen", "short_group"):
-            q, reps, pruned, _ = H.case_kvstar(name)
-            run_single(q, reps, pruned)
-        q, reps, pruned, _ = H.case_kvstar("odd")
-        with pytest.raises(N.UcmxError):
-            run_single(q, reps, pruned)
-    finally:
-        os.environ.pop("UCMX_KVSTAR_REQUIRE_TC", None)
+def test_the_seeded_cases_cover_every_kernel():
+    """The shape decides the kernel; the seeded cases between them run all three, the benchmark shapes on tensor cores."""
+    seen = set()
+    for name in sorted(H.KVSTAR_CASES):
+        q, reps, _, _ = H.case_kvstar(name)
+        seen.add(kernel_choice(q, reps))
+    for name in ("llama", "qwen", "short_group"):
+        q, reps, _, _ = H.case_kvstar(name)
+        assert kernel_choice(q, reps) >= 1
+    q, reps, _, _ = H.case_kvstar("odd")
+    assert kernel_choice(q, reps) == 0
+    assert N.lib.ucmx_kvstar_kernel_choice(1000, 64, 8, 32, 8, 32) == 2        # the benchmark's shape
+    assert seen == {0, 1, 2}
 
 
 def test_ragged_batch_with_slots_and_per_request_channels(oracle):
@@ -87,20 +85,13 @@ def test_ragged_batch_with_slots_and_per_request_channels(oracle):
     pruned = np.stack([np.stack([rng.permutation(D)[:dp] for _ in range(Hk)]) for _ in xs]).astype(np.int64)
     off = np.concatenate([[0], np.cumsum(n_blocks)]).astype(np.int32)
     qoff = np.concatenate([[0], np.cumsum(xs)]).astype(np.int32)
-    for mode in sorted(MODES):
-        if MODES[mode]:
-            os.environ[MODES[mode]] = "1"
-        try:
-            got = ops.kvstar_scores(half(table), torch.from_numpy(off).cuda(), half(q), torch.from_numpy(qoff).cuda(),
-                                    total=int(off[-1]), max_q_tokens=8, slot_ids=torch.from_numpy(slots).cuda(),
-                                    pruned_index=torch.from_numpy(pruned).cuda()).cpu().numpy()
-        finally:
-            if MODES[mode]:
-                os.environ.pop(MODES[mode], None)
-        assert N.device_error() == 0
-        for r in range(len(xs)):
-            want = oracle.kvstar_scores(q[qoff[r]:qoff[r + 1]], table[slots[off[r]:off[r + 1]]], pruned[r])
-            np.testing.assert_allclose(got[off[r]:off[r + 1]], want, rtol=RTOL, atol=1e-6)
+    got = ops.kvstar_scores(half(table), torch.from_numpy(off).cuda(), half(q), torch.from_numpy(qoff).cuda(),
+                            total=int(off[-1]), max_q_tokens=8, slot_ids=torch.from_numpy(slots).cuda(),
+                            pruned_index=torch.from_numpy(pruned).cuda()).cpu().numpy()
+    assert N.device_error() == 0
+    for r in range(len(xs)):
+        want = oracle.kvstar_scores(q[qoff[r]:qoff[r + 1]], table[slots[off[r]:off[r + 1]]], pruned[r])
+        np.testing.assert_allclose(got[off[r]:off[r + 1]], want, rtol=RTOL, atol=1e-6)
 
 
 def test_many_blocks_votes_sum_to_rows():

@@ -1,8 +1,9 @@
-"""Exchange of partial block scores through peer-mapped memory, summed inside the top-k kernel.
+"""Exchange of partial block scores through peer-mapped memory: delivered by the scoring kernel, summed
+inside the top-k kernel.
 
 On one GPU several "ranks" are emulated in ONE process: each gets its own buffer on the device,
-all ranks score and raise their flags first and only then do the top-k kernels run, so no kernel
-ever waits for another one that is not yet complete.  With two or more GPUs the real thing runs in
+all ranks score (which also raises their flags) first and only then do the top-k kernels run, so no
+kernel ever waits for another one that is not yet complete.  With two or more GPUs the real thing runs in
 child processes over symmetric memory and is compared with the NCCL all-reduce route."""
 import os
 import sys
@@ -40,25 +41,24 @@ def test_emulated_ranks_on_one_gpu(oracle):
     q = H.bf16_to_f32(H.randn_bf16(rng, (len(counts), Hkv, D)))
     ks = np.array([30, 3, 9, 25], np.int32)
     koff = H.ragged_offsets(np.minimum(ks, counts))
-    bufs = [torch.zeros(PeerScoreExchange.words_needed(total), dtype=torch.float32, device=DEV) for _ in range(world)]
+    bufs = [torch.zeros(PeerScoreExchange.words_needed(world, total), dtype=torch.float32, device=DEV) for _ in range(world)]
     ex = [PeerScoreExchange([b.data_ptr() for b in bufs], r, total, torch.device(DEV), bufs[r]) for r in range(world)]
     d_off, d_slots, d_k, d_koff = dev_i32(off), dev_i32(slots), dev_i32(ks), dev_i32(koff)
     full = oracle.score_dot_esa(H.bf16_to_f32(reps16).reshape(n_slots, -1), off, slots, q.reshape(len(counts), -1))
-    for rnd in range(3):                                                  # three rounds: both halves, growing epochs
+    for rnd in range(3):                                                  # three rounds: both halves, growing round numbers
         scale = float(rnd + 1)
         for r in range(world):
             lo, hi = head_range(Hkv, r, world)
             table = dev_bf16(np.ascontiguousarray(reps16[:, lo:hi]))
             qr = torch.from_numpy(np.ascontiguousarray(q[:, lo:hi].reshape(len(counts), -1))).to(DEV)
             ops.score_dot(table, d_off, qr, total=total, slot_ids=d_slots, n_kv_heads=hi - lo, head_dim=D, scale=scale,
-                          out=ex[r].begin_round())
-            ex[r].signal()
+                          exchange=ex[r])
         sels = []
         for r in range(world):
             idx = torch.full((int(koff[-1]),), -1, dtype=torch.int32, device=DEV)
             cnt = torch.zeros((len(counts),), dtype=torch.int32, device=DEV)
-            ex[r].topk(d_off, d_k, out_stride=int(ks.max()), order=ops.ORDER_SCORE_DESC, out_idx=idx, out_counts=cnt,
-                       id_map=d_slots, out_offsets=d_koff)
+            ex[r].topk(d_off, d_k, total=total, out_stride=int(ks.max()), order=ops.ORDER_SCORE_DESC, out_idx=idx,
+                       out_counts=cnt, id_map=d_slots, out_offsets=d_koff)
             sels.append((idx.cpu().numpy(), cnt.cpu().numpy(), ex[r].summed.cpu().numpy()))
         for r in range(1, world):                                          # every rank: identical bits
             assert np.array_equal(sels[r][0], sels[0][0]) and np.array_equal(sels[r][2], sels[0][2])
@@ -69,19 +69,84 @@ def test_emulated_ranks_on_one_gpu(oracle):
     assert _native.device_error() == 0
 
 
+def test_wide_rows_and_replay_from_a_cuda_graph(oracle):
+    """Two emulated ranks with 2 KiB rows each (the copy-engine scoring kernel with the raw query folded in); the
+    round counter lives in the exchange buffer, so score + top-k of both ranks is captured once and replayed."""
+    from ucmx import _native, ops
+    from ucmx.parallel import PeerScoreExchange, head_range
+    rng = np.random.default_rng(112)
+    world, Hkv, Hq, D, n_slots = 2, 16, 32, 128, 900
+    reps16 = H.randn_bf16(rng, (n_slots, Hkv, D), 0.09)
+    counts = [500, 37, 240]
+    off = H.ragged_offsets(counts)
+    total = int(off[-1])
+    slots = rng.integers(0, n_slots, total).astype(np.int32)
+    q16 = H.randn_bf16(rng, (len(counts), Hq, D))
+    ks = np.array([40, 5, 12], np.int32)
+    koff = H.ragged_offsets(ks)
+    dev = torch.device(DEV)
+    bufs = [torch.zeros(PeerScoreExchange.words_needed(world, total), dtype=torch.float32, device=DEV) for _ in range(world)]
+    ex = [PeerScoreExchange([b.data_ptr() for b in bufs], r, total, dev, bufs[r]) for r in range(world)]
+    d_off, d_slots, d_k, d_koff = dev_i32(off), dev_i32(slots), dev_i32(ks), dev_i32(koff)
+    tables, queries = [], []
+    for r in range(world):
+        lo, hi = head_range(Hkv, r, world)
+        tables.append(dev_bf16(np.ascontiguousarray(reps16[:, lo:hi])))
+        queries.append(dev_bf16(np.ascontiguousarray(q16[:, lo * 2:hi * 2])))      # two query heads per KV head
+    idx = [torch.full((int(koff[-1]),), -1, dtype=torch.int32, device=DEV) for _ in range(world)]
+    cnt = [torch.zeros((len(counts),), dtype=torch.int32, device=DEV) for _ in range(world)]
+
+    def one_round():
+        for r in range(world):
+            ops.score_dot_query(tables[r], d_off, queries[r], total=total, slot_ids=d_slots, n_kv_heads=Hkv // world,
+                                exchange=ex[r])
+        for r in range(world):
+            ex[r].topk(d_off, d_k, total=total, out_stride=int(ks.max()), order=ops.ORDER_SCORE_DESC, out_idx=idx[r],
+                       out_counts=cnt[r], id_map=d_slots, out_offsets=d_koff)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        one_round()                                             # sets up lazily initialised state outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    qbar = oracle.query_group_mean(q16, Hkv, True)
+    full = oracle.score_dot_esa(H.bf16_to_f32(reps16).reshape(n_slots, -1), off, slots, qbar)
+    want = np.concatenate([oracle.topk_esa(full[off[i]:off[i + 1]], int(ks[i]), slots[off[i]:off[i + 1]])[0]
+                           for i in range(len(counts))])
+    first = idx[0].cpu().numpy().copy()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_round()
+    for _ in range(3):                                          # odd and even rounds: both halves of the inbox
+        for t in idx:
+            t.fill_(-1)
+        graph.replay()
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert np.array_equal(idx[r].cpu().numpy(), first)
+    np.testing.assert_allclose(ex[0].summed.cpu().numpy(), full, rtol=1e-3, atol=1e-3 * float(np.abs(full).std()))
+    # the sums differ from the checker's by rounding only; where that does not reorder anything the ids agree
+    assert (np.sort(first) == np.sort(want)).mean() > 0.97
+    assert _native.device_error() == 0
+
+
 def test_missing_signal_is_reported_not_hung():
-    """A peer that never raises its flag: the bounded wait gives up, records code 4 and the kernel returns."""
+    """A peer that never delivers: the bounded wait gives up, records code 4 and the kernel returns."""
     from ucmx import _native, ops
     from ucmx.parallel import PeerScoreExchange
     total = 64
-    bufs = [torch.zeros(PeerScoreExchange.words_needed(total), dtype=torch.float32, device=DEV) for _ in range(2)]
-    ex0 = PeerScoreExchange([b.data_ptr() for b in bufs], 0, total, torch.device(DEV), bufs[0])
-    ex0.begin_round().fill_(1.0)
-    ex0.signal()                                               # rank 1 stays silent
+    dev = torch.device(DEV)
+    bufs = [torch.zeros(PeerScoreExchange.words_needed(2, total), dtype=torch.float32, device=DEV) for _ in range(2)]
+    ex0 = PeerScoreExchange([b.data_ptr() for b in bufs], 0, total, dev, bufs[0])
+    table = torch.ones((total, 1, 1, 128), dtype=torch.bfloat16, device=DEV)
+    q = torch.ones((1, 128), dtype=torch.float32, device=DEV)
+    ops.score_dot(table, dev_i32([0, total]), q, total=total, n_kv_heads=1, head_dim=128, exchange=ex0)   # rank 1 stays silent
     idx = torch.full((4,), -1, dtype=torch.int32, device=DEV)
     cnt = torch.zeros((1,), dtype=torch.int32, device=DEV)
     _native.device_error()
-    ex0.topk(dev_i32([0, total]), dev_i32([4]), out_stride=4, order=ops.ORDER_SCORE_DESC, out_idx=idx, out_counts=cnt)
+    ex0.topk(dev_i32([0, total]), dev_i32([4]), total=total, out_stride=4, order=ops.ORDER_SCORE_DESC, out_idx=idx,
+             out_counts=cnt)
     torch.cuda.synchronize()
     assert _native.device_error() == 4
     assert cnt.item() == 4                                     # the context is intact and the kernel completed
@@ -116,12 +181,11 @@ def _two_gpu_worker(rank, world, port, out_dir):
     ex = PeerScoreExchange.create(total, dev)
     res = []
     for rnd in range(4):
-        ops.score_dot(table, d_off, qr, total=total, slot_ids=d_slots, n_kv_heads=hi - lo, head_dim=D, out=ex.begin_round())
-        ex.signal()
+        ops.score_dot(table, d_off, qr, total=total, slot_ids=d_slots, n_kv_heads=hi - lo, head_dim=D, exchange=ex)
         idx = torch.full((int(koff[-1]),), -1, dtype=torch.int32, device=dev)
         cnt = torch.zeros((3,), dtype=torch.int32, device=dev)
-        ex.topk(d_off, d_k, out_stride=100, order=ops.ORDER_SCORE_DESC, out_idx=idx, out_counts=cnt, id_map=d_slots,
-                out_offsets=d_koff)
+        ex.topk(d_off, d_k, total=total, out_stride=100, order=ops.ORDER_SCORE_DESC, out_idx=idx, out_counts=cnt,
+                id_map=d_slots, out_offsets=d_koff)
         res.append(idx.cpu().numpy())
     # the library route: all-reduce between the two kernels
     part = ops.score_dot(table, d_off, qr, total=total, slot_ids=d_slots, n_kv_heads=hi - lo, head_dim=D)

@@ -226,6 +226,87 @@ def test_esa_hooks_select_and_load_the_right_blocks(oracle):
     store.close()
 
 
+def test_esa_requests_at_different_decode_steps(oracle):
+    """Continuous batching: request B starts decoding one iteration after request A, so with stride 3 A collects a
+    retrieval in the very iteration in which B starts one (and the other way round an iteration later).  Each
+    request must get its own selection, from the query of its own step 2, loaded at its own step 3."""
+    from ucmx.sparse.base import UcmSparseRole
+    from ucmx.sparse.esa import ESA, ESASparseMetaData, ReqMeta, block_hashes_of
+    from ucmx.store.dramstore import UcmDramStore, store_offset
+
+    slice_bytes = T * HKV * D * 2
+    store = UcmDramStore({"role": "worker", "max_cache_size": 512 * slice_bytes, "kv_block_size": slice_bytes, "device": DEV})
+    cfg = {"init_window_sz": 1, "local_window_sz": 2, "min_blocks": 4, "sparse_ratio": 0.3, "retrieval_stride": 3}
+    esa = ESA(make_config("ESA", cfg, store), UcmSparseRole.WORKER)
+    run = Runner(esa, seed=83)
+    rng = run.rng
+    prompts = {"A": list(rng.integers(0, 1000, 22 * T)), "B": list(rng.integers(0, 1000, 30 * T))}
+    prefill_blocks = {"A": list(range(0, 22)), "B": list(range(22, 52))}
+    sparse_range = {"A": 20, "B": 28}
+    top_k = {"A": 6, "B": 8}
+    decode_blocks = {"A": list(range(60, 60 + 6 + 2)), "B": list(range(70, 70 + 8 + 2))}
+    hashes = {r: block_hashes_of(prompts[r], T) for r in prompts}
+
+    def dump_to_store(r):
+        for l in range(LAYERS):
+            n = len(hashes[r])
+            ok = store_offset((T, HKV, D), 0, 1, 2, l, False)
+            ov = store_offset((T, HKV, D), 0, 1, 2, l, True)
+            assert store.wait(store.dump(hashes[r], [ok] * n, [run.kv[l][0][b] for b in prefill_blocks[r][:n]])) == 0
+            assert store.wait(store.dump(hashes[r], [ov] * n, [run.kv[l][1][b] for b in prefill_blocks[r][:n]])) == 0
+            run.kv[l][:, decode_blocks[r]] = 0
+
+    def expected(l, r, q_tok_u16):
+        reps = oracle.pool_blocks(run.kv_host[l][0], np.asarray(prefill_blocks[r][:sparse_range[r]], np.int32), 0, True)
+        qbar = oracle.query_group_mean(q_tok_u16[None], HKV, True)
+        s = oracle.score_dot_esa(reps, np.array([0, len(reps)], np.int32), None, qbar)
+        idx, _ = oracle.topk_esa(s, top_k[r])
+        return {hashes[r][int(i)] for i in idx}
+
+    def check_loaded(l, r, want_hashes):
+        held = esa.req_states[r].pre_topk[l]
+        assert set(held.values()) == want_hashes and set(held) == set(decode_blocks[r][:top_k[r]])
+        for blk, h in held.items():
+            src = prefill_blocks[r][hashes[r].index(h)]
+            assert torch.equal(run.kv[l][0][blk], dev_bf16(run.kv_host[l][0][src]))
+
+    out = {"A": [], "B": []}
+    q_of = {"A": {}, "B": {}}          # request -> its decode step -> per-layer query row (uint16)
+    # iteration 0: A prefills.  iteration i >= 1: A is at decode step i; B prefills in iteration 1 and is at step i-1 after.
+    n_a = len(prompts["A"])
+    run.step([ReqMeta("A", 0, n_a, 0, prefill_blocks["A"], 0, prompts["A"], [])],
+             [dev_bf16(H.randn_bf16(rng, (n_a, HQ, D))) for _ in range(LAYERS)], ESASparseMetaData())
+    dump_to_store("A")
+    for it in range(1, 7):
+        out["A"].append(it)
+        metas = [ReqMeta("A", 0, 1, n_a + it - 1, decode_blocks["A"], 0, prompts["A"], list(out["A"]))]
+        if it == 1:
+            n_b = len(prompts["B"])
+            metas.append(ReqMeta("B", 1, n_b, 0, prefill_blocks["B"], 1, prompts["B"], []))
+            rows = 1 + n_b
+        else:
+            out["B"].append(it - 1)
+            metas.append(ReqMeta("B", 1, 1, len(prompts["B"]) + it - 2, decode_blocks["B"], 1, prompts["B"], list(out["B"])))
+            rows = 2
+        q_u16 = [H.randn_bf16(rng, (rows, HQ, D)) for _ in range(LAYERS)]
+        q_of["A"][it] = [q[0] for q in q_u16]
+        if it >= 2:
+            q_of["B"][it - 1] = [q[1] for q in q_u16]
+        run.step(metas, [dev_bf16(q) for q in q_u16], ESASparseMetaData())
+        if it == 1:
+            dump_to_store("B")
+        # a request's selection is in place after its step 1 (query of step 1) and after its steps 3 and 6 (query of steps 2 and 5)
+        for r, step in (("A", it), ("B", it - 1)):
+            src_step = {1: 1, 3: 2, 4: 2, 6: 5}.get(step)
+            if src_step is None:
+                continue
+            if step in (3, 6):                      # loads were launched in this iteration; they are waited for at the next step
+                esa._wait_transfer_task_done(0), esa._wait_transfer_task_done(1)
+            for l in range(LAYERS):
+                check_loaded(l, r, expected(l, r, q_of[r][src_step][l]))
+    store.close()
+
+
 def test_kvcomp_hooks_select_and_load(oracle):
     from ucmx.sparse.base import UcmSparseRole
     from ucmx.sparse.kvcomp import KvComp, KvCompSparseMetaData, ReqMeta, block_hash

@@ -122,3 +122,43 @@ def test_remap_replays_recorded_prefetch_engine(name):
             assert ll[l * k: l * k + lc[l]].tolist() == want["miss_idx"][l][: lc[l]]
             assert [int(p) for p, f in zip(phys, free[l]) if f] == want["free"][l]
             assert {str(int(p)): int(x) for p, x in zip(phys, logical[l])} == want["blocks_map"][l]
+
+
+def test_packed_move_list_equals_the_per_request_load_lists():
+    """With a move list, a round also leaves ONE list (block to read in the pool -> HBM block) for the whole batch:
+    the same loads as the per-request lists hold, each mapped through the request's row of the block table."""
+    from ucmx import ops
+    rng = np.random.default_rng(303)
+    n_req = 9
+    n_blocks = rng.integers(30, 200, n_req)
+    ks = np.maximum(4, n_blocks // 6).astype(np.int32)
+    boff = np.concatenate([[0], np.cumsum(n_blocks)]).astype(np.int32)
+    koff = np.concatenate([[0], np.cumsum(ks)]).astype(np.int32)
+    block_table = rng.permutation(int(boff[-1])).astype(np.int32)         # pool block of every logical block
+    total_k = int(koff[-1])
+    d_logical = dev(np.full(total_k, -1, np.int32))
+    d_free = dev(np.ones(total_k, np.uint8), np.uint8)
+    d_phys = dev(np.arange(total_k, dtype=np.int32))
+    moves = ops.MoveList(total_k, torch.device(DEV))
+    seen_moves = 0
+    for rnd in range(4):
+        sel = np.concatenate([np.sort(rng.choice(n_blocks[r], ks[r], replace=False)) for r in range(n_req)]).astype(np.int32)
+        table, ll, lp, lc = ops.remap_resident(d_logical, d_free, d_phys, dev(koff), dev(sel), dev(koff),
+                                               max_logical=int(n_blocks.max()), max_slots=int(ks.max()),
+                                               src_map=dev(block_table), src_map_offsets=dev(boff), moves=moves)
+        torch.cuda.synchronize()
+        n = int(moves.count[0])
+        ll, lp, lc = ll.cpu().numpy(), lp.cpu().numpy(), lc.cpu().numpy()
+        assert n == int(lc.sum()) and int(moves.count[1]) == 0
+        want = set()
+        for r in range(n_req):
+            for j in range(lc[r]):
+                want.add((int(block_table[boff[r] + ll[koff[r] + j]]), int(lp[koff[r] + j])))
+            assert (ll[koff[r] + lc[r]: koff[r + 1]] == -1).all() and (lp[koff[r] + lc[r]: koff[r + 1]] == -1).all()
+        got = set(zip(moves.src[:n].cpu().tolist(), moves.dst[:n].cpu().tolist()))
+        assert got == want and len(got) == n
+        seen_moves += n
+        moves.count.zero_()                                    # (move_blocks would do this)
+        if rnd == 0:
+            assert n == total_k                                # nothing was resident: every selected block is a load
+    assert seen_moves < 4 * total_k                            # later rounds hit resident blocks

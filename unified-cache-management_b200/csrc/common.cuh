@@ -18,6 +18,12 @@ int32_t* error_word();  // device-visible int that bounded waits report into (NU
 int32_t cuda_status(const char* what, cudaError_t e);
 int sm_count();  // multiprocessors of the current device (cached)
 
+// scoring with an explicit error word (NULL: out-of-range ids and lost copies are skipped without a report)
+int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads, int32_t n_rep,
+                       int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids, const float* q,
+                       int32_t n_req, int32_t total, float scale, float* out_scores, const ucmx_peer_exchange* ex,
+                       int32_t* err, cudaStream_t st);
+
 // tensor-core (tcgen05) sign-hash encoder; g == NULL: dense vectors, else paged blocks. UCMX_EUNSUPPORTED = not applicable
 int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucmx_kv_geometry* g, const int32_t* ids,
                        const int32_t* out_slots, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
@@ -127,6 +133,28 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
         "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+// The same with an L2 eviction policy: data that is read (or written) once and not again soon is marked
+// evict-first, so that a pass over gigabytes does not push the small hot arrays of the next kernels out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_hint(void* gdst, const void* smem_src, uint32_t bytes, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(gdst),
+                 "r"(smem_u32(smem_src)), "r"(bytes), "l"(policy)
+                 : "memory");
+}
 // shared -> global bulk copy, tracked by the issuing thread's bulk async-group
 __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes)
 {
@@ -149,6 +177,70 @@ __device__ __forceinline__ void bulk_wait_all()
 __device__ __forceinline__ void fence_proxy_async()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ------------------------------------------------------------------ tensor-parallel score exchange
+//
+// Exchange buffer of one rank (ucmx_peer_exchange in the C ABI; every rank can address every rank's buffer):
+//   bytes [0,128)   flag[r]: the last round rank r has delivered into this buffer
+//   bytes [128,132) arrival counter of this rank's scoring kernel (thread blocks that are done)
+//   bytes [132,136) round counter of this rank (rounds its scoring kernel has completed)
+//   bytes [256,..)  inbox[parity][source rank][part_bytes]: partial scores, two halves used alternately
+// A round: every rank's scoring kernel stores its partial scores into inbox[round & 1][my_rank] of EVERY rank,
+// its last thread block publishes the round number into flag[my_rank] of every rank, and the top-k kernel that
+// follows waits for all flags of its own buffer and adds the inbox rows up in rank order.  The round number
+// lives in the buffer, not in a kernel argument, so the same launches can be replayed from a CUDA graph.
+constexpr int kPeerHeaderBytes = 256;
+constexpr int kPeerArriveOffset = 128;
+constexpr int kPeerRoundOffset = 132;
+
+// bytes one rank's partial scores take inside a half of the inbox
+inline int64_t peer_part_bytes(int64_t n_scores) { return ((n_scores * 4 + 127) / 128) * 128; }
+
+struct PeerPush {
+    unsigned char* const* bases;   // device array: base of every rank's exchange buffer, in rank order
+    int32_t world, my_rank;
+    int64_t part_bytes;            // bytes of one rank's partial scores inside a half (multiple of 128)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// round this rank's scoring kernel is working on (read by every thread block at its start; the counter moves
+// only after all of them have arrived at the end, so they all see the same value)
+__device__ __forceinline__ uint32_t peer_round_now(const PeerPush& px)
+{
+    return *reinterpret_cast<const volatile uint32_t*>(px.bases[px.my_rank] + kPeerRoundOffset) + 1u;
+}
+__device__ __forceinline__ int64_t peer_inbox_offset(const PeerPush& px, uint32_t round, int src_rank)
+{
+    return (int64_t)kPeerHeaderBytes + ((int64_t)(round & 1u) * px.world + src_rank) * px.part_bytes;
+}
+// End of a scoring kernel under tensor parallelism; called by every thread of every thread block after its last
+// score store.  The block that arrives last makes the round visible: counter, then one flag per rank.
+__device__ __forceinline__ void peer_publish_round(const PeerPush& px, uint32_t round)
+{
+    __threadfence_system();          // this thread's stores into the peers' inboxes are performed
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned char* mine = px.bases[px.my_rank];
+        uint32_t* arrive = reinterpret_cast<uint32_t*>(mine + kPeerArriveOffset);
+        const uint32_t blocks = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(arrive, 1u) == blocks - 1u) {
+            __threadfence_system();
+            *reinterpret_cast<volatile uint32_t*>(arrive) = 0u;
+            *reinterpret_cast<volatile uint32_t*>(mine + kPeerRoundOffset) = round;
+            for (int t = 0; t < px.world; ++t)
+                st_release_sys_u32(reinterpret_cast<uint32_t*>(px.bases[t]) + px.my_rank, round);
+        }
+    }
 }
 
 __device__ __forceinline__ float warp_sum(float v)

@@ -362,7 +362,7 @@ extern "C" int32_t ucmx_hash_encode(const void* x, int64_t n_vec, int64_t x_stri
     if (n_vec == 0) return UCMX_OK;
     if (!x || !w || !out || x_stride < dim || (x_stride % 8) || ((uintptr_t)x & 15) || ((uintptr_t)out & 3))
         return UCMX_EPARAM;
-    if (!getenv("UCMX_HASH_NO_TC")) {
+    {
         const int32_t rc = hash_encode_tc(x, n_vec, x_stride, nullptr, nullptr, nullptr, 0, w, dim, bits, 0, out,
                                           (cudaStream_t)stream);
         if (rc != UCMX_EUNSUPPORTED) return rc;
@@ -389,7 +389,7 @@ extern "C" int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_ge
     if (!k_cache || !block_ids || !w || !out || ((uintptr_t)k_cache & 15) || ((uintptr_t)out & 3)) return UCMX_EPARAM;
     if (g->block_tokens < 1 || g->n_kv_heads < 1 || g->head_dim < 8) return UCMX_EPARAM;
     if ((g->token_stride % 8) || (g->block_stride % 8) || (g->head_dim % 8)) return UCMX_EPARAM;
-    if (!getenv("UCMX_HASH_NO_TC")) {
+    {
         const int32_t rc = hash_encode_tc(k_cache, 0, 0, g, block_ids, out_slots, n, w, g->head_dim, bits, head_major, out,
                                           (cudaStream_t)stream);
         if (rc != UCMX_EUNSUPPORTED) return rc;

@@ -973,6 +973,50 @@ extern "C" int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_ge
     return UCMX_OK;
 }
 
+namespace ucmx {
+namespace {
+// Does the shape take the tensor-core kernels, and which one: 0 = no (CUDA-core kernel), 1 = one block per tile,
+// 2 = two blocks per instruction.  Needs p.M, p.H, p.dp, p.C, p.Rp; fills the tiling fields of p.
+int plan_tensor_core(KsParams& p, int64_t n_slots)
+{
+    const int M = p.M, H = p.H, d_pruned = p.dp, C = p.C;
+    // several heads per 128-row instruction, whole 64-element K chunks per head group
+    bool tc = encode_fn() != nullptr && p.Rp <= kRows && (d_pruned % 16) == 0 && (M % 32) == 0 && M <= 256 &&
+              (C % 64) == 0 && n_slots * M < 0x7fffffffll;
+    if (!tc) return 0;
+    p.hpg = kRows / p.Rp < H ? kRows / p.Rp : H;
+    while (p.hpg > 1 && (H % p.hpg || (p.hpg * d_pruned) % 64)) --p.hpg;
+    if (!(H % p.hpg == 0 && (p.hpg * d_pruned) % 64 == 0)) return 0;
+    p.G = H / p.hpg;
+    p.cpg = p.hpg * d_pruned / 64;
+    if (p.G * M > 256) return 0;                 // two accumulator sets must fit the 512 TMEM columns
+    p.n_acc = p.G * M <= 128 ? 4 : 2;
+    p.tile_bytes = M * C * 2;
+    const size_t a_bytes = (size_t)p.G * p.cpg * kChunkA;
+    const int64_t budget = 220 * 1024 - 1024 - (int64_t)a_bytes - (int64_t)sizeof(KsBarriers) - 64;
+    p.stages = budget > 0 ? (int)(budget / p.tile_bytes) : 0;
+    if (p.stages > 8) p.stages = 8;
+    if (p.stages < 2) return 0;                  // wide heads (no channel pruning) do not fit: CUDA-core kernel
+    return (M == 64 && C == 256 && p.cpg == 2 && p.G == 2) ? 2 : 1;
+}
+}  // namespace
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_kvstar_kernel_choice(int32_t n_slots, int32_t M, int32_t n_kv_heads, int32_t d_pruned,
+                                             int32_t max_q_tokens, int32_t n_q_heads)
+{
+    using namespace ucmx;
+    if (M < 1 || n_kv_heads < 1 || d_pruned < 1 || n_q_heads < n_kv_heads || n_q_heads % n_kv_heads || max_q_tokens < 1)
+        return UCMX_EPARAM;
+    KsParams p{};
+    p.M = M;
+    p.H = n_kv_heads;
+    p.dp = d_pruned;
+    p.C = n_kv_heads * d_pruned;
+    p.Rp = row_pad(max_q_tokens * (n_q_heads / n_kv_heads));
+    return plan_tensor_core(p, n_slots);
+}
+
 extern "C" size_t ucmx_kvstar_workspace_bytes(int32_t total_blocks, int32_t n_req, int32_t max_q_tokens, int32_t n_q_heads,
                                               int32_t n_kv_heads)
 {
@@ -1020,29 +1064,11 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
     p.out = out_scores;
     p.err = error_word();
 
-    // tensor-core path: several heads per 128-row instruction, whole 64-element K chunks per head group
-    bool tc = getenv("UCMX_KVSTAR_NO_TC") == nullptr && encode_fn() != nullptr && p.Rp <= kRows && (d_pruned % 16) == 0 &&
-              (M % 32) == 0 && M <= 256 && (C % 64) == 0 && (int64_t)n_slots * M < 0x7fffffffll;
-    if (tc) {
-        p.hpg = kRows / p.Rp < H ? kRows / p.Rp : H;
-        while (p.hpg > 1 && (H % p.hpg || (p.hpg * d_pruned) % 64)) --p.hpg;
-        tc = H % p.hpg == 0 && (p.hpg * d_pruned) % 64 == 0;
-    }
-    if (tc) {
-        p.G = H / p.hpg;
-        p.cpg = p.hpg * d_pruned / 64;
-        tc = p.G * M <= 256;                         // two accumulator sets must fit the 512 TMEM columns
-        p.n_acc = p.G * M <= 128 ? 4 : 2;
-    }
+    bool tc = plan_tensor_core(p, n_slots) != 0;
     if (tc) {
         p.idesc = (1u << 4) | ((uint32_t)(M >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);   // D fp32, A and B half, K-major
-        p.tile_bytes = M * C * 2;
         const size_t a_bytes = (size_t)p.G * p.cpg * kChunkA;
-        const int64_t budget = 220 * 1024 - 1024 - (int64_t)a_bytes - (int64_t)sizeof(KsBarriers) - 64;
-        p.stages = budget > 0 ? (int)(budget / p.tile_bytes) : 0;
-        if (p.stages > 8) p.stages = 8;
-        tc = p.stages >= 2;                          // wide heads (no channel pruning) do not fit: CUDA-core kernel
-        if (tc) {
+        {
             alignas(64) CUtensorMap tmap;
             const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)n_slots * M};
             const cuuint64_t strides[1] = {(cuuint64_t)C * 2};
@@ -1055,7 +1081,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
                 const size_t smem = 1024 + a_bytes + (size_t)p.stages * p.tile_bytes + sizeof(KsBarriers) + 64;
                 int grid = sm_count();
                 if (grid > total) grid = total;
-                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2 && getenv("UCMX_KVSTAR_ONE_BLOCK_TILES") == nullptr) {
+                if (M == 64 && C == 256 && p.cpg == 2 && p.G == 2) {
                     const size_t psmem = 1024 + 4 * (size_t)kChunkA + 2 * (size_t)kPairStage + sizeof(KsBarriers) + 64;
                     UCMX_CUDA(cudaFuncSetAttribute(kvstar_partial_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
                     int pgrid = sm_count();
@@ -1075,10 +1101,6 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
         }
     }
     if (!tc) {
-        if (getenv("UCMX_KVSTAR_REQUIRE_TC")) {
-            set_last_text("kvstar: this shape does not take the tensor-core path");
-            return UCMX_EUNSUPPORTED;
-        }
         const size_t smem = (size_t)M * C * 2;
         if (smem > 200 * 1024) {
             set_last_text("kvstar: a block's representations do not fit in shared memory");

@@ -50,8 +50,9 @@ int32_t scratch_for_current_device(float** out)
 }  // namespace
 }  // namespace ucmx
 
-extern "C" int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dtype, int32_t n_kv_heads,
-                                              int32_t n_rep, int32_t head_dim, const int32_t* req_offsets,
+extern "C" int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dtype, int64_t n_slots,
+                                              int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
+                                              const int32_t* req_offsets,
                                               const int32_t* slot_ids, const float* q, int32_t n_req,
                                               int32_t total, float scale, const int32_t* k_per_req,
                                               int32_t start_win, int32_t end_win, int32_t window_mode,
@@ -72,8 +73,9 @@ extern "C" int32_t ucmx_retrieve_topk_noalloc(const void* reps, int32_t reps_dty
     if (rc != UCMX_OK) return rc;
     // Every score in [0, total) is written by the scoring kernel before the top-k kernel, next on the
     // same stream, reads it; nothing in the scratch has to start from zero.
-    rc = ucmx_score_dot(reps, reps_dtype, n_kv_heads, n_rep, head_dim, req_offsets, slot_ids, q, n_req, total,
-                        scale, scratch, stream);
+    // (no error word on this path: the one ucmx_device_error reads is allocated on first use)
+    rc = score_dot_impl(reps, reps_dtype, n_slots, n_kv_heads, n_rep, head_dim, req_offsets, slot_ids, q, n_req,
+                        total, scale, scratch, nullptr, nullptr, (cudaStream_t)stream);
     if (rc != UCMX_OK) return rc;
     return ucmx_topk_ragged(scratch, UCMX_DT_F32, req_offsets, k_per_req, n_req, start_win, end_win, window_mode,
                             order, id_map, out_stride, out_offsets, out_idx, out_scores, out_counts, stream);

@@ -416,7 +416,7 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
     p.out_bf16 = (uint16_t*)out_bf16;
     p.out_f32 = out_f32;
     p.err = error_word();
-    if (!getenv("UCMX_POOL_NO_TILE")) {
+    {
         PoolParams pt = p;
         const int32_t rc = launch_pool_tile(pt, g, mode, (cudaStream_t)stream);
         if (rc != UCMX_EUNSUPPORTED) return rc;
@@ -428,10 +428,6 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
     int cs = 1;
     const int n_cg_row = p.E / 8;
     while ((int64_t)n * cs < 4 * (int64_t)sms && cs < 8 && n_cg_row % (cs * 2) == 0 && n_cg_row / (cs * 2) >= 16) cs *= 2;
-    if (const char* e = getenv("UCMX_POOL_CS")) {  // tuning knob
-        const int v = atoi(e);
-        if (v >= 1 && v <= 8 && n_cg_row % v == 0) cs = v;
-    }
     p.cs = cs;
     p.cg_per_item = n_cg_row / cs;
     const int64_t piece_bytes = (int64_t)p.cg_per_item * 16;

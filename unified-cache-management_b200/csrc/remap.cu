@@ -23,10 +23,12 @@ struct RemapParams {
     const int32_t* sel_offsets;
     const int32_t* sel_counts;  // optional: valid entries of each request's selection
     int32_t max_logical;
+    int32_t max_slots;          // slots per request the shared-memory lists were sized for
     int32_t* table;
     int32_t* load_logical;
     int32_t* load_phys;
     int32_t* load_counts;
+    ucmx_remap_moves mv;             // optional (mv.move_count != NULL): one packed move list for all requests
     int32_t* err;
 };
 
@@ -71,6 +73,20 @@ __global__ void __launch_bounds__(kRemapThreads) remap_resident_kernel(RemapPara
     int32_t* free_list = lookup + p.max_logical;       // n_slots entries
     int32_t* hit = free_list + n_slots;                // n_slots entries
 
+    if (n_slots > p.max_slots || n_slots < 0) {
+        // more slots than the lists behind the lookup table were sized for: refuse the request, touch nothing
+        for (int j = tid; j < n_sel; j += kRemapThreads) table[j] = -1;
+        const int room = __ldg(p.sel_offsets + r + 1) - j0;
+        for (int j = tid; j < room; j += kRemapThreads) {
+            p.load_logical[j0 + j] = -1;
+            p.load_phys[j0 + j] = -1;
+        }
+        if (tid == 0) {
+            p.load_counts[r] = 0;
+            if (p.err) atomicExch(p.err, 3);
+        }
+        return;
+    }
     for (int i = tid; i < p.max_logical; i += kRemapThreads) lookup[i] = -1;
     for (int i = tid; i < n_slots; i += kRemapThreads) hit[i] = 0;
     __syncthreads();
@@ -128,7 +144,26 @@ __global__ void __launch_bounds__(kRemapThreads) remap_resident_kernel(RemapPara
     }
     __syncthreads();
     for (int s = tid; s < n_slots; s += kRemapThreads) slot_free[s] = hit[s] ? 0 : 1;
-    if (tid == 0) p.load_counts[r] = min(n_miss, n_free);
+    // the rest of this request's room in the load lists is marked empty, so that a block mover can take the lists
+    // of all requests as one array and skip what is not a load
+    const int n_load = min(n_miss, n_free);
+    const int room = __ldg(p.sel_offsets + r + 1) - j0;
+    for (int j = n_load + tid; j < room; j += kRemapThreads) {
+        p.load_logical[j0 + j] = -1;
+        p.load_phys[j0 + j] = -1;
+    }
+    if (tid == 0) p.load_counts[r] = n_load;
+    if (p.mv.move_count && n_load > 0) {
+        // this request's loads join the list of moves of the whole batch
+        __shared__ int s_base;
+        if (tid == 0) s_base = atomicAdd(p.mv.move_count, n_load);
+        __syncthreads();
+        const int src0 = p.mv.src_map_offsets ? __ldg(p.mv.src_map_offsets + r) : 0;
+        for (int j = tid; j < n_load; j += kRemapThreads) {
+            p.mv.move_src[s_base + j] = __ldg(p.mv.src_map + src0 + p.load_logical[j0 + j]);
+            p.mv.move_dst[s_base + j] = p.load_phys[j0 + j];
+        }
+    }
 }
 
 }  // namespace
@@ -138,7 +173,7 @@ extern "C" int32_t ucmx_remap_resident(int32_t* slot_logical, uint8_t* slot_free
                                        const int32_t* slot_offsets, const int32_t* sel, const int32_t* sel_offsets,
                                        const int32_t* sel_counts, int32_t n_req, int32_t max_logical,
                                        int32_t max_slots, int32_t* table, int32_t* load_logical, int32_t* load_phys,
-                                       int32_t* load_counts, ucmx_stream_t stream)
+                                       int32_t* load_counts, const ucmx_remap_moves* moves, ucmx_stream_t stream)
 {
     using namespace ucmx;
     if (n_req < 0 || max_logical < 1 || max_slots < 0) return UCMX_EPARAM;
@@ -146,12 +181,17 @@ extern "C" int32_t ucmx_remap_resident(int32_t* slot_logical, uint8_t* slot_free
     if (!slot_logical || !slot_free || !slot_phys || !slot_offsets || !sel || !sel_offsets || !table || !load_logical ||
         !load_phys || !load_counts)
         return UCMX_EPARAM;
+    ucmx_remap_moves mv{};
+    if (moves) {
+        if (!moves->src_map || !moves->move_src || !moves->move_dst || !moves->move_count) return UCMX_EPARAM;
+        mv = *moves;
+    }
     const size_t smem = ((size_t)max_logical + 2 * (size_t)max_slots) * sizeof(int32_t);
     if (smem > 200 * 1024) return UCMX_EUNSUPPORTED;
     if (smem > 48 * 1024)
         UCMX_CUDA(cudaFuncSetAttribute(remap_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     RemapParams p{slot_logical, slot_free, slot_phys, slot_offsets, sel, sel_offsets, sel_counts, max_logical,
-                  table, load_logical, load_phys, load_counts, error_word()};
+                  max_slots, table, load_logical, load_phys, load_counts, mv, error_word()};
     remap_resident_kernel<<<n_req, kRemapThreads, smem, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("remap_resident_kernel");
     return UCMX_OK;

@@ -3,6 +3,7 @@
 // condition variables (ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp, ucm/store/task/*,
 // ucm/store/device/ibuffered_device.h) with CUDA streams and events: submitting work enqueues
 // kernels, polling is an event query, waiting is a bounded event wait.
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstring>
@@ -200,27 +201,69 @@ __global__ void f32_to_bf16_rows_kernel(const float* __restrict__ src, const int
     if (dst_f32) dst_f32[slot * dim + d] = v;
 }
 
-__global__ void fill_regular_offsets_kernel(int32_t* offsets, int32_t* k_per_req, int32_t batch, int32_t max_idx,
-                                            int32_t k)
-{
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i <= batch) offsets[i] = i * max_idx;
-    if (i < batch) k_per_req[i] = k;
-}
+// Page-locked host memory that grows by doubling (contents kept).
+struct PinnedBuf {
+    unsigned char* p = nullptr;
+    size_t size = 0, cap = 0;
+    int32_t reserve(size_t want)
+    {
+        if (want <= cap) return UCMX_OK;
+        size_t ncap = cap ? cap : (size_t)64 << 10;
+        while (ncap < want) ncap *= 2;
+        unsigned char* np = nullptr;
+        UCMX_CUDA(cudaHostAlloc((void**)&np, ncap, cudaHostAllocPortable));
+        if (p) {
+            memcpy(np, p, size);
+            cudaFreeHost(p);
+        }
+        p = np;
+        cap = ncap;
+        return UCMX_OK;
+    }
+    int32_t append(const void* src, size_t bytes)
+    {
+        const int32_t rc = reserve(size + bytes);
+        if (rc != UCMX_OK) return rc;
+        memcpy(p + size, src, bytes);
+        size += bytes;
+        return UCMX_OK;
+    }
+    void release()
+    {
+        if (p) cudaFreeHost(p);
+        p = nullptr;
+        size = cap = 0;
+    }
+};
 
-struct Request {
-    int32_t id = -1;
-    int32_t batch = 0, k = 0, topk = 0;
-    // pinned host staging
-    unsigned char* h_in = nullptr;
-    size_t h_in_cap = 0;
-    unsigned char* h_out = nullptr;
-    size_t h_out_cap = 0;
-    // device buffers
+// A batch is what goes to the GPU in one piece: the query rows and candidate lists of every submit that
+// arrived since the last launch.  One ragged score + top-k serves them all.
+struct Batch {
+    PinnedBuf h_q, h_idx, h_out;
+    std::vector<int32_t> off{0}, kk, ooff{0};   // CSR of candidates, k per row, CSR of outputs
+    PinnedBuf h_meta;
     unsigned char* d_buf = nullptr;
     size_t d_cap = 0;
     cudaEvent_t done = nullptr;
-    bool in_flight = false;
+    int32_t open = 0;          // requests whose result has not been collected yet
+    int32_t kmax = 1;
+    bool launched = false, failed = false;
+    size_t o_counts = 0, o_idx = 0;   // byte offsets inside h_out once launched
+    void reset()
+    {
+        h_q.size = h_idx.size = h_out.size = h_meta.size = 0;
+        off.assign(1, 0);
+        kk.clear();
+        ooff.assign(1, 0);
+        open = 0;
+        kmax = 1;
+        launched = failed = false;
+    }
+};
+
+struct Request {
+    Batch* batch = nullptr;
+    int32_t row0 = 0, rows = 0, k = 0;
 };
 
 }  // namespace
@@ -235,8 +278,10 @@ struct ucmx_retrieval {
     cudaStream_t stream = nullptr;
     std::mutex mu;
     int32_t next_id = 0;
-    std::unordered_map<int32_t, ucmx::Request*> live;
-    std::vector<ucmx::Request*> pool;
+    int64_t launches = 0;
+    std::unordered_map<int32_t, ucmx::Request> live;
+    ucmx::Batch* building = nullptr;
+    std::vector<ucmx::Batch*> pool;
 };
 
 namespace ucmx {
@@ -258,41 +303,100 @@ struct DeviceGuard {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-int32_t ensure_caps(Request* rq, size_t in_bytes, size_t out_bytes, size_t dev_bytes)
+constexpr int32_t kFlushRows = 2048;               // a batch under construction is launched at this many query rows
+constexpr size_t kFlushCandidates = (size_t)4 << 20;   // or this many candidates
+
+void free_batch(Batch* b)
 {
-    if (rq->h_in_cap < in_bytes) {
-        if (rq->h_in) cudaFreeHost(rq->h_in);
-        rq->h_in = nullptr;
-        rq->h_in_cap = 0;
-        UCMX_CUDA(cudaHostAlloc((void**)&rq->h_in, in_bytes, cudaHostAllocPortable));
-        rq->h_in_cap = in_bytes;
+    if (!b) return;
+    b->h_q.release();
+    b->h_idx.release();
+    b->h_out.release();
+    b->h_meta.release();
+    if (b->d_buf) cudaFree(b->d_buf);
+    if (b->done) cudaEventDestroy(b->done);
+    delete b;
+}
+
+// Launches the batch under construction (caller holds the lock, the object's device is current).  A failure marks
+// the batch: its requests then report the error from wait / get_result.
+int32_t flush_locked(ucmx_retrieval* r)
+{
+    Batch* b = r->building;
+    if (!b || b->kk.empty()) return UCMX_OK;
+    r->building = nullptr;
+    b->launched = true;
+    const size_t rows = b->kk.size();
+    const size_t total = (size_t)b->off.back();
+    const size_t ksum = (size_t)b->ooff.back();
+    const size_t s_q = align_up(b->h_q.size, 256), s_idx = align_up(total * 4, 256);
+    const size_t m_off = align_up((rows + 1) * 4, 256), m_k = align_up(rows * 4, 256);
+    const size_t s_meta = 2 * m_off + m_k;
+    const size_t s_scores = align_up(total * 4, 256);
+    b->o_counts = align_up(rows * 4, 256);
+    b->o_idx = align_up((ksum ? ksum : 1) * 4, 256);
+    const size_t out_bytes = b->o_counts + 2 * b->o_idx;
+    const size_t dev_bytes = s_q + s_idx + s_meta + s_scores + out_bytes;
+    auto fail = [&](int32_t rc) {
+        b->failed = true;
+        cudaStreamSynchronize(r->stream);      // nothing of this batch is in flight when its buffers are reused
+        return rc;
+    };
+    if (b->d_cap < dev_bytes) {
+        if (b->d_buf) cudaFree(b->d_buf);
+        b->d_buf = nullptr;
+        b->d_cap = 0;
+        const cudaError_t e = cudaMalloc((void**)&b->d_buf, dev_bytes + dev_bytes / 2);
+        if (e != cudaSuccess) return fail(cuda_status("cudaMalloc(batch)", e));
+        b->d_cap = dev_bytes + dev_bytes / 2;
     }
-    if (rq->h_out_cap < out_bytes) {
-        if (rq->h_out) cudaFreeHost(rq->h_out);
-        rq->h_out = nullptr;
-        rq->h_out_cap = 0;
-        UCMX_CUDA(cudaHostAlloc((void**)&rq->h_out, out_bytes, cudaHostAllocPortable));
-        rq->h_out_cap = out_bytes;
+    int32_t rc = b->h_out.reserve(out_bytes);
+    if (rc == UCMX_OK) rc = b->h_meta.reserve(s_meta);
+    if (rc != UCMX_OK) return fail(rc);
+    if (!b->done) {
+        const cudaError_t e = cudaEventCreateWithFlags(&b->done, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(cuda_status("cudaEventCreate", e));
     }
-    if (rq->d_cap < dev_bytes) {
-        if (rq->d_buf) cudaFree(rq->d_buf);
-        rq->d_buf = nullptr;
-        rq->d_cap = 0;
-        UCMX_CUDA(cudaMalloc((void**)&rq->d_buf, dev_bytes));
-        rq->d_cap = dev_bytes;
-    }
-    if (!rq->done) UCMX_CUDA(cudaEventCreateWithFlags(&rq->done, cudaEventDisableTiming));
+    memcpy(b->h_meta.p, b->off.data(), (rows + 1) * 4);
+    memcpy(b->h_meta.p + m_off, b->ooff.data(), (rows + 1) * 4);
+    memcpy(b->h_meta.p + 2 * m_off, b->kk.data(), rows * 4);
+
+    unsigned char* d = b->d_buf;
+    float* d_q = (float*)d;
+    int32_t* d_slots = (int32_t*)(d + s_q);
+    int32_t* d_off = (int32_t*)(d + s_q + s_idx);
+    int32_t* d_ooff = (int32_t*)((unsigned char*)d_off + m_off);
+    int32_t* d_k = (int32_t*)((unsigned char*)d_off + 2 * m_off);
+    float* d_scores = (float*)(d + s_q + s_idx + s_meta);
+    unsigned char* d_out = (unsigned char*)d_scores + s_scores;
+    int32_t* d_counts = (int32_t*)d_out;
+    int32_t* d_oidx = (int32_t*)(d_out + b->o_counts);
+    float* d_osc = (float*)(d_out + b->o_counts + b->o_idx);
+
+    cudaStream_t st = r->stream;
+    cudaError_t e = cudaMemcpyAsync(d_q, b->h_q.p, b->h_q.size, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_slots, b->h_idx.p, total * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_off, b->h_meta.p, s_meta, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(cuda_status("submit H2D", e));
+    rc = ucmx_score_dot(r->table, r->dtype, r->n_items, 1, 1, r->dim, d_off, d_slots, d_q, (int32_t)rows, (int32_t)total,
+                        1.0f, d_scores, nullptr, st);
+    if (rc == UCMX_OK && ksum > 0)
+        rc = ucmx_topk_ragged(d_scores, UCMX_DT_F32, d_off, d_k, (int32_t)rows, 0, 0, UCMX_WIN_NONE, UCMX_ORDER_SCORE_DESC,
+                              d_slots, b->kmax, d_ooff, d_oidx, d_osc, d_counts, st);
+    if (rc != UCMX_OK) return fail(rc);
+    r->launches += ksum > 0 ? 2 : 1;
+    if (ksum == 0) e = cudaMemsetAsync(d_counts, 0, rows * 4, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(b->h_out.p, d_out, out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaEventRecord(b->done, st);
+    if (e != cudaSuccess) return fail(cuda_status("submit D2H", e));
     return UCMX_OK;
 }
 
-void free_request(Request* rq)
+void retire_if_done(ucmx_retrieval* r, Batch* b)
 {
-    if (!rq) return;
-    if (rq->h_in) cudaFreeHost(rq->h_in);
-    if (rq->h_out) cudaFreeHost(rq->h_out);
-    if (rq->d_buf) cudaFree(rq->d_buf);
-    if (rq->done) cudaEventDestroy(rq->done);
-    delete rq;
+    if (b->open > 0) return;
+    b->reset();
+    r->pool.push_back(b);
 }
 
 }  // namespace
@@ -408,81 +512,78 @@ extern "C" int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_qu
         return UCMX_EPARAM;
     }
     if (batch < 1 || max_idx < 1 || topk < 0) return UCMX_EPARAM;
-    if ((int64_t)batch * max_idx > 0x7fffffffll) return UCMX_EUNSUPPORTED;
+    if ((int64_t)batch * max_idx > 0x3fffffffll) return UCMX_EUNSUPPORTED;
     const int32_t k = topk < max_idx ? topk : max_idx;
     if (k > 8192) return UCMX_EUNSUPPORTED;
-    const int32_t kcap = k > 0 ? k : 1;
+    const size_t cand = (size_t)batch * max_idx;
+    // The index lists are in host memory here, so a bad one is refused before anything reaches the GPU
+    // (-1 pads a row; the reference bounds its loop by the table it owns, retrieval_backend.cpp:170-181).
+    for (size_t i = 0; i < cand; ++i) {
+        const int32_t v = host_indexes[i];
+        if (v < -1 || (int64_t)v >= r->n_items) {
+            set_last_text("ucmx_retrieval_submit: an index is outside the table (allowed: -1 for padding, 0 .. n_items-1)");
+            return UCMX_EPARAM;
+        }
+    }
     DeviceGuard g(r->device);
+    if (!g.ok) return UCMX_EPARAM;
     std::lock_guard<std::mutex> lk(r->mu);
 
-    Request* rq = nullptr;
-    if (!r->pool.empty()) {
-        rq = r->pool.back();
-        r->pool.pop_back();
-    } else {
-        rq = new (std::nothrow) Request();
-        if (!rq) return UCMX_EOOM;
+    Batch* b = r->building;
+    if (b && ((int32_t)b->kk.size() + batch > kFlushRows || (size_t)b->off.back() + cand > kFlushCandidates)) {
+        flush_locked(r);           // a failure is recorded in that batch and reported to its own requests
+        b = nullptr;
     }
-    const size_t total = (size_t)batch * max_idx;
-    // host -> device block: [query fp32 b*dim | slot ids int32 total]
-    const size_t in_q = align_up((size_t)batch * r->dim * 4, 256);
-    const size_t in_idx = align_up(total * 4, 256);
-    // device scratch behind it: [offsets b+1 | k_per_req b | scores total | counts b | out_idx b*k | out_scores b*k]
-    const size_t s_off = align_up((size_t)(batch + 1) * 4, 256);
-    const size_t s_k = align_up((size_t)batch * 4, 256);
-    const size_t s_scores = align_up(total * 4, 256);
-    const size_t o_counts = align_up((size_t)batch * 4, 256);
-    const size_t o_idx = align_up((size_t)batch * kcap * 4, 256);
-    const size_t o_sc = align_up((size_t)batch * kcap * 4, 256);
-    const size_t out_bytes = o_counts + o_idx + o_sc;
-    const size_t dev_bytes = in_q + in_idx + s_off + s_k + s_scores + out_bytes;
-    int32_t rc = ensure_caps(rq, in_q + in_idx, out_bytes, dev_bytes);
+    if (!b) {
+        if (!r->pool.empty()) {
+            b = r->pool.back();
+            r->pool.pop_back();
+        } else {
+            b = new (std::nothrow) Batch();
+            if (!b) return UCMX_EOOM;
+        }
+        r->building = b;
+    }
+    const size_t q_size = b->h_q.size, idx_size = b->h_idx.size;
+    int32_t rc = b->h_q.append(host_query, (size_t)batch * r->dim * 4);
+    if (rc == UCMX_OK) rc = b->h_idx.append(host_indexes, cand * 4);
     if (rc != UCMX_OK) {
-        free_request(rq);
+        b->h_q.size = q_size;
+        b->h_idx.size = idx_size;
         return rc;
     }
-    memcpy(rq->h_in, host_query, (size_t)batch * r->dim * 4);
-    memcpy(rq->h_in + in_q, host_indexes, total * 4);
+    Request rq;
+    rq.batch = b;
+    rq.row0 = (int32_t)b->kk.size();
+    rq.rows = batch;
+    rq.k = k;
+    for (int32_t i = 0; i < batch; ++i) {
+        b->off.push_back(b->off.back() + max_idx);
+        b->kk.push_back(k);
+        b->ooff.push_back(b->ooff.back() + k);
+    }
+    if (k > b->kmax) b->kmax = k;
+    b->open += 1;
+    const int32_t id = r->next_id++;
+    r->live[id] = rq;
+    *req_id = id;
+    return UCMX_OK;
+}
 
-    unsigned char* d = rq->d_buf;
-    float* d_q = (float*)d;
-    int32_t* d_slots = (int32_t*)(d + in_q);
-    int32_t* d_off = (int32_t*)(d + in_q + in_idx);
-    int32_t* d_k = (int32_t*)((unsigned char*)d_off + s_off);
-    float* d_scores = (float*)((unsigned char*)d_k + s_k);
-    unsigned char* d_out = (unsigned char*)d_scores + s_scores;
-    int32_t* d_counts = (int32_t*)d_out;
-    int32_t* d_oidx = (int32_t*)(d_out + o_counts);
-    float* d_osc = (float*)(d_out + o_counts + o_idx);
+extern "C" int32_t ucmx_retrieval_flush(ucmx_retrieval* r)
+{
+    using namespace ucmx;
+    if (!r) return UCMX_EPARAM;
+    DeviceGuard g(r->device);
+    std::lock_guard<std::mutex> lk(r->mu);
+    return flush_locked(r);
+}
 
-    cudaStream_t st = r->stream;
-    cudaError_t e = cudaMemcpyAsync(d, rq->h_in, in_q + in_idx, cudaMemcpyHostToDevice, st);
-    if (e != cudaSuccess) {
-        r->pool.push_back(rq);
-        return cuda_status("submit H2D", e);
-    }
-    fill_regular_offsets_kernel<<<(batch + 256) / 256, 256, 0, st>>>(d_off, d_k, batch, max_idx, k);
-    rc = ucmx_score_dot(r->table, r->dtype, 1, 1, r->dim, d_off, d_slots, d_q, batch, (int32_t)total, 1.0f, d_scores, st);
-    if (rc == UCMX_OK && k > 0)
-        rc = ucmx_topk_ragged(d_scores, UCMX_DT_F32, d_off, d_k, batch, 0, 0, UCMX_WIN_NONE, UCMX_ORDER_SCORE_DESC,
-                              d_slots, kcap, nullptr, d_oidx, d_osc, d_counts, st);
-    if (rc != UCMX_OK) {
-        r->pool.push_back(rq);
-        return rc;
-    }
-    e = cudaMemcpyAsync(rq->h_out, d_out, out_bytes, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaEventRecord(rq->done, st);
-    if (e != cudaSuccess) {
-        r->pool.push_back(rq);
-        return cuda_status("submit D2H", e);
-    }
-    rq->id = r->next_id++;
-    rq->batch = batch;
-    rq->k = k;
-    rq->topk = topk;
-    rq->in_flight = true;
-    r->live[rq->id] = rq;
-    *req_id = rq->id;
+extern "C" int32_t ucmx_retrieval_launches(ucmx_retrieval* r, int64_t* kernels)
+{
+    if (!r || !kernels) return UCMX_EPARAM;
+    std::lock_guard<std::mutex> lk(r->mu);
+    *kernels = r->launches;
     return UCMX_OK;
 }
 
@@ -490,18 +591,19 @@ extern "C" int32_t ucmx_retrieval_poll(ucmx_retrieval* r, int32_t req_id, int32_
 {
     using namespace ucmx;
     if (!r || !ready) return UCMX_EPARAM;
+    DeviceGuard g(r->device);
     std::lock_guard<std::mutex> lk(r->mu);
+    *ready = 0;
     auto it = r->live.find(req_id);
-    if (it == r->live.end()) {
-        *ready = 0;
-        return UCMX_OK;  // the reference's poll answers "not there" with false, not an error
-    }
-    cudaError_t e = cudaEventQuery(it->second->done);
+    if (it == r->live.end()) return UCMX_OK;  // the reference's poll answers "not there" with false, not an error
+    Batch* b = it->second.batch;
+    if (!b->launched) flush_locked(r);
+    if (b->failed) return UCMX_ERROR;
+    const cudaError_t e = cudaEventQuery(b->done);
     if (e == cudaSuccess) {
         *ready = 1;
         return UCMX_OK;
     }
-    *ready = 0;
     if (e == cudaErrorNotReady) {
         cudaGetLastError();
         return UCMX_OK;
@@ -515,10 +617,14 @@ extern "C" int32_t ucmx_retrieval_wait(ucmx_retrieval* r, int32_t req_id)
     if (!r) return UCMX_EPARAM;
     cudaEvent_t ev = nullptr;
     {
+        DeviceGuard g(r->device);
         std::lock_guard<std::mutex> lk(r->mu);
         auto it = r->live.find(req_id);
         if (it == r->live.end()) return UCMX_ENOOBJ;  // "Bad req_id"
-        ev = it->second->done;
+        Batch* b = it->second.batch;
+        if (!b->launched) flush_locked(r);
+        if (b->failed) return UCMX_ERROR;
+        ev = b->done;
     }
     UCMX_CUDA(cudaEventSynchronize(ev));
     return UCMX_OK;
@@ -530,8 +636,8 @@ extern "C" int32_t ucmx_retrieval_result_shape(ucmx_retrieval* r, int32_t req_id
     std::lock_guard<std::mutex> lk(r->mu);
     auto it = r->live.find(req_id);
     if (it == r->live.end()) return UCMX_ENOOBJ;
-    if (batch) *batch = it->second->batch;
-    if (topk) *topk = it->second->k;
+    if (batch) *batch = it->second.rows;
+    if (topk) *topk = it->second.k;
     return UCMX_OK;
 }
 
@@ -539,32 +645,41 @@ extern "C" int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, 
 {
     using namespace ucmx;
     if (!r || !host_indices || !host_scores) return UCMX_EPARAM;
+    DeviceGuard g(r->device);
     std::lock_guard<std::mutex> lk(r->mu);
     auto it = r->live.find(req_id);
     if (it == r->live.end()) return UCMX_ENOOBJ;
-    Request* rq = it->second;
-    cudaError_t e = cudaEventQuery(rq->done);
+    const Request rq = it->second;
+    Batch* b = rq.batch;
+    if (!b->launched) flush_locked(r);
+    if (b->failed) {
+        r->live.erase(it);
+        b->open -= 1;
+        retire_if_done(r, b);
+        return UCMX_ERROR;
+    }
+    const cudaError_t e = cudaEventQuery(b->done);
     if (e == cudaErrorNotReady) {
         cudaGetLastError();
         return UCMX_ENOOBJ;  // "Result not ready"
     }
     if (e != cudaSuccess) return cuda_status("cudaEventQuery", e);
-    const int32_t b = rq->batch, k = rq->k, kcap = k > 0 ? k : 1;
-    const size_t o_counts = align_up((size_t)b * 4, 256);
-    const size_t o_idx = align_up((size_t)b * kcap * 4, 256);
-    const int32_t* counts = (const int32_t*)rq->h_out;
-    const int32_t* idx = (const int32_t*)(rq->h_out + o_counts);
-    const float* sc = (const float*)(rq->h_out + o_counts + o_idx);
-    for (int32_t i = 0; i < b; ++i) {
+    const int32_t k = rq.k;
+    const int32_t* counts = (const int32_t*)b->h_out.p;
+    const int32_t* idx = (const int32_t*)(b->h_out.p + b->o_counts);
+    const float* sc = (const float*)(b->h_out.p + b->o_counts + b->o_idx);
+    for (int32_t i = 0; i < rq.rows; ++i) {
+        const int32_t row = rq.row0 + i;
+        const size_t o = (size_t)b->ooff[row];
         for (int32_t j = 0; j < k; ++j) {
-            const bool valid = j < counts[i] && idx[(size_t)i * kcap + j] >= 0;
-            host_indices[(size_t)i * k + j] = valid ? idx[(size_t)i * kcap + j] : -1;
-            host_scores[(size_t)i * k + j] = valid ? sc[(size_t)i * kcap + j] : -INFINITY;
+            const bool valid = j < counts[row] && idx[o + j] >= 0;
+            host_indices[(size_t)i * k + j] = valid ? idx[o + j] : -1;
+            host_scores[(size_t)i * k + j] = valid ? sc[o + j] : -INFINITY;
         }
     }
     r->live.erase(it);
-    rq->in_flight = false;
-    r->pool.push_back(rq);
+    b->open -= 1;
+    retire_if_done(r, b);
     return UCMX_OK;
 }
 
@@ -574,8 +689,14 @@ extern "C" int32_t ucmx_retrieval_destroy(ucmx_retrieval* r)
     if (!r) return UCMX_EPARAM;
     DeviceGuard g(r->device);
     if (r->stream) cudaStreamSynchronize(r->stream);
-    for (auto& kv : r->live) free_request(kv.second);
-    for (auto* rq : r->pool) free_request(rq);
+    std::vector<Batch*> seen;
+    for (auto& kv : r->live) {
+        Batch* b = kv.second.batch;
+        if (b != r->building && std::find(seen.begin(), seen.end(), b) == seen.end()) seen.push_back(b);
+    }
+    for (Batch* b : seen) free_batch(b);
+    free_batch(r->building);
+    for (Batch* b : r->pool) free_batch(b);
     if (r->table) cudaFree(r->table);
     if (r->stream) cudaStreamDestroy(r->stream);
     delete r;

@@ -2,12 +2,15 @@
 //
 // score_dot: every candidate block contributes one table row (2 KiB of bf16 for 8 heads x 128)
 // that is read exactly once and dotted with its request's query, so the kernel is a gather-GEMV
-// bound by HBM (about 1 flop per byte); it runs on CUDA cores with 16-byte streaming loads, one
-// warp per row and four rows in flight per warp, the query held in registers.  Tensor cores would
-// add nothing here.  The grid is one resident wave (a multiple of the SM count), each warp owning
-// a contiguous slice of the candidate list.  The per-KV-head query mean of the reference
-// (ucm/sparse/esa/esa.py:291-296) can be folded into the same kernel so that a decode step needs
-// no separate prologue launch.
+// bound by HBM (about 1 flop per byte); the arithmetic runs on CUDA cores, tensor cores would add
+// nothing.  Rows are brought in by the copy engine (one bulk async copy per row into a per-warp
+// ring in shared memory), so a warp keeps a fixed number of rows in flight without holding them
+// in registers.  The grid is one resident wave (a multiple of the SM count), each warp owning a
+// contiguous slice of the candidate list.  The per-KV-head query mean of the reference
+// (ucm/sparse/esa/esa.py:291-296) is folded into the same kernel so that a decode step needs no
+// separate prologue launch.  Under tensor parallelism the kernel also delivers its partial scores
+// into every peer's inbox and raises the peers' flags when its last thread block is done: the
+// all-gather half of the score all-reduce costs no launch of its own.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -16,8 +19,10 @@ namespace ucmx {
 namespace {
 
 constexpr int kScoreThreads = 256;
-constexpr int kMaxSmemOffsets = 2049;
-constexpr int kRowsInFlight = 4;
+constexpr int kMaxRingStages = 16;
+constexpr int kMaxSmemOffsets = 2049;        // request offsets kept in shared memory (more requests: read from global)
+constexpr int kRingSmemPerSm = 200 * 1024;   // shared memory the row rings of one SM may take
+constexpr int kRingStages = 3;               // rows a warp keeps in flight (measured at 2 KiB rows: 2-3 best, 6 slower)
 
 // ------------------------------------------------------------------ query group mean
 
@@ -49,15 +54,19 @@ __global__ void query_group_mean_kernel(const uint16_t* __restrict__ q, int n_to
 
 struct ScoreParams {
     const void* reps;
+    int64_t n_slots;         // rows of the table; a slot id at or beyond it is skipped and reported
     const int32_t* offsets;
     const int32_t* slot_ids;
     const float* q;          // fp32 [n_req, E] (already reduced per KV head), or NULL
     const uint16_t* q_raw;   // bf16 [n_req, Hq, D] when the group mean is folded in
     int64_t q_raw_stride;    // elements between requests in q_raw
     int32_t Hq, D, round_bf16;
-    float* out;
+    float* out;              // may be NULL when the scores only go to the peers' inboxes
     int32_t n_req, total, E;
     float scale;
+    int32_t stages;          // ring depth per warp
+    PeerPush px;             // px.world == 0: single rank
+    int32_t* err;
 };
 
 // Element layout per lane: a row is cut into 16-byte pieces; piece j of a row belongs to lane
@@ -101,17 +110,74 @@ struct RowDot {
     }
     // q from the raw bf16 query [Hq, D]: mean over the head group in fp32 (heads in ascending
     // order, times 1/group), optionally rounded to bf16 — the arithmetic of query_group_mean_kernel.
-    __device__ __noinline__ void load_q_raw(const uint16_t* __restrict__ qreq, int lane, int Hq, int Hkv, int D,
+    // All loads of a lane are requested before the first one is used (the query comes from L2 or HBM).
+    template <int G>
+    __device__ __forceinline__ void load_q_raw_g(const uint16_t* __restrict__ qreq, int lane, int rep, int D, bool mean,
+                                                 int round_bf16)
+    {
+        constexpr int kChunks = QN / 4;      // four consecutive elements of the flattened [Hkv, D] query each
+        constexpr int kBatch = kChunks * G > 32 ? (32 / G) : kChunks;   // at most 32 loads of 8 bytes in flight
+        const float inv = 1.0f / (float)G;
+#pragma unroll
+        for (int c0 = 0; c0 < kChunks; c0 += kBatch) {
+            uint2 w[kBatch][G];
+#pragma unroll
+            for (int cc = 0; cc < kBatch; ++cc) {
+                const int c = c0 + cc;
+                const int e0 = ((c / (kPerPiece / 4)) * 32 + lane) * kPerPiece + (c % (kPerPiece / 4)) * 4;
+                const int h = e0 / D, d = e0 - h * D;
+                const uint16_t* src = qreq + (int64_t)((h / rep) * G) * D + d;
+#pragma unroll
+                for (int j = 0; j < G; ++j) w[cc][j] = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * D));
+            }
+#pragma unroll
+            for (int cc = 0; cc < kBatch; ++cc) {
+                const int c = c0 + cc;
+                float a0 = bf16lo(w[cc][0].x), a1 = bf16hi(w[cc][0].x), a2 = bf16lo(w[cc][0].y), a3 = bf16hi(w[cc][0].y);
+#pragma unroll
+                for (int j = 1; j < G; ++j) {
+                    a0 += bf16lo(w[cc][j].x);
+                    a1 += bf16hi(w[cc][j].x);
+                    a2 += bf16lo(w[cc][j].y);
+                    a3 += bf16hi(w[cc][j].y);
+                }
+                if (mean) {
+                    a0 *= inv;
+                    a1 *= inv;
+                    a2 *= inv;
+                    a3 *= inv;
+                    if (round_bf16) {
+                        a0 = bf16_round(a0);
+                        a1 = bf16_round(a1);
+                        a2 = bf16_round(a2);
+                        a3 = bf16_round(a3);
+                    }
+                }
+                q[c * 4 + 0] = a0;
+                q[c * 4 + 1] = a1;
+                q[c * 4 + 2] = a2;
+                q[c * 4 + 3] = a3;
+            }
+        }
+    }
+    __device__ __forceinline__ void load_q_raw(const uint16_t* __restrict__ qreq, int lane, int Hq, int Hkv, int D,
                                                int round_bf16)
     {
         const int g = Hq >= Hkv ? Hq / Hkv : 1;
         const int rep = Hq >= Hkv ? 1 : Hkv / Hq;
-        const float inv = 1.0f / (float)g;
+        const bool mean = Hq >= Hkv;
+        switch (g) {
+            case 1: load_q_raw_g<1>(qreq, lane, rep, D, mean, round_bf16); return;
+            case 2: load_q_raw_g<2>(qreq, lane, rep, D, mean, round_bf16); return;
+            case 4: load_q_raw_g<4>(qreq, lane, rep, D, mean, round_bf16); return;
+            case 8: load_q_raw_g<8>(qreq, lane, rep, D, mean, round_bf16); return;
+            default: break;
+        }
+        const float inv = 1.0f / (float)g;      // any other group size: one head at a time
 #pragma unroll
         for (int i = 0; i < kPieces; ++i) {
 #pragma unroll
             for (int half = 0; half < kPerPiece / 4; ++half) {
-                // four consecutive elements e0..e0+3 of the flattened [Hkv, D] query
                 const int e0 = (i * 32 + lane) * kPerPiece + half * 4;
                 const int h = e0 / D, d = e0 - h * D;
                 const uint16_t* src = qreq + (int64_t)((h / rep) * g) * D + d;
@@ -124,17 +190,15 @@ struct RowDot {
                     a2 += bf16lo(w.y);
                     a3 += bf16hi(w.y);
                 }
-                if (Hq >= Hkv) {
-                    a0 *= inv;
-                    a1 *= inv;
-                    a2 *= inv;
-                    a3 *= inv;
-                    if (round_bf16) {
-                        a0 = bf16_round(a0);
-                        a1 = bf16_round(a1);
-                        a2 = bf16_round(a2);
-                        a3 = bf16_round(a3);
-                    }
+                a0 *= inv;
+                a1 *= inv;
+                a2 *= inv;
+                a3 *= inv;
+                if (round_bf16) {
+                    a0 = bf16_round(a0);
+                    a1 = bf16_round(a1);
+                    a2 = bf16_round(a2);
+                    a3 = bf16_round(a3);
                 }
                 q[i * kPerPiece + half * 4 + 0] = a0;
                 q[i * kPerPiece + half * 4 + 1] = a1;
@@ -180,198 +244,202 @@ struct RowDot {
     }
 };
 
+// One warp per table row, rows fetched by the copy engine: every warp owns a contiguous slice of the
+// candidate list and a private ring of `stages` row buffers in shared memory.  Lane 0 keeps the ring full with
+// one bulk async copy per row (completion on the stage's mbarrier); the warp takes a row out of shared memory
+// as soon as it has landed, and the stage is refilled before the partial sums are even added up, so a warp has
+// `stages` rows in flight at all times without holding any of them in registers.  Scores are collected one per
+// lane and leave 32 at a time.  With `push` set (tensor-parallel ranks) every score is also written into each
+// peer's inbox, so the exchange of partial scores rides on the scoring kernel's own stores.
 template <int DT, int QN, bool FUSEQ>
-__global__ void __launch_bounds__(kScoreThreads, 2) score_dot_rows_kernel(ScoreParams p)
+__global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScoreParams p)
 {
-    __shared__ int32_t s_off[kMaxSmemOffsets];
-    const int lane = threadIdx.x & 31;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t W = (int64_t)gridDim.x * warps_per_cta;
-    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + warp;
     const int begin = (int)((int64_t)p.total * w / W);
     const int end = (int)((int64_t)p.total * (w + 1) / W);
 
     using RD = RowDot<DT, QN>;
-    RD rd;
-    const size_t row_bytes = (size_t)p.E * (DT == UCMX_DT_BF16 ? 2 : 4);
+    constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
+    const int stages = p.stages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem) + warp * kMaxRingStages;
+    unsigned char* ring = smem + (size_t)warps_per_cta * kMaxRingStages * 8 + (size_t)warp * stages * kRowBytes;
     const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
 
-    // Slot ids are held 32 rows at a time, one per lane (my_slot: rows [win, win+32); next_slot: the
-    // 32 after).  The first batch of row loads is issued before anything else in the kernel, so that
-    // HBM is already busy while the offsets and the queries are being staged.
+    if (lane == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    uint32_t round = 0;
+    int64_t push_off = 0;
+    if (p.px.world > 0) {
+        round = peer_round_now(p.px);
+        push_off = peer_inbox_offset(p.px, round, p.px.my_rank);
+    }
+    // A decode step runs this kernel right after gigabytes of block traffic, so nothing it needs is in L2.  What
+    // does not depend on anything is therefore requested first and used late: the request offsets (one coalesced
+    // read per thread block, searched in shared memory afterwards) and the slot ids; the rows follow as soon as
+    // the slot ids are there, and the query while the rows are on their way.
+    __shared__ int32_t s_off[kMaxSmemOffsets];
+    const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
+    int32_t off_reg[(kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads];
+    if (off_in_smem) {
+#pragma unroll
+        for (int j = 0; j < (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads; ++j) {
+            const int i = (int)threadIdx.x + j * kScoreThreads;
+            off_reg[j] = i <= p.n_req ? __ldg(p.offsets + i) : 0;
+        }
+    }
+    const uint64_t read_once = l2_evict_first_policy();      // every table row is read exactly once
+
+    RD rd;
+    int win = begin;
+    int cur = -1, nxt = -1;
     auto load_slots = [&](int first) {
         int v = -1;
-        if (first + lane < end) v = p.slot_ids ? __ldg(p.slot_ids + first + lane) : (first + lane);
+        if (first + lane < end) {
+            v = p.slot_ids ? __ldg(p.slot_ids + first + lane) : (first + lane);
+            if (v >= 0 && (int64_t)v >= p.n_slots) {
+                if (p.err) atomicExch(p.err, 3);
+                v = -1;
+            }
+        }
         return v;
     };
-    int win = begin;
-    int my_slot = load_slots(begin);
-    int next_slot = load_slots(begin + 32);
-    int s[kRowsInFlight];
-    uint4 buf[kRowsInFlight][RD::kPieces];
-    auto issue = [&](int c) {
-#pragma unroll
-        for (int t = 0; t < kRowsInFlight; ++t) {
-            const int v = __shfl_sync(0xffffffffu, my_slot, (c + t - win) & 31);
-            s[t] = (c + t < end) ? v : -1;
-            if (s[t] >= 0) rd.load_row(base + (size_t)s[t] * row_bytes, lane, buf[t]);
-            else rd.zero_row(buf[t]);
+    auto slot_at = [&](int row) {
+        const int a = __shfl_sync(0xffffffffu, cur, (row - win) & 31);
+        const int b = __shfl_sync(0xffffffffu, nxt, (row - win) & 31);
+        return row < win + 32 ? a : b;
+    };
+    auto fetch = [&](int row) {      // called by the whole warp
+        const int slot = slot_at(row);
+        if (lane == 0 && slot >= 0) {
+            const int s = (row - begin) % stages;
+            mbar_expect_tx(&full[s], kRowBytes);
+            bulk_g2s_hint(ring + (size_t)s * kRowBytes, base + (size_t)slot * kRowBytes, kRowBytes, &full[s], read_once);
         }
     };
-    issue(begin);
-
-    const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
-    if (off_in_smem) {
-        for (int i = threadIdx.x; i <= p.n_req; i += blockDim.x) s_off[i] = __ldg(p.offsets + i);
-        __syncthreads();
+    if (begin < end) {
+        // Slot ids are held 32 rows at a time, one per lane: `cur` covers rows [win, win+32), `nxt` the 32
+        // after; the row being fetched is at most `stages` (<= 16) ahead of the row being consumed, so both
+        // are always inside the two windows.  A slot outside the table is reported and treated as empty.
+        cur = load_slots(begin);
+        nxt = load_slots(begin + 32);
+        const int pre = min(end, begin + stages);
+        for (int row = begin; row < pre; ++row) fetch(row);
     }
+    if (off_in_smem) {
+#pragma unroll
+        for (int j = 0; j < (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads; ++j) {
+            const int i = (int)threadIdx.x + j * kScoreThreads;
+            if (i <= p.n_req) s_off[i] = off_reg[j];
+        }
+    }
+    __syncthreads();
     const int32_t* off = off_in_smem ? s_off : p.offsets;
-    const int Hkv = p.E / p.D;
 
-    // With the query mean folded in, the CTA first reduces the raw queries of the (at most
-    // kStagedReq) requests its slice starts in into shared memory, all threads at once; a warp that
-    // runs past them falls back to reducing its query on its own.
-    constexpr int kStagedReq = 2;
-    __shared__ __align__(16) float s_q[FUSEQ ? kStagedReq * QN * 32 : 4];
-    int r_cta = 0;
-    if (FUSEQ) {
-        const int cta_begin = (int)((int64_t)p.total * ((int64_t)blockIdx.x * warps_per_cta) / W);
+    if (begin < end) {
+        const int Hkv = p.E / p.D;
+        int r;
         {
-            int lo = 0, hi = p.n_req;
+            int lo = 0, hi = p.n_req;             // invariant: off[lo] <= begin < off[hi]
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;
-                if (off[mid] <= cta_begin) lo = mid; else hi = mid;
+                if (off[mid] <= begin) lo = mid; else hi = mid;
             }
-            r_cta = lo;
+            r = lo;
         }
-        const int g = p.Hq >= Hkv ? p.Hq / Hkv : 1;
-        const int rep = p.Hq >= Hkv ? 1 : Hkv / p.Hq;
-        const float inv = 1.0f / (float)g;
-        for (int idx = threadIdx.x; idx < kStagedReq * (p.E / 4); idx += blockDim.x) {
-            const int rr = idx / (p.E / 4);
-            const int e0 = (idx - rr * (p.E / 4)) * 4;
-            const int req = r_cta + rr;
-            if (req >= p.n_req) break;
-            const int h = e0 / p.D, d = e0 - h * p.D;
-            const uint16_t* src = p.q_raw + (int64_t)req * p.q_raw_stride + (int64_t)((h / rep) * g) * p.D + d;
-            uint2 w0 = __ldg(reinterpret_cast<const uint2*>(src));
-            float a0 = bf16lo(w0.x), a1 = bf16hi(w0.x), a2 = bf16lo(w0.y), a3 = bf16hi(w0.y);
-            if (g == 4) {
-                const uint2 w1 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)p.D));
-                const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)2 * p.D));
-                const uint2 w3 = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)3 * p.D));
-                a0 = ((a0 + bf16lo(w1.x)) + bf16lo(w2.x)) + bf16lo(w3.x);
-                a1 = ((a1 + bf16hi(w1.x)) + bf16hi(w2.x)) + bf16hi(w3.x);
-                a2 = ((a2 + bf16lo(w1.y)) + bf16lo(w2.y)) + bf16lo(w3.y);
-                a3 = ((a3 + bf16hi(w1.y)) + bf16hi(w2.y)) + bf16hi(w3.y);
-            } else {
-                for (int j = 1; j < g; ++j) {
-                    const uint2 wj = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * p.D));
-                    a0 += bf16lo(wj.x);
-                    a1 += bf16hi(wj.x);
-                    a2 += bf16lo(wj.y);
-                    a3 += bf16hi(wj.y);
-                }
-            }
-            if (p.Hq >= Hkv) {
-                a0 *= inv;
-                a1 *= inv;
-                a2 *= inv;
-                a3 *= inv;
-                if (p.round_bf16) {
-                    a0 = bf16_round(a0);
-                    a1 = bf16_round(a1);
-                    a2 = bf16_round(a2);
-                    a3 = bf16_round(a3);
-                }
-            }
-            *reinterpret_cast<float4*>(&s_q[rr * p.E + e0]) = make_float4(a0, a1, a2, a3);
-        }
-        __syncthreads();
-    }
-    if (begin >= end) return;
+        int r_end = off[r + 1];
+        auto fetch_q = [&](int req) {
+            if (FUSEQ) rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
+            else rd.load_q(p.q + (int64_t)req * p.E, lane);
+        };
+        fetch_q(r);
 
-    int r;
-    {
-        int lo = 0, hi = p.n_req;
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (off[mid] <= begin) lo = mid; else hi = mid;
-        }
-        r = lo;
-    }
-    int r_end = off[r + 1];
-
-    auto fetch_q = [&](int req) {
-        if (FUSEQ) {
-            if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * p.E], lane);
-            else rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
-        } else {
-            rd.load_q(p.q + (int64_t)req * p.E, lane);
-        }
-    };
-    bool q_valid = false;
-
-    for (int c = begin; c < end; c += kRowsInFlight) {
-        float v[kRowsInFlight];
-#pragma unroll
-        for (int t = 0; t < kRowsInFlight; ++t) {
-            v[t] = 0.0f;
-            const int row = c + t;
-            if (row < end) {
-                if (row >= r_end) {
-                    while (row >= r_end) {
-                        ++r;
-                        r_end = off[r + 1];
-                    }
-                    q_valid = false;
-                }
-                if (!q_valid) {
-                    fetch_q(r);
-                    q_valid = true;
-                }
-                v[t] = rd.dot(buf[t]);
+        float mine = 0.0f;        // score of row (flush_from + lane), once computed
+        int flush_from = begin;
+        uint32_t phase = 0;       // bit s: parity of the next completion of stage s (empty entries fetch nothing)
+        bool failed = false;
+        auto flush = [&](int upto) {   // rows [flush_from, upto), upto - flush_from <= 32
+            const int row = flush_from + lane;
+            if (row < upto) {
+                if (p.out) p.out[row] = mine;
+                for (int t = 0; t < p.px.world; ++t)
+                    reinterpret_cast<float*>(p.px.bases[t] + push_off)[row] = mine;
             }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-            for (int t = 0; t < kRowsInFlight; ++t) v[t] += __shfl_xor_sync(0xffffffffu, v[t], o);
-        }
-        if (lane < kRowsInFlight && c + lane < end) {
-            float mine = v[0];
-            int slot = s[0];
-#pragma unroll
-            for (int t = 1; t < kRowsInFlight; ++t)
-                if (lane == t) {
-                    mine = v[t];
-                    slot = s[t];
-                }
-            p.out[c + lane] = slot < 0 ? -INFINITY : mine * p.scale;
-        }
-        const int next = c + kRowsInFlight;
-        if (next < end) {
-            if (next >= win + 32) {  // 32 is a multiple of the batch, so a batch never straddles windows
+            flush_from = upto;
+        };
+
+        for (int row = begin; row < end; ++row) {
+            if (row >= r_end) {
+                do {
+                    ++r;
+                    r_end = off[r + 1];
+                } while (row >= r_end);
+                fetch_q(r);
+            }
+            if (row >= win + 32) {
                 win += 32;
-                my_slot = next_slot;
-                next_slot = load_slots(win + 32);
+                cur = nxt;
+                nxt = load_slots(win + 32);
             }
-            issue(next);
+            const int slot = slot_at(row);
+            const int s = (row - begin) % stages;
+            float v = 0.0f;
+            if (slot >= 0 && !failed) {
+                if (!mbar_wait(&full[s], (phase >> s) & 1u)) {
+                    failed = true;                      // the copy never landed: report, stop fetching
+                    if (p.err) atomicExch(p.err, 1);
+                } else {
+                    phase ^= 1u << s;
+                    uint4 buf[RD::kPieces];
+                    const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * kRowBytes);
+#pragma unroll
+                    for (int i = 0; i < RD::kPieces; ++i) buf[i] = src[i * 32 + lane];
+                    v = rd.dot(buf);
+                }
+            }
+            __syncwarp();                               // every lane has taken its part of stage s
+            if (row + stages < end && !failed) fetch(row + stages);
+            v = warp_sum(v);
+            if (lane == ((row - flush_from) & 31)) mine = slot < 0 ? -INFINITY : v * p.scale;
+            if (row - flush_from == 31) flush(row + 1);
         }
+        flush(end);
     }
+    if (p.px.world > 0) peer_publish_round(p.px, round);
 }
 
 // ------------------------------------------------------------------ general path: any n_rep
 
 struct ScoreGenParams {
     const void* reps;
+    int64_t n_slots;
     const int32_t* offsets;
     const int32_t* slot_ids;
     const float* q;
     float* out;
     int32_t n_req, total, H, R, D;
     float scale;
+    PeerPush px;
+    int32_t* err;
 };
+
+// slot id of candidate c, or -1 for an empty entry; an id beyond the table is reported (code 3) and skipped
+__device__ __forceinline__ int checked_slot(const int32_t* __restrict__ slot_ids, int64_t c, int64_t n_slots, int32_t* err)
+{
+    const int slot = slot_ids ? __ldg(slot_ids + c) : (int)c;
+    if (slot >= 0 && (int64_t)slot >= n_slots) {
+        if (err) atomicExch(err, 3);
+        return -1;
+    }
+    return slot;
+}
 
 // One warp per candidate.  For each KV head the warp takes the dot product of the query head with
 // each of the block's n_rep representatives and keeps the largest; head results are summed
@@ -391,7 +459,7 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
 
     for (int64_t c = w0; c < p.total; c += W) {
         const int r = find_request(p.offsets, p.n_req, (int)c);
-        const int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        const int slot = checked_slot(p.slot_ids, c, p.n_slots, p.err);
         if (slot < 0) {
             if (lane == 0) p.out[c] = -INFINITY;
             continue;
@@ -432,21 +500,64 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
     }
 }
 
+// Launch geometry of the ring kernel: one resident wave of `ctas_per_sm` thread blocks of 8 warps per SM, the
+// shared memory of an SM split evenly between the warps' rings.
+struct RingGeometry {
+    int grid, stages;
+    size_t smem;
+};
+
+RingGeometry ring_geometry(int32_t total, uint32_t row_bytes)
+{
+    constexpr int warps_per_cta = kScoreThreads / 32;
+    const size_t bar_bytes = (size_t)warps_per_cta * kMaxRingStages * 8;
+    int ctas_per_sm = 2;
+    int stages = (int)((kRingSmemPerSm / ctas_per_sm - bar_bytes) / ((size_t)warps_per_cta * row_bytes));
+    if (stages < 2) {                         // very wide rows: one thread block per SM gets all of it
+        ctas_per_sm = 1;
+        stages = (int)((kRingSmemPerSm - bar_bytes) / ((size_t)warps_per_cta * row_bytes));
+    }
+    if (stages > kRingStages) stages = kRingStages;
+    RingGeometry g;
+    int64_t grid = (int64_t)sm_count() * ctas_per_sm;
+    const int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;   // at least a row per warp
+    if (grid > want) grid = want;
+    g.grid = (int)(grid < 1 ? 1 : grid);
+    g.stages = stages;
+    g.smem = bar_bytes + (size_t)warps_per_cta * stages * row_bytes;
+    return g;
+}
+
+template <int DT, int QN, bool FUSEQ>
+int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
+{
+    constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
+    const RingGeometry g = ring_geometry(p.total, kRowBytes);
+    if (g.stages < 1) return UCMX_EUNSUPPORTED;
+    static int smem_set[64];                  // per device: dynamic shared memory limit already raised to this
+    int dev = 0;
+    UCMX_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && smem_set[dev] < (int)g.smem) {
+        UCMX_CUDA(cudaFuncSetAttribute(score_dot_ring_kernel<DT, QN, FUSEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)g.smem));
+        smem_set[dev] = (int)g.smem;
+    }
+    p.stages = g.stages;
+    score_dot_ring_kernel<DT, QN, FUSEQ><<<g.grid, kScoreThreads, g.smem, st>>>(p);
+    UCMX_LAUNCH_CHECK("score_dot_ring_kernel");
+    return UCMX_OK;
+}
+
 template <int DT, bool FUSEQ>
-int32_t launch_rows(const ScoreParams& p, int qn, int grid, cudaStream_t st)
+int32_t launch_ring(const ScoreParams& p, int qn, cudaStream_t st)
 {
     switch (qn) {
-#define UCMX_ROWS_CASE(Q) \
-    case Q: score_dot_rows_kernel<DT, Q, FUSEQ><<<grid, kScoreThreads, 0, st>>>(p); break;
-        UCMX_ROWS_CASE(8)
-        UCMX_ROWS_CASE(16)
-        UCMX_ROWS_CASE(32)
-        UCMX_ROWS_CASE(64)
-#undef UCMX_ROWS_CASE
+        case 8: return launch_ring_one<DT, 8, FUSEQ>(p, st);
+        case 16: return launch_ring_one<DT, 16, FUSEQ>(p, st);
+        case 32: return launch_ring_one<DT, 32, FUSEQ>(p, st);
+        case 64: return launch_ring_one<DT, 64, FUSEQ>(p, st);
         default: return UCMX_EUNSUPPORTED;
     }
-    UCMX_LAUNCH_CHECK("score_dot_rows_kernel");
-    return UCMX_OK;
 }
 
 bool rows_path_ok(int32_t reps_dtype, int32_t n_rep, int64_t E, int* qn)
@@ -461,15 +572,28 @@ int rows_grid(int32_t total)
 {
     // one resident wave: two CTAs of 8 warps per SM; fewer when there is less than a row per warp
     const int warps_per_cta = kScoreThreads / 32;
-    static const int per_sm = [] {
-        const char* e = getenv("UCMX_SCORE_CTAS_PER_SM");  // tuning knob; default = resident CTAs per SM
-        const int v = e ? atoi(e) : 0;
-        return v > 0 && v <= 64 ? v : 2;
-    }();
-    int64_t grid = (int64_t)sm_count() * per_sm;
+    int64_t grid = (int64_t)sm_count() * 2;
     const int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
     if (grid > want) grid = want;
     return (int)(grid < 1 ? 1 : grid);
+}
+
+// Checks a ucmx_peer_exchange descriptor against the batch and turns it into the kernels' form.
+int32_t peer_push_from(const ucmx_peer_exchange* ex, int32_t total, PeerPush* out)
+{
+    out->bases = nullptr;
+    out->world = 0;
+    out->my_rank = 0;
+    out->part_bytes = 0;
+    if (!ex) return UCMX_OK;
+    if (!ex->bases || ex->world < 1 || ex->world > 32 || ex->my_rank < 0 || ex->my_rank >= ex->world ||
+        ex->n_scores < total)
+        return UCMX_EPARAM;
+    out->bases = (unsigned char* const*)ex->bases;
+    out->world = ex->world;
+    out->my_rank = ex->my_rank;
+    out->part_bytes = peer_part_bytes(ex->n_scores);
+    return UCMX_OK;
 }
 
 // Narrow rows, one representative per head: a row of 32 to 256 bytes (for instance one KV head of 128 bf16
@@ -489,58 +613,73 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_narrow_kernel(ScoreGe
     const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
     const int begin = (int)((int64_t)p.total * w / W);
     const int end = (int)((int64_t)p.total * (w + 1) / W);
-    if (begin >= end) return;
-    const int E = p.H * p.D;
-    const size_t row_bytes = (size_t)E * (DT == UCMX_DT_BF16 ? 2 : 4);
-    const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
-    int r = find_request(p.offsets, p.n_req, begin);
-    int r_end = __ldg(p.offsets + r + 1);
-    for (int c = begin; c < end; c += kRows * kU) {
-        uint4 v[kU];
-        int slot[kU];
+    uint32_t round = 0;
+    int64_t push_off = 0;
+    if (p.px.world > 0) {
+        round = peer_round_now(p.px);
+        push_off = peer_inbox_offset(p.px, round, p.px.my_rank);
+    }
+    if (begin < end) {
+        const int E = p.H * p.D;
+        const size_t row_bytes = (size_t)E * (DT == UCMX_DT_BF16 ? 2 : 4);
+        const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
+        int r = find_request(p.offsets, p.n_req, begin);
+        int r_end = __ldg(p.offsets + r + 1);
+        for (int c = begin; c < end; c += kRows * kU) {
+            uint4 v[kU];
+            int slot[kU];
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int row = c + u * kRows + sub;
-            slot[u] = -2;                    // -2: past the end, -1: an empty entry of the table
-            v[u] = make_uint4(0, 0, 0, 0);
-            if (row < end) {
-                slot[u] = p.slot_ids ? __ldg(p.slot_ids + row) : row;
-                if (slot[u] >= 0) v[u] = ld_stream16(base + (size_t)slot[u] * row_bytes + (size_t)pc * 16);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int row = c + u * kRows + sub;
-            float acc = 0.0f;
-            if (slot[u] >= 0) {
-                while (row >= r_end) {
-                    ++r;
-                    r_end = __ldg(p.offsets + r + 1);
-                }
-                const float4* qq = reinterpret_cast<const float4*>(p.q + (int64_t)r * E + pc * kPer);
-                const float4 q0 = __ldg(qq);
-                if (DT == UCMX_DT_BF16) {
-                    const float4 q1 = __ldg(qq + 1);
-                    acc = fmaf(q0.x, bf16lo(v[u].x), acc);
-                    acc = fmaf(q0.y, bf16hi(v[u].x), acc);
-                    acc = fmaf(q0.z, bf16lo(v[u].y), acc);
-                    acc = fmaf(q0.w, bf16hi(v[u].y), acc);
-                    acc = fmaf(q1.x, bf16lo(v[u].z), acc);
-                    acc = fmaf(q1.y, bf16hi(v[u].z), acc);
-                    acc = fmaf(q1.z, bf16lo(v[u].w), acc);
-                    acc = fmaf(q1.w, bf16hi(v[u].w), acc);
-                } else {
-                    acc = fmaf(q0.x, __uint_as_float(v[u].x), acc);
-                    acc = fmaf(q0.y, __uint_as_float(v[u].y), acc);
-                    acc = fmaf(q0.z, __uint_as_float(v[u].z), acc);
-                    acc = fmaf(q0.w, __uint_as_float(v[u].w), acc);
+            for (int u = 0; u < kU; ++u) {
+                const int row = c + u * kRows + sub;
+                slot[u] = -2;                    // -2: past the end, -1: an empty entry of the table
+                v[u] = make_uint4(0, 0, 0, 0);
+                if (row < end) {
+                    slot[u] = checked_slot(p.slot_ids, row, p.n_slots, p.err);
+                    if (slot[u] >= 0) v[u] = ld_stream16(base + (size_t)slot[u] * row_bytes + (size_t)pc * 16);
                 }
             }
 #pragma unroll
-            for (int o = LPR >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (pc == 0 && slot[u] != -2) p.out[row] = slot[u] >= 0 ? acc * p.scale : -INFINITY;
+            for (int u = 0; u < kU; ++u) {
+                const int row = c + u * kRows + sub;
+                float acc = 0.0f;
+                if (slot[u] >= 0) {
+                    while (row >= r_end) {
+                        ++r;
+                        r_end = __ldg(p.offsets + r + 1);
+                    }
+                    const float4* qq = reinterpret_cast<const float4*>(p.q + (int64_t)r * E + pc * kPer);
+                    const float4 q0 = __ldg(qq);
+                    if (DT == UCMX_DT_BF16) {
+                        const float4 q1 = __ldg(qq + 1);
+                        acc = fmaf(q0.x, bf16lo(v[u].x), acc);
+                        acc = fmaf(q0.y, bf16hi(v[u].x), acc);
+                        acc = fmaf(q0.z, bf16lo(v[u].y), acc);
+                        acc = fmaf(q0.w, bf16hi(v[u].y), acc);
+                        acc = fmaf(q1.x, bf16lo(v[u].z), acc);
+                        acc = fmaf(q1.y, bf16hi(v[u].z), acc);
+                        acc = fmaf(q1.z, bf16lo(v[u].w), acc);
+                        acc = fmaf(q1.w, bf16hi(v[u].w), acc);
+                    } else {
+                        acc = fmaf(q0.x, __uint_as_float(v[u].x), acc);
+                        acc = fmaf(q0.y, __uint_as_float(v[u].y), acc);
+                        acc = fmaf(q0.z, __uint_as_float(v[u].z), acc);
+                        acc = fmaf(q0.w, __uint_as_float(v[u].w), acc);
+                    }
+                }
+#pragma unroll
+                for (int o = LPR >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (slot[u] != -2) {
+                    // the lanes of a row's group all hold the score: lane pc of the group delivers to rank pc
+                    // (and lane 0 to the local output), so the stores to the peers leave side by side
+                    const float val = slot[u] >= 0 ? acc * p.scale : -INFINITY;
+                    if (pc == 0 && p.out) p.out[row] = val;
+                    for (int t = pc; t < p.px.world; t += LPR)
+                        reinterpret_cast<float*>(p.px.bases[t] + push_off)[row] = val;
+                }
+            }
         }
     }
+    if (p.px.world > 0) peer_publish_round(p.px, round);
 }
 
 template <int DT>
@@ -577,24 +716,27 @@ extern "C" int32_t ucmx_query_group_mean(const void* q, int32_t n_tok, int32_t n
     return UCMX_OK;
 }
 
-extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t n_rep,
-                                  int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
-                                  const float* q, int32_t n_req, int32_t total, float scale, float* out_scores,
-                                  ucmx_stream_t stream)
+namespace ucmx {
+int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads, int32_t n_rep,
+                       int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids, const float* q,
+                       int32_t n_req, int32_t total, float scale, float* out_scores, const ucmx_peer_exchange* ex,
+                       int32_t* err, cudaStream_t st)
 {
-    using namespace ucmx;
-    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req < 0 || total < 0 || n_slots < 0) return UCMX_EPARAM;
     if (n_req == 0 || total == 0) return UCMX_OK;
-    if (!reps || !req_offsets || !q || !out_scores) return UCMX_EPARAM;
+    if (!reps || !req_offsets || !q || (!out_scores && !ex)) return UCMX_EPARAM;
     if (reps_dtype != UCMX_DT_BF16 && reps_dtype != UCMX_DT_F32) return UCMX_EPARAM;
     if (n_kv_heads < 1 || n_rep < 1 || head_dim < 8 || head_dim % 8) return UCMX_EPARAM;
     if (((uintptr_t)reps & 15) || ((uintptr_t)q & 15)) return UCMX_EPARAM;
-    cudaStream_t st = (cudaStream_t)stream;
+    PeerPush px;
+    const int32_t rc = peer_push_from(ex, total, &px);
+    if (rc != UCMX_OK) return rc;
     const int64_t E = (int64_t)n_kv_heads * head_dim;
     int qn = 0;
     if (rows_path_ok(reps_dtype, n_rep, E, &qn)) {
         ScoreParams p{};
         p.reps = reps;
+        p.n_slots = n_slots;
         p.offsets = req_offsets;
         p.slot_ids = slot_ids;
         p.q = q;
@@ -604,19 +746,24 @@ extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t 
         p.total = total;
         p.E = (int32_t)E;
         p.scale = scale;
-        const int grid = rows_grid(total);
-        if (reps_dtype == UCMX_DT_BF16) return launch_rows<UCMX_DT_BF16, false>(p, qn, grid, st);
-        return launch_rows<UCMX_DT_F32, false>(p, qn, grid, st);
+        p.px = px;
+        p.err = err;
+        if (reps_dtype == UCMX_DT_BF16) return launch_ring<UCMX_DT_BF16, false>(p, qn, st);
+        return launch_ring<UCMX_DT_F32, false>(p, qn, st);
     }
-    ScoreGenParams g{reps, req_offsets, slot_ids, q, out_scores, n_req, total, n_kv_heads, n_rep, head_dim, scale};
-    static const bool no_narrow = getenv("UCMX_SCORE_NO_NARROW") != nullptr;   // comparison knob: the one-row-per-warp kernel for every shape
-    if (n_rep == 1 && !no_narrow) {
+    ScoreGenParams g{reps, n_slots, req_offsets, slot_ids, q, out_scores, n_req, total, n_kv_heads, n_rep, head_dim, scale, px, err};
+    if (n_rep == 1) {
         const int64_t row_bytes = E * (reps_dtype == UCMX_DT_BF16 ? 2 : 4);
         const bool done = reps_dtype == UCMX_DT_BF16 ? launch_narrow<UCMX_DT_BF16>(g, row_bytes, st) : launch_narrow<UCMX_DT_F32>(g, row_bytes, st);
         if (done) {
             UCMX_LAUNCH_CHECK("score_dot_narrow_kernel");
             return UCMX_OK;
         }
+    }
+    if (ex) {
+        set_last_text("score_dot: the peer exchange is available for one representative per head and rows of 32-256 bytes "
+                      "or a multiple of 512 bytes up to 4 KiB (bf16) / 8 KiB (fp32)");
+        return UCMX_EUNSUPPORTED;
     }
     const int warps_per_cta = kScoreThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
@@ -629,6 +776,16 @@ extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int32_t 
     UCMX_LAUNCH_CHECK("score_dot_general_kernel");
     return UCMX_OK;
 }
+}  // namespace ucmx
+
+extern "C" int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads,
+                                  int32_t n_rep, int32_t head_dim, const int32_t* req_offsets,
+                                  const int32_t* slot_ids, const float* q, int32_t n_req, int32_t total, float scale,
+                                  float* out_scores, const ucmx_peer_exchange* exchange, ucmx_stream_t stream)
+{
+    return ucmx::score_dot_impl(reps, reps_dtype, n_slots, n_kv_heads, n_rep, head_dim, req_offsets, slot_ids, q, n_req,
+                                total, scale, out_scores, exchange, ucmx::error_word(), (cudaStream_t)stream);
+}
 
 namespace ucmx {
 namespace {
@@ -640,6 +797,8 @@ namespace {
 // per (head, representative) - as a broadcast - and the reduction is a short one inside the group.
 struct ScoreHeadsParams {
     const void* reps;           // [slot][H][R][D] bf16
+    int64_t n_slots;
+    int32_t* err;
     const int32_t* offsets;
     const int32_t* slot_ids;
     const uint16_t* q;          // bf16 [n_req][Hq][D], q_stride elements between requests
@@ -666,7 +825,7 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_heads_kernel(ScoreHea
 
     for (int64_t c = w0; c < p.total; c += W) {
         const int r = find_request(p.offsets, p.n_req, (int)c);
-        const int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        const int slot = checked_slot(p.slot_ids, c, p.n_slots, p.err);
         if (slot < 0) {
             if (lane == 0) p.out[c] = -INFINITY;
             continue;
@@ -707,14 +866,14 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_heads_kernel(ScoreHea
 }  // namespace
 }  // namespace ucmx
 
-extern "C" int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, int32_t n_rep, int32_t head_dim,
-                                        const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
+extern "C" int32_t ucmx_score_dot_heads(const void* reps, int64_t n_slots, int32_t n_kv_heads, int32_t n_rep,
+                                        int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
                                         int32_t n_q_heads, int64_t query_stride, int32_t n_req, int32_t total,
                                         const uint8_t* include_mask, const uint8_t* exclude_mask, float* out_scores,
                                         ucmx_stream_t stream)
 {
     using namespace ucmx;
-    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req < 0 || total < 0 || n_slots < 0) return UCMX_EPARAM;
     if (n_req == 0 || total == 0) return UCMX_OK;
     if (!reps || !req_offsets || !query || !out_scores) return UCMX_EPARAM;
     if (n_kv_heads < 1 || n_rep < 1 || head_dim < 4 || (head_dim & 3) || n_q_heads < n_kv_heads || n_q_heads % n_kv_heads) return UCMX_EPARAM;
@@ -726,6 +885,8 @@ extern "C" int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, in
     if (query_stride < (int64_t)n_q_heads * head_dim || (query_stride & 3) || ((uintptr_t)reps & 7) || ((uintptr_t)query & 7)) return UCMX_EPARAM;
     ScoreHeadsParams p{};
     p.reps = reps;
+    p.n_slots = n_slots;
+    p.err = error_word();
     p.offsets = req_offsets;
     p.slot_ids = slot_ids;
     p.q = (const uint16_t*)query;
@@ -747,15 +908,16 @@ extern "C" int32_t ucmx_score_dot_heads(const void* reps, int32_t n_kv_heads, in
     return UCMX_OK;
 }
 
-extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int32_t n_kv_heads, int32_t head_dim,
-                                        const int32_t* req_offsets, const int32_t* slot_ids, const void* query,
-                                        int32_t n_q_heads, int64_t query_stride, int32_t round_bf16, int32_t n_req,
-                                        int32_t total, float scale, float* out_scores, ucmx_stream_t stream)
+extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads,
+                                        int32_t head_dim, const int32_t* req_offsets, const int32_t* slot_ids,
+                                        const void* query, int32_t n_q_heads, int64_t query_stride, int32_t round_bf16,
+                                        int32_t n_req, int32_t total, float scale, float* out_scores,
+                                        const ucmx_peer_exchange* exchange, ucmx_stream_t stream)
 {
     using namespace ucmx;
-    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req < 0 || total < 0 || n_slots < 0) return UCMX_EPARAM;
     if (n_req == 0 || total == 0) return UCMX_OK;
-    if (!reps || !req_offsets || !query || !out_scores) return UCMX_EPARAM;
+    if (!reps || !req_offsets || !query || (!out_scores && !exchange)) return UCMX_EPARAM;
     if (reps_dtype != UCMX_DT_BF16 && reps_dtype != UCMX_DT_F32) return UCMX_EPARAM;
     if (n_kv_heads < 1 || n_q_heads < 1 || head_dim < 8 || head_dim % 8) return UCMX_EPARAM;
     if (n_q_heads >= n_kv_heads ? (n_q_heads % n_kv_heads) : (n_kv_heads % n_q_heads)) return UCMX_EPARAM;
@@ -765,7 +927,10 @@ extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, in
     int qn = 0;
     if (!rows_path_ok(reps_dtype, 1, E, &qn)) return UCMX_EUNSUPPORTED;
     ScoreParams p{};
+    const int32_t rc = peer_push_from(exchange, total, &p.px);
+    if (rc != UCMX_OK) return rc;
     p.reps = reps;
+    p.n_slots = n_slots;
     p.offsets = req_offsets;
     p.slot_ids = slot_ids;
     p.q_raw = (const uint16_t*)query;
@@ -778,7 +943,7 @@ extern "C" int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, in
     p.total = total;
     p.E = (int32_t)E;
     p.scale = scale;
-    const int grid = rows_grid(total);
-    if (reps_dtype == UCMX_DT_BF16) return launch_rows<UCMX_DT_BF16, true>(p, qn, grid, (cudaStream_t)stream);
-    return launch_rows<UCMX_DT_F32, true>(p, qn, grid, (cudaStream_t)stream);
+    p.err = error_word();
+    if (reps_dtype == UCMX_DT_BF16) return launch_ring<UCMX_DT_BF16, true>(p, qn, (cudaStream_t)stream);
+    return launch_ring<UCMX_DT_F32, true>(p, qn, (cudaStream_t)stream);
 }

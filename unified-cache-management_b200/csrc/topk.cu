@@ -1,14 +1,17 @@
 // Stage 3: per-request top-k over a ragged batch — one thread block per request.
 //
-// Selection is a most-significant-digit radix select (4 passes of 8 bits over order-preserving
-// uint32 keys) that finds the k-th largest key exactly; an ordered compaction then emits every
-// candidate above the threshold plus the first few equal to it, so ties always go to the lower
-// position (what std::stable_sort gives in TopkBlockSelector::TopKImpl,
+// Selection is a most-significant-digit radix select over order-preserving uint32 keys that finds
+// the k-th largest key exactly.  Digits are 12, 12 and 8 bits wide: the leading digit of an fp32
+// score then holds the sign, the exponent and three mantissa bits, which spreads scores of one
+// magnitude over many buckets (with 8-bit digits nearly all of them land in two or three buckets
+// and their shared-memory adds serialise).  A request of up to eight candidates per thread is read
+// once and kept in registers for all passes.  An ordered compaction then emits every candidate
+// above the threshold plus the first few equal to it, so ties always go to the lower position
+// (what std::stable_sort gives in TopkBlockSelector::TopKImpl,
 // ucm/sparse/gsa/offload_ops/src/select_topk_block.cpp:39-42).  Index-ascending output falls out of
 // the compaction; score-descending output (RetrievalWorkerBackend's partial_sort order,
-// ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:182-189) adds a bitonic sort of the k winners
-// in shared memory.  Scores were written by the scoring kernel a moment earlier and are re-read
-// from L2, so the passes cost latency, not HBM traffic.
+// ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:182-189) adds a sort of the k winners in shared
+// memory.  Scores were written by the scoring kernel a moment earlier and come from L2.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -28,23 +31,27 @@ struct TopkParams {
     int32_t* out_idx;
     uint32_t* out_scores;
     int32_t* out_counts;
-    // tensor-parallel score exchange folded into the prologue (NULL / 0 on a single rank)
-    const unsigned char* const* peer_bases;  // base of every rank's exchange buffer, peer-mapped
-    int32_t world, my_rank;
-    int64_t parts_offset;                    // byte offset of this round's partial scores inside a buffer
-    uint32_t epoch;                          // value every rank's flag must have reached
-    float* sum_out;                          // where the summed scores go (local), then read as `scores`
+    // tensor-parallel score exchange folded into the prologue (px.world == 0 on a single rank)
+    PeerPush px;
+    float* sum_out;          // where the summed scores go (local); needed beyond 8 candidates per thread
     int32_t* err;
 };
 
-constexpr uint32_t kPeerSpinLimit = 1u << 21;
+#ifdef UCMX_PHASE_CLOCKS   // development aid: cycle stamps of thread block 0 at the phase boundaries
+__device__ unsigned long long g_topk_clk[16];
+#define UCMX_PHASE(i)                                                     \
+    do {                                                                  \
+        if (blockIdx.x == 0 && threadIdx.x == 0) g_topk_clk[i] = clock64(); \
+    } while (0)
+#else
+#define UCMX_PHASE(i) do { } while (0)
+#endif
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+constexpr uint32_t kPeerSpinLimit = 1u << 21;
+constexpr int kKeysPerThread = 8;          // candidates a thread keeps in registers
+constexpr int kHistWords = 4096 + 4096 + 256;
+constexpr int kListMax = 128;              // keys sharing the digits fixed so far that are ranked directly
+constexpr int kSelectWords = kHistWords + 512 + 2 * kListMax;   // histograms, partial sums, the list (32-bit words)
 
 __device__ __forceinline__ uint32_t to_key(uint32_t bits, bool is_float)
 {
@@ -58,110 +65,173 @@ __device__ __forceinline__ uint32_t from_key(uint32_t key, bool is_float)
     return (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
 }
 
-// exclusive prefix sums of two small counts over the thread block, in thread order (one pass, two barriers);
-// the block totals come back in tot_a / tot_b.  s_warp needs 64 ints.
-__device__ __forceinline__ void block_excl_scan_pair(int a, int b, int* s_warp, int& before_a, int& before_b, int& tot_a, int& tot_b)
+// exclusive prefix sums of two counts over the thread block, in thread order (two barriers); the block totals
+// come back in tot_a / tot_b.  Both counts travel in one 64-bit word.  s_warp needs 32 entries.
+__device__ __forceinline__ void block_excl_scan_pair(int a, int b, unsigned long long* s_warp, int& before_a, int& before_b,
+                                                     int& tot_a, int& tot_b)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-    int ia = a, ib = b;
+    const unsigned long long mine = (unsigned long long)(uint32_t)a | ((unsigned long long)(uint32_t)b << 32);
+    unsigned long long incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const int va = __shfl_up_sync(0xffffffffu, ia, o), vb = __shfl_up_sync(0xffffffffu, ib, o);
-        if (lane >= o) {
-            ia += va;
-            ib += vb;
-        }
+        const unsigned long long v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
     }
-    if (lane == 31) {
-        s_warp[warp] = ia;
-        s_warp[32 + warp] = ib;
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    // every warp scans the (at most 32) warp totals by itself
+    const unsigned long long wt = lane < nwarp ? s_warp[lane] : 0ull;
+    unsigned long long winc = wt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long v = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += v;
+    }
+    const unsigned long long total = __shfl_sync(0xffffffffu, winc, 31);
+    const unsigned long long wbefore = __shfl_sync(0xffffffffu, winc - wt, warp);
+    __syncthreads();
+    const unsigned long long before = wbefore + incl - mine;
+    before_a = (int)(uint32_t)before;
+    before_b = (int)(before >> 32);
+    tot_a = (int)(uint32_t)total;
+    tot_b = (int)(total >> 32);
+}
+
+// Inclusive scan of one value per lane.
+__device__ __forceinline__ uint32_t warp_incl_scan(uint32_t v)
+{
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+    }
+    return v;
+}
+
+// Which bucket holds the krem-th largest key of a histogram (digits counted from the top).  Called by the whole
+// thread block: every thread adds up runs of eight buckets into s_part (buckets/8 partial sums), then warp 0
+// narrows the search in three steps of one shuffle scan each - which 32nd of the partial sums, which partial sum,
+// which bucket - and leaves the bucket, the keys above it and the keys in it in s_found[0..2].  Two barriers.
+__device__ __forceinline__ void block_find_bucket(const uint32_t* hist, int buckets, int krem, uint32_t* s_part, int* s_found)
+{
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int parts = buckets >> 3;                         // 512 or 32
+    for (int t = tid; t < parts; t += blockDim.x) {
+        uint32_t sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += hist[buckets - 1 - (t * 8 + ((j + t) & 7))];   // rotated: fewer bank conflicts
+        s_part[t] = sum;
     }
     __syncthreads();
-    int ba = 0, bb = 0, ta = 0, tb = 0;
-    for (int w = 0; w < nwarp; ++w) {
-        const int va = s_warp[w], vb = s_warp[32 + w];
-        if (w < warp) {
-            ba += va;
-            bb += vb;
+    if (tid < 32) {
+        const int per_lane = parts >> 5;                    // 16 or 1
+        uint32_t sum = 0;
+        for (int j = 0; j < per_lane; ++j) sum += s_part[lane * per_lane + ((j + lane) % per_lane)];
+        const uint32_t incl = warp_incl_scan(sum);
+        const unsigned holds = __ballot_sync(0xffffffffu, incl - sum < (uint32_t)krem && (uint32_t)krem <= incl);
+        const int owner = holds ? __ffs(holds) - 1 : 31;    // (krem never exceeds the histogram's total)
+        uint32_t above = __shfl_sync(0xffffffffu, incl - sum, owner);
+        // which partial sum of the owner's
+        const uint32_t pv = lane < per_lane ? s_part[owner * per_lane + lane] : 0u;
+        const uint32_t pincl = warp_incl_scan(pv);
+        const unsigned ph = __ballot_sync(0xffffffffu, lane < per_lane && above + pincl - pv < (uint32_t)krem &&
+                                                           (uint32_t)krem <= above + pincl);
+        const int pl = ph ? __ffs(ph) - 1 : per_lane - 1;
+        above += __shfl_sync(0xffffffffu, pincl - pv, pl);
+        const int part = owner * per_lane + pl;
+        // which of its eight buckets
+        const uint32_t bv = lane < 8 ? hist[buckets - 1 - (part * 8 + lane)] : 0u;
+        const uint32_t bincl = warp_incl_scan(bv);
+        const unsigned bh = __ballot_sync(0xffffffffu, lane < 8 && above + bincl - bv < (uint32_t)krem &&
+                                                           (uint32_t)krem <= above + bincl);
+        const int bl = bh ? __ffs(bh) - 1 : 7;
+        above += __shfl_sync(0xffffffffu, bincl - bv, bl);
+        const uint32_t cnt = __shfl_sync(0xffffffffu, bv, bl);
+        if (lane == 0) {
+            s_found[0] = buckets - 1 - (part * 8 + bl);
+            s_found[1] = (int)above;
+            s_found[2] = (int)cnt;
         }
-        ta += va;
-        tb += vb;
     }
     __syncthreads();
-    before_a = ba + ia - a;
-    before_b = bb + ib - b;
-    tot_a = ta;
-    tot_b = tb;
 }
 
 template <bool PEER>
 __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 {
-    extern __shared__ __align__(16) unsigned long long s_sort[];  // score-descending order only
-    __shared__ uint32_t s_hist[4][256];  // one histogram per radix pass, cleared once
-    __shared__ int s_warp[64];
+    extern __shared__ __align__(16) unsigned char s_dyn[];
+    uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn);                                    // three histograms
+    unsigned long long* s_sort = reinterpret_cast<unsigned long long*>(s_dyn + kSelectWords * 4);  // score-descending order only
+    __shared__ unsigned long long s_warp[32];
     __shared__ uint32_t s_prefix;
-    __shared__ int s_krem;
+    __shared__ int s_krem, s_cnt, s_found[3];
 
+    UCMX_PHASE(0);
     const int r = blockIdx.x;
     const int tid = threadIdx.x;
     const int base = __ldg(p.offsets + r);
     const int n = __ldg(p.offsets + r + 1) - base;
     const int k = __ldg(p.k_per_req + r);
     const bool is_float = p.is_float != 0;
+
+    // every thread owns a contiguous run of positions; up to kKeysPerThread of them live in registers
+    const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int i_begin = min(tid * per, n), i_end = min(i_begin + per, n);
+    const bool in_regs = per <= kKeysPerThread;
+    uint32_t kreg[kKeysPerThread];
+
+    const uint32_t* sc = p.scores + base;
     if (PEER) {
-        // One-shot all-reduce fused into the selection: every rank scored its own KV heads into its
-        // exchange buffer and then raised its flag on every peer; wait (bounded) for all flags, then
-        // add the partial scores of this request straight out of the peers' memory, in rank order, so
-        // that every rank computes bit-identical sums and therefore identical selections.
-        if (tid < p.world) {
-            const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.peer_bases[p.my_rank]) + tid;
+        // The all-reduce of partial scores ends here: every rank's scoring kernel has stored its part into this
+        // rank's inbox and raised its flag; wait (bounded) for all flags, then add the parts in rank order, so
+        // that every rank forms bit-identical sums and therefore identical selections.
+        const unsigned char* mine = p.px.bases[p.px.my_rank];
+        const uint32_t round = *reinterpret_cast<const volatile uint32_t*>(mine + kPeerRoundOffset);
+        if (tid < p.px.world) {
+            const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + tid;
             bool ok = false;
             for (uint32_t it = 0; it < kPeerSpinLimit; ++it) {
-                if ((int32_t)(ld_acquire_sys(flag) - p.epoch) >= 0) {
+                if ((int32_t)(ld_acquire_sys_u32(flag) - round) >= 0) {
                     ok = true;
                     break;
                 }
                 __nanosleep(64);
             }
-            if (!ok) {
-                if (p.err) atomicExch(p.err, 4);   // a peer never signalled: sums below are incomplete
-            }
+            if (!ok && p.err) atomicExch(p.err, 4);   // a peer never delivered: the sums below are incomplete
         }
         __syncthreads();
-        // The loads cross NVLink, so latency is what matters: up to eight ranks x eight elements per
-        // thread are requested before the first one is used (L1 is bypassed: the data is a peer's).
-        constexpr int kU = 4, kW = 8;
-        for (int i0 = tid; i0 < n; i0 += blockDim.x * kU) {
-            float acc[kU];
+        const float* inbox = reinterpret_cast<const float*>(mine + peer_inbox_offset(p.px, round, 0)) + base;
+        const int64_t part = p.px.part_bytes / 4;
+        if (in_regs) {
 #pragma unroll
-            for (int u = 0; u < kU; ++u) acc[u] = 0.0f;
-            for (int r0 = 0; r0 < p.world; r0 += kW) {
-                float v[kW][kU];
-#pragma unroll
-                for (int w = 0; w < kW; ++w) {
-                    const bool live = r0 + w < p.world;
-                    const float* part = reinterpret_cast<const float*>(p.peer_bases[live ? r0 + w : p.my_rank] + p.parts_offset);
-#pragma unroll
-                    for (int u = 0; u < kU; ++u) {
-                        const int i = i0 + u * blockDim.x;
-                        v[w][u] = (live && i < n) ? __ldcg(part + base + i) : 0.0f;
-                    }
+            for (int j = 0; j < kKeysPerThread; ++j) {
+                const int i = i_begin + j;
+                float acc = 0.0f;
+                if (j < per && i < i_end) {
+                    for (int t = 0; t < p.px.world; ++t) acc += __ldcg(inbox + (int64_t)t * part + i);
+                    if (p.sum_out) p.sum_out[base + i] = acc;
                 }
-#pragma unroll
-                for (int w = 0; w < kW; ++w)
-#pragma unroll
-                    for (int u = 0; u < kU; ++u) acc[u] += v[w][u];   // rank order: the same sum on every rank
+                kreg[j] = to_key(__float_as_uint(acc), true);
             }
-#pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                const int i = i0 + u * blockDim.x;
-                if (i < n) p.sum_out[base + i] = acc[u];
+        } else {
+            for (int i = tid; i < n; i += blockDim.x) {
+                float acc = 0.0f;
+                for (int t = 0; t < p.px.world; ++t) acc += __ldcg(inbox + (int64_t)t * part + i);
+                p.sum_out[base + i] = acc;
             }
+            __syncthreads();
+            sc = reinterpret_cast<const uint32_t*>(p.sum_out) + base;
         }
-        __syncthreads();
+    } else if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kKeysPerThread; ++j) {
+            const int i = i_begin + j;
+            kreg[j] = (j < per && i < i_end) ? to_key(__ldg(sc + i), is_float) : 0u;
+        }
     }
-    const uint32_t* sc = (PEER ? reinterpret_cast<const uint32_t*>(p.sum_out) : p.scores) + base;
+    UCMX_PHASE(1);
     const int64_t orow = p.out_offsets ? (int64_t)__ldg(p.out_offsets + r) : (int64_t)r * p.out_stride;
     const int cap = p.out_offsets ? min(__ldg(p.out_offsets + r + 1) - (int)orow, p.out_stride) : p.out_stride;
 
@@ -185,11 +255,25 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
         kk = min(max(k, 0), n);
     }
 
+    // key of position i (inside this thread's run when the keys are in registers)
+    auto key_of = [&](int i, int j) -> uint32_t { return in_regs ? kreg[j] : to_key(sc[i], is_float); };
+
     if (identity) {
         const int cnt = min(n, cap);
-        for (int i = tid; i < cnt; i += blockDim.x) {
-            p.out_idx[orow + i] = p.id_map ? __ldg(p.id_map + base + i) : i;
-            if (p.out_scores) p.out_scores[orow + i] = sc[i];
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < kKeysPerThread; ++j) {
+                const int i = i_begin + j;
+                if (j < per && i < i_end && i < cnt) {
+                    p.out_idx[orow + i] = p.id_map ? __ldg(p.id_map + base + i) : i;
+                    if (p.out_scores) p.out_scores[orow + i] = from_key(kreg[j], is_float);
+                }
+            }
+        } else {
+            for (int i = tid; i < cnt; i += blockDim.x) {
+                p.out_idx[orow + i] = p.id_map ? __ldg(p.id_map + base + i) : i;
+                if (p.out_scores) p.out_scores[orow + i] = sc[i];
+            }
         }
         if (tid == 0) p.out_counts[r] = cnt;
         return;
@@ -201,58 +285,88 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     int need = 0;
 
     if (!all && kk > 0) {
-        if (tid == 0) {
-            s_prefix = 0;
-            s_krem = kk;
-        }
-        for (int i = tid; i < 4 * 256; i += blockDim.x) (&s_hist[0][0])[i] = 0;
-        __syncthreads();
-        uint32_t mask = 0;
+        // Digit passes from the top (12, 12, 8 bits).  After a pass, if only a few keys share the digits fixed so
+        // far (the usual case after the first pass), they are listed and ranked directly instead of histogrammed
+        // again; a crowded digit (heavy ties, a narrow score range) takes the next pass.
+        uint32_t* hist = s_hist;
+        uint32_t* s_part = s_hist + kHistWords;                                               // 512 partial sums
+        unsigned long long* s_list = reinterpret_cast<unsigned long long*>(s_part + 512);     // kListMax entries
+        uint32_t mask = 0, prefix = 0;
+        int krem = kk;
+        bool done = false;
 #pragma unroll 1
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            const uint32_t prefix = s_prefix;
-            // (plain shared-memory adds: aggregating equal buckets within a warp by votes or match was measured slower)
-            for (int i = lo + tid; i < hi; i += blockDim.x) {
-                const uint32_t key = to_key(sc[i], is_float);
-                if ((key & mask) == prefix) atomicAdd(&s_hist[pass][(key >> shift) & 255u], 1u);
+        for (int pass = 0; pass < 3 && !done; ++pass) {
+            const int shift = pass == 0 ? 20 : (pass == 1 ? 8 : 0);
+            const int buckets = pass == 2 ? 256 : 4096;
+            for (int i = tid; i < buckets; i += blockDim.x) hist[i] = 0;
+            if (tid == 0) s_cnt = 0;
+            __syncthreads();
+            if (in_regs) {
+#pragma unroll
+                for (int j = 0; j < kKeysPerThread; ++j) {
+                    const int i = i_begin + j;
+                    if (j < per && i < i_end && i >= lo && i < hi && (kreg[j] & mask) == prefix)
+                        atomicAdd(&hist[(kreg[j] >> shift) & (uint32_t)(buckets - 1)], 1u);
+                }
+            } else {
+                for (int i = lo + tid; i < hi; i += blockDim.x) {
+                    const uint32_t key = to_key(sc[i], is_float);
+                    if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & (uint32_t)(buckets - 1)], 1u);
+                }
             }
             __syncthreads();
-            if (tid < 32) {
-                // lane l owns buckets 255-8l .. 248-8l, scanned from the largest digit down
-                uint32_t h[8];
-                uint32_t sum = 0;
+            block_find_bucket(hist, buckets, krem, s_part, s_found);
+            prefix |= (uint32_t)s_found[0] << shift;
+            krem -= s_found[1];
+            const int in_bucket = s_found[2];
+            mask |= (uint32_t)(buckets - 1) << shift;
+            UCMX_PHASE(3 + pass);
+            if (pass == 2) {
+                T = prefix;
+                need = krem;
+                done = true;
+            } else if (in_bucket <= kListMax) {
+                // list the keys that share the digits so far; each warp takes listed keys in turn and its lanes
+                // count together how many of the others beat it - the one beaten by exactly krem-1 is the threshold
+                if (in_regs) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    h[j] = s_hist[pass][255 - 8 * tid - j];
-                    sum += h[j];
-                }
-                uint32_t incl = sum;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (tid >= o) incl += v;
-                }
-                uint32_t before = incl - sum;
-                const uint32_t krem = (uint32_t)s_krem;
-                if (before < krem && krem <= incl) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (before < krem && krem <= before + h[j]) {
-                            s_prefix = prefix | ((uint32_t)(255 - 8 * tid - j) << shift);
-                            s_krem = (int)(krem - before);
-                            before = 0xffffffffu;  // stop
-                        } else if (before != 0xffffffffu) {
-                            before += h[j];
-                        }
+                    for (int j = 0; j < kKeysPerThread; ++j) {
+                        const int i = i_begin + j;
+                        if (j < per && i < i_end && i >= lo && i < hi && (kreg[j] & mask) == prefix)
+                            s_list[atomicAdd(&s_cnt, 1)] = ((unsigned long long)kreg[j] << 32) | (uint32_t)(~(uint32_t)i);
+                    }
+                } else {
+                    for (int i = lo + tid; i < hi; i += blockDim.x) {
+                        const uint32_t key = to_key(sc[i], is_float);
+                        if ((key & mask) == prefix)
+                            s_list[atomicAdd(&s_cnt, 1)] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
                     }
                 }
+                __syncthreads();
+                const int lane = tid & 31, warp = tid >> 5, nwarp = (int)blockDim.x >> 5;
+                for (int e = warp; e < in_bucket; e += nwarp) {
+                    const unsigned long long me = s_list[e];
+                    int beaten_by = 0, greater_key = 0;
+                    for (int j = lane; j < in_bucket; j += 32) {
+                        const unsigned long long o = s_list[j];
+                        beaten_by += o > me;                              // larger key, or equal key at a lower position
+                        greater_key += (uint32_t)(o >> 32) > (uint32_t)(me >> 32);
+                    }
+                    beaten_by = warp_sum_i(beaten_by);
+                    greater_key = warp_sum_i(greater_key);
+                    if (lane == 0 && beaten_by == krem - 1) {
+                        s_prefix = (uint32_t)(me >> 32);
+                        s_krem = krem - greater_key;
+                    }
+                }
+                __syncthreads();
+                T = s_prefix;
+                need = s_krem;
+                done = true;
             }
-            mask |= 0xffu << shift;
-            __syncthreads();
+            hist += buckets;
         }
-        T = s_prefix;
-        need = s_krem;
+        UCMX_PHASE(6);
     }
 
     // Ordered compaction over all positions.  Every thread owns a contiguous run of positions, counts what it will
@@ -260,11 +374,9 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     // counts over the block gives each run its first output place (ties go to the lowest positions: of the equal keys
     // before a run, the first `need` are taken), then the run is written out in order.
     const bool desc = p.order == UCMX_ORDER_SCORE_DESC;
-    const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;
-    const int i_begin = min(tid * per, n), i_end = min(i_begin + per, n);
     const bool ranged = kk > 0;
     int sure = 0, ties = 0;
-    for (int i = i_begin; i < i_end; ++i) {
+    auto count_one = [&](int i, uint32_t key) {
         const bool forced = (i < fstart) || (i >= n - fend);
         if (forced) {
             ++sure;
@@ -272,28 +384,65 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             if (all) {
                 ++sure;
             } else {
-                const uint32_t key = to_key(sc[i], is_float);
                 sure += key > T;
                 ties += key == T;
             }
         }
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kKeysPerThread; ++j)
+            if (j < per && i_begin + j < i_end) count_one(i_begin + j, kreg[j]);
+    } else {
+        for (int i = i_begin; i < i_end; ++i) count_one(i, to_key(sc[i], is_float));
     }
     int sure_before, ties_before, sure_total, ties_total;
     block_excl_scan_pair(sure, ties, s_warp, sure_before, ties_before, sure_total, ties_total);
+    UCMX_PHASE(7);
     int pos = sure_before + min(ties_before, need);
     int tie_rank = ties_before;
-    for (int i = i_begin; i < i_end; ++i) {
+    // take: is position i part of the output; advances the tie counter
+    auto takes = [&](int i, uint32_t key) -> bool {
         const bool forced = (i < fstart) || (i >= n - fend);
-        const bool in_range = i >= lo && i < hi;
-        if (!forced && !(ranged && in_range)) continue;
-        const uint32_t key = to_key(sc[i], is_float);
-        bool take = forced;
-        if (!forced) {
-            if (all) take = true;
-            else if (key > T) take = true;
-            else if (key == T) take = tie_rank++ < need;
+        if (forced) return true;
+        if (!(ranged && i >= lo && i < hi)) return false;
+        if (all || key > T) return true;
+        if (key == T) return tie_rank++ < need;
+        return false;
+    };
+    if (in_regs) {
+        // places first (registers only), then every id-map load of the run at once, then the stores
+        int opos[kKeysPerThread];
+#pragma unroll
+        for (int j = 0; j < kKeysPerThread; ++j) {
+            opos[j] = -1;
+            if (j < per && i_begin + j < i_end && takes(i_begin + j, kreg[j])) {
+                if (pos < cap) opos[j] = pos;
+                ++pos;
+            }
         }
-        if (take) {
+        if (desc) {
+#pragma unroll
+            for (int j = 0; j < kKeysPerThread; ++j)
+                if (opos[j] >= 0)
+                    s_sort[opos[j]] = ((unsigned long long)kreg[j] << 32) | (unsigned long long)(~(uint32_t)(i_begin + j));
+        } else {
+            int ids[kKeysPerThread];
+#pragma unroll
+            for (int j = 0; j < kKeysPerThread; ++j)
+                ids[j] = (opos[j] >= 0 && p.id_map) ? __ldg(p.id_map + base + i_begin + j) : i_begin + j;
+#pragma unroll
+            for (int j = 0; j < kKeysPerThread; ++j) {
+                if (opos[j] >= 0) {
+                    p.out_idx[orow + opos[j]] = ids[j];
+                    if (p.out_scores) p.out_scores[orow + opos[j]] = from_key(kreg[j], is_float);
+                }
+            }
+        }
+    } else {
+        for (int i = i_begin; i < i_end; ++i) {
+            const uint32_t key = to_key(sc[i], is_float);
+            if (!takes(i, key)) continue;
             if (pos < cap) {
                 if (desc) {
                     s_sort[pos] = ((unsigned long long)key << 32) | (unsigned long long)(~(uint32_t)i);
@@ -305,6 +454,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             ++pos;
         }
     }
+    UCMX_PHASE(8);
     const int out_base = sure_total + min(ties_total, need);
     const int cnt = min(out_base, cap);
     if (tid == 0) p.out_counts[r] = cnt;
@@ -349,6 +499,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             }
         }
         __syncthreads();
+        UCMX_PHASE(9);
         for (int j = tid; j < cnt; j += blockDim.x) {
             const unsigned long long v = s_sort[j];
             const int i = (int)(~(uint32_t)(v & 0xffffffffull));
@@ -356,6 +507,7 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
             if (p.out_scores) p.out_scores[orow + j] = from_key((uint32_t)(v >> 32), is_float);
         }
     }
+    UCMX_PHASE(10);
 }
 
 }  // namespace
@@ -363,25 +515,23 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 
 namespace ucmx {
 static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_t* req_offsets,
-                                    const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
-                                    int32_t window_mode, int32_t order, const int32_t* id_map, int32_t out_stride,
-                                    const int32_t* out_offsets, int32_t* out_idx, void* out_scores,
-                                    int32_t* out_counts, const unsigned char* const* peer_bases, int32_t world,
-                                    int32_t my_rank, int64_t parts_offset, uint32_t epoch, float* sum_out,
-                                    ucmx_stream_t stream)
+                           const int32_t* k_per_req, int32_t n_req, int32_t start_win, int32_t end_win,
+                           int32_t window_mode, int32_t order, const int32_t* id_map, int32_t out_stride,
+                           const int32_t* out_offsets, int32_t* out_idx, void* out_scores, int32_t* out_counts,
+                           const PeerPush& px, float* sum_out, ucmx_stream_t stream)
 {
     if (n_req < 0) return UCMX_EPARAM;
     if (n_req == 0) return UCMX_OK;
-    if (!scores || !req_offsets || !k_per_req || !out_idx || !out_counts) return UCMX_EPARAM;
+    if ((!scores && px.world == 0) || !req_offsets || !k_per_req || !out_idx || !out_counts) return UCMX_EPARAM;
     if (score_dtype != UCMX_DT_F32 && score_dtype != UCMX_DT_I32) return UCMX_EPARAM;
     if (window_mode < 0 || window_mode > 2 || (order != 0 && order != 1)) return UCMX_EPARAM;
     if (start_win < 0 || end_win < 0 || out_stride < 1) return UCMX_EPARAM;
-    size_t smem = 0;
+    size_t smem = (size_t)kSelectWords * 4;
     if (order == UCMX_ORDER_SCORE_DESC) {
         if (out_stride > 8192) return UCMX_EUNSUPPORTED;
         int P = 1;
         while (P < out_stride) P <<= 1;
-        smem = (size_t)P * 8;
+        smem += (size_t)P * 8;
     }
     TopkParams p;
     p.scores = (const uint32_t*)scores;
@@ -398,23 +548,15 @@ static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_
     p.out_idx = out_idx;
     p.out_scores = (uint32_t*)out_scores;
     p.out_counts = out_counts;
-    p.peer_bases = peer_bases;
-    p.world = world;
-    p.my_rank = my_rank;
-    p.parts_offset = parts_offset;
-    p.epoch = epoch;
+    p.px = px;
     p.sum_out = sum_out;
-    p.err = peer_bases ? error_word() : nullptr;
-    void (*kern)(TopkParams) = peer_bases ? topk_ragged_kernel<true> : topk_ragged_kernel<false>;
+    p.err = px.world > 0 ? error_word() : nullptr;
+    void (*kern)(TopkParams) = px.world > 0 ? topk_ragged_kernel<true> : topk_ragged_kernel<false>;
     if (smem > 48 * 1024) UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    // block size: enough threads for about two candidates each (the host does not know the ragged
-    // sizes, only the output width, so k is the hint), never fewer than the rank sort needs
-    int threads = 1024;
-    if (out_stride <= 64) threads = 512;
-    if (const char* e = getenv("UCMX_TOPK_THREADS")) {  // tuning knob
-        const int v = atoi(e);
-        if (v == 256 || v == 512 || v == 1024) threads = v;
-    }
+    // block size: enough threads for a few candidates each (the host does not know the ragged sizes, only the
+    // output width, so k is the hint), never fewer than the rank sort of up to 256 winners needs
+    int threads = out_stride <= 64 ? 512 : 1024;
+    if (const char* e = getenv("UCMX_T_TOPK_THREADS")) threads = atoi(e);   // TUNING-ONLY (to be removed)
     kern<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("topk_ragged_kernel");
     return UCMX_OK;
@@ -427,48 +569,37 @@ extern "C" int32_t ucmx_topk_ragged(const void* scores, int32_t score_dtype, con
                                     const int32_t* out_offsets, int32_t* out_idx, void* out_scores,
                                     int32_t* out_counts, ucmx_stream_t stream)
 {
+    ucmx::PeerPush none{nullptr, 0, 0, 0};
     return ucmx::topk_launch(scores, score_dtype, req_offsets, k_per_req, n_req, start_win, end_win, window_mode, order,
-                             id_map, out_stride, out_offsets, out_idx, out_scores, out_counts, nullptr, 1, 0, 0, 0, nullptr,
-                             stream);
+                             id_map, out_stride, out_offsets, out_idx, out_scores, out_counts, none, nullptr, stream);
 }
 
-namespace ucmx {
-namespace {
-__global__ void peer_signal_kernel(unsigned char* const* peer_bases, int world, int my_rank, uint32_t epoch)
+extern "C" size_t ucmx_peer_exchange_bytes(int32_t world, int64_t n_scores)
 {
-    // everything this rank wrote before (its partial scores) must be visible to a peer that sees the flag
-    __threadfence_system();
-    const int r = threadIdx.x;
-    if (r < world) {
-        uint32_t* flag = reinterpret_cast<uint32_t*>(peer_bases[r]) + my_rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
-    }
-}
-}  // namespace
-}  // namespace ucmx
-
-extern "C" int32_t ucmx_peer_signal(void* const* peer_bases, int32_t world, int32_t my_rank, uint32_t epoch,
-                                    ucmx_stream_t stream)
-{
-    if (!peer_bases || world < 1 || world > 32 || my_rank < 0 || my_rank >= world) return UCMX_EPARAM;
-    ucmx::peer_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned char* const*)peer_bases, world, my_rank, epoch);
-    UCMX_LAUNCH_CHECK("peer_signal_kernel");
-    return UCMX_OK;
+    if (world < 1 || n_scores < 0) return 0;
+    return (size_t)ucmx::kPeerHeaderBytes + (size_t)2 * (size_t)world * (size_t)ucmx::peer_part_bytes(n_scores);
 }
 
-extern "C" int32_t ucmx_topk_ragged_peer_sum(void* const* peer_bases, int32_t world, int32_t my_rank,
-                                             int64_t parts_offset_bytes, uint32_t epoch, float* summed_scores,
+extern "C" int32_t ucmx_topk_ragged_peer_sum(const ucmx_peer_exchange* exchange, float* summed_scores,
                                              const int32_t* req_offsets, const int32_t* k_per_req, int32_t n_req,
-                                             int32_t start_win, int32_t end_win, int32_t window_mode, int32_t order,
-                                             const int32_t* id_map, int32_t out_stride, const int32_t* out_offsets,
-                                             int32_t* out_idx, float* out_scores, int32_t* out_counts,
-                                             ucmx_stream_t stream)
+                                             int32_t total, int32_t start_win, int32_t end_win, int32_t window_mode,
+                                             int32_t order, const int32_t* id_map, int32_t out_stride,
+                                             const int32_t* out_offsets, int32_t* out_idx, float* out_scores,
+                                             int32_t* out_counts, ucmx_stream_t stream)
 {
-    if (!peer_bases || !summed_scores || world < 1 || world > 32 || my_rank < 0 || my_rank >= world ||
-        parts_offset_bytes < 128 || (parts_offset_bytes & 15))
+    using namespace ucmx;
+    if (!exchange || !exchange->bases || exchange->world < 1 || exchange->world > 32 || exchange->my_rank < 0 ||
+        exchange->my_rank >= exchange->world || total < 0 || exchange->n_scores < total || !summed_scores)
         return UCMX_EPARAM;
-    return ucmx::topk_launch(summed_scores, UCMX_DT_F32, req_offsets, k_per_req, n_req, start_win, end_win, window_mode,
-                             order, id_map, out_stride, out_offsets, out_idx, out_scores, out_counts,
-                             (const unsigned char* const*)peer_bases, world, my_rank, parts_offset_bytes, epoch,
-                             summed_scores, stream);
+    PeerPush px{(unsigned char* const*)exchange->bases, exchange->world, exchange->my_rank,
+                peer_part_bytes(exchange->n_scores)};
+    return topk_launch(summed_scores, UCMX_DT_F32, req_offsets, k_per_req, n_req, start_win, end_win, window_mode, order,
+                       id_map, out_stride, out_offsets, out_idx, out_scores, out_counts, px, summed_scores, stream);
 }
+
+#ifdef UCMX_PHASE_CLOCKS
+extern "C" int32_t ucmx_debug_topk_clocks(unsigned long long* host16)
+{
+    return cudaMemcpyFromSymbol(host16, ucmx::g_topk_clk, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -20,13 +20,19 @@ namespace {
 constexpr int kMaxPlanes = 8;
 
 struct XferParams {
-    // mode 0: planes + block ids <-> staging;  mode 1: pointer pairs
+    // mode 0: planes + block ids <-> staging;  mode 1: pointer pairs;  mode 2: planes + ids -> other planes + ids
     int32_t mode;
     int32_t to_staging;  // mode 0: 1 = gather (paged -> staging), 0 = scatter
     unsigned char* planes[kMaxPlanes];
     int32_t n_planes;
     int64_t block_stride;
     const int32_t* ids;
+    int64_t n_blocks;     // blocks a plane holds: an id at or beyond it is skipped and reported
+    unsigned char* dst_planes[kMaxPlanes];   // mode 2
+    int64_t dst_block_stride;
+    const int32_t* dst_ids;
+    int64_t n_dst_blocks;
+    const int32_t* n_dev;  // mode 2, optional: entries to process, read on the device (then cleared by the kernel)
     unsigned char* staging;
     void* const* dst_ptrs;
     const void* const* src_ptrs;
@@ -51,7 +57,8 @@ __device__ __forceinline__ void resolve(const XferParams& p, int64_t item, const
         const int64_t i = slice / p.n_planes;
         const int32_t pl = (int32_t)(slice - i * p.n_planes);
         const int32_t id = __ldg(p.ids + i);
-        if (id < 0) {
+        if (id < 0 || (int64_t)id >= p.n_blocks) {
+            if (id >= 0 && p.err) atomicExch(p.err, 3);   // outside the cache: reported, not touched
             bytes = 0;
             src = nullptr;
             dst = nullptr;
@@ -61,6 +68,19 @@ __device__ __forceinline__ void resolve(const XferParams& p, int64_t item, const
         unsigned char* stag = p.staging + slice * p.slice_bytes + off;
         src = p.to_staging ? paged : stag;
         dst = p.to_staging ? stag : paged;
+    } else if (p.mode == 2) {
+        const int64_t i = slice / p.n_planes;
+        const int32_t pl = (int32_t)(slice - i * p.n_planes);
+        const int32_t sid = __ldg(p.ids + i), did = __ldg(p.dst_ids + i);
+        if (sid < 0 || did < 0 || (int64_t)sid >= p.n_blocks || (int64_t)did >= p.n_dst_blocks) {
+            if (sid >= 0 && did >= 0 && p.err) atomicExch(p.err, 3);
+            bytes = 0;
+            src = nullptr;
+            dst = nullptr;
+            return;
+        }
+        src = p.planes[pl] + (int64_t)sid * p.block_stride + off;
+        dst = p.dst_planes[pl] + (int64_t)did * p.dst_block_stride + off;
     } else {
         const unsigned char* s = (const unsigned char*)p.src_ptrs[slice];
         unsigned char* d = (unsigned char*)p.dst_ptrs[slice];
@@ -82,24 +102,25 @@ __device__ __forceinline__ void resolve(const XferParams& p, int64_t item, const
 // when the item count allows, and the block id of the next chunk is requested one chunk ahead, so that its
 // latency (an L2 access once the id list outgrows what L1 keeps beside the ring) is not waited for.
 template <int STAGES>
-__global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
+__device__ __forceinline__ void xfer_bulk_body(const XferParams& p, const int64_t items)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ unsigned char* s_dst[STAGES];
     __shared__ uint32_t s_bytes[STAGES];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     unsigned char* ring = smem + 128;
-    if (threadIdx.x != 0) return;
-
     for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
+    // every byte passes through L2 exactly once in each direction: evict-first keeps what the neighbouring kernels
+    // of a decode step reuse (block tables, offsets, queries, scores) resident across a gather of gigabytes
+    const uint64_t stream_once = l2_evict_first_policy();
 
     const int64_t G = gridDim.x;
     const int64_t first = blockIdx.x;
-    if (first >= p.items) return;
-    const int64_t my_count = (p.items - first + G - 1) / G;
+    if (first >= items) return;
+    const int64_t my_count = (items - first + G - 1) / G;
     const bool ids_mode = p.mode == 0;
-    const bool small = p.items < 0x7fffffffll;      // every index fits 32 bits
+    const bool small = items < 0x7fffffffll;      // every index fits 32 bits
 
     // block index (into p.ids) of work item `item`
     auto block_of = [&](int64_t item) -> int64_t {
@@ -129,7 +150,9 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
             }
             const int64_t off = (int64_t)c * p.chunk_bytes;
             const int64_t left = p.slice_bytes - off;
-            if (id >= 0) {
+            if (id >= 0 && (int64_t)id >= p.n_blocks) {
+                if (p.err) atomicExch(p.err, 3);           // outside the cache: reported, not touched
+            } else if (id >= 0) {
                 bytes = (uint32_t)(left < p.chunk_bytes ? left : p.chunk_bytes);
                 const int32_t pl = small ? (int32_t)((uint32_t)slice % (uint32_t)p.n_planes) : (int32_t)(slice % p.n_planes);
                 unsigned char* paged = p.planes[pl] + (int64_t)id * p.block_stride + off;
@@ -143,7 +166,7 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
         s_dst[s] = dst;
         s_bytes[s] = bytes;
         mbar_expect_tx(&full[s], bytes);
-        if (bytes) bulk_g2s(ring + (size_t)s * p.chunk_bytes, src, bytes, &full[s]);
+        if (bytes) bulk_g2s_hint(ring + (size_t)s * p.chunk_bytes, src, bytes, &full[s], stream_once);
     };
 
     const int64_t pre = my_count < STAGES ? my_count : STAGES;
@@ -159,7 +182,7 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
             break;
         }
         const uint32_t bytes = s_bytes[s];
-        if (bytes) bulk_s2g(s_dst[s], ring + (size_t)s * p.chunk_bytes, bytes);
+        if (bytes) bulk_s2g_hint(s_dst[s], ring + (size_t)s * p.chunk_bytes, bytes, stream_once);
         bulk_commit();
         // refill the stage whose store was committed one group ago
         if (j >= 1 && j - 1 + STAGES < my_count) {
@@ -173,6 +196,30 @@ __global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
         for (int s = 0; s < STAGES; ++s) {
             (void)mbar_wait(&full[s], 0);
             (void)mbar_wait(&full[s], 1);
+        }
+    }
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(32) xfer_bulk_kernel(XferParams p)
+{
+    if (threadIdx.x != 0) return;
+    int64_t items = p.items;
+    if (p.n_dev) {
+        // the number of entries is known on the device only (the load list a remap round left behind)
+        int64_t n = *reinterpret_cast<const volatile int32_t*>(p.n_dev);
+        n = n < 0 ? 0 : (n > p.n ? p.n : n);
+        items = n * p.n_planes * p.chunks_per_slice;
+    }
+    xfer_bulk_body<STAGES>(p, items);
+    if (p.n_dev) {
+        // every thread block has read the count by now; the last one to finish clears it (and the arrival word
+        // beside it) for the next round
+        __threadfence();
+        unsigned* arrive = reinterpret_cast<unsigned*>(const_cast<int32_t*>(p.n_dev)) + 1;
+        if (atomicAdd(arrive, 1u) == gridDim.x - 1) {
+            *reinterpret_cast<volatile int32_t*>(const_cast<int32_t*>(p.n_dev)) = 0;
+            *reinterpret_cast<volatile unsigned*>(arrive) = 0u;
         }
     }
 }
@@ -213,40 +260,27 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
     if (host_memory) {
         p.chunk_bytes = 4096;
         p.chunks_per_slice = (int32_t)((p.slice_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
-        p.items = p.n * (p.mode == 0 ? p.n_planes : 1) * p.chunks_per_slice;
+        p.items = p.n * (p.mode == 1 ? 1 : p.n_planes) * p.chunks_per_slice;
         int64_t want = (p.items + 7) / 8;
         int grid = (int)(want > (int64_t)sms * 4 ? (int64_t)sms * 4 : want);
         xfer_plain_kernel<<<grid, 256, 0, st>>>(p);
         UCMX_LAUNCH_CHECK("xfer_plain_kernel");
         return UCMX_OK;
     }
-    // tuning knobs (read once): chunk size, ring depth, CTAs per SM.  Measured defaults: the same 24 chunks of 8 KiB
-    // in flight per SM either way, as two CTAs with rings of twelve for slices of 128 KiB and more (256 KiB: 6.7 TB/s
-    // against 6.0) and as three CTAs with rings of eight for smaller ones (32 KiB: 6.5 TB/s against 6.1; 64 KiB:
-    // 6.7 against 6.4).
-    static const int k_chunk = [] { const char* e = getenv("UCMX_XFER_CHUNK"); const int v = e ? atoi(e) : 0; return (v >= 1024 && v <= 65536 && v % 16 == 0) ? v : 8192; }();
-    static const int env_stages = [] { const char* e = getenv("UCMX_XFER_STAGES"); const int v = e ? atoi(e) : 0; return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8 || v == 12 || v == 16) ? v : 0; }();
-    static const int env_per_sm = [] { const char* e = getenv("UCMX_XFER_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 16) ? v : 0; }();
-    static const int64_t k_large = [] { const char* e = getenv("UCMX_XFER_LARGE_SLICE"); const long long v = e ? atoll(e) : 0; return v > 0 ? (int64_t)v : (int64_t)131072; }();
-    const bool large = p.slice_bytes >= k_large;
-    const int k_stages = env_stages ? env_stages : (large ? 12 : 8);
-    const int k_per_sm = env_per_sm ? env_per_sm : (large ? 2 : 3);
+    // Measured: the same 24 chunks of 8 KiB in flight per SM either way, as two CTAs with rings of twelve for slices
+    // of 128 KiB and more (256 KiB: 6.7 TB/s against 6.0) and as three CTAs with rings of eight for smaller ones
+    // (32 KiB: 6.5 TB/s against 6.1; 64 KiB: 6.7 against 6.4).
+    constexpr int k_chunk = 8192;
+    const bool large = p.slice_bytes >= 131072;
+    const int k_stages = large ? 12 : 8;
+    const int k_per_sm = large ? 2 : 3;
     p.chunk_bytes = k_chunk;
     if (p.slice_bytes < p.chunk_bytes) p.chunk_bytes = (int32_t)p.slice_bytes;
     p.chunks_per_slice = (int32_t)((p.slice_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
-    p.items = p.n * (p.mode == 0 ? p.n_planes : 1) * p.chunks_per_slice;
+    p.items = p.n * (p.mode == 1 ? 1 : p.n_planes) * p.chunks_per_slice;
     const size_t smem = 128 + (size_t)k_stages * p.chunk_bytes;
     if (smem > 220 * 1024) return UCMX_EUNSUPPORTED;
-    void (*kern)(XferParams) = xfer_bulk_kernel<8>;
-    switch (k_stages) {
-        case 4: kern = xfer_bulk_kernel<4>; break;
-        case 2: kern = xfer_bulk_kernel<2>; break;
-        case 3: kern = xfer_bulk_kernel<3>; break;
-        case 6: kern = xfer_bulk_kernel<6>; break;
-        case 12: kern = xfer_bulk_kernel<12>; break;
-        case 16: kern = xfer_bulk_kernel<16>; break;
-        default: break;
-    }
+    void (*kern)(XferParams) = k_stages == 12 ? xfer_bulk_kernel<12> : xfer_bulk_kernel<8>;
     UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int ctas_per_sm = k_per_sm;
     while (ctas_per_sm > 1 && (size_t)ctas_per_sm * (smem + 1024) > 227 * 1024) --ctas_per_sm;
@@ -257,11 +291,11 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
     return UCMX_OK;
 }
 
-int32_t blocks_common(void* const* planes, int32_t n_planes, int64_t block_stride_bytes, const int32_t* block_ids,
-                      int32_t n, int64_t slice_bytes, void* staging, int32_t staging_is_host, int to_staging,
-                      cudaStream_t st)
+int32_t blocks_common(void* const* planes, int32_t n_planes, int64_t block_stride_bytes, int64_t n_blocks,
+                      const int32_t* block_ids, int32_t n, int64_t slice_bytes, void* staging, int32_t staging_is_host,
+                      int to_staging, cudaStream_t st)
 {
-    if (n < 0 || n_planes < 1 || n_planes > kMaxPlanes) return UCMX_EPARAM;
+    if (n < 0 || n_planes < 1 || n_planes > kMaxPlanes || n_blocks < 1) return UCMX_EPARAM;
     if (n == 0) return UCMX_OK;
     if (!planes || !block_ids || !staging) return UCMX_EPARAM;
     if (slice_bytes <= 0 || (slice_bytes & 15) || (block_stride_bytes & 15) || ((uintptr_t)staging & 15))
@@ -276,6 +310,7 @@ int32_t blocks_common(void* const* planes, int32_t n_planes, int64_t block_strid
     p.n_planes = n_planes;
     p.block_stride = block_stride_bytes;
     p.ids = block_ids;
+    p.n_blocks = n_blocks;
     p.staging = (unsigned char*)staging;
     p.n = n;
     p.slice_bytes = slice_bytes;
@@ -286,19 +321,49 @@ int32_t blocks_common(void* const* planes, int32_t n_planes, int64_t block_strid
 }  // namespace ucmx
 
 extern "C" int32_t ucmx_gather_blocks(const void* const* planes, int32_t n_planes, int64_t block_stride_bytes,
-                                      const int32_t* block_ids, int32_t n, int64_t slice_bytes, void* staging,
-                                      int32_t staging_is_host, ucmx_stream_t stream)
+                                      int64_t n_blocks, const int32_t* block_ids, int32_t n, int64_t slice_bytes,
+                                      void* staging, int32_t staging_is_host, ucmx_stream_t stream)
 {
-    return ucmx::blocks_common((void* const*)planes, n_planes, block_stride_bytes, block_ids, n, slice_bytes,
+    return ucmx::blocks_common((void* const*)planes, n_planes, block_stride_bytes, n_blocks, block_ids, n, slice_bytes,
                                staging, staging_is_host, 1, (cudaStream_t)stream);
 }
 
 extern "C" int32_t ucmx_scatter_blocks(void* const* planes, int32_t n_planes, int64_t block_stride_bytes,
-                                       const int32_t* block_ids, int32_t n, int64_t slice_bytes,
+                                       int64_t n_blocks, const int32_t* block_ids, int32_t n, int64_t slice_bytes,
                                        const void* staging, int32_t staging_is_host, ucmx_stream_t stream)
 {
-    return ucmx::blocks_common(planes, n_planes, block_stride_bytes, block_ids, n, slice_bytes, (void*)staging,
+    return ucmx::blocks_common(planes, n_planes, block_stride_bytes, n_blocks, block_ids, n, slice_bytes, (void*)staging,
                                staging_is_host, 0, (cudaStream_t)stream);
+}
+
+extern "C" int32_t ucmx_move_blocks(const void* const* src_planes, void* const* dst_planes, int32_t n_planes,
+                                    int64_t src_block_stride_bytes, int64_t n_src_blocks, const int32_t* src_ids,
+                                    int64_t dst_block_stride_bytes, int64_t n_dst_blocks, const int32_t* dst_ids,
+                                    int32_t n, const int32_t* n_device, int64_t slice_bytes, ucmx_stream_t stream)
+{
+    using namespace ucmx;
+    if (n < 0 || n_planes < 1 || n_planes > kMaxPlanes || n_src_blocks < 1 || n_dst_blocks < 1) return UCMX_EPARAM;
+    if (n == 0) return UCMX_OK;
+    if (!src_planes || !dst_planes || !src_ids || !dst_ids) return UCMX_EPARAM;
+    if (slice_bytes <= 0 || (slice_bytes & 15) || (src_block_stride_bytes & 15) || (dst_block_stride_bytes & 15)) return UCMX_EPARAM;
+    XferParams p{};
+    p.mode = 2;
+    for (int i = 0; i < n_planes; ++i) {
+        if (!src_planes[i] || !dst_planes[i] || (((uintptr_t)src_planes[i] | (uintptr_t)dst_planes[i]) & 15)) return UCMX_EPARAM;
+        p.planes[i] = (unsigned char*)src_planes[i];
+        p.dst_planes[i] = (unsigned char*)dst_planes[i];
+    }
+    p.n_planes = n_planes;
+    p.block_stride = src_block_stride_bytes;
+    p.ids = src_ids;
+    p.n_blocks = n_src_blocks;
+    p.dst_block_stride = dst_block_stride_bytes;
+    p.dst_ids = dst_ids;
+    p.n_dst_blocks = n_dst_blocks;
+    p.n_dev = n_device;
+    p.n = n;
+    p.slice_bytes = slice_bytes;
+    return launch_xfer(p, false, (cudaStream_t)stream);
 }
 
 extern "C" int32_t ucmx_copy_batch(void* const* dst_ptrs, const void* const* src_ptrs, int32_t number,

@@ -63,20 +63,21 @@ SIGNATURES = {
     "ucmx_hash_encode": [_vp, _i64, _i64, _vp, _i32, _i32, _vp, _vp],
     "ucmx_hash_encode_blocks": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp],
     "ucmx_query_group_mean": [_vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp],
-    "ucmx_score_dot": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp],
-    "ucmx_score_dot_query": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp],
-    "ucmx_score_dot_heads": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp],
+    "ucmx_score_dot": [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp, _vp],
+    "ucmx_score_dot_query": [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp],
+    "ucmx_score_dot_heads": [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp],
     "ucmx_score_hamming": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "ucmx_topk_ragged": [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
-    "ucmx_peer_signal": [_vp, _i32, _i32, C.c_uint32, _vp],
-    "ucmx_topk_ragged_peer_sum": [_vp, _i32, _i32, _i64, C.c_uint32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32,
-                                  _vp, _vp, _vp, _vp, _vp],
-    "ucmx_remap_resident": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
-    "ucmx_retrieve_topk_noalloc": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i32, _i32, _i32,
+    "ucmx_peer_exchange_bytes": [_i32, _i64],
+    "ucmx_topk_ragged_peer_sum": [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp,
+                                  _vp],
+    "ucmx_remap_resident": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ucmx_retrieve_topk_noalloc": [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i32, _i32, _i32,
                                    _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "ucmx_noalloc_max_candidates": [],
-    "ucmx_gather_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
-    "ucmx_scatter_blocks": [_pvp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
+    "ucmx_gather_blocks": [_pvp, _i32, _i64, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
+    "ucmx_scatter_blocks": [_pvp, _i32, _i64, _i64, _vp, _i32, _i64, _vp, _i32, _vp],
+    "ucmx_move_blocks": [_pvp, _pvp, _i32, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _vp, _i64, _vp],
     "ucmx_copy_batch": [_vp, _vp, _i32, _i64, _i32, _vp],
     "ucmx_memcpy_async": [_vp, _vp, _i64, _vp],
     "ucmx_ring_create": [_sz, _sz, _pvp],
@@ -93,6 +94,8 @@ SIGNATURES = {
     "ucmx_retrieval_update_rows": [_vp, _vp, _i32, _vp],
     "ucmx_retrieval_table": [_vp, _pvp, _pi32],
     "ucmx_retrieval_submit": [_vp, _vp, _i32, _i32, _i32, _vp, _i32, _pi32],
+    "ucmx_retrieval_flush": [_vp],
+    "ucmx_retrieval_launches": [_vp, C.POINTER(C.c_int64)],
     "ucmx_retrieval_poll": [_vp, _i32, _pi32],
     "ucmx_retrieval_wait": [_vp, _i32],
     "ucmx_retrieval_result_shape": [_vp, _i32, _pi32, _pi32],
@@ -109,11 +112,24 @@ SIGNATURES = {
     "ucmx_fstore_wait": [_vp, _sz],
     "ucmx_fstore_check": [_vp, _sz, _pi32],
     "ucmx_kvstar_block_repre": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp],
+    "ucmx_kvstar_kernel_choice": [_i32, _i32, _i32, _i32, _i32, _i32],
     "ucmx_kvstar_workspace_bytes": [_i32, _i32, _i32, _i32, _i32],
     "ucmx_kvstar_scores": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz,
                            _vp, _vp],
 }
-_RESTYPES = {"ucmx_last_error": C.c_char_p, "ucmx_kvstar_workspace_bytes": C.c_size_t}
+_RESTYPES = {"ucmx_last_error": C.c_char_p, "ucmx_kvstar_workspace_bytes": C.c_size_t,
+             "ucmx_peer_exchange_bytes": C.c_size_t}
+
+
+class RemapMoves(C.Structure):
+    """ucmx_remap_moves: the packed (pool block -> HBM block) move list a remap round writes for ucmx_move_blocks."""
+    _fields_ = [("src_map", C.c_void_p), ("src_map_offsets", C.c_void_p), ("move_src", C.c_void_p),
+                ("move_dst", C.c_void_p), ("move_count", C.c_void_p)]
+
+
+class PeerExchange(C.Structure):
+    """ucmx_peer_exchange: where a tensor-parallel rank's partial scores go."""
+    _fields_ = [("bases", C.c_void_p), ("world", C.c_int32), ("my_rank", C.c_int32), ("n_scores", C.c_int64)]
 
 
 def _load() -> C.CDLL:

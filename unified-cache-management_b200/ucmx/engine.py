@@ -23,12 +23,16 @@ from .workloads import KvShape, RaggedBatch
 class DecodeRetrievalEngine:
     def __init__(self, shape: KvShape, batch: RaggedBatch, device: torch.device, *, n_layers: Optional[int] = None,
                  with_kv_pool: bool = True, heads_local: Optional[int] = None, seed: int = 0,
-                 score_reduce=None, peer_exchange=None):
+                 score_reduce=None, peer_exchange=None, order: int = ops.ORDER_SCORE_DESC, delta: bool = False):
         """heads_local: KV heads held by this rank under tensor parallelism (default: all).
         score_reduce: callable applied in place to the fp32 score vector between scoring and top-k
         (the tensor-parallel all-reduce); None on a single rank.
         peer_exchange: a parallel.PeerScoreExchange; partial scores then go into peer-mapped memory and are
-        summed inside the top-k kernel instead of by score_reduce."""
+        summed inside the top-k kernel instead of by score_reduce.
+        order: order of the selected ids (best first, or ascending block position).
+        delta: keep a resident working set per layer and request and move only the blocks that are new with respect
+        to the previous step's selection (what ESA does, ucm/sparse/esa/esa.py:313-338): top-k of block positions in
+        ascending order -> resident-set remap -> block-to-block move of the misses."""
         self.shape, self.batch, self.device = shape, batch, device
         self.L = n_layers if n_layers is not None else shape.n_layers
         self.H = heads_local if heads_local is not None else shape.n_kv_heads
@@ -36,6 +40,8 @@ class DecodeRetrievalEngine:
         self.D, self.T = shape.head_dim, shape.block_tokens
         self.score_reduce = score_reduce
         self.peer_exchange = peer_exchange
+        self.order = ops.ORDER_INDEX_ASC if delta else order
+        self.delta = delta
         i32 = dict(dtype=torch.int32, device=device)
         self.offsets = torch.from_numpy(batch.offsets).to(device)
         self.k_per_req = torch.from_numpy(batch.k_per_req).to(device)
@@ -77,6 +83,19 @@ class DecodeRetrievalEngine:
         self.host_graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = self.L * (3 if with_kv_pool else 2) + (1 if with_kv_pool else 0)
         self._pool_all = None
+        if delta:
+            if not with_kv_pool:
+                raise ValueError("the delta step moves blocks: it needs the K/V pool")
+            # resident working set: request r owns slots [k_offsets[r], k_offsets[r+1]) of `staging` in every layer
+            n = batch.total_k
+            self.slot_phys = torch.arange(n, **i32)
+            self.slot_logical = torch.full((self.L, n), -1, **i32)
+            self.slot_free = torch.ones((self.L, n), dtype=torch.uint8, device=device)
+            self.remap_out = [(torch.full((n,), -1, **i32), torch.full((n,), -1, **i32), torch.full((n,), -1, **i32),
+                               torch.zeros((batch.n_req,), **i32)) for _ in range(self.L)]
+            self.moves = ops.MoveList(n, device)
+            self.max_logical = int(batch.blocks_per_req.max())
+            self.launches_per_step = self.L * 4 + 1
 
     # ---------------------------------------------------------------------------------- stages
     def make_queries(self) -> torch.Tensor:
@@ -106,27 +125,54 @@ class DecodeRetrievalEngine:
         ops.pool_blocks(self.kv_pool[0], self.block_table, out_slots=self.block_table, out_bf16=self.rep_tables[layer])
 
     def score_layer(self, layer: int) -> None:
-        out = self.scores if self.peer_exchange is None else self.peer_exchange.begin_round()
-        ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
-                            slot_ids=self.block_table, n_kv_heads=self.H, out=out)
         if self.peer_exchange is not None:
-            self.peer_exchange.signal()
-        elif self.score_reduce is not None:
+            # the partial scores go straight into every rank's inbox; nothing is kept locally
+            ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
+                                slot_ids=self.block_table, n_kv_heads=self.H, exchange=self.peer_exchange)
+            return
+        ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
+                            slot_ids=self.block_table, n_kv_heads=self.H, out=self.scores)
+        if self.score_reduce is not None:
             self.score_reduce(self.scores)
 
     def topk_layer(self, layer: int) -> None:
+        id_map = None if self.delta else self.block_table      # the delta step selects block positions, not pool ids
         if self.peer_exchange is not None:
-            self.peer_exchange.topk(self.offsets, self.k_per_req, out_stride=self.out_stride, order=ops.ORDER_SCORE_DESC,
-                                    id_map=self.block_table, out_offsets=self.k_offsets, out_idx=self.sel_ids[layer],
+            self.peer_exchange.topk(self.offsets, self.k_per_req, total=self.batch.total, out_stride=self.out_stride,
+                                    order=self.order,
+                                    id_map=id_map, out_offsets=self.k_offsets, out_idx=self.sel_ids[layer],
                                     out_scores=self.sel_scores[layer], out_counts=self.sel_counts[layer])
             return
         ops.topk_ragged(self.scores, self.offsets, self.k_per_req, out_stride=self.out_stride,
-                        order=ops.ORDER_SCORE_DESC, id_map=self.block_table, out_offsets=self.k_offsets,
+                        order=self.order, id_map=id_map, out_offsets=self.k_offsets,
                         out_idx=self.sel_ids[layer], out_scores=self.sel_scores[layer],
                         out_counts=self.sel_counts[layer])
 
     def gather_layer(self, layer: int) -> None:
+        if self.delta:
+            self.remap_layer(layer)
+            self.move_layer(layer)
+            return
         ops.gather_blocks([self.kv_pool[0], self.kv_pool[1]], self.sel_ids[layer], self.staging)
+
+    def remap_layer(self, layer: int) -> None:
+        """Which resident slot serves each selected block, and the (pool block -> resident slot) list of the misses."""
+        ops.remap_resident(self.slot_logical[layer], self.slot_free[layer], self.slot_phys, self.k_offsets,
+                           self.sel_ids[layer], self.k_offsets, max_logical=self.max_logical, max_slots=self.out_stride,
+                           sel_counts=self.sel_counts[layer], src_map=self.block_table, src_map_offsets=self.offsets,
+                           moves=self.moves, out=self.remap_out[layer])
+
+    def move_layer(self, layer: int) -> None:
+        ops.move_blocks([self.kv_pool[0], self.kv_pool[1]], self.moves, [self.staging[:, 0], self.staging[:, 1]])
+
+    def drift_queries(self, rho: float = 0.98) -> None:
+        """Next decode step's queries: a seeded random walk, q <- rho*q + sqrt(1-rho^2)*noise, so that consecutive
+        selections overlap the way consecutive decode steps of one sequence do."""
+        noise = torch.randn(self.q_dev.shape, generator=self.gen, device=self.device)
+        self.q_dev.copy_((self.q_dev.float() * rho + noise * (1.0 - rho * rho) ** 0.5).to(torch.bfloat16))
+
+    def loads_of_last_step(self) -> int:
+        return int(sum(int(o[3].sum().item()) for o in self.remap_out))
 
     def layer_step(self, layer: int, gather_events=None) -> None:
         """Score, select and gather one layer (pooling of new blocks is done for all layers at the start of a step).

@@ -26,6 +26,11 @@ def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
 
 
+def _exchange(ex):
+    """Host pointer to a PeerScoreExchange's ucmx_peer_exchange descriptor (NULL for a single rank)."""
+    return None if ex is None else C.byref(ex.desc)
+
+
 def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -94,9 +99,10 @@ def query_group_mean(query: torch.Tensor, n_kv_heads: int, *, round_bf16: bool =
 
 def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *, total: int,
               slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, head_dim: int, n_rep: int = 1,
-              scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None) -> torch.Tensor:
     """Ragged query-to-block dot scores. reps: bf16 or fp32 table [slots, n_kv_heads, n_rep, head_dim]
-    (any shape with that memory layout); q fp32 [n_req, n_kv_heads*head_dim]. Returns fp32 [total]."""
+    (any shape with that memory layout); q fp32 [n_req, n_kv_heads*head_dim]. Returns fp32 [total].
+    exchange: a parallel.PeerScoreExchange under tensor parallelism; the scores then also go to every rank's inbox."""
     _need_cuda(reps, req_offsets, q, slot_ids, out)
     if reps.dtype == torch.bfloat16:
         dt = DT_BF16
@@ -109,18 +115,19 @@ def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *,
     n_req = req_offsets.numel() - 1
     if q.numel() != n_req * n_kv_heads * head_dim:
         raise ValueError("q must hold n_req rows of n_kv_heads*head_dim values")
-    if out is None:
+    if out is None and exchange is None:
         out = torch.empty((total,), dtype=torch.float32, device=reps.device)
-    st = N.lib.ucmx_score_dot(_ptr(reps), dt, n_kv_heads, n_rep, head_dim, _ptr(_i32(req_offsets, "req_offsets")),
+    n_slots = reps.numel() // (n_kv_heads * n_rep * head_dim)
+    st = N.lib.ucmx_score_dot(_ptr(reps), dt, n_slots, n_kv_heads, n_rep, head_dim, _ptr(_i32(req_offsets, "req_offsets")),
                               _ptr(_i32(slot_ids, "slot_ids")), _ptr(q), n_req, total, float(scale), _ptr(out),
-                              _stream(reps))
+                              _exchange(exchange), _stream(reps))
     N.check("ucmx_score_dot", st, 1 if total and n_req else 0)
     return out
 
 
 def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.Tensor, *, total: int,
                     slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, round_bf16: bool = True,
-                    scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None) -> torch.Tensor:
     """score_dot with the per-KV-head query mean folded in: query is the raw bf16 [n_req, n_q_heads, head_dim].
     Shapes the single-pass kernel does not cover go through query_group_mean + score_dot (two launches)."""
     _need_cuda(reps, req_offsets, query, slot_ids, out)
@@ -134,15 +141,16 @@ def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.
     dt = DT_BF16 if reps.dtype == torch.bfloat16 else DT_F32 if reps.dtype == torch.float32 else None
     if dt is None or not reps.is_contiguous():
         raise ValueError("reps must be contiguous bf16 or fp32")
-    if out is None:
+    if out is None and exchange is None:
         out = torch.empty((total,), dtype=torch.float32, device=reps.device)
-    st = N.lib.ucmx_score_dot_query(_ptr(reps), dt, n_kv_heads, D, _ptr(_i32(req_offsets, "req_offsets")),
+    n_slots = reps.numel() // (n_kv_heads * D)
+    st = N.lib.ucmx_score_dot_query(_ptr(reps), dt, n_slots, n_kv_heads, D, _ptr(_i32(req_offsets, "req_offsets")),
                                     _ptr(_i32(slot_ids, "slot_ids")), _ptr(query), Hq, query.stride(0), int(round_bf16),
-                                    n_req, total, float(scale), _ptr(out), _stream(reps))
+                                    n_req, total, float(scale), _ptr(out), _exchange(exchange), _stream(reps))
     if st == N.EUNSUPPORTED:
         qbar = query_group_mean(query, n_kv_heads, round_bf16=round_bf16)
         return score_dot(reps, req_offsets, qbar, total=total, slot_ids=slot_ids, n_kv_heads=n_kv_heads, head_dim=D,
-                         scale=scale, out=out)
+                         scale=scale, out=out, exchange=exchange)
     N.check("ucmx_score_dot_query", st, 1 if total and n_req else 0)
     return out
 
@@ -164,7 +172,7 @@ def score_dot_heads(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.
     n_req = req_offsets.numel() - 1
     if out is None:
         out = torch.empty((total,), dtype=torch.float32, device=reps.device)
-    st = N.lib.ucmx_score_dot_heads(_ptr(reps), H, R, D, _ptr(_i32(req_offsets, "req_offsets")), _ptr(_i32(slot_ids, "slot_ids")),
+    st = N.lib.ucmx_score_dot_heads(_ptr(reps), n_slots, H, R, D, _ptr(_i32(req_offsets, "req_offsets")), _ptr(_i32(slot_ids, "slot_ids")),
                                     _ptr(query), query.shape[1], query.stride(0), n_req, total, _ptr(include_mask),
                                     _ptr(exclude_mask), _ptr(out), _stream(reps))
     N.check("ucmx_score_dot_heads", st, 1 if total and n_req else 0)
@@ -304,8 +312,8 @@ def gather_blocks(planes: Sequence[torch.Tensor], block_ids: torch.Tensor, stagi
         raise ValueError("host staging must be pinned")
     if staging.numel() * staging.element_size() < n * len(planes) * slice_bytes:
         raise ValueError("staging too small")
-    st = N.lib.ucmx_gather_blocks(_planes(planes), len(planes), stride_b, _ptr(ids), n, slice_bytes, _ptr(staging),
-                                  int(host), _stream(planes[0]))
+    st = N.lib.ucmx_gather_blocks(_planes(planes), len(planes), stride_b, planes[0].shape[0], _ptr(ids), n, slice_bytes,
+                                  _ptr(staging), int(host), _stream(planes[0]))
     N.check("ucmx_gather_blocks", st, 1 if n else 0)
     return staging
 
@@ -321,9 +329,35 @@ def scatter_blocks(planes: Sequence[torch.Tensor], block_ids: torch.Tensor, stag
         raise ValueError("host staging must be pinned")
     if staging.numel() * staging.element_size() < n * len(planes) * slice_bytes:
         raise ValueError("staging too small")
-    st = N.lib.ucmx_scatter_blocks(_planes(planes), len(planes), stride_b, _ptr(ids), n, slice_bytes, _ptr(staging),
-                                   int(host), _stream(planes[0]))
+    st = N.lib.ucmx_scatter_blocks(_planes(planes), len(planes), stride_b, planes[0].shape[0], _ptr(ids), n, slice_bytes,
+                                   _ptr(staging), int(host), _stream(planes[0]))
     N.check("ucmx_scatter_blocks", st, 1 if n else 0)
+
+
+def move_blocks(src_planes: Sequence[torch.Tensor], src_ids, dst_planes: Sequence[torch.Tensor],
+                dst_ids: Optional[torch.Tensor] = None) -> None:
+    """Block src_ids[i] of every source plane -> block dst_ids[i] of the matching destination plane (device memory on
+    both sides); an entry with a negative id on either side is skipped.  This is the delta load of a decode step.
+    src_ids may be a MoveList that remap_resident filled: its device-side length decides how many entries move, and
+    the list is empty again afterwards."""
+    moves = src_ids if isinstance(src_ids, MoveList) else None
+    if moves is not None:
+        src_ids, dst_ids = moves.src, moves.dst
+    _need_cuda(src_ids, dst_ids, *src_planes, *dst_planes)
+    if len(src_planes) != len(dst_planes):
+        raise ValueError("as many destination planes as source planes")
+    s_stride, slice_bytes = _block_layout(src_planes)
+    d_stride, d_slice = _block_layout(dst_planes)
+    if d_slice != slice_bytes:
+        raise ValueError("source and destination blocks differ in size")
+    sid, did = _i32(src_ids, "src_ids"), _i32(dst_ids, "dst_ids")
+    if sid.numel() != did.numel():
+        raise ValueError("one destination id per source id")
+    n = sid.numel()
+    st = N.lib.ucmx_move_blocks(_planes(src_planes), _planes(dst_planes), len(src_planes), s_stride, src_planes[0].shape[0],
+                                _ptr(sid), d_stride, dst_planes[0].shape[0], _ptr(did), n,
+                                None if moves is None else _ptr(moves.count), slice_bytes, _stream(src_planes[0]))
+    N.check("ucmx_move_blocks", st, 1 if n else 0)
 
 
 def copy_batch(dst_ptrs: torch.Tensor, src_ptrs: torch.Tensor, count: int, *, any_host_memory: bool = False) -> None:
@@ -336,28 +370,54 @@ def copy_batch(dst_ptrs: torch.Tensor, src_ptrs: torch.Tensor, count: int, *, an
     N.check("ucmx_copy_batch", st, 1 if n and count else 0)
 
 
+class MoveList:
+    """One list of block moves for a whole batch, built on the device by remap_resident and consumed by move_blocks:
+    src[i] -> dst[i] for i < count[0].  count is two int32 (the length and the mover's scratch), zero between rounds."""
+
+    def __init__(self, capacity: int, device: torch.device):
+        self.src = torch.full((capacity,), -1, dtype=torch.int32, device=device)
+        self.dst = torch.full((capacity,), -1, dtype=torch.int32, device=device)
+        self.count = torch.zeros((2,), dtype=torch.int32, device=device)
+        self.capacity = capacity
+
+
 def remap_resident(slot_logical: torch.Tensor, slot_free: torch.Tensor, slot_phys: torch.Tensor,
                    slot_offsets: torch.Tensor, sel: torch.Tensor, sel_offsets: torch.Tensor, *, max_logical: int,
-                   max_slots: int, sel_counts: Optional[torch.Tensor] = None):
+                   max_slots: int, sel_counts: Optional[torch.Tensor] = None, src_map: Optional[torch.Tensor] = None,
+                   src_map_offsets: Optional[torch.Tensor] = None, moves: Optional[MoveList] = None,
+                   out: Optional[tuple] = None):
     """One round of the resident-set remap for every request (state tensors are updated in place).
 
     slot_logical int32, slot_free uint8, slot_phys int32: flat per-request state (CSR by slot_offsets);
     sel: ascending selected logical blocks (CSR by sel_offsets).  Returns (table, load_logical, load_phys,
-    load_counts): table[j] = physical block serving sel[j]; the load lists are packed like sel."""
-    _need_cuda(slot_logical, slot_free, slot_phys, slot_offsets, sel, sel_offsets, sel_counts)
+    load_counts): table[j] = physical block serving sel[j]; the load lists are packed like sel, unused entries -1.
+    With `moves` (and src_map, optionally src_map_offsets) the loads of all requests are also appended to that list
+    as (src_map[src_map_offsets[r] + logical block] -> HBM block), ready for move_blocks.
+    out: the result tensors of an earlier call, to be reused."""
+    _need_cuda(slot_logical, slot_free, slot_phys, slot_offsets, sel, sel_offsets, sel_counts, src_map, src_map_offsets)
     if slot_free.dtype != torch.uint8 or not slot_free.is_contiguous():
         raise ValueError("slot_free must be contiguous uint8")
     n_req = slot_offsets.numel() - 1
     dev = sel.device
-    table = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
-    load_logical = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
-    load_phys = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
-    load_counts = torch.zeros((n_req,), dtype=torch.int32, device=dev)
+    if out is None:
+        table = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+        load_logical = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+        load_phys = torch.full((sel.numel(),), -1, dtype=torch.int32, device=dev)
+        load_counts = torch.zeros((n_req,), dtype=torch.int32, device=dev)
+    else:
+        table, load_logical, load_phys, load_counts = out[:4]
+    mv = None
+    if moves is not None:
+        if src_map is None or moves.capacity < sel.numel():
+            raise ValueError("a move list needs src_map and room for every selected block")
+        mv = C.byref(N.RemapMoves(_i32(src_map, "src_map").data_ptr(),
+                                  0 if src_map_offsets is None else _i32(src_map_offsets, "src_map_offsets").data_ptr(),
+                                  moves.src.data_ptr(), moves.dst.data_ptr(), moves.count.data_ptr()))
     st = N.lib.ucmx_remap_resident(_ptr(_i32(slot_logical, "slot_logical")), _ptr(slot_free), _ptr(_i32(slot_phys, "slot_phys")),
                                    _ptr(_i32(slot_offsets, "slot_offsets")), _ptr(_i32(sel, "sel")),
                                    _ptr(_i32(sel_offsets, "sel_offsets")), _ptr(_i32(sel_counts, "sel_counts")), n_req,
                                    max_logical, max_slots, _ptr(table), _ptr(load_logical), _ptr(load_phys),
-                                   _ptr(load_counts), _stream(sel))
+                                   _ptr(load_counts), mv, _stream(sel))
     N.check("ucmx_remap_resident", st, 1 if n_req else 0)
     return table, load_logical, load_phys, load_counts
 

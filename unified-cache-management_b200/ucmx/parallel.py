@@ -63,34 +63,39 @@ def max_over_ranks(value: float, device: torch.device) -> float:
 
 
 class PeerScoreExchange:
-    """Partial block scores exchanged through peer-mapped memory and summed inside the top-k kernel
-    (ucmx_peer_signal + ucmx_topk_ragged_peer_sum) instead of a library all-reduce between two kernels.
+    """The all-reduce of partial block scores, carried by the scoring and top-k kernels themselves over peer
+    memory instead of a library collective between them (ucmx_score_dot* with an exchange + ucmx_topk_ragged_peer_sum).
 
-    Each rank owns one buffer every rank can address: 128 bytes of flags followed by two halves of
-    `n_scores` fp32 partial scores that alternate from round to round.  `bases` lists the buffers'
-    addresses in rank order; with torch.distributed they come from symmetric memory (`create`), and a
-    test can pass plain allocations of one device to emulate several ranks in one process."""
-
-    FLAG_BYTES = 128
+    Each rank owns one buffer every rank can address: a 256-byte header (one flag per rank, this rank's arrival and
+    round counters) followed by an inbox of two halves x world parts of `n_scores` fp32 partial scores.  A rank's
+    scoring kernel stores its scores into its part of EVERY rank's inbox and, when its last thread block is done,
+    publishes the round into its flag on every rank; the top-k kernel that follows waits (bounded) for all flags of
+    its own buffer and adds the parts in rank order.  The round counter lives in the buffer and advances on the
+    device, so score + top-k can be captured into a CUDA graph and replayed.  `bases` lists the buffers' addresses
+    in rank order; with torch.distributed they come from symmetric memory (`create`), and a test can pass plain
+    allocations of one device to emulate several ranks in one process (their launches then run one after the
+    other: all scoring launches of a round first, then the top-k launches)."""
 
     def __init__(self, bases: Sequence[int], my_rank: int, n_scores: int, device: torch.device, local: torch.Tensor):
+        from . import _native as N
+        import ctypes as C
         self.world, self.my_rank, self.n, self.device = len(bases), my_rank, n_scores, device
-        self.local = local                                    # this rank's buffer as a float32 tensor
+        self.local = local                                    # this rank's buffer (keeps it alive)
         self.bases_dev = torch.tensor(list(bases), dtype=torch.int64, device=device)
-        self.half_bytes = ((n_scores * 4 + 127) // 128) * 128
-        self.epoch = 0
+        self.desc = N.PeerExchange(C.c_void_p(self.bases_dev.data_ptr()), self.world, my_rank, n_scores)
         self.summed = torch.empty((n_scores,), dtype=torch.float32, device=device)
 
     @staticmethod
-    def words_needed(n_scores: int) -> int:
-        half = ((n_scores * 4 + 127) // 128) * 128
-        return (PeerScoreExchange.FLAG_BYTES + 2 * half) // 4
+    def words_needed(world: int, n_scores: int) -> int:
+        from . import _native as N
+        return (int(N.lib.ucmx_peer_exchange_bytes(world, n_scores)) + 3) // 4
 
     @classmethod
     def create(cls, n_scores: int, device: torch.device, group=None) -> "PeerScoreExchange":
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
-        buf = symm.empty(cls.words_needed(n_scores), dtype=torch.float32, device=device)
+        world = dist.get_world_size(group)
+        buf = symm.empty(cls.words_needed(world, n_scores), dtype=torch.float32, device=device)
         buf.zero_()
         hdl = symm.rendezvous(buf, group)
         torch.cuda.synchronize(device)
@@ -99,32 +104,15 @@ class PeerScoreExchange:
         obj._handle = hdl
         return obj
 
-    def parts(self) -> torch.Tensor:
-        """Where this round's partial scores go (a view into this rank's buffer); call begin_round first."""
-        off = (self.FLAG_BYTES + (self.epoch & 1) * self.half_bytes) // 4
-        return self.local[off: off + self.n]
-
-    def begin_round(self) -> torch.Tensor:
-        self.epoch += 1
-        return self.parts()
-
-    def signal(self) -> None:
-        from . import _native as N
-        import ctypes as C
-        st = N.lib.ucmx_peer_signal(C.c_void_p(self.bases_dev.data_ptr()), self.world, self.my_rank, self.epoch,
-                                    C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
-        N.check("ucmx_peer_signal", st, 1)
-
-    def topk(self, req_offsets: torch.Tensor, k_per_req: torch.Tensor, *, out_stride: int, order: int, out_idx: torch.Tensor,
-             out_counts: torch.Tensor, id_map: Optional[torch.Tensor] = None, out_offsets: Optional[torch.Tensor] = None,
-             out_scores: Optional[torch.Tensor] = None, start_win: int = 0, end_win: int = 0, window_mode: int = 0) -> None:
+    def topk(self, req_offsets: torch.Tensor, k_per_req: torch.Tensor, *, total: int, out_stride: int, order: int,
+             out_idx: torch.Tensor, out_counts: torch.Tensor, id_map: Optional[torch.Tensor] = None,
+             out_offsets: Optional[torch.Tensor] = None, out_scores: Optional[torch.Tensor] = None, start_win: int = 0,
+             end_win: int = 0, window_mode: int = 0) -> None:
         from . import _native as N
         import ctypes as C
         p = lambda t: C.c_void_p(0 if t is None else t.data_ptr())  # noqa: E731
-        parts_off = self.FLAG_BYTES + (self.epoch & 1) * self.half_bytes
-        st = N.lib.ucmx_topk_ragged_peer_sum(p(self.bases_dev), self.world, self.my_rank, parts_off, self.epoch, p(self.summed),
-                                             p(req_offsets), p(k_per_req), req_offsets.numel() - 1, start_win, end_win,
-                                             window_mode, order, p(id_map), out_stride, p(out_offsets), p(out_idx),
-                                             p(out_scores), p(out_counts),
-                                             C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        st = N.lib.ucmx_topk_ragged_peer_sum(C.byref(self.desc), p(self.summed), p(req_offsets), p(k_per_req),
+                                             req_offsets.numel() - 1, total, start_win, end_win, window_mode, order,
+                                             p(id_map), out_stride, p(out_offsets), p(out_idx), p(out_scores),
+                                             p(out_counts), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         N.check("ucmx_topk_ragged_peer_sum", st, 1)

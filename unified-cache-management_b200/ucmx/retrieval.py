@@ -1,8 +1,10 @@
 """RetrievalWorkerBackend / RetrievalWorker with the interface of the reference's ESA native
 back-end (ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:17-225 and
 ucm/sparse/esa/retrieval/retrieval_worker.py:10-34), backed by the device-resident object of the
-C ABI (ucmx_retrieval_*): the representative table lives in HBM, submit() enqueues the scoring and
-top-k kernels on a private stream and returns at once, poll() is an event query.
+C ABI (ucmx_retrieval_*): the representative table lives in HBM; submit() stores the request and
+returns at once, and everything submitted since the last launch goes to the GPU as one ragged
+score + top-k on a private stream when the first of those requests is polled, waited for or
+collected (or on flush()).  poll() is an event query.
 
 Host arrays in, host arrays out: submit copies the query and the index matrix to the device,
 get_result returns numpy arrays, exactly like the pybind11 module it replaces.  Errors the
@@ -32,20 +34,28 @@ class RetrievalWorkerBackend:
         st = N.lib.ucmx_retrieval_create(arr.ctypes.data_as(C.c_void_p), self.n_items, self.dim, dt, device,
                                          C.byref(self._h))
         N.check("ucmx_retrieval_create", st, 0)
+        self._shapes = {}                      # request id -> (rows, k) of its result
 
     # -- the reference's four methods -------------------------------------------------------------
     def submit(self, query, topk: int, indexes) -> int:
-        q = np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
-        idx = np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
+        # arrays that are already what the C side reads (the common case) go through untouched
+        q = query if _is_plain(query, np.float32) else np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
+        idx = indexes if _is_plain(indexes, np.int32) else np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
         if q.ndim != 2 or q.shape[1] != self.dim:
             raise RuntimeError("Query dim mismatch")
         if idx.ndim != 2 or idx.shape[0] != q.shape[0]:
             raise RuntimeError("Query and indexes batch mismatch")
         rid = C.c_int32(-1)
-        st = N.lib.ucmx_retrieval_submit(self._h, q.ctypes.data_as(C.c_void_p), q.shape[0], q.shape[1], int(topk),
-                                         idx.ctypes.data_as(C.c_void_p), idx.shape[1], C.byref(rid))
-        N.check("ucmx_retrieval_submit", st, 3)   # offsets fill + score + top-k
+        st = _submit(self._h, q.__array_interface__["data"][0], q.shape[0], q.shape[1], int(topk),
+                     idx.__array_interface__["data"][0], idx.shape[1], C.byref(rid))
+        if st != N.OK:
+            N.check("ucmx_retrieval_submit", st, 0)
+        self._shapes[rid.value] = (q.shape[0], min(int(topk), idx.shape[1]))
         return rid.value
+
+    def flush(self) -> None:
+        """Send everything submitted so far to the GPU now (otherwise the first poll/wait/get_result does it)."""
+        N.check("ucmx_retrieval_flush", N.lib.ucmx_retrieval_flush(self._h), 0)
 
     def poll(self, req_id: int) -> bool:
         ready = C.c_int32(0)
@@ -53,24 +63,24 @@ class RetrievalWorkerBackend:
         return bool(ready.value)
 
     def wait(self, req_id: int) -> None:
-        st = N.lib.ucmx_retrieval_wait(self._h, req_id)
+        st = _wait(self._h, req_id)
         if st == N.ENOOBJ:
             raise RuntimeError("Bad req_id")
-        N.check("ucmx_retrieval_wait", st, 0)
+        if st != N.OK:
+            N.check("ucmx_retrieval_wait", st, 0)
 
     def get_result(self, req_id: int) -> dict:
-        b, k = C.c_int32(0), C.c_int32(0)
-        st = N.lib.ucmx_retrieval_result_shape(self._h, req_id, C.byref(b), C.byref(k))
+        shape = self._shapes.get(req_id)
+        if shape is None:
+            raise RuntimeError("Result not ready")
+        indices = np.empty(shape, np.int32)
+        scores = np.empty(shape, np.float32)
+        st = _get(self._h, req_id, indices.__array_interface__["data"][0], scores.__array_interface__["data"][0])
         if st == N.ENOOBJ:
             raise RuntimeError("Result not ready")
-        N.check("ucmx_retrieval_result_shape", st, 0)
-        indices = np.empty((b.value, k.value), np.int32)
-        scores = np.empty((b.value, k.value), np.float32)
-        st = N.lib.ucmx_retrieval_get_result(self._h, req_id, indices.ctypes.data_as(C.c_void_p),
-                                             scores.ctypes.data_as(C.c_void_p))
-        if st == N.ENOOBJ:
-            raise RuntimeError("Result not ready")
-        N.check("ucmx_retrieval_get_result", st, 0)
+        del self._shapes[req_id]
+        if st != N.OK:
+            N.check("ucmx_retrieval_get_result", st, 0)
         return {"indices": indices, "scores": scores}
 
     # -- additions ---------------------------------------------------------------------------------
@@ -82,6 +92,13 @@ class RetrievalWorkerBackend:
         st = N.lib.ucmx_retrieval_update_rows(self._h, s.ctypes.data_as(C.c_void_p), len(s),
                                               r.ctypes.data_as(C.c_void_p))
         N.check("ucmx_retrieval_update_rows", st, 1)
+
+    @property
+    def launches(self) -> int:
+        """Kernels this object has launched so far (one ragged score + one top-k per batch of submits)."""
+        n = C.c_int64(0)
+        N.check("ucmx_retrieval_launches", N.lib.ucmx_retrieval_launches(self._h, C.byref(n)), 0)
+        return n.value
 
     def table_ptr(self):
         p, dt = C.c_void_p(), C.c_int32(0)
@@ -98,6 +115,15 @@ class RetrievalWorkerBackend:
             self.close()
         except Exception:
             pass
+
+
+_submit = N.lib.ucmx_retrieval_submit
+_wait = N.lib.ucmx_retrieval_wait
+_get = N.lib.ucmx_retrieval_get_result
+
+
+def _is_plain(x, dtype) -> bool:
+    return type(x) is np.ndarray and x.dtype == dtype and x.flags.c_contiguous
 
 
 def _as_numpy(x):

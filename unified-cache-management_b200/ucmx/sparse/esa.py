@@ -140,6 +140,9 @@ class ReqState:
         self.top_k = int(self.sparse_range * cfg["sparse_ratio"])
         self.repre_layers = set()                                   # layers whose representatives exist
         self.pre_topk: List[Dict[int, str]] = [dict() for _ in range(n_layers)]  # HBM block -> hash, per layer
+        # retrieval under way per layer: (record shared by the requests launched together, this request's row in it).
+        # The reference keeps a retrieval_task per request and layer (ReqStatePerLayer, ucm/sparse/esa/esa.py:157-170).
+        self.pending: List[Optional[tuple]] = [None] * n_layers
 
 
 class ESA(UcmSparseBase):
@@ -161,10 +164,9 @@ class ESA(UcmSparseBase):
             self.pool = ReprePool(self.num_slots)
             self.tables: List[Optional[torch.Tensor]] = [None] * self.n_layers
             self.device: Optional[torch.device] = None
-            self._retrieval: List[Optional[dict]] = [None] * self.n_layers
+            self._pinned_free: List[torch.Tensor] = []
             self._load_tasks: List[list] = [[] for _ in range(self.n_layers)]
             self._csr_cache: Optional[tuple] = None
-            self._pinned: Dict[int, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ helpers
     @staticmethod
@@ -234,11 +236,27 @@ class ESA(UcmSparseBase):
         self._csr_cache = (key, pack)
         return pack
 
+    def _take_pinned(self, n: int) -> torch.Tensor:
+        for i, t in enumerate(self._pinned_free):
+            if t.numel() >= n:
+                return self._pinned_free.pop(i)
+        return torch.empty((max(n, 1024),), dtype=torch.int32).pin_memory()
+
+    def _drop_pending(self, st: ReqState, layer: int) -> None:
+        """Forget a request's retrieval under way; the record's host buffer is reused once nobody refers to it."""
+        p = st.pending[layer]
+        st.pending[layer] = None
+        if p is not None:
+            rec = p[0]
+            rec["refs"] -= 1
+            if rec["refs"] == 0:
+                self._pinned_free.append(rec["host"])
+
     def _start_retrieval(self, layer: int, states: List[ReqState], query: torch.Tensor) -> None:
-        """start_retrieval for every request that retrieves this step: one score and one top-k launch."""
+        """start_retrieval for every request that retrieves this step: one score and one top-k launch.  Each of
+        these requests gets its own pending entry; entries of requests that are at another step are left alone."""
         states = [st for st in states if st.slots and st.top_k > 0 and layer in st.repre_layers]
         if not states:
-            self._retrieval[layer] = None
             return
         dev = query.device
         c = self._csr(states, dev)
@@ -250,28 +268,30 @@ class ESA(UcmSparseBase):
         # positions inside the request's slot list = relative block indices (slots are allocated in block order)
         ops.topk_ragged(scores, c["off"], c["ks"], out_stride=max(c["max_k"], 1), order=ops.ORDER_SCORE_DESC,
                         out_offsets=c["koff"], out_idx=sel, out_counts=cnt, want_scores=False)
-        host = self._pinned.get(layer)
-        if host is None or host.numel() < sel.numel():
-            host = torch.empty((max(sel.numel(), 1024),), dtype=torch.int32).pin_memory()
-            self._pinned[layer] = host
+        host = self._take_pinned(sel.numel())
         host[: sel.numel()].copy_(sel, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        self._retrieval[layer] = dict(states=states, koff=c["koff_host"], host=host, event=ev)
+        rec = dict(koff=c["koff_host"], host=host, event=ev, refs=len(states))
+        for i, st in enumerate(states):
+            self._drop_pending(st, layer)                             # a retrieval that was never collected
+            st.pending[layer] = (rec, i)
 
-    def _wait_retrieval_and_start_load(self, layer: int, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
-        """wait_retrieval_and_start_load for the whole layer: delta against the previous selection
-        (esa.py:313-334), then ONE load of K and ONE of V for every request's new blocks."""
-        r = self._retrieval[layer]
-        self._retrieval[layer] = None
-        if r is None:
-            return
-        r["event"].synchronize()
-        host = r["host"].numpy()
+    def _wait_retrieval_and_start_load(self, layer: int, states: List[ReqState], k_cache: torch.Tensor,
+                                       v_cache: torch.Tensor) -> None:
+        """wait_retrieval_and_start_load for the requests that are due in this layer: each one's own retrieval
+        result, the delta against its previous selection (esa.py:313-334), then ONE load of K and ONE of V for
+        the new blocks of all of them."""
         hashes: List[str] = []
         hbm_ids: List[int] = []
-        for i, st in enumerate(r["states"]):
-            rel = host[r["koff"][i]: r["koff"][i + 1]]
+        for st in states:
+            p = st.pending[layer]
+            if p is None:
+                continue
+            rec, i = p
+            rec["event"].synchronize()
+            rel = rec["host"].numpy()[rec["koff"][i]: rec["koff"][i + 1]].copy()
+            self._drop_pending(st, layer)
             sel_hashes = [st.block_hashes[int(j)] for j in rel]
             top_k = len(sel_hashes)
             sparse_vllm_block_ids = st.meta.vllm_block_ids[:top_k]
@@ -329,7 +349,7 @@ class ESA(UcmSparseBase):
         first = [st for st in at_one if st.meta.step == 1]
         if first:
             self._start_retrieval(layer, first, query)
-            self._wait_retrieval_and_start_load(layer, k_cache, v_cache)
+            self._wait_retrieval_and_start_load(layer, first, k_cache, v_cache)
         self._wait_transfer_task_done(layer)
 
     def attention_finished(self, query, key, value, attn_output, layer_name, forward_context) -> None:
@@ -344,8 +364,9 @@ class ESA(UcmSparseBase):
         retrieve = [st for st in decode if st.meta.step % stride == 2]
         if retrieve:
             self._start_retrieval(layer, retrieve, query)
-        if any(st.meta.step % stride == 0 for st in decode):
-            self._wait_retrieval_and_start_load(layer, k_cache, v_cache)
+        due = [st for st in decode if st.meta.step % stride == 0]
+        if due:
+            self._wait_retrieval_and_start_load(layer, due, k_cache, v_cache)
 
     # ------------------------------------------------------------------ scheduler / bookkeeping
     def is_sparsed_request(self, req) -> bool:
@@ -371,6 +392,8 @@ class ESA(UcmSparseBase):
     def request_finished_in_worker(self, request_id: ReqType):
         st = self.req_states.pop(request_id, None)
         if st is not None:
+            for layer in range(self.n_layers):
+                self._drop_pending(st, layer)
             self.pool.free(st.slots)
             self._csr_cache = None
 

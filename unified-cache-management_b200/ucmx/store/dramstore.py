@@ -202,15 +202,19 @@ class UcmDramStore(UcmKVStoreBase):
         self._ensure_slab()
         if len(set(size)) > 1:
             raise ValueError("one transfer moves slices of one size")
-        slots = []
+        slots, taken = [], []
         for i, b in enumerate(block_ids):
             key = f"{b}_{offset[i]}"
             s = self.slot_of.get(key)
             if s is None:
                 s = self._acquire()
                 if s < 0:
+                    for k2, s2 in taken:       # roll back what this call took
+                        N.lib.ucmx_ring_release(self._ring, s2)
+                        del self.slot_of[k2]
                     return DramTask(task_id="-1")
                 self.slot_of[key] = s
+                taken.append((key, s))
             slots.append(s)
         dst = np.asarray([self._base + s * self.io_size for s in slots], dtype=np.int64)
         return self._launch(dst, np.asarray(src_addr, dtype=np.int64), size[0] if size else 0, [], True)
@@ -221,8 +225,22 @@ class UcmDramStore(UcmKVStoreBase):
         if task.handle is None:
             return FAILURE
         st = N.lib.ucmx_task_wait(C.c_void_p(task.handle), self.timeout_ms)
-        task.keep = []
-        return SUCCESS if st == N.OK else FAILURE
+        if st == N.OK:
+            task.keep = []                     # the kernel is done with the tensors, tables and staging it borrowed
+            return SUCCESS
+        # Timed out or failed: the copy may still be running, so what it reads and writes stays referenced.  The
+        # references go when a later check() or wait() sees the task finished, or with the task object itself.
+        self._lingering = [t for t in getattr(self, "_lingering", []) if not self._finished(t)]
+        self._lingering.append(task)
+        return FAILURE
+
+    def _finished(self, task: DramTask) -> bool:
+        fin = C.c_int32(0)
+        st = N.lib.ucmx_task_check(C.c_void_p(task.handle), C.byref(fin))
+        if st == N.OK and fin.value:
+            task.keep = []
+            return True
+        return False
 
     def commit(self, block_ids: List[str], is_success: bool = True) -> None:
         if is_success:
