@@ -45,7 +45,8 @@ typedef struct ucmx_kv_geometry {
     int32_t block_tokens;
     int32_t n_kv_heads;
     int32_t head_dim;
-    int32_t reserved; /* number of blocks in the cache if known, else 0; lets small batches use tiled TMA loads */
+    int32_t reserved; /* number of blocks in the cache (required): a block id at or beyond it is dropped and reported
+                         (ucmx_device_error code 3), never turned into an address; also sizes the tensor maps */
 } ucmx_kv_geometry;
 
 /* Library version and the SM architecture the kernels were compiled for (100 for sm_100a). */
@@ -74,13 +75,15 @@ int32_t ucmx_device_error(int32_t* code, int32_t clear);
  * at representative index rep_index.  mode: 0 mean, 1 max, 2 min, 3 sum.  Tokens are accumulated in
  * fp32 in token order; the mean is sum*(1/block_tokens).  round_bf16 != 0 rounds the result to bf16
  * (nearest even) before it is stored, which is what the reference keeps; out_f32 then receives the
- * widened bf16 value.  Either of out_bf16 / out_f32 may be NULL. */
+ * widened bf16 value.  Either of out_bf16 / out_f32 may be NULL.  n_out_slots is the number of rows
+ * of the output table: a row index at or beyond it (like a block id beyond the cache) drops the entry
+ * and is reported (code 3). */
 #define UCMX_POOL_MEAN 0
 #define UCMX_POOL_MAX 1
 #define UCMX_POOL_MIN 2
 #define UCMX_POOL_SUM 3
 int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry* geom /* host */,
-                         const int32_t* block_ids, const int32_t* out_slots, int32_t n, int32_t mode,
+                         const int32_t* block_ids, const int32_t* out_slots, int64_t n_out_slots, int32_t n, int32_t mode,
                          int32_t round_bf16, int32_t n_rep, int32_t rep_index, void* out_bf16,
                          float* out_f32, ucmx_stream_t stream);
 
@@ -97,11 +100,12 @@ int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry* geom /* ho
  *   of block i go to row out_slots[i] (or i) of a table uint8 [slot, n_kv_heads, block_tokens,
  *   bits/8] when head_major != 0 (the layout KVComp keeps) or [slot, block_tokens, n_kv_heads,
  *   bits/8] when head_major == 0 (compute_hash's own output order).
- * w is bf16 [dim, bits] row major.  dim and bits must be multiples of 32; dim = head_dim. */
+ * w is bf16 [dim, bits] row major.  dim and bits must be multiples of 32; dim = head_dim.
+ * n_out_slots: rows of the code table (bounds out_slots, as in ucmx_pool_blocks). */
 int32_t ucmx_hash_encode(const void* x, int64_t n_vec, int64_t x_stride, const void* w, int32_t dim,
                          int32_t bits, uint8_t* out, ucmx_stream_t stream);
 int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_geometry* geom /* host */,
-                                const int32_t* block_ids, const int32_t* out_slots, int32_t n,
+                                const int32_t* block_ids, const int32_t* out_slots, int64_t n_out_slots, int32_t n,
                                 const void* w, int32_t bits, int32_t head_major, uint8_t* out,
                                 ucmx_stream_t stream);
 
@@ -184,8 +188,9 @@ int32_t ucmx_score_dot_query(const void* reps, int32_t reps_dtype, int64_t n_slo
  * bits/8].  score = sum over (i, j, s) of (bits - 2*popcount(q_i xor k_{j,s})) over every
  * (query head i, key head j) pair when cross_head != 0 (what the reference's einsum does), or over
  * matching heads only (i == j, needs n_q_heads == n_kv_heads) when cross_head == 0.
- * bits must be a multiple of 128.  Ragged batch and slot_ids as in ucmx_score_dot. */
-int32_t ucmx_score_hamming(const uint8_t* codes, int32_t n_kv_heads, int32_t block_tokens,
+ * bits must be a multiple of 128.  Ragged batch, slot_ids and n_slots (rows of the code table) as in
+ * ucmx_score_dot; a candidate without a valid slot scores INT32_MIN. */
+int32_t ucmx_score_hamming(const uint8_t* codes, int64_t n_slots, int32_t n_kv_heads, int32_t block_tokens,
                            int32_t bits, const int32_t* req_offsets, const int32_t* slot_ids,
                            const uint8_t* q_codes, int32_t n_q_heads, int32_t n_req, int32_t total,
                            int32_t cross_head, int32_t* out_scores, ucmx_stream_t stream);
@@ -264,10 +269,13 @@ int32_t ucmx_topk_ragged_peer_sum(const ucmx_peer_exchange* exchange /* host */,
  * (ucm/sparse/esa/esa.py:313-334).
  *
  * State, per request r (slots [slot_offsets[r], slot_offsets[r+1])): slot_phys[s] is the physical id
- * of the s-th HBM block the request owns (ascending), slot_logical[s] the logical block it holds
- * (-1 = none), slot_free[s] != 0 marks slots the previous round left on the free list.
+ * of the s-th HBM block the request owns (ascending; a negative id marks a slot that does not
+ * exist, which lets requests with different numbers of blocks share one slot stride), slot_logical[s]
+ * the logical block it holds (-1 = none), slot_free[s] != 0 marks slots the previous round left on
+ * the free list.
  * Selection, per request (entries [sel_offsets[r], sel_offsets[r+1]), of which only the first
- * sel_counts[r] are used when sel_counts is given): ascending logical block ids (negative = skip).
+ * sel_counts[r] are used when sel_counts is given; a negative count leaves the request's state and
+ * outputs untouched): ascending logical block ids (negative = skip).
  * One round: a selected block that is resident keeps its slot; the others, in selection order, take
  * the free-listed slots that are not hits now, in slot order; slot_logical is updated and the new
  * free list is every slot that is neither a hit nor newly filled.
@@ -511,7 +519,7 @@ int32_t ucmx_fstore_check(ucmx_fstore* store, size_t task_id, int32_t* finished)
  * Shapes with H*d_pruned % 64 == 0, d_pruned % 16 == 0, M % 32 == 0, max_q_tokens*Hq/H <= 128 run on the
  * tensor cores (tcgen05); all others on a CUDA-core kernel with the same results to rounding. */
 int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_geometry* geom, const int32_t* block_ids,
-                                const int32_t* out_slots, int32_t n, const int64_t* pruned_index,
+                                const int32_t* out_slots, int64_t n_out_slots, int32_t n, const int64_t* pruned_index,
                                 int32_t d_pruned, int32_t merge, void* reps_f16, ucmx_stream_t stream);
 /* Which kernel ucmx_kvstar_scores runs for a shape: 0 = CUDA cores, 1 = tensor cores with one block per tile,
  * 2 = tensor cores with two blocks per instruction (host-side arithmetic only, nothing is launched). */

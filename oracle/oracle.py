@@ -21,17 +21,23 @@ _REF_DIR = os.path.join(_HERE, "_ref")
 POOL_MEAN, POOL_MAX, POOL_MIN, POOL_SUM = 0, 1, 2, 3
 
 
+def reference_root():
+    """Where a checkout of the reference project lies: $UCM_REFERENCE, else a directory named `reference` beside this
+    repository; None when there is none (the GPU box: only the prebuilt oracle/_ref travels)."""
+    cand = os.environ.get("UCM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "ucm")) else None
+
+
 def build(ref: bool = True) -> None:
     """Compile the C restatement, and the reference's own CPU sources when a checkout is present."""
     targets = ["oracle"]
-    if ref and os.path.isdir(os.environ.get("UCM_REFERENCE", "/root/reference")):
-        targets.append("ref")
+    root = reference_root() if ref else None
     env = dict(os.environ)
     env.pop("CC", None)
     env.pop("CXX", None)
     cmd = ["make", "-s", "-C", _HERE] + targets
-    if "UCM_REFERENCE" in os.environ:
-        cmd.append("REF=" + os.environ["UCM_REFERENCE"])
+    if root:
+        cmd += ["ref", "REF=" + root]
     subprocess.run(cmd, check=True, env=env)
 
 

@@ -21,13 +21,16 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("UCM_REFERENCE", "/root/reference")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
-sys.path.insert(0, REF)
 
 import helpers as H  # noqa: E402
 from oracle import oracle as orc  # noqa: E402
+
+REF = orc.reference_root()
+if REF is None:
+    raise SystemExit("set UCM_REFERENCE to a checkout of the reference project")
+sys.path.insert(0, REF)
 
 
 def bf(u16):

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def test_parameter_errors_need_no_gpu():
     from ucmx import _native as N
     # argument validation happens before any CUDA call
-    assert N.lib.ucmx_pool_blocks(None, None, None, None, 1, 0, 1, 1, 0, None, None, None) == N.EPARAM
+    assert N.lib.ucmx_pool_blocks(None, None, None, None, 1, 1, 0, 1, 1, 0, None, None, None) == N.EPARAM
     assert N.lib.ucmx_topk_ragged(None, 1, None, None, 3, 0, 0, 0, 0, None, 4, None, None, None, None, None) == N.EPARAM
     assert N.lib.ucmx_score_dot(None, 0, 0, 8, 1, 128, None, None, None, 0, 0, 1.0, None, None, None) == N.OK  # empty batch
     assert N.lib.ucmx_ring_release(None, 0) == N.EPARAM

@@ -12,7 +12,9 @@ import torch
 from ucmx.connector import ReqMeta, UCConnectorV1Metadata, UnifiedCacheConnectorV1, _extract_layer_index
 from ucmx.store.ucmstore import Task, UcmKVStoreBase
 
-REF = os.environ.get("UCM_REFERENCE", "/root/reference")
+from oracle import oracle as _orc  # noqa: E402
+
+REF = _orc.reference_root() or ""
 REF_FILE = os.path.join(REF, "ucm", "integration", "vllm", "uc_connector.py")
 
 # (tp, rank, layer, is_v, is_mla) -> offset, recorded from the reference's DataOffset for a

@@ -148,3 +148,43 @@ def test_retrieval_submit_refuses_indexes_outside_the_table():
     assert be.get_result(rid)["indices"].shape == (1, 2)
     be.close()
     assert _native.device_error() == 0
+
+
+def test_pooling_hashing_and_hamming_drop_ids_beyond_their_tables(oracle):
+    """Block ids beyond the cache, output rows beyond the table, code-table slots beyond the table: dropped, reported."""
+    from ucmx import _native, ops
+    rng = np.random.default_rng(206)
+    k16 = H.randn_bf16(rng, (6, 16, 2, 128))
+    k = dev_bf16(k16)
+    table = torch.zeros((4, 2, 1, 128), dtype=torch.bfloat16, device=DEV)
+    _native.device_error()
+    ops.pool_blocks(k, dev_i32([1, 6, 2, 5]), out_slots=dev_i32([0, 1, 4, 3]), out_bf16=table)   # id 6 and row 4 do not exist
+    torch.cuda.synchronize()
+    assert _native.device_error() == 3
+    want = H.f32_to_bf16(oracle.pool_blocks(k16, np.asarray([1, 5], np.int32), 0, True))
+    got = table.view(torch.int16).cpu().numpy().view(np.uint16).reshape(4, -1)
+    assert np.array_equal(got[[0, 3]], want) and not got[[1, 2]].any()
+    # a larger batch takes the streaming kernel
+    ids = np.arange(600, dtype=np.int32) % 6
+    ids[[17, 400]] = [6, 99]
+    big = torch.zeros((600, 2, 1, 128), dtype=torch.bfloat16, device=DEV)
+    ops.pool_blocks(k, dev_i32(ids), out_bf16=big)
+    torch.cuda.synchronize()
+    assert _native.device_error() == 3
+    gotb = big.view(torch.int16).cpu().numpy().view(np.uint16).reshape(600, -1)
+    ref = H.f32_to_bf16(oracle.pool_blocks(k16, np.arange(6, dtype=np.int32), 0, True))
+    assert not gotb[[17, 400]].any() and np.array_equal(gotb[5], ref[5]) and np.array_equal(gotb[599], ref[599 % 6])
+    # hash codes of blocks: tensor-core shape (128 channels, 128 bits)
+    w = dev_bf16(H.randn_bf16(rng, (128, 128), 2.0))
+    codes = torch.zeros((3, 2, 16, 16), dtype=torch.uint8, device=DEV)
+    ops.hash_encode_blocks(k, dev_i32([0, 7, 3]), w, out=codes)
+    torch.cuda.synchronize()
+    assert _native.device_error() == 3
+    assert not bool(codes[1].any()) and bool(codes[0].any()) and bool(codes[2].any())
+    # Hamming scores: a slot beyond the code table
+    ctab = torch.randint(0, 255, (5, 2, 16, 16), dtype=torch.uint8, device=DEV)
+    qc = torch.randint(0, 255, (1, 2, 16), dtype=torch.uint8, device=DEV)
+    s = ops.score_hamming(ctab, dev_i32([0, 4]), qc, total=4, slot_ids=dev_i32([0, 5, 4, -1])).cpu().numpy()
+    torch.cuda.synchronize()
+    assert _native.device_error() == 3
+    assert s[1] == np.iinfo(np.int32).min and s[3] == np.iinfo(np.int32).min and s[0] > np.iinfo(np.int32).min

@@ -26,7 +26,7 @@ int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, in
 
 // tensor-core (tcgen05) sign-hash encoder; g == NULL: dense vectors, else paged blocks. UCMX_EUNSUPPORTED = not applicable
 int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucmx_kv_geometry* g, const int32_t* ids,
-                       const int32_t* out_slots, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
+                       const int32_t* out_slots, int64_t n_out_rows, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
                        int32_t head_major, uint8_t* out, cudaStream_t st);
 
 #define UCMX_CUDA(call)                                                  \
@@ -254,6 +254,28 @@ __device__ __forceinline__ int warp_sum_i(int v)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// Block id of entry i of an id list, and the table row its result goes to.  An id outside the cache (or a row outside
+// the table) is never used: the entry is dropped and code 3 is left for ucmx_device_error.  Negative values are the
+// documented way to skip an entry and are not reported.
+__device__ __forceinline__ int checked_block_id(const int32_t* __restrict__ ids, int64_t i, int64_t n_blocks, int32_t* err)
+{
+    const int id = __ldg(ids + i);
+    if (id >= 0 && (int64_t)id >= n_blocks) {
+        if (err) atomicExch(err, 3);
+        return -1;
+    }
+    return id;
+}
+__device__ __forceinline__ int64_t checked_out_row(const int32_t* __restrict__ out_slots, int64_t i, int64_t n_rows, int32_t* err)
+{
+    const int64_t row = out_slots ? (int64_t)__ldg(out_slots + i) : i;
+    if (row >= 0 && row >= n_rows) {
+        if (err) atomicExch(err, 3);
+        return -1;
+    }
+    return row;
 }
 
 // lower_bound-style search: the request r with offsets[r] <= c < offsets[r+1]

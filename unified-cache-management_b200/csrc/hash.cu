@@ -33,6 +33,8 @@ struct HashParams {
     int32_t paged;
     const int32_t* ids;
     const int32_t* out_slots;
+    int64_t cache_blocks, out_rows;   // paged: blocks in the cache, rows of the code table
+    int32_t* err;
     int64_t block_stride, token_stride;
     int32_t T, H, head_major;
 };
@@ -48,8 +50,8 @@ __device__ __forceinline__ void hash_locate(const HashParams& p, int64_t v, cons
     const int64_t i = v / per_block;
     const int32_t rem = (int32_t)(v - i * per_block);
     const int32_t t = rem / p.H, h = rem - t * p.H;
-    const int32_t id = __ldg(p.ids + i);
-    const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + i) : i;
+    const int32_t id = checked_block_id(p.ids, i, p.cache_blocks, p.err);
+    const int64_t slot = id < 0 ? -1 : checked_out_row(p.out_slots, i, p.out_rows, p.err);
     src = (id < 0) ? nullptr : p.x + (int64_t)id * p.block_stride + (int64_t)t * p.token_stride + (int64_t)h * p.dim;
     orow = (slot < 0) ? -1 : (p.head_major ? (slot * p.H + h) * p.T + t : slot * per_block + rem);
 }
@@ -154,6 +156,8 @@ int32_t launch_hash(HashParams& p, cudaStream_t st)
 
 struct HamParams {
     const uint8_t* codes;
+    int64_t n_slots;     // rows of the code table
+    int32_t* err;
     const int32_t* offsets;
     const int32_t* slot_ids;
     const uint8_t* q_codes;
@@ -186,7 +190,11 @@ __global__ void __launch_bounds__(kHamThreads, CROSS ? 2 : 4) score_hamming_kern
 
     for (int64_t c = w0; c < p.total; c += W) {
         const int r = find_request(p.offsets, p.n_req, (int)c);
-        const int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        if (slot >= 0 && (int64_t)slot >= p.n_slots) {      // outside the table: reported, treated as empty
+            if (p.err && lane == 0) atomicExch(p.err, 3);
+            slot = -1;
+        }
         if (slot < 0) {
             if (lane == 0) p.out[c] = INT32_MIN;
             continue;
@@ -328,7 +336,11 @@ __global__ void __launch_bounds__(kHamThreads) score_hamming_generic_kernel(HamP
     const int64_t words_per_row = (int64_t)codes_per_row * p.words;
     for (int64_t c = w0; c < p.total; c += W) {
         const int r = find_request(p.offsets, p.n_req, (int)c);
-        const int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        int slot = p.slot_ids ? __ldg(p.slot_ids + c) : (int)c;
+        if (slot >= 0 && (int64_t)slot >= p.n_slots) {      // outside the table: reported, treated as empty
+            if (p.err && lane == 0) atomicExch(p.err, 3);
+            slot = -1;
+        }
         if (slot < 0) {
             if (lane == 0) p.out[c] = INT32_MIN;
             continue;
@@ -363,7 +375,7 @@ extern "C" int32_t ucmx_hash_encode(const void* x, int64_t n_vec, int64_t x_stri
     if (!x || !w || !out || x_stride < dim || (x_stride % 8) || ((uintptr_t)x & 15) || ((uintptr_t)out & 3))
         return UCMX_EPARAM;
     {
-        const int32_t rc = hash_encode_tc(x, n_vec, x_stride, nullptr, nullptr, nullptr, 0, w, dim, bits, 0, out,
+        const int32_t rc = hash_encode_tc(x, n_vec, x_stride, nullptr, nullptr, nullptr, 0, 0, w, dim, bits, 0, out,
                                           (cudaStream_t)stream);
         if (rc != UCMX_EUNSUPPORTED) return rc;
     }
@@ -380,18 +392,22 @@ extern "C" int32_t ucmx_hash_encode(const void* x, int64_t n_vec, int64_t x_stri
 }
 
 extern "C" int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_geometry* g, const int32_t* block_ids,
-                                           const int32_t* out_slots, int32_t n, const void* w, int32_t bits,
-                                           int32_t head_major, uint8_t* out, ucmx_stream_t stream)
+                                           const int32_t* out_slots, int64_t n_out_slots, int32_t n, const void* w,
+                                           int32_t bits, int32_t head_major, uint8_t* out, ucmx_stream_t stream)
 {
     using namespace ucmx;
     if (n < 0 || !g) return UCMX_EPARAM;
     if (n == 0) return UCMX_OK;
+    if (g->reserved < 1 || n_out_slots < 1) {
+        set_last_text("hash_encode_blocks: the geometry must carry the number of blocks in the cache and the call the rows of the table");
+        return UCMX_EPARAM;
+    }
     if (!k_cache || !block_ids || !w || !out || ((uintptr_t)k_cache & 15) || ((uintptr_t)out & 3)) return UCMX_EPARAM;
     if (g->block_tokens < 1 || g->n_kv_heads < 1 || g->head_dim < 8) return UCMX_EPARAM;
     if ((g->token_stride % 8) || (g->block_stride % 8) || (g->head_dim % 8)) return UCMX_EPARAM;
     {
-        const int32_t rc = hash_encode_tc(k_cache, 0, 0, g, block_ids, out_slots, n, w, g->head_dim, bits, head_major, out,
-                                          (cudaStream_t)stream);
+        const int32_t rc = hash_encode_tc(k_cache, 0, 0, g, block_ids, out_slots, n_out_slots, n, w, g->head_dim, bits,
+                                          head_major, out, (cudaStream_t)stream);
         if (rc != UCMX_EUNSUPPORTED) return rc;
     }
     HashParams p{};
@@ -404,6 +420,9 @@ extern "C" int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_ge
     p.paged = 1;
     p.ids = block_ids;
     p.out_slots = out_slots;
+    p.cache_blocks = g->reserved;
+    p.out_rows = n_out_slots;
+    p.err = error_word();
     p.block_stride = g->block_stride;
     p.token_stride = g->token_stride;
     p.T = g->block_tokens;
@@ -412,13 +431,13 @@ extern "C" int32_t ucmx_hash_encode_blocks(const void* k_cache, const ucmx_kv_ge
     return launch_hash(p, (cudaStream_t)stream);
 }
 
-extern "C" int32_t ucmx_score_hamming(const uint8_t* codes, int32_t n_kv_heads, int32_t block_tokens, int32_t bits,
+extern "C" int32_t ucmx_score_hamming(const uint8_t* codes, int64_t n_slots, int32_t n_kv_heads, int32_t block_tokens, int32_t bits,
                                       const int32_t* req_offsets, const int32_t* slot_ids, const uint8_t* q_codes,
                                       int32_t n_q_heads, int32_t n_req, int32_t total, int32_t cross_head,
                                       int32_t* out_scores, ucmx_stream_t stream)
 {
     using namespace ucmx;
-    if (n_req < 0 || total < 0) return UCMX_EPARAM;
+    if (n_req < 0 || total < 0 || n_slots < 0) return UCMX_EPARAM;
     if (n_req == 0 || total == 0) return UCMX_OK;
     if (!codes || !req_offsets || !q_codes || !out_scores) return UCMX_EPARAM;
     if (n_kv_heads < 1 || block_tokens < 1 || bits < 32 || bits % 32 || n_q_heads < 1) return UCMX_EPARAM;
@@ -426,7 +445,7 @@ extern "C" int32_t ucmx_score_hamming(const uint8_t* codes, int32_t n_kv_heads, 
     if (((uintptr_t)codes & 15) || ((uintptr_t)q_codes & 3)) return UCMX_EPARAM;
     // scores must fit int32: pairs*bits
     if ((long long)n_kv_heads * block_tokens * (cross_head ? n_q_heads : 1) * bits > 0x7fffffffll) return UCMX_EUNSUPPORTED;
-    HamParams p{codes, req_offsets, slot_ids, q_codes, out_scores, n_req, total, n_kv_heads, block_tokens,
+    HamParams p{codes, n_slots, error_word(), req_offsets, slot_ids, q_codes, out_scores, n_req, total, n_kv_heads, block_tokens,
                 bits / 32, n_q_heads, cross_head ? 1 : 0};
     const int warps_per_cta = kHamThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;

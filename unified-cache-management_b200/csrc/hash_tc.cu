@@ -63,6 +63,7 @@ struct TcParams {
     int32_t paged, H, T, head_major, tiles_per_block;
     const int32_t* ids;
     const int32_t* out_slots;
+    int64_t cache_blocks, out_rows;   // paged: blocks in the cache, rows of the code table
     int32_t* err;
 };
 
@@ -143,8 +144,8 @@ __device__ __forceinline__ int64_t out_row_of(const TcParams& p, int64_t tile, i
     if (p.paged) {
         const int64_t blk = tile / p.tiles_per_block;
         const int sub = (int)(tile - blk * p.tiles_per_block);
-        const int id = __ldg(p.ids + blk);
-        const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
+        const int id = checked_block_id(p.ids, blk, p.cache_blocks, p.err);
+        const int64_t slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, p.err);
         const int t = sub * (kTileM / p.H) + m / p.H, h = m % p.H;
         if (id < 0 || slot < 0) return -1;
         return p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
@@ -265,7 +266,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                         const int sub = (int)(tile - blk * p.tiles_per_block);
                         const int id = __ldg(p.ids + blk);
                         const int t0 = sub * (kTileM / p.H);
-                        // a negative id reads outside the tensor: TMA fills zeros, the tile's codes are not stored
+                        // an id outside the cache reads outside the tensor map: TMA fills zeros, the tile's codes are not stored
                         tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
                         tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
                     } else {
@@ -318,8 +319,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             if (p.paged) {
                 blk = tile / p.tiles_per_block;
                 sub = (int)(tile - blk * p.tiles_per_block);
-                id = __ldg(p.ids + blk);
-                slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : blk;
+                id = checked_block_id(p.ids, blk, p.cache_blocks, nullptr);
+                slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, nullptr);
             }
             if (!mbar_wait(&bars->fix_ready[s], par)) {
                 bars->abort_flag = 1;
@@ -601,8 +602,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
 // Returns UCMX_EUNSUPPORTED when the tensor-core path does not apply; the caller then runs the
 // CUDA-core kernel, which produces the same codes.
 int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucmx_kv_geometry* g, const int32_t* ids,
-                       const int32_t* out_slots, int32_t n_blocks, const void* w, int32_t dim, int32_t bits,
-                       int32_t head_major, uint8_t* out, cudaStream_t st)
+                       const int32_t* out_slots, int64_t n_out_rows, int32_t n_blocks, const void* w, int32_t dim,
+                       int32_t bits, int32_t head_major, uint8_t* out, cudaStream_t st)
 {
     EncodeTiledFn enc = encode_fn();
     if (!enc || dim != kDim || bits != kBits || ((uintptr_t)out & 15) || ((uintptr_t)x & 15)) return UCMX_EUNSUPPORTED;
@@ -630,6 +631,8 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.tiles_per_block = T * H / kTileM;
         p.ids = ids;
         p.out_slots = out_slots;
+        p.cache_blocks = g->reserved;
+        p.out_rows = n_out_rows;
         p.n_tiles = (int64_t)n_blocks * p.tiles_per_block;
     } else {
         if (x_stride % 8 || n_vec < 1 || n_vec > 0x7fffffffll) return UCMX_EUNSUPPORTED;

@@ -64,6 +64,8 @@ struct KsParams {
     const uint16_t* reps;       // half [n_slots][M][H][dp]
     const int32_t* offsets;     // [n_req+1] candidate blocks of each request
     const int32_t* slot_ids;    // [total] table slot of each candidate, or NULL = identity
+    int32_t n_slots;            // rows of the table (the tensor-core kernels read through a tensor map of that extent,
+                                // so a slot beyond it reads zeros there; the CUDA-core kernel checks it)
     float2* part;               // [total][Rtot] (m, p)
     float2* stats;              // [n_req][Rtot] (m_row, 1/Z_row)
     float* out;                 // [total] votes
@@ -751,7 +753,11 @@ kvstar_partial_generic_kernel(KsParams p)
     extern __shared__ __align__(16) unsigned char smem_g[];
     uint16_t* sk = reinterpret_cast<uint16_t*>(smem_g);     // [M][H][dp]
     const int t = blockIdx.x;
-    const int slot = p.slot_ids ? __ldg(p.slot_ids + t) : t;
+    int slot = p.slot_ids ? __ldg(p.slot_ids + t) : t;
+    if (slot >= 0 && slot >= p.n_slots) {                    // outside the table: reported, treated as an empty entry
+        if (p.err && threadIdx.x == 0) atomicExch(p.err, 3);
+        slot = -1;
+    }
     const int req = find_request(p.offsets, p.n_req, t);
     const int q0 = __ldg(p.q_offsets + req), nx = min(__ldg(p.q_offsets + req + 1) - q0, p.Rp / p.gq);
     const int n_el = p.M * p.C;
@@ -891,6 +897,8 @@ struct ReprParams {
     ucmx_kv_geometry g;
     const int32_t* ids;
     const int32_t* out_slots;
+    int64_t out_rows;
+    int32_t* err;
     const int64_t* pruned;
     uint16_t* out;
     int32_t dp, merge, M;
@@ -902,8 +910,8 @@ kvstar_block_repre_kernel(ReprParams p)
     extern __shared__ __align__(16) unsigned char smem_r[];
     uint16_t* st = reinterpret_cast<uint16_t*>(smem_r);     // [tokens_per_step][H*D]
     const int i = blockIdx.x;
-    const int id = __ldg(p.ids + i);
-    const int slot = p.out_slots ? __ldg(p.out_slots + i) : i;
+    const int id = checked_block_id(p.ids, i, p.g.reserved, p.err);
+    const int64_t slot = id < 0 ? -1 : checked_out_row(p.out_slots, i, p.out_rows, p.err);
     if (id < 0 || slot < 0) return;
     const int E = p.g.n_kv_heads * p.g.head_dim;
     const int C = p.g.n_kv_heads * p.dp;
@@ -945,11 +953,13 @@ int row_pad(int rows)
 using namespace ucmx;
 
 extern "C" int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_geometry* geom, const int32_t* block_ids,
-                                           const int32_t* out_slots, int32_t n, const int64_t* pruned_index,
-                                           int32_t d_pruned, int32_t merge, void* reps_f16, ucmx_stream_t stream)
+                                           const int32_t* out_slots, int64_t n_out_slots, int32_t n,
+                                           const int64_t* pruned_index, int32_t d_pruned, int32_t merge, void* reps_f16,
+                                           ucmx_stream_t stream)
 {
     if (n < 0) return UCMX_EPARAM;
     if (n == 0) return UCMX_OK;
+    if (!geom || geom->reserved < 1 || n_out_slots < 1) return UCMX_EPARAM;
     if (!k_cache || !geom || !block_ids || !reps_f16 || merge < 1 || d_pruned < 1) return UCMX_EPARAM;
     const int T = geom->block_tokens, H = geom->n_kv_heads, D = geom->head_dim;
     if (T < 1 || H < 1 || D < 8 || (D & 7) || T % merge || d_pruned > D || (!pruned_index && d_pruned != D)) return UCMX_EPARAM;
@@ -959,6 +969,8 @@ extern "C" int32_t ucmx_kvstar_block_repre(const void* k_cache, const ucmx_kv_ge
     p.g = *geom;
     p.ids = block_ids;
     p.out_slots = out_slots;
+    p.out_rows = n_out_slots;
+    p.err = error_word();
     p.pruned = pruned_index;
     p.out = (uint16_t*)reps_f16;
     p.dp = d_pruned;
@@ -1048,6 +1060,7 @@ extern "C" int32_t ucmx_kvstar_scores(const void* reps_f16, int32_t n_slots, int
     p.reps = (const uint16_t*)reps_f16;
     p.offsets = req_offsets;
     p.slot_ids = slot_ids;
+    p.n_slots = n_slots;
     p.n_req = n_req;
     p.total = total;
     p.M = M;

@@ -30,6 +30,8 @@ struct PoolParams {
     int32_t T, H, D, E;    // tokens per block, heads, head dim, E = H*D
     const int32_t* ids;
     const int32_t* out_slots;
+    int64_t cache_blocks;  // blocks in the cache: ids at or beyond it are dropped and reported
+    int64_t out_rows;      // rows of the output table
     int32_t n;
     int32_t round_bf16;
     int32_t n_rep, rep_index;
@@ -90,7 +92,8 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
         const int c = g - li * p.chunks_per_block;
         const int item = (int)blockIdx.x + li * (int)gridDim.x;
         const int blk = item / p.cs, split = item - blk * p.cs;
-        const int id = __ldg(p.ids + blk);
+        int id = checked_block_id(p.ids, blk, p.cache_blocks, p.err);
+        if (id < 0) id = 0;              // a dropped entry streams block 0 (its result is not stored)
         const int t0 = c * p.rows_per_stage;
         const int rows = min(p.rows_per_stage, p.T - t0);
         const int s = g % n_stages;
@@ -160,7 +163,8 @@ __global__ void __launch_bounds__(CGT == 4 ? 1024 : 256) pool_blocks_kernel(Pool
             // block finished: finalise and store
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
             const int blk = item / p.cs, split = item - blk * p.cs;
-            const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : (int64_t)blk;
+            const int64_t slot = checked_block_id(p.ids, blk, p.cache_blocks, nullptr) < 0
+                                     ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, p.err);
 #pragma unroll
             for (int j = 0; j < CGT; ++j) {
                 const int cg = tid + j * (int)blockDim.x;
@@ -282,7 +286,8 @@ __global__ void __launch_bounds__(128) pool_blocks_tile_kernel(const __grid_cons
     const int cols = p.cg_per_item * 8;  // elements per piece
     const int item = blockIdx.x;
     const int blk = item / p.cs, split = item - blk * p.cs;
-    const int id = __ldg(p.ids + blk);
+    const int id_in = checked_block_id(p.ids, blk, p.cache_blocks, p.err);
+    const int id = id_in < 0 ? 0 : id_in;
     if (tid == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
@@ -309,7 +314,7 @@ __global__ void __launch_bounds__(128) pool_blocks_tile_kernel(const __grid_cons
             a0 *= inv;
             a1 *= inv;
         }
-        const int64_t slot = p.out_slots ? (int64_t)__ldg(p.out_slots + blk) : (int64_t)blk;
+        const int64_t slot = id_in < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, p.err);
         if (slot >= 0) {
             const int e0 = split * cols + c2;
             const int h = e0 / p.D, d = e0 - h * p.D;
@@ -380,7 +385,7 @@ int32_t launch_pool_tile(PoolParams& p, const ucmx_kv_geometry* g, int mode, cud
 }  // namespace ucmx
 
 extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry* g, const int32_t* block_ids,
-                                    const int32_t* out_slots, int32_t n, int32_t mode, int32_t round_bf16,
+                                    const int32_t* out_slots, int64_t n_out_slots, int32_t n, int32_t mode, int32_t round_bf16,
                                     int32_t n_rep, int32_t rep_index, void* out_bf16, float* out_f32,
                                     ucmx_stream_t stream)
 {
@@ -388,6 +393,10 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
     if (n < 0) return UCMX_EPARAM;
     if (n == 0) return UCMX_OK;
     if (!k_cache || !g || !block_ids || (!out_bf16 && !out_f32)) return UCMX_EPARAM;
+    if (g->reserved < 1 || n_out_slots < 1) {
+        set_last_text("pool_blocks: the geometry must carry the number of blocks in the cache and the call the rows of the table");
+        return UCMX_EPARAM;
+    }
     if (mode < 0 || mode > 3 || n_rep < 1 || rep_index < 0 || rep_index >= n_rep) return UCMX_EPARAM;
     if (g->block_tokens < 1 || g->n_kv_heads < 1 || g->head_dim < 8 || g->head_dim % 8) return UCMX_EPARAM;
     const int64_t E64 = (int64_t)g->n_kv_heads * g->head_dim;
@@ -409,6 +418,8 @@ extern "C" int32_t ucmx_pool_blocks(const void* k_cache, const ucmx_kv_geometry*
     p.E = (int32_t)E64;
     p.ids = block_ids;
     p.out_slots = out_slots;
+    p.cache_blocks = g->reserved;
+    p.out_rows = n_out_slots;
     p.n = n;
     p.round_bf16 = round_bf16;
     p.n_rep = n_rep;

@@ -63,7 +63,11 @@ __global__ void __launch_bounds__(kRemapThreads) remap_resident_kernel(RemapPara
     const int s0 = __ldg(p.slot_offsets + r), n_slots = __ldg(p.slot_offsets + r + 1) - s0;
     const int j0 = __ldg(p.sel_offsets + r);
     int n_sel = __ldg(p.sel_offsets + r + 1) - j0;
-    if (p.sel_counts) n_sel = min(n_sel, __ldg(p.sel_counts + r));
+    if (p.sel_counts) {
+        const int c = __ldg(p.sel_counts + r);
+        if (c < 0) return;                          // a negative count: this request sits the round out, state untouched
+        n_sel = min(n_sel, c);
+    }
     int32_t* slot_logical = p.slot_logical + s0;
     uint8_t* slot_free = p.slot_free + s0;
     const int32_t* slot_phys = p.slot_phys + s0;
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(kRemapThreads) remap_resident_kernel(RemapPara
     int n_free = 0;
     for (int c0 = 0; c0 < n_slots; c0 += kRemapThreads) {
         const int s = c0 + tid;
-        const bool f = s < n_slots && slot_free[s] != 0 && hit[s] == 0;
+        const bool f = s < n_slots && slot_free[s] != 0 && hit[s] == 0 && __ldg(slot_phys + s) >= 0;
         int tot;
         const int pos = n_free + excl_scan(f, s_warp, tot);
         if (f) free_list[pos] = s;
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(kRemapThreads) remap_resident_kernel(RemapPara
         n_miss += tot;
     }
     __syncthreads();
-    for (int s = tid; s < n_slots; s += kRemapThreads) slot_free[s] = hit[s] ? 0 : 1;
+    for (int s = tid; s < n_slots; s += kRemapThreads) slot_free[s] = (hit[s] || __ldg(slot_phys + s) < 0) ? 0 : 1;
     // the rest of this request's room in the load lists is marked empty, so that a block mover can take the lists
     // of all requests as one array and skip what is not a load
     const int n_load = min(n_miss, n_free);

@@ -343,6 +343,83 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
     __syncthreads();
     const int32_t* off = off_in_smem ? s_off : p.offsets;
 
+    // With the query mean folded in, the thread block reduces the raw queries of the (at most kStagedReq) requests
+    // its slice touches first into shared memory, all threads at once and every load requested before the first
+    // sum; a warp that runs past them reduces its query on its own.
+    constexpr int kStagedReq = 3;
+    __shared__ __align__(16) float s_q[FUSEQ ? kStagedReq * QN * 32 : 4];
+    int r_cta = 0;
+    if (FUSEQ) {
+        const int Hkv = p.E / p.D;
+        const int cta_begin = (int)((int64_t)p.total * ((int64_t)blockIdx.x * warps_per_cta) / W);
+        {
+            int lo = 0, hi = p.n_req;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (off[mid] <= cta_begin) lo = mid; else hi = mid;
+            }
+            r_cta = lo;
+        }
+        const int g = p.Hq >= Hkv ? p.Hq / Hkv : 1;
+        const int rep = p.Hq >= Hkv ? 1 : Hkv / p.Hq;
+        const float inv = 1.0f / (float)g;
+        constexpr int kIters = (kStagedReq * QN * 8 + kScoreThreads - 1) / kScoreThreads;   // chunks of 4 elements per thread
+        uint2 w4[kIters][4];
+        const uint16_t* srcs[kIters];
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+            const int idx = (int)threadIdx.x + it * kScoreThreads;
+            const int rr = idx / (p.E / 4);
+            const int e0 = (idx - rr * (p.E / 4)) * 4;
+            const int req = r_cta + rr;
+            srcs[it] = nullptr;
+            if (rr < kStagedReq && req < p.n_req) {
+                const int h = e0 / p.D, d = e0 - h * p.D;
+                srcs[it] = p.q_raw + (int64_t)req * p.q_raw_stride + (int64_t)((h / rep) * g) * p.D + d;
+                if (g == 4) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w4[it][j] = __ldg(reinterpret_cast<const uint2*>(srcs[it] + (int64_t)j * p.D));
+                }
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+            if (!srcs[it]) continue;
+            const int idx = (int)threadIdx.x + it * kScoreThreads;
+            float a0, a1, a2, a3;
+            if (g == 4) {
+                a0 = ((bf16lo(w4[it][0].x) + bf16lo(w4[it][1].x)) + bf16lo(w4[it][2].x)) + bf16lo(w4[it][3].x);
+                a1 = ((bf16hi(w4[it][0].x) + bf16hi(w4[it][1].x)) + bf16hi(w4[it][2].x)) + bf16hi(w4[it][3].x);
+                a2 = ((bf16lo(w4[it][0].y) + bf16lo(w4[it][1].y)) + bf16lo(w4[it][2].y)) + bf16lo(w4[it][3].y);
+                a3 = ((bf16hi(w4[it][0].y) + bf16hi(w4[it][1].y)) + bf16hi(w4[it][2].y)) + bf16hi(w4[it][3].y);
+            } else {
+                uint2 w0 = __ldg(reinterpret_cast<const uint2*>(srcs[it]));
+                a0 = bf16lo(w0.x), a1 = bf16hi(w0.x), a2 = bf16lo(w0.y), a3 = bf16hi(w0.y);
+                for (int j = 1; j < g; ++j) {
+                    const uint2 wj = __ldg(reinterpret_cast<const uint2*>(srcs[it] + (int64_t)j * p.D));
+                    a0 += bf16lo(wj.x);
+                    a1 += bf16hi(wj.x);
+                    a2 += bf16lo(wj.y);
+                    a3 += bf16hi(wj.y);
+                }
+            }
+            if (p.Hq >= Hkv) {
+                a0 *= inv;
+                a1 *= inv;
+                a2 *= inv;
+                a3 *= inv;
+                if (p.round_bf16) {
+                    a0 = bf16_round(a0);
+                    a1 = bf16_round(a1);
+                    a2 = bf16_round(a2);
+                    a3 = bf16_round(a3);
+                }
+            }
+            *reinterpret_cast<float4*>(&s_q[idx * 4]) = make_float4(a0, a1, a2, a3);
+        }
+        __syncthreads();
+    }
+
     if (begin < end) {
         const int Hkv = p.E / p.D;
         int r;
@@ -356,8 +433,12 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
         }
         int r_end = off[r + 1];
         auto fetch_q = [&](int req) {
-            if (FUSEQ) rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
-            else rd.load_q(p.q + (int64_t)req * p.E, lane);
+            if (FUSEQ) {
+                if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * p.E], lane);
+                else rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
+            } else {
+                rd.load_q(p.q + (int64_t)req * p.E, lane);
+            }
         };
         fetch_q(r);
 

@@ -59,14 +59,14 @@ SIGNATURES = {
     "ucmx_compiled_arch": [],
     "ucmx_last_error": [],
     "ucmx_device_error": [_pi32, _i32],
-    "ucmx_pool_blocks": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+    "ucmx_pool_blocks": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
     "ucmx_hash_encode": [_vp, _i64, _i64, _vp, _i32, _i32, _vp, _vp],
-    "ucmx_hash_encode_blocks": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp],
+    "ucmx_hash_encode_blocks": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i64, _i32, _vp, _i32, _i32, _vp, _vp],
     "ucmx_query_group_mean": [_vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp],
     "ucmx_score_dot": [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp, _vp],
     "ucmx_score_dot_query": [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp],
     "ucmx_score_dot_heads": [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp],
-    "ucmx_score_hamming": [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
+    "ucmx_score_hamming": [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "ucmx_topk_ragged": [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "ucmx_peer_exchange_bytes": [_i32, _i64],
     "ucmx_topk_ragged_peer_sum": [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp,
@@ -111,7 +111,7 @@ SIGNATURES = {
                            C.POINTER(C.c_size_t), C.POINTER(_sz), _sz, C.POINTER(_sz)],
     "ucmx_fstore_wait": [_vp, _sz],
     "ucmx_fstore_check": [_vp, _sz, _pi32],
-    "ucmx_kvstar_block_repre": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp],
+    "ucmx_kvstar_block_repre": [_vp, C.POINTER(KvGeometry), _vp, _vp, _i64, _i32, _vp, _i32, _i32, _vp, _vp],
     "ucmx_kvstar_kernel_choice": [_i32, _i32, _i32, _i32, _i32, _i32],
     "ucmx_kvstar_workspace_bytes": [_i32, _i32, _i32, _i32, _i32],
     "ucmx_kvstar_scores": [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz,

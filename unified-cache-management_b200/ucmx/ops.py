@@ -73,7 +73,9 @@ def pool_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, *, mode: str = "
         raise ValueError("out_bf16 must be contiguous bf16")
     if out_f32 is not None and (out_f32.dtype != torch.float32 or not out_f32.is_contiguous()):
         raise ValueError("out_f32 must be contiguous fp32")
-    st = N.lib.ucmx_pool_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+    table = out_bf16 if out_bf16 is not None else out_f32
+    rows = table.numel() // (g.n_kv_heads * n_rep * g.head_dim)          # rows of the output table
+    st = N.lib.ucmx_pool_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), rows, n,
                                 _POOL_MODES[mode], int(round_bf16), n_rep, rep_index, _ptr(out_bf16),
                                 _ptr(out_f32), _stream(k_cache))
     N.check("ucmx_pool_blocks", st, 1 if n else 0)
@@ -194,7 +196,7 @@ def score_hamming(codes: torch.Tensor, req_offsets: torch.Tensor, q_codes: torch
         raise ValueError("q_codes shape does not match")
     if out is None:
         out = torch.empty((total,), dtype=torch.int32, device=codes.device)
-    st = N.lib.ucmx_score_hamming(_ptr(codes), H, T, nb * 8, _ptr(_i32(req_offsets, "req_offsets")),
+    st = N.lib.ucmx_score_hamming(_ptr(codes), codes.shape[0], H, T, nb * 8, _ptr(_i32(req_offsets, "req_offsets")),
                                   _ptr(_i32(slot_ids, "slot_ids")), _ptr(q_codes), q_codes.shape[1], n_req, total,
                                   int(cross_head), _ptr(out), _stream(codes))
     N.check("ucmx_score_hamming", st, 1 if total and n_req else 0)
@@ -270,7 +272,8 @@ def hash_encode_blocks(k_cache: torch.Tensor, block_ids: torch.Tensor, w: torch.
     if out is None:
         shape = (n, g.n_kv_heads, g.block_tokens, bits // 8) if head_major else (n, g.block_tokens, g.n_kv_heads, bits // 8)
         out = torch.empty(shape, dtype=torch.uint8, device=k_cache.device)
-    st = N.lib.ucmx_hash_encode_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+    rows = out.numel() // (g.n_kv_heads * g.block_tokens * (bits // 8))   # rows of the code table
+    st = N.lib.ucmx_hash_encode_blocks(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), rows, n,
                                        _ptr(w.contiguous()), bits, int(head_major), _ptr(out), _stream(k_cache))
     N.check("ucmx_hash_encode_blocks", st, 1 if n else 0)
     return out
@@ -445,7 +448,7 @@ def kvstar_block_repre(k_cache: torch.Tensor, block_ids: torch.Tensor, *, merge:
         out = torch.empty((n, M, g.n_kv_heads, dp), dtype=torch.float16, device=k_cache.device)
     if out.dtype != torch.float16 or not out.is_contiguous() or tuple(out.shape[1:]) != (M, g.n_kv_heads, dp):
         raise ValueError("out must be contiguous fp16 [n_slots, T/merge, n_kv_heads, d_pruned]")
-    st = N.lib.ucmx_kvstar_block_repre(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), n,
+    st = N.lib.ucmx_kvstar_block_repre(_ptr(k_cache), C.byref(g), _ptr(ids), _ptr(_i32(out_slots, "out_slots")), out.shape[0], n,
                                        _ptr(pruned_index), dp, merge, _ptr(out), _stream(k_cache))
     N.check("ucmx_kvstar_block_repre", st, 1 if n else 0)
     return out
