@@ -47,11 +47,14 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 N_PLUGIN_TABLES = 4          # distinct representative tables the retrieval objects of both arms cycle through
 
-# DRAM bytes per launch of the gather kernel over its algorithmic bytes, from an ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum) of a small case of this benchmark, scaled by the blocks moved:
-# reads equal the payload, a few per cent of the writes are still dirty in L2 when the kernel ends.
-GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.969
-GATHER_TRAFFIC_SOURCE = "ncu capture of xfer_bulk_kernel on the --profile-case batch, scaled by blocks moved"
+# DRAM traffic of one launch of the gather kernel, from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum)
+# of the --profile-case batch (274 blocks, 143.65 MB of payload): reads = the payload (143.71 MB), writes = the
+# payload minus what is still dirty in L2 when the kernel ends (84.0-87.0 MB written: 58.6 MB on average stay behind,
+# about half of the 126 MB L2).  Reads grow with the blocks moved, the residue does not (an earlier full-size capture
+# showed the same 57 MB), so a full launch moves its algorithmic bytes minus that residue.
+GATHER_L2_DIRTY_RESIDUE_BYTES = 58.6e6
+GATHER_TRAFFIC_SOURCE = ("ncu dram__bytes_read+write of xfer_bulk_kernel on the --profile-case batch: reads = payload, "
+                         "writes = payload - 58.6 MB still dirty in L2; scaled to this launch by blocks moved")
 
 
 def env_int(name, default):
@@ -1114,7 +1117,7 @@ def main():
         roofline = {"kernel": ("remap_resident_kernel + xfer_bulk_kernel (delta load of one layer)" if delta
                                else "xfer_bulk_kernel (gather of selected K,V blocks, one layer)"), "bound": "hbm",
                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None if delta else moved_bytes * GATHER_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                    "traffic": None if delta else moved_bytes - GATHER_L2_DIRTY_RESIDUE_BYTES,
                     "traffic_source": None if delta else GATHER_TRAFFIC_SOURCE,
                     "algorithmic_bytes_per_launch": moved_bytes, "avg_launch_us": gather_avg_ms * 1e3,
                     "launches_timed": len(gather_ms)}

@@ -22,7 +22,7 @@ constexpr int kScoreThreads = 256;
 constexpr int kMaxRingStages = 16;
 constexpr int kMaxSmemOffsets = 2049;        // request offsets kept in shared memory (more requests: read from global)
 constexpr int kRingSmemPerSm = 200 * 1024;   // shared memory the row rings of one SM may take
-constexpr int kRingStages = 3;               // rows a warp keeps in flight (measured at 2 KiB rows: 2-3 best, 6 slower)
+constexpr int kRingStages = 4;               // rows a warp keeps in flight: two pairs (measured at 2 KiB rows: 6 is slower)
 
 // ------------------------------------------------------------------ query group mean
 
@@ -65,6 +65,8 @@ struct ScoreParams {
     int32_t n_req, total, E;
     float scale;
     int32_t stages;          // ring depth per warp
+    int32_t rows_per_warp;   // candidates per warp (the last warps may get fewer or none)
+    int32_t d_shift;         // log2(D) when D is a power of two, else -1
     PeerPush px;             // px.world == 0: single rank
     int32_t* err;
 };
@@ -246,27 +248,31 @@ struct RowDot {
 
 // One warp per table row, rows fetched by the copy engine: every warp owns a contiguous slice of the
 // candidate list and a private ring of `stages` row buffers in shared memory.  Lane 0 keeps the ring full with
-// one bulk async copy per row (completion on the stage's mbarrier); the warp takes a row out of shared memory
-// as soon as it has landed, and the stage is refilled before the partial sums are even added up, so a warp has
-// `stages` rows in flight at all times without holding any of them in registers.  Scores are collected one per
-// lane and leave 32 at a time.  With `push` set (tensor-parallel ranks) every score is also written into each
-// peer's inbox, so the exchange of partial scores rides on the scoring kernel's own stores.
+// one bulk async copy per row (completion on the stage's mbarrier); the warp takes rows out of shared memory
+// two at a time (two independent multiply-add chains and one interleaved reduction), and the stages are
+// refilled before the partial sums are even added up, so a warp has `stages` rows in flight at all times
+// without holding any of them in registers.  Scores are collected one per lane and leave 32 at a time.  With a
+// peer exchange (tensor-parallel ranks) every score is also written into each rank's inbox, so the exchange of
+// partial scores rides on the scoring kernel's own stores.
+// The kernel is as much bound by instruction issue as by memory (a row of 2 KiB is 130 instructions of a warp
+// against 50 ns of HBM time per SM), so everything outside the row loop is kept short: no 64-bit divisions, the
+// stage index counted instead of computed, slot ids read once.
 template <int DT, int QN, bool FUSEQ>
-__global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScoreParams p)
+__global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreParams p)
 {
     extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int kWarps = kScoreThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int warps_per_cta = blockDim.x >> 5;
-    const int64_t W = (int64_t)gridDim.x * warps_per_cta;
-    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + warp;
-    const int begin = (int)((int64_t)p.total * w / W);
-    const int end = (int)((int64_t)p.total * (w + 1) / W);
+    const int w = (int)blockIdx.x * kWarps + warp;
+    const int begin = min(w * p.rows_per_warp, p.total);
+    const int end = min(begin + p.rows_per_warp, p.total);
 
     using RD = RowDot<DT, QN>;
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
+    constexpr int E = QN * 32;
     const int stages = p.stages;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem) + warp * kMaxRingStages;
-    unsigned char* ring = smem + (size_t)warps_per_cta * kMaxRingStages * 8 + (size_t)warp * stages * kRowBytes;
+    unsigned char* ring = smem + (size_t)kWarps * kMaxRingStages * 8 + (size_t)warp * stages * kRowBytes;
     const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
 
     if (lane == 0) {
@@ -287,71 +293,63 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
     // the slot ids are there, and the query while the rows are on their way.
     __shared__ int32_t s_off[kMaxSmemOffsets];
     const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
-    int32_t off_reg[(kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads];
+    constexpr int kOffIters = (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads;
+    int32_t off_reg[kOffIters];
     if (off_in_smem) {
 #pragma unroll
-        for (int j = 0; j < (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads; ++j) {
+        for (int j = 0; j < kOffIters; ++j) {
             const int i = (int)threadIdx.x + j * kScoreThreads;
             off_reg[j] = i <= p.n_req ? __ldg(p.offsets + i) : 0;
         }
     }
     const uint64_t read_once = l2_evict_first_policy();      // every table row is read exactly once
 
-    RD rd;
-    int win = begin;
-    int cur = -1, nxt = -1;
-    auto load_slots = [&](int first) {
-        int v = -1;
-        if (first + lane < end) {
-            v = p.slot_ids ? __ldg(p.slot_ids + first + lane) : (first + lane);
-            if (v >= 0 && (int64_t)v >= p.n_slots) {
-                if (p.err) atomicExch(p.err, 3);
-                v = -1;
-            }
+    // slot id of a row (the same value in every lane); one outside the table is reported and treated as empty
+    auto slot_of = [&](int row) -> int {
+        if (row >= end) return -1;
+        int v = p.slot_ids ? __ldg(p.slot_ids + row) : row;
+        if (v >= 0 && (int64_t)v >= p.n_slots) {
+            if (p.err) atomicExch(p.err, 3);
+            v = -1;
         }
         return v;
     };
-    auto slot_at = [&](int row) {
-        const int a = __shfl_sync(0xffffffffu, cur, (row - win) & 31);
-        const int b = __shfl_sync(0xffffffffu, nxt, (row - win) & 31);
-        return row < win + 32 ? a : b;
-    };
-    auto fetch = [&](int row) {      // called by the whole warp
-        const int slot = slot_at(row);
-        if (lane == 0 && slot >= 0) {
-            const int s = (row - begin) % stages;
-            mbar_expect_tx(&full[s], kRowBytes);
-            bulk_g2s_hint(ring + (size_t)s * kRowBytes, base + (size_t)slot * kRowBytes, kRowBytes, &full[s], read_once);
+    uint32_t valid = 0;        // bit s: stage s holds (or is about to hold) a row
+    auto fetch = [&](int s, int slot) {
+        if (slot >= 0) {
+            valid |= 1u << s;
+            if (lane == 0) {
+                mbar_expect_tx(&full[s], kRowBytes);
+                bulk_g2s_hint(ring + (size_t)s * kRowBytes, base + (size_t)slot * kRowBytes, kRowBytes, &full[s], read_once);
+            }
+        } else {
+            valid &= ~(1u << s);
         }
     };
     if (begin < end) {
-        // Slot ids are held 32 rows at a time, one per lane: `cur` covers rows [win, win+32), `nxt` the 32
-        // after; the row being fetched is at most `stages` (<= 16) ahead of the row being consumed, so both
-        // are always inside the two windows.  A slot outside the table is reported and treated as empty.
-        cur = load_slots(begin);
-        nxt = load_slots(begin + 32);
-        const int pre = min(end, begin + stages);
-        for (int row = begin; row < pre; ++row) fetch(row);
+        // the first `stages` slot ids with one coalesced read, then one copy each
+        const int mine_slot = lane < stages ? slot_of(begin + lane) : -1;
+        for (int s = 0; s < stages; ++s) fetch(s, __shfl_sync(0xffffffffu, mine_slot, s));
     }
     if (off_in_smem) {
 #pragma unroll
-        for (int j = 0; j < (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads; ++j) {
+        for (int j = 0; j < kOffIters; ++j) {
             const int i = (int)threadIdx.x + j * kScoreThreads;
             if (i <= p.n_req) s_off[i] = off_reg[j];
         }
     }
     __syncthreads();
     const int32_t* off = off_in_smem ? s_off : p.offsets;
+    const int Hkv = E / p.D;
 
     // With the query mean folded in, the thread block reduces the raw queries of the (at most kStagedReq) requests
     // its slice touches first into shared memory, all threads at once and every load requested before the first
     // sum; a warp that runs past them reduces its query on its own.
     constexpr int kStagedReq = 3;
-    __shared__ __align__(16) float s_q[FUSEQ ? kStagedReq * QN * 32 : 4];
+    __shared__ __align__(16) float s_q[FUSEQ ? kStagedReq * E : 4];
     int r_cta = 0;
     if (FUSEQ) {
-        const int Hkv = p.E / p.D;
-        const int cta_begin = (int)((int64_t)p.total * ((int64_t)blockIdx.x * warps_per_cta) / W);
+        const int cta_begin = min((int)blockIdx.x * kWarps * p.rows_per_warp, p.total);
         {
             int lo = 0, hi = p.n_req;
             while (hi - lo > 1) {
@@ -363,18 +361,19 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
         const int g = p.Hq >= Hkv ? p.Hq / Hkv : 1;
         const int rep = p.Hq >= Hkv ? 1 : Hkv / p.Hq;
         const float inv = 1.0f / (float)g;
-        constexpr int kIters = (kStagedReq * QN * 8 + kScoreThreads - 1) / kScoreThreads;   // chunks of 4 elements per thread
+        constexpr int kIters = (kStagedReq * (E / 4) + kScoreThreads - 1) / kScoreThreads;   // chunks of 4 elements per thread
         uint2 w4[kIters][4];
         const uint16_t* srcs[kIters];
 #pragma unroll
         for (int it = 0; it < kIters; ++it) {
             const int idx = (int)threadIdx.x + it * kScoreThreads;
-            const int rr = idx / (p.E / 4);
-            const int e0 = (idx - rr * (p.E / 4)) * 4;
+            const int rr = idx / (E / 4);
+            const int e0 = (idx - rr * (E / 4)) * 4;
             const int req = r_cta + rr;
             srcs[it] = nullptr;
             if (rr < kStagedReq && req < p.n_req) {
-                const int h = e0 / p.D, d = e0 - h * p.D;
+                const int h = p.d_shift >= 0 ? (e0 >> p.d_shift) : e0 / p.D;
+                const int d = e0 - h * p.D;
                 srcs[it] = p.q_raw + (int64_t)req * p.q_raw_stride + (int64_t)((h / rep) * g) * p.D + d;
                 if (g == 4) {
 #pragma unroll
@@ -421,7 +420,7 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
     }
 
     if (begin < end) {
-        const int Hkv = p.E / p.D;
+        RD rd;
         int r;
         {
             int lo = 0, hi = p.n_req;             // invariant: off[lo] <= begin < off[hi]
@@ -434,17 +433,17 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
         int r_end = off[r + 1];
         auto fetch_q = [&](int req) {
             if (FUSEQ) {
-                if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * p.E], lane);
+                if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * E], lane);
                 else rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
             } else {
-                rd.load_q(p.q + (int64_t)req * p.E, lane);
+                rd.load_q(p.q + (int64_t)req * E, lane);
             }
         };
         fetch_q(r);
 
         float mine = 0.0f;        // score of row (flush_from + lane), once computed
         int flush_from = begin;
-        uint32_t phase = 0;       // bit s: parity of the next completion of stage s (empty entries fetch nothing)
+        uint32_t phase = 0;       // bit s: parity of the next completion of stage s
         bool failed = false;
         auto flush = [&](int upto) {   // rows [flush_from, upto), upto - flush_from <= 32
             const int row = flush_from + lane;
@@ -455,8 +454,33 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
             }
             flush_from = upto;
         };
+        // the row in stage s as 16-byte pieces (zeros when the stage holds nothing or its copy never landed)
+        auto take = [&](int s, uint4 (&buf)[RD::kPieces]) -> bool {
+            const bool has = (valid >> s) & 1u;
+            bool ok = has && !failed;
+            if (ok && !mbar_wait(&full[s], (phase >> s) & 1u)) {
+                failed = true;                          // the copy never landed: report, stop fetching
+                if (p.err) atomicExch(p.err, 1);
+                ok = false;
+            }
+            if (ok) {
+                phase ^= 1u << s;
+                const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * kRowBytes);
+#pragma unroll
+                for (int i = 0; i < RD::kPieces; ++i) buf[i] = src[i * 32 + lane];
+            } else {
+                rd.zero_row(buf);
+            }
+            return has;
+        };
+        auto keep = [&](int row, bool has, float v) {
+            if (lane == ((row - flush_from) & 31)) mine = has ? v * p.scale : -INFINITY;
+            if (row - flush_from == 31) flush(row + 1);
+        };
 
-        for (int row = begin; row < end; ++row) {
+        int cs = 0;               // stage of the row being consumed (rows take the stages round robin)
+        int row = begin;
+        while (row < end) {
             if (row >= r_end) {
                 do {
                     ++r;
@@ -464,32 +488,40 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_ring_kernel(ScorePara
                 } while (row >= r_end);
                 fetch_q(r);
             }
-            if (row >= win + 32) {
-                win += 32;
-                cur = nxt;
-                nxt = load_slots(win + 32);
-            }
-            const int slot = slot_at(row);
-            const int s = (row - begin) % stages;
-            float v = 0.0f;
-            if (slot >= 0 && !failed) {
-                if (!mbar_wait(&full[s], (phase >> s) & 1u)) {
-                    failed = true;                      // the copy never landed: report, stop fetching
-                    if (p.err) atomicExch(p.err, 1);
-                } else {
-                    phase ^= 1u << s;
-                    uint4 buf[RD::kPieces];
-                    const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * kRowBytes);
-#pragma unroll
-                    for (int i = 0; i < RD::kPieces; ++i) buf[i] = src[i * 32 + lane];
-                    v = rd.dot(buf);
+            const int cs1 = cs + 1 == stages ? 0 : cs + 1;
+            if (QN <= 32 && row + 1 < end && row + 1 < r_end) {        // (the widest rows leave no registers for a pair)
+                // two rows of one request: independent chains, one interleaved reduction
+                const int n0 = slot_of(row + stages), n1 = slot_of(row + 1 + stages);   // in flight during the waits
+                uint4 a[RD::kPieces], b[RD::kPieces];
+                const bool ha = take(cs, a);
+                const bool hb = take(cs1, b);
+                float x = rd.dot(a), y = rd.dot(b);
+                __syncwarp();                           // every lane has taken its part of both stages
+                if (!failed) {
+                    fetch(cs, n0);
+                    fetch(cs1, n1);
                 }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    x += __shfl_xor_sync(0xffffffffu, x, o);
+                    y += __shfl_xor_sync(0xffffffffu, y, o);
+                }
+                keep(row, ha, x);
+                keep(row + 1, hb, y);
+                row += 2;
+                cs = cs1 + 1 == stages ? 0 : cs1 + 1;
+            } else {
+                const int n0 = slot_of(row + stages);
+                uint4 a[RD::kPieces];
+                const bool ha = take(cs, a);
+                float x = rd.dot(a);
+                __syncwarp();
+                if (!failed) fetch(cs, n0);
+                x = warp_sum(x);
+                keep(row, ha, x);
+                row += 1;
+                cs = cs1;
             }
-            __syncwarp();                               // every lane has taken its part of stage s
-            if (row + stages < end && !failed) fetch(row + stages);
-            v = warp_sum(v);
-            if (lane == ((row - flush_from) & 31)) mine = slot < 0 ? -INFINITY : v * p.scale;
-            if (row - flush_from == 31) flush(row + 1);
         }
         flush(end);
     }
@@ -624,6 +656,11 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
         smem_set[dev] = (int)g.smem;
     }
     p.stages = g.stages;
+    const int64_t warps = (int64_t)g.grid * (kScoreThreads / 32);
+    p.rows_per_warp = (int32_t)((p.total + warps - 1) / warps);
+    p.d_shift = -1;
+    for (int sh = 0; sh < 16; ++sh)
+        if ((1 << sh) == p.D) p.d_shift = sh;
     score_dot_ring_kernel<DT, QN, FUSEQ><<<g.grid, kScoreThreads, g.smem, st>>>(p);
     UCMX_LAUNCH_CHECK("score_dot_ring_kernel");
     return UCMX_OK;
