@@ -51,3 +51,35 @@ def test_host_step_and_its_graph_match_the_device_step():
 
     from ucmx import _native
     assert _native.device_error() == 0
+
+
+@pytest.mark.parametrize("heads_local", [1, 2, 8])
+def test_tensor_parallel_step_replays_from_a_graph(heads_local):
+    """What one rank of a tensor-parallel run does (here alone, as rank 0 of a one-rank exchange): the scoring
+    kernel delivers into the exchange buffer and publishes the round, the top-k kernel collects; captured once and
+    replayed.  One KV head per rank takes the narrow-row kernel after a separate query-mean launch, two or more
+    take the copy-engine kernel with the mean folded in.  The selections must equal the plain engine's."""
+    from ucmx import _native, ops
+    from ucmx.engine import DecodeRetrievalEngine
+    from ucmx.parallel import PeerScoreExchange
+    from ucmx.workloads import KvShape, fixed_batch
+    shape = KvShape(n_q_heads=64, n_kv_heads=8, head_dim=128, block_tokens=128, n_layers=2)
+    batch = fixed_batch(3, 700, 90, seed=77)
+    plain = DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=False, heads_local=heads_local, seed=5,
+                                  order=ops.ORDER_INDEX_ASC)
+    plain.make_queries()
+    plain.step()
+    torch.cuda.synchronize()
+    want = plain.sel_ids.cpu().numpy().copy()
+    buf = torch.zeros(PeerScoreExchange.words_needed(1, batch.total), dtype=torch.float32, device=DEV)
+    ex = PeerScoreExchange([buf.data_ptr()], 0, batch.total, DEV, buf)
+    eng = DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=False, heads_local=heads_local, seed=5,
+                                peer_exchange=ex, order=ops.ORDER_INDEX_ASC)
+    eng.make_queries()                                     # the same seed: the same tables and queries
+    eng.capture()
+    for _ in range(3):                                     # odd and even rounds
+        eng.sel_ids.fill_(-7)
+        eng.step()
+        torch.cuda.synchronize()
+        assert np.array_equal(eng.sel_ids.cpu().numpy(), want)
+    assert _native.device_error() == 0

@@ -28,11 +28,12 @@ def dev_bf16(u16):
     return torch.from_numpy(np.ascontiguousarray(u16).view(np.int16)).to(DEV).view(torch.bfloat16)
 
 
-def test_emulated_ranks_on_one_gpu(oracle):
+@pytest.mark.parametrize("world", [4, 8])        # two heads per rank: 512-byte rows; one head: the narrow-row kernel
+def test_emulated_ranks_on_one_gpu(oracle, world):
     from ucmx import _native, ops
     from ucmx.parallel import PeerScoreExchange, head_range
     rng = np.random.default_rng(111)
-    world, Hkv, D, n_slots = 4, 8, 128, 700
+    Hkv, D, n_slots = 8, 128, 700
     reps16 = H.randn_bf16(rng, (n_slots, Hkv, D), 0.09)
     counts = [300, 0, 91, 256]
     off = H.ragged_offsets(counts)
