@@ -67,8 +67,8 @@ def test_large_batch_matches_the_checker(oracle):
 
 
 def test_zero_and_tiny_vectors(oracle):
-    """Rows of zeros (every projection is exactly zero: all bits 0), rows whose squares underflow, and enough
-    of them in one tile to overflow the fixer warp's queue."""
+    """Rows of zeros (every projection is exactly zero: all bits 0; they take no exact chain at all) and rows whose
+    squares underflow (every bit of them goes through the exact chain)."""
     from ucmx import ops
     rng = np.random.default_rng(104)
     n = 128 * 20
@@ -98,3 +98,48 @@ def test_repeated_runs_are_identical(oracle):
         got = ops.hash_encode(x, w)
         bad = (got.view(torch.int32) != ref.view(torch.int32)).nonzero()
         assert bad.numel() == 0, f"run {rep}: {bad.shape[0]} words differ, first (row, word): {bad[:8].tolist()}"
+
+
+def test_every_bit_doubtful_on_every_sm(oracle):
+    """Every bit of every vector is doubtful (squares underflow, so no tensor-core sign is trusted) and every thread
+    block gets several tiles: the fixer warp's queue (256 words a tile) overflows in each of them, so most words are
+    settled by the epilogue warps' pooled fallback.  Same bytes as the checker either way."""
+    from ucmx import ops
+    rng = np.random.default_rng(106)
+    n = 148 * 8 * 128
+    x = H.bf16_to_f32(H.randn_bf16(rng, (n, 128))) * 1e-24
+    x16, w16 = H.f32_to_bf16(x), H.randn_bf16(rng, (128, 128), 2.0)
+    got = ops.hash_encode(dev_bf16(x16), dev_bf16(w16)).cpu().numpy()
+    assert np.array_equal(got, oracle.hash_encode(x16, w16))
+    from ucmx import _native
+    assert _native.device_error() == 0
+
+
+def test_two_and_a_half_million_vectors(oracle):
+    """2.5 million vectors (19 532 tiles, 66 per thread block).  The input is a 100 000-vector batch repeated 25 times,
+    so the checker runs once."""
+    from ucmx import ops
+    rng = np.random.default_rng(107)
+    base16 = H.randn_bf16(rng, (100_000, 128))
+    w16 = H.randn_bf16(rng, (128, 128), 2.0)
+    x = dev_bf16(base16).repeat(25, 1).contiguous()
+    got = ops.hash_encode(x, dev_bf16(w16)).view(25, 100_000, 16)
+    want = torch.from_numpy(oracle.hash_encode(base16, w16)).to(DEV)
+    assert bool((got == want.unsqueeze(0)).all())
+
+
+def test_outlier_channels_and_unwritten_blocks(oracle):
+    """Keys whose channels differ in scale by orders of magnitude (the margin test is relative to the row norm, so the
+    small channels' contributions sit far below it), in a paged cache half of whose blocks were never written."""
+    from ucmx import ops
+    rng = np.random.default_rng(108)
+    scale = np.exp(rng.standard_normal(128) * 1.5).astype(np.float32)
+    k = H.bf16_to_f32(H.randn_bf16(rng, (24, 128, 8, 128))) * scale
+    k[12:] = 0.0
+    k[3, 64:] = 0.0
+    k16, w16 = H.f32_to_bf16(k), H.randn_bf16(rng, (128, 128), 2.0)
+    ids = rng.permutation(24).astype(np.int32)
+    got = ops.hash_encode_blocks(dev_bf16(k16), torch.from_numpy(ids).to(DEV), dev_bf16(w16), head_major=False).cpu().numpy()
+    want = oracle.hash_encode(k16[ids], w16)
+    assert np.array_equal(got, want)
+    assert not want[ids >= 12].any()

@@ -7,14 +7,18 @@
 // tile, and four epilogue warps read the accumulator back with tcgen05.ld, take signs and pack bits.
 //
 // Codes must be bit-identical to the checker's definition - the sign of an fp32 fused-multiply-add
-// chain over d = 0..127 - while the tensor core adds in its own order.  Both sums differ from the
-// exact sum S by at most a few 2^-18 * sum|x_d w_d|, so wherever |acc| is clearly above that they
-// have the sign of S and agree.  The epilogue therefore trusts the tensor-core sign only when
-// |acc| > 2^-13 * |x| * |w_j| (Cauchy-Schwarz bounds sum|x_d w_d|; 2^-13 leaves a wide margin) and
-// hands the few remaining bits (about one per thousand for Gaussian data) to a fixer warp, which runs
-// the exact chain from the tile still sitting in shared memory and patches the stored code.  A chain is
-// 128 dependent multiply-adds: run by the epilogue warps themselves it cost a quarter of the kernel's
-// time (plus as much again for pooling the work); on a warp of its own it overlaps with everything else.
+// chain over d = 0..127 - while the tensor core adds in its own order.  With S the exact sum, the chain
+// is off by at most 128 * 2^-24 * sum|x_d w_d| = 2^-17 * sum|x_d w_d| (the standard bound for recursive
+// summation), and sum|x_d w_d| <= |x| |w_j| (Cauchy-Schwarz).  The epilogue trusts the tensor-core sign
+// only when |acc| > 2^-15 * |x| * max_j|w_j|, four times that bound: the two sums then agree in sign as
+// long as the tensor core's own error stays under 3 * 2^-17 * sum|x_d w_d|, that is, as long as it keeps
+// about 15 bits against the sum of magnitudes.  Measured on 805 million bits (Gaussian keys, two seeds,
+// and keys with outlier channels), the two signs never differed until the margin was lowered to 2^-30,
+// so the tensor core in fact keeps about 24.  The few remaining bits (about one in four thousand for
+// Gaussian data) go to a fixer warp, which runs the exact chain from the tile still sitting in shared
+// memory and patches the stored code.  A chain is 128 dependent multiply-adds: run by the epilogue
+// warps themselves it cost a quarter of the kernel's time (plus as much again for pooling the work); on
+// a warp of its own it overlaps with everything else.
 #include <cuda.h>
 
 #include <mutex>
@@ -31,7 +35,7 @@ constexpr int kStagesA = 2;                       // with two CTAs per SM that i
 constexpr int kHalfBytes = kTileM * 128;          // one 64-element K half of a tile: 128 rows x 128 B
 constexpr int kTileBytes = 2 * kHalfBytes;        // 32 KiB
 constexpr int kThreads = 192;                     // warp 0: exact-chain fixer, warp 1: TMA + MMA issue and TMEM owner, warps 2-5: epilogue
-constexpr float kTau = 1.0f / 8192.0f;            // 2^-13
+constexpr float kTau = 1.0f / 32768.0f;           // 2^-15
 constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
 constexpr int kFixSlots = 256;                    // code words with doubtful bits the fixer warp takes per tile (about 20 are typical)
 
@@ -433,7 +437,22 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             }
             // one threshold for the whole row: |acc| <= tau |x| max_j|w_j| (a little wider than per column, no table look-up)
             // a row so small that its squares underflow in bf16 gets no trusted bits at all (threshold = infinity)
-            const float thr = x2 >= 1e-30f ? kTau * sqrtf(x2 * 1.05f) * 1.0001f * __uint_as_float(*wmax_bits) : INFINITY;
+            // - unless every element is zero, as in the unwritten part of a block: the chain of such a row ends at +0
+            // whatever the weights, so all of its bits are 0 and nothing is doubtful
+            float thr;
+            uint32_t keep = 0xffffffffu;
+            if (x2 >= 1e-30f) {
+                thr = kTau * sqrtf(x2 * 1.05f) * 1.0001f * __uint_as_float(*wmax_bits);
+            } else {
+                uint32_t any = 0;
+#pragma unroll 4
+                for (int c = 0; c < 16; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xa + sw_offset(m, c * 8));
+                    any |= (v.x | v.y | v.z | v.w) & 0x7fff7fffu;
+                }
+                thr = any ? INFINITY : -1.0f;
+                keep = any ? 0xffffffffu : 0u;
+            }
             uint32_t code[4], doubt[4];
 #pragma unroll
             for (int cw = 0; cw < 4; ++cw) {
@@ -459,7 +478,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                             unsure |= (fabsf(__uint_as_float(v[g8 * 8 + j])) <= thr ? 1u : 0u) << (g8 * 8 + j);
                     }
                 }
-                code[cw] = ~neg;
+                code[cw] = ~neg & keep;
                 doubt[cw] = unsure;
             }
             // the accumulator is read: hand it back to the MMA warp

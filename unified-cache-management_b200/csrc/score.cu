@@ -220,8 +220,22 @@ struct RowDot {
 #pragma unroll
         for (int i = 0; i < kPieces; ++i) buf[i] = make_uint4(0, 0, 0, 0);
     }
+    // The lane's share of q . row.  bf16 rows go through the packed fp32 multiply-add (two products per instruction)
+    // into two independent pairs of partial sums: half the instructions of a scalar chain and a quarter of its depth.
     __device__ __forceinline__ float dot(const uint4 (&buf)[kPieces]) const
     {
+        if (DT == UCMX_DT_BF16) {
+            float2 s0 = make_float2(0.0f, 0.0f), s1 = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) {
+                const uint4 v = buf[i];
+                s0 = __ffma2_rn(make_float2(q[i * 8 + 0], q[i * 8 + 1]), make_float2(bf16lo(v.x), bf16hi(v.x)), s0);
+                s1 = __ffma2_rn(make_float2(q[i * 8 + 2], q[i * 8 + 3]), make_float2(bf16lo(v.y), bf16hi(v.y)), s1);
+                s0 = __ffma2_rn(make_float2(q[i * 8 + 4], q[i * 8 + 5]), make_float2(bf16lo(v.z), bf16hi(v.z)), s0);
+                s1 = __ffma2_rn(make_float2(q[i * 8 + 6], q[i * 8 + 7]), make_float2(bf16lo(v.w), bf16hi(v.w)), s1);
+            }
+            return (s0.x + s1.x) + (s0.y + s1.y);
+        }
         float acc = 0.0f;
 #pragma unroll
         for (int i = 0; i < kPieces; ++i) {
@@ -501,10 +515,17 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
                     fetch(cs, n0);
                     fetch(cs1, n1);
                 }
+                // One reduction for both rows: neighbouring lanes first swap what the other one sums, so that the lanes
+                // whose parity is that of the first row's place in the output batch add up the first row and the others
+                // the second; four more steps and every lane holds the total its parity stands for - among them the two
+                // lanes that keep these rows' scores.
+                {
+                    const bool second = (lane ^ (row - flush_from)) & 1;
+                    const float got = __shfl_xor_sync(0xffffffffu, second ? x : y, 1);
+                    float z = (second ? y : x) + got;
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    x += __shfl_xor_sync(0xffffffffu, x, o);
-                    y += __shfl_xor_sync(0xffffffffu, y, o);
+                    for (int o = 2; o < 32; o <<= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+                    x = y = z;
                 }
                 keep(row, ha, x);
                 keep(row + 1, hb, y);
