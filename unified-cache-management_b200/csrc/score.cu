@@ -651,7 +651,9 @@ RingGeometry ring_geometry(int32_t total, uint32_t row_bytes)
         ctas_per_sm = 1;
         stages = (int)((kRingSmemPerSm - bar_bytes) / ((size_t)warps_per_cta * row_bytes));
     }
-    if (stages > kRingStages) stages = kRingStages;
+    // about 8 KiB in flight per warp: four buffers for rows of 2 KiB and more, up to sixteen for narrower ones
+    const int cap = row_bytes >= 2048 ? kRingStages : row_bytes >= 1024 ? 8 : kMaxRingStages;
+    if (stages > cap) stages = cap;
     RingGeometry g;
     int64_t grid = (int64_t)sm_count() * ctas_per_sm;
     const int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;   // at least a row per warp
@@ -736,15 +738,17 @@ int32_t peer_push_from(const ucmx_peer_exchange* ex, int32_t total, PeerPush* ou
 }
 
 // Narrow rows, one representative per head: a row of 32 to 256 bytes (for instance one KV head of 128 bf16
-// channels, which is what a rank holds under eight-way head parallelism) is too short for a warp.  Here a group of
-// LPR lanes owns a row, a warp covers 32 / LPR rows with one load instruction and keeps four such instructions in
-// flight; every lane walks the request boundaries for its own rows (they only grow) and takes its eight (bf16) or
-// four (fp32) query elements from the L1-resident query.
+// channels, which is what a rank holds under eight-way head parallelism) is too short for a warp and a copy of its
+// own.  Here a group of LPR lanes owns a row, a warp covers 32 / LPR rows with one load instruction and keeps up to
+// sixteen such instructions (32 rows) in flight; the slot ids of an iteration's rows come in with one coalesced read, asked for
+// an iteration ahead, so that a row's load never waits for its id.  Every lane walks the request boundaries for its
+// own rows (they only grow) and takes its eight (bf16) or four (fp32) query elements from the L1-resident query.
 template <int DT, int LPR>
 __global__ void __launch_bounds__(kScoreThreads) score_dot_narrow_kernel(ScoreGenParams p)
 {
     constexpr int kRows = 32 / LPR;          // rows per load instruction of a warp
-    constexpr int kU = 4;                    // load instructions in flight
+    constexpr int kU = kRows * 16 <= 32 ? 16 : 32 / kRows;   // load instructions in flight (their rows' ids fit one warp-wide read)
+    constexpr int kStep = kRows * kU;        // rows per iteration
     constexpr int kPer = (DT == UCMX_DT_BF16) ? 8 : 4;
     const int lane = threadIdx.x & 31, sub = lane / LPR, pc = lane % LPR;
     const int warps_per_cta = blockDim.x >> 5;
@@ -762,20 +766,24 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_narrow_kernel(ScoreGe
         const int E = p.H * p.D;
         const size_t row_bytes = (size_t)E * (DT == UCMX_DT_BF16 ? 2 : 4);
         const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
+        // slot of row c + lane for the first kStep lanes (-2: past the end, -1: an empty entry of the table)
+        auto ids_of = [&](int c) -> int {
+            const int row = c + lane;
+            return (lane < kStep && row < end) ? checked_slot(p.slot_ids, row, p.n_slots, p.err) : -2;
+        };
+        int ids_next = ids_of(begin);
         int r = find_request(p.offsets, p.n_req, begin);
         int r_end = __ldg(p.offsets + r + 1);
-        for (int c = begin; c < end; c += kRows * kU) {
+        for (int c = begin; c < end; c += kStep) {
+            const int ids = ids_next;
+            ids_next = ids_of(c + kStep);
             uint4 v[kU];
             int slot[kU];
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
-                const int row = c + u * kRows + sub;
-                slot[u] = -2;                    // -2: past the end, -1: an empty entry of the table
+                slot[u] = __shfl_sync(0xffffffffu, ids, u * kRows + sub);
                 v[u] = make_uint4(0, 0, 0, 0);
-                if (row < end) {
-                    slot[u] = checked_slot(p.slot_ids, row, p.n_slots, p.err);
-                    if (slot[u] >= 0) v[u] = ld_stream16(base + (size_t)slot[u] * row_bytes + (size_t)pc * 16);
-                }
+                if (slot[u] >= 0) v[u] = ld_stream16(base + (size_t)slot[u] * row_bytes + (size_t)pc * 16);
             }
 #pragma unroll
             for (int u = 0; u < kU; ++u) {

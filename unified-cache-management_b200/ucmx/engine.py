@@ -187,6 +187,34 @@ class DecodeRetrievalEngine:
                 gather_events[1].record()
 
     # ------------------------------------------------------------------------------------ steps
+    @property
+    def exchanges_scores(self) -> bool:
+        return self.peer_exchange is not None or self.score_reduce is not None
+
+    def all_layers(self, gather_events=None) -> None:
+        """The launches of one step after pooling.  A single rank goes layer by layer.  Tensor-parallel ranks score one
+        layer ahead: layer l+1's partial scores are computed and exchanged before layer l's blocks move, so the exchange
+        (and whatever the ranks have drifted apart) is over long before layer l+1's top-k asks for the sums, instead of
+        being waited for once per layer.  (Queries of all layers are known when the step starts: retrieval works on the
+        previous decode step's queries, ucm/sparse/esa/esa.py:286-339.)  The peer exchange allows it: the top-k of a
+        layer still follows that layer's scoring with no other scoring in between, and a rank can only be two rounds
+        ahead of another after a top-k that waited for that rank's previous round."""
+        if not self.exchanges_scores:
+            for l in range(self.L):
+                self.layer_step(l, None if gather_events is None else gather_events[l])
+            return
+        self.score_layer(0)
+        for l in range(self.L):
+            self.topk_layer(l)
+            if l + 1 < self.L:
+                self.score_layer(l + 1)
+            if self.kv_pool is not None:
+                if gather_events is not None:
+                    gather_events[l][0].record()
+                self.gather_layer(l)
+                if gather_events is not None:
+                    gather_events[l][1].record()
+
     def step(self) -> None:
         """All layers, inputs and outputs resident on the device."""
         if self.graph is not None:
@@ -194,8 +222,7 @@ class DecodeRetrievalEngine:
             return
         if self.kv_pool is not None:
             self.pool_all_layers()
-        for l in range(self.L):
-            self.layer_step(l)
+        self.all_layers()
 
     def capture(self, gather_events=None) -> torch.cuda.CUDAGraph:
         """Record the whole step once into a CUDA graph and return it.  Without events the graph also becomes the
@@ -209,16 +236,14 @@ class DecodeRetrievalEngine:
         with torch.cuda.stream(s):
             if self.kv_pool is not None:
                 self.pool_all_layers()
-            for l in range(min(self.L, 2)):
-                self.layer_step(l)          # warm up lazily initialised state outside capture
+            self.all_layers()               # warm up lazily initialised state outside capture
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             if self.kv_pool is not None:
                 self.pool_all_layers()
-            for l in range(self.L):
-                self.layer_step(l, None if gather_events is None else gather_events[l])
+            self.all_layers(gather_events)
         if gather_events is None:
             self.graph = graph
         return graph
