@@ -427,9 +427,10 @@ def run_tp_long(args, rank, world, local_rank, dev, barrier, *, layers, steps, w
     batch = W.fixed_batch(8, 8192, 2048, seed=5005)
     lo, hi = head_range(shape.n_kv_heads, rank, world)
     peer = PeerScoreExchange.create(batch.total, dev) if (world > 1 and allreduce == "peer") else None
+    use_graph_overlap = world == 1 or peer is not None    # selection of layer l+1 on a second stream beside layer l's block moves
     eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=layers, seed=1000 + rank, heads_local=hi - lo,
                                 score_reduce=ScoreAllReduce() if (world > 1 and peer is None) else None,
-                                peer_exchange=peer, order=ops.ORDER_INDEX_ASC)
+                                peer_exchange=peer, order=ops.ORDER_INDEX_ASC, overlap=use_graph_overlap)
     # every rank must hold the same queries' head slices of the same requests; seeds differ per rank, which is fine
     # for timing, and for the identity check below only the SUMS matter (they are formed from all ranks' parts)
     eng.make_queries()

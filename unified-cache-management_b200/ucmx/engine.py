@@ -23,7 +23,8 @@ from .workloads import KvShape, RaggedBatch
 class DecodeRetrievalEngine:
     def __init__(self, shape: KvShape, batch: RaggedBatch, device: torch.device, *, n_layers: Optional[int] = None,
                  with_kv_pool: bool = True, heads_local: Optional[int] = None, seed: int = 0,
-                 score_reduce=None, peer_exchange=None, order: int = ops.ORDER_SCORE_DESC, delta: bool = False):
+                 score_reduce=None, peer_exchange=None, order: int = ops.ORDER_SCORE_DESC, delta: bool = False,
+                 overlap: bool = False):
         """heads_local: KV heads held by this rank under tensor parallelism (default: all).
         score_reduce: callable applied in place to the fp32 score vector between scoring and top-k
         (the tensor-parallel all-reduce); None on a single rank.
@@ -32,7 +33,9 @@ class DecodeRetrievalEngine:
         order: order of the selected ids (best first, or ascending block position).
         delta: keep a resident working set per layer and request and move only the blocks that are new with respect
         to the previous step's selection (what ESA does, ucm/sparse/esa/esa.py:313-338): top-k of block positions in
-        ascending order -> resident-set remap -> block-to-block move of the misses."""
+        ascending order -> resident-set remap -> block-to-block move of the misses.
+        overlap: scoring and selection of layer l+1 run on a second stream while layer l's blocks move (they do not
+        depend on each other); the step is then bounded by the block moves alone."""
         self.shape, self.batch, self.device = shape, batch, device
         self.L = n_layers if n_layers is not None else shape.n_layers
         self.H = heads_local if heads_local is not None else shape.n_kv_heads
@@ -42,6 +45,8 @@ class DecodeRetrievalEngine:
         self.peer_exchange = peer_exchange
         self.order = ops.ORDER_INDEX_ASC if delta else order
         self.delta = delta
+        self.overlap = bool(overlap) and with_kv_pool and not delta
+        self._select_stream = torch.cuda.Stream(device=device) if self.overlap else None
         i32 = dict(dtype=torch.int32, device=device)
         self.offsets = torch.from_numpy(batch.offsets).to(device)
         self.k_per_req = torch.from_numpy(batch.k_per_req).to(device)
@@ -199,6 +204,9 @@ class DecodeRetrievalEngine:
         previous decode step's queries, ucm/sparse/esa/esa.py:286-339.)  The peer exchange allows it: the top-k of a
         layer still follows that layer's scoring with no other scoring in between, and a rank can only be two rounds
         ahead of another after a top-k that waited for that rank's previous round."""
+        if self.overlap:
+            self._all_layers_two_streams(gather_events)
+            return
         if not self.exchanges_scores:
             for l in range(self.L):
                 self.layer_step(l, None if gather_events is None else gather_events[l])
@@ -214,6 +222,35 @@ class DecodeRetrievalEngine:
                 self.gather_layer(l)
                 if gather_events is not None:
                     gather_events[l][1].record()
+
+    def _all_layers_two_streams(self, gather_events=None) -> None:
+        """Selection (score + top-k, with the exchange under tensor parallelism) on a stream of its own, one layer ahead of
+        the block moves on the current stream.  Each layer has its own selection buffers, so layer l+1 may be selected
+        while layer l's blocks move; the moves wait for their layer's selection through an event.  Works inside a graph
+        capture (the second stream forks from and joins the capturing one)."""
+        main = torch.cuda.current_stream(self.device)
+        side = self._select_stream
+        fork = torch.cuda.Event()
+        fork.record(main)
+        side.wait_event(fork)
+        selected = [torch.cuda.Event() for _ in range(self.L)]
+        with torch.cuda.stream(side):
+            self.score_layer(0)
+            self.topk_layer(0)
+            selected[0].record(side)
+        for l in range(self.L):
+            if l + 1 < self.L:
+                with torch.cuda.stream(side):
+                    self.score_layer(l + 1)
+                    self.topk_layer(l + 1)
+                    selected[l + 1].record(side)
+            main.wait_event(selected[l])
+            if gather_events is not None:
+                gather_events[l][0].record()
+            self.gather_layer(l)
+            if gather_events is not None:
+                gather_events[l][1].record()
+        main.wait_stream(side)
 
     def step(self) -> None:
         """All layers, inputs and outputs resident on the device."""
