@@ -17,6 +17,33 @@ def make_engine():
     return DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=True)
 
 
+def test_selection_on_a_second_stream_changes_nothing():
+    """Scoring and top-k of layer l+1 on a stream of their own beside layer l's block moves: the same selections and
+    the same gathered blocks as layer by layer, call by call and replayed from the captured graph."""
+    from ucmx.engine import DecodeRetrievalEngine
+    from ucmx.workloads import KvShape, ragged_decode_batch
+    shape = KvShape(n_q_heads=32, n_kv_heads=8, head_dim=128, block_tokens=128, n_layers=3)
+    batch = ragged_decode_batch(seed=31, n_req=6, min_ctx=2048, max_ctx=8192, ratio=0.1, min_k=4)
+    plain = DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=True, seed=9)
+    plain.make_queries()
+    plain.step()
+    torch.cuda.synchronize()
+    eng = DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=True, seed=9, overlap=True)
+    eng.make_queries()
+    assert torch.equal(eng.q_dev, plain.q_dev)
+    for replay in (False, True, True):
+        if replay and eng.graph is None:
+            eng.capture()
+        eng.sel_ids.fill_(-7)
+        eng.staging.zero_()
+        eng.step()
+        torch.cuda.synchronize()
+        assert torch.equal(eng.sel_ids, plain.sel_ids) and torch.equal(eng.sel_counts, plain.sel_counts)
+        assert torch.equal(eng.staging, plain.staging)
+    from ucmx import _native
+    assert _native.device_error() == 0
+
+
 def test_host_step_and_its_graph_match_the_device_step():
     eng = make_engine()
     eng.make_queries()
