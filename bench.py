@@ -626,7 +626,7 @@ def _time_launches(fn, iters, reps=3):
 
 
 def run_kernel_workload(args, dev):
-    """hamming | hash | pool | kvstar | connector | filestore: one kernel (or one call path) of the other benchmark
+    """hamming | hash | pool | gsa | kvstar | connector | filestore: one kernel (or one call path) of the other benchmark
     configurations, timed alone on inputs larger than L2 (or rotated over several tables)."""
     import numpy as np
     import torch
@@ -699,6 +699,27 @@ def run_kernel_workload(args, dev):
                     roofline=roofline("pool_blocks_kernel<mean>", nbytes, res["mean"]),
                     max_pooling={"us": res["max"], "gbs": nbytes / res["max"] / 1e3},
                     decode_64_blocks={"us": small, "gbs": 64 * (shape.slice_bytes + 2048) / small / 1e3})
+    elif name == "gsa":
+        # GSA's two scoring forms on the 64-request batch with two representatives per head (config 1's pooling, at
+        # config 2's size): sum over heads of the best representative's dot product (host-side SelectTopKBS semantics,
+        # score_dot_general_kernel) and the device-side block weights of gsa.py:386-412 (score_dot_heads_kernel)
+        R = 2
+        n_tables = 3
+        reps = [(torch.randn((batch.n_slots, H, R, D), generator=g, device=dev) * 0.0884).to(torch.bfloat16) for _ in range(n_tables)]
+        q = torch.randn((batch.n_req, shape.n_q_heads, D), generator=g, device=dev).to(torch.bfloat16)
+        qbar = ops.query_group_mean(q, H)
+        scores = torch.empty((batch.total,), dtype=torch.float32, device=dev)
+        nbytes = batch.total * (H * R * D * 2 + 8)
+        us_gen = _time_launches(lambda i: ops.score_dot(reps[i % n_tables], off, qbar, total=batch.total, slot_ids=table,
+                                                        n_kv_heads=H, head_dim=D, n_rep=R, out=scores), iters=12)
+        us_heads = _time_launches(lambda i: ops.score_dot_heads(reps[i % n_tables], off, q, total=batch.total, slot_ids=table,
+                                                                out=scores), iters=12)
+        line.update(metric="gsa_scored_kv_tokens_per_s", unit=UNIT, value=batch.total * T / (us_gen * 1e-6), ms_per_step=us_gen * 1e-3,
+                    dtype="bf16", config={"workload": "GSA scoring with two representatives per head, the 64-request ragged batch",
+                                          "blocks": int(batch.total), "l2_policy": "three 137 MB tables in rotation"},
+                    roofline=roofline("score_dot_reps_kernel<8 loads, 2 representatives>", nbytes, us_gen),
+                    per_head_weights={"kernel": "score_dot_heads_kernel", "us": us_heads, "gbs": nbytes / us_heads / 1e3,
+                                      "frac": nbytes / us_heads / 1e3 / peak})
     elif name == "kvstar":
         Mp, dp, xq, Hq = 64, 32, 8, shape.n_q_heads
         nb = batch.total
@@ -877,7 +898,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline numbers only: no parity check, plug-in timing or tp_long object")
     ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
     ap.add_argument("--workload", default="decode64",
-                    choices=["decode64", "decode64-delta", "tp-long", "offload", "hamming", "hash", "pool", "kvstar",
+                    choices=["decode64", "decode64-delta", "tp-long", "offload", "hamming", "hash", "pool", "gsa", "kvstar",
                              "connector", "filestore"],
                     help="decode64: the 64-request ragged decode batch, data parallel over requests (default); "
                          "decode64-delta: the same batch with a resident working set per request and layer - queries drift "
@@ -927,7 +948,7 @@ def main():
     if args.workload == "offload":
         run_offload(args, rank, world, local_rank, dev, barrier)
         return finish()
-    if args.workload in ("hamming", "hash", "pool", "kvstar", "connector", "filestore"):
+    if args.workload in ("hamming", "hash", "pool", "gsa", "kvstar", "connector", "filestore"):
         if rank == 0:
             run_kernel_workload(args, dev)
         return finish()
@@ -958,7 +979,7 @@ def main():
     # weak scaling: every rank serves requests of the same lengths (the same work per GPU) over its own block
     # table, keys and queries
     batch = W.ragged_decode_batch(seed=2002, n_req=n_req, table_seed=None if rank == 0 else 7007 + rank)
-    eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank, delta=delta, overlap=not delta)
+    eng = DecodeRetrievalEngine(shape, batch, dev, n_layers=args.layers, seed=1000 + rank, delta=delta, overlap=True)
     eng.make_queries()
     torch.cuda.synchronize()
 
@@ -1122,7 +1143,7 @@ def main():
                     "traffic_source": None if delta else GATHER_TRAFFIC_SOURCE,
                     "algorithmic_bytes_per_launch": moved_bytes, "avg_launch_us": gather_avg_ms * 1e3,
                     "launches_timed": len(gather_ms)}
-        if eng.overlap:
+        if eng.overlap and not delta:
             roofline["note"] = ("timed inside the step, where the next layer's scoring and top-k run beside the gather on a "
                                 "second stream and share HBM with it; alone (stages_us_per_layer.gather) a launch takes "
                                 f"{stages_us['gather']:.1f} us = {moved_bytes / (stages_us['gather'] * 1e-6) / 1e9 / peak:.3f} of the peak")
@@ -1258,8 +1279,7 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": workload_config(batch),
             "cuda_graph": use_graph,
-            "schedule": ("layer by layer on one stream" if delta else
-                         "score + top-k of layer l+1 on a second stream beside the gather of layer l (same graph)"),
+            "schedule": "score + top-k of layer l+1 on a second stream beside the block moves of layer l (same graph)",
             "stages": ("pool(64 new blocks of each of the 32 layers, one launch per step) + per layer score + top-k + "
                        + ("remap + move of newly selected K,V blocks" if delta else "gather(K,V of selected)")),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],

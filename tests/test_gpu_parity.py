@@ -206,7 +206,8 @@ def test_score_dot_matches_compiled_reference(ops):
         np.testing.assert_allclose(top, G["esa_scores"][r], **_score_tol(G["esa_scores"][r]))
 
 
-@pytest.mark.parametrize("n_rep,H_,D", [(3, 8, 128), (1, 4, 64), (2, 2, 256)])
+@pytest.mark.parametrize("n_rep,H_,D", [(3, 8, 128), (1, 4, 64), (2, 2, 256), (2, 8, 128), (4, 8, 128), (2, 4, 128), (4, 4, 128),
+                                        (2, 1, 128)])
 def test_score_dot_gsa_multi_rep(ops, oracle, n_rep, H_, D):
     rng = np.random.default_rng(22)
     n_slots = 120
@@ -215,12 +216,15 @@ def test_score_dot_gsa_multi_rep(ops, oracle, n_rep, H_, D):
     counts = [50, 70]
     off = H.ragged_offsets(counts)
     slots = rng.permutation(n_slots).astype(np.int32)
+    slots[[3, 77]] = -1                      # entries without a block score -inf
     q = H.bf16_to_f32(H.randn_bf16(rng, (2, H_ * D)))
+    ok = slots >= 0
     for table in (dev_bf16(reps16), torch.from_numpy(reps32).to(DEV)):
         got = ops.score_dot(table, dev_i32(off), torch.from_numpy(q).to(DEV), total=120, slot_ids=dev_i32(slots),
                             n_kv_heads=H_, head_dim=D, n_rep=n_rep).cpu().numpy()
-        ref = oracle.score_dot_gsa(reps32, H_, n_rep, D, off, slots, q)
-        np.testing.assert_allclose(got, ref, **_score_tol(ref))
+        ref = oracle.score_dot_gsa(reps32, H_, n_rep, D, off, np.maximum(slots, 0), q)
+        np.testing.assert_allclose(got[ok], ref[ok], **_score_tol(ref))
+        assert np.isneginf(got[~ok]).all()
 
 
 def test_score_dot_gsa_reference_vectors(ops):

@@ -146,3 +146,41 @@ def test_noalloc_rejects_batches_beyond_its_scratch():
                                           N.WIN_NONE, N.ORDER_SCORE_DESC, None, 1, None, None, None, None, None)
     assert st == N.EUNSUPPORTED
     assert "1048576" in N.last_error()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_noalloc_on_a_second_device(oracle):
+    """The scratch array's address is looked up per device: a call with the second GPU current uses that GPU's copy
+    and returns the checker's selection."""
+    from ucmx import _native as N
+    rng = np.random.default_rng(73)
+    dev = "cuda:1"
+    n_slots, Hkv, D = 1500, 8, 128
+    reps16 = H.randn_bf16(rng, (n_slots, Hkv * D), 0.09)
+    counts = [400, 31, 270]
+    off = H.ragged_offsets(counts)
+    total = int(off[-1])
+    slots = rng.integers(0, n_slots, total).astype(np.int32)
+    q = H.bf16_to_f32(H.randn_bf16(rng, (3, Hkv * D)))
+    ks = np.array([40, 4, 27], np.int32)
+    koff = H.ragged_offsets(ks)
+    with torch.cuda.device(dev):
+        to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)   # noqa: E731
+        reps = to(reps16.view(np.int16)).view(torch.bfloat16)
+        d_off, d_slots, d_q, d_k, d_koff = to(off), to(slots), to(q), to(ks), to(koff)
+        idx = torch.full((int(ks.sum()),), -7, dtype=torch.int32, device=dev)
+        sc = torch.zeros((int(ks.sum()),), dtype=torch.float32, device=dev)
+        cnt = torch.zeros((3,), dtype=torch.int32, device=dev)
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        st = N.lib.ucmx_retrieve_topk_noalloc(_ptr(reps), N.DT_BF16, n_slots, Hkv, 1, D, _ptr(d_off), _ptr(d_slots),
+                                              _ptr(d_q), 3, total, 1.0, _ptr(d_k), 0, 0, N.WIN_NONE, N.ORDER_SCORE_DESC,
+                                              _ptr(d_slots), int(ks.max()), _ptr(d_koff), _ptr(idx), _ptr(sc), _ptr(cnt),
+                                              stream)
+        assert st == N.OK, N.last_error()
+        torch.cuda.synchronize(dev)
+    assert cnt.cpu().tolist() == [40, 4, 27]
+    ref = oracle.score_dot_esa(H.bf16_to_f32(reps16), off, slots, q)
+    got = idx.cpu().numpy()
+    for r in range(3):
+        want_ids, _ = oracle.topk_esa(ref[off[r]:off[r + 1]], int(ks[r]), slots[off[r]:off[r + 1]])
+        assert np.array_equal(np.sort(got[koff[r]:koff[r + 1]]), np.sort(want_ids))

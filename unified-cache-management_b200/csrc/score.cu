@@ -634,6 +634,74 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
     }
 }
 
+// The same for the shape GSA uses - bf16, 128 channels per head, a power-of-two number of representatives - with
+// the whole row in flight at once: a vector of 128 bf16 is 16 lanes of 16 bytes, so a warp-wide load brings two
+// vectors (for two representatives per head: both representatives of one head), NV = H * n_rep / 2 loads bring the
+// row, and all of them are requested before the first is used.  Each half-warp reduces its vector's dot product
+// (four shuffle steps); the best of a head's representatives is a maximum over the head's loads and, last, over
+// the two halves.  Slot ids are read a candidate ahead.
+template <int NV, int R>
+__global__ void __launch_bounds__(kScoreThreads) score_dot_reps_kernel(ScoreGenParams p)
+{
+    static_assert(R >= 2 && (R & (R - 1)) == 0, "representatives per head: a power of two, at least 2");
+    constexpr int kLoadsPerHead = R / 2;
+    constexpr int kHeads = NV / kLoadsPerHead;
+    const int lane = threadIdx.x & 31, half = lane >> 4, pc = lane & 15;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int64_t W = (int64_t)gridDim.x * warps_per_cta;
+    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int begin = (int)((int64_t)p.total * w / W);
+    const int end = (int)((int64_t)p.total * (w + 1) / W);
+    if (begin >= end) return;
+    const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
+    constexpr size_t kRowBytes = (size_t)NV * 512;
+    int slot_next = checked_slot(p.slot_ids, begin, p.n_slots, p.err);
+    int r = find_request(p.offsets, p.n_req, begin);
+    int r_end = __ldg(p.offsets + r + 1);
+    for (int c = begin; c < end; ++c) {
+        const int slot = slot_next;
+        if (c + 1 < end) slot_next = checked_slot(p.slot_ids, c + 1, p.n_slots, p.err);
+        if (slot < 0) {
+            if (lane == 0) p.out[c] = -INFINITY;
+            continue;
+        }
+        uint4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] = ld_stream16(base + (size_t)slot * kRowBytes + (size_t)i * 512 + (size_t)lane * 16);
+        while (c >= r_end) {
+            ++r;
+            r_end = __ldg(p.offsets + r + 1);
+        }
+        const float* qr = p.q + (int64_t)r * kHeads * 128 + pc * 8;
+        float total = 0.0f;
+#pragma unroll
+        for (int h = 0; h < kHeads; ++h) {
+            const float4 q0 = __ldg(reinterpret_cast<const float4*>(qr + h * 128));
+            const float4 q1 = __ldg(reinterpret_cast<const float4*>(qr + h * 128) + 1);
+            float best = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kLoadsPerHead; ++j) {
+                const uint4 x = v[h * kLoadsPerHead + j];
+                float acc = q0.x * bf16lo(x.x);
+                acc = fmaf(q0.y, bf16hi(x.x), acc);
+                acc = fmaf(q0.z, bf16lo(x.y), acc);
+                acc = fmaf(q0.w, bf16hi(x.y), acc);
+                acc = fmaf(q1.x, bf16lo(x.z), acc);
+                acc = fmaf(q1.y, bf16hi(x.z), acc);
+                acc = fmaf(q1.z, bf16lo(x.w), acc);
+                acc = fmaf(q1.w, bf16hi(x.w), acc);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                best = fmaxf(best, acc);
+            }
+            best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 16));
+            total += best;
+        }
+        if (lane == 0) p.out[c] = total * p.scale;
+        (void)half;
+    }
+}
+
 // Launch geometry of the ring kernel: one resident wave of `ctas_per_sm` thread blocks of 8 warps per SM, the
 // shared memory of an SM split evenly between the warps' rings.
 struct RingGeometry {
@@ -911,6 +979,24 @@ int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, in
         set_last_text("score_dot: the peer exchange is available for one representative per head and rows of 32-256 bytes "
                       "or a multiple of 512 bytes up to 4 KiB (bf16) / 8 KiB (fp32)");
         return UCMX_EUNSUPPORTED;
+    }
+    if (reps_dtype == UCMX_DT_BF16 && head_dim == 128) {
+        // GSA's shapes: the whole row in flight (see score_dot_reps_kernel)
+        int64_t g4 = (int64_t)sm_count() * 4;          // four thread blocks of 8 warps per SM: 128 KiB of rows in flight
+        const int64_t want4 = ((int64_t)total + 7) / 8;
+        const int grid2 = (int)(g4 < want4 ? g4 : (want4 < 1 ? 1 : want4));
+        bool done = true;
+        if (n_rep == 2 && n_kv_heads == 8) score_dot_reps_kernel<8, 2><<<grid2, kScoreThreads, 0, st>>>(g);
+        else if (n_rep == 2 && n_kv_heads == 4) score_dot_reps_kernel<4, 2><<<grid2, kScoreThreads, 0, st>>>(g);
+        else if (n_rep == 2 && n_kv_heads == 2) score_dot_reps_kernel<2, 2><<<grid2, kScoreThreads, 0, st>>>(g);
+        else if (n_rep == 2 && n_kv_heads == 1) score_dot_reps_kernel<1, 2><<<grid2, kScoreThreads, 0, st>>>(g);
+        else if (n_rep == 4 && n_kv_heads == 8) score_dot_reps_kernel<16, 4><<<grid2, kScoreThreads, 0, st>>>(g);
+        else if (n_rep == 4 && n_kv_heads == 4) score_dot_reps_kernel<8, 4><<<grid2, kScoreThreads, 0, st>>>(g);
+        else done = false;
+        if (done) {
+            UCMX_LAUNCH_CHECK("score_dot_reps_kernel");
+            return UCMX_OK;
+        }
     }
     const int warps_per_cta = kScoreThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;

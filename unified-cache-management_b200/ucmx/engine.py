@@ -45,7 +45,7 @@ class DecodeRetrievalEngine:
         self.peer_exchange = peer_exchange
         self.order = ops.ORDER_INDEX_ASC if delta else order
         self.delta = delta
-        self.overlap = bool(overlap) and with_kv_pool and not delta
+        self.overlap = bool(overlap) and with_kv_pool
         self._select_stream = torch.cuda.Stream(device=device) if self.overlap else None
         i32 = dict(dtype=torch.int32, device=device)
         self.offsets = torch.from_numpy(batch.offsets).to(device)
