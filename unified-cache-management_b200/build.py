@@ -1,4 +1,5 @@
-"""Compile the CUDA sources under csrc/ into ucmx/_lib/libucmx.so for sm_100a.
+"""Compile the CUDA sources under csrc/ into ucmx/_lib/libucmx.so for sm_100a, and the CPython front of the
+retrieval object (csrc/pybackend.c, plain C) into ucmx/_lib/_ucmx_fast.<abi>.so.
 
 Usage: python build.py [--force] [--verbose]
 The library links the CUDA runtime statically and depends on nothing else, so the built file can
@@ -11,12 +12,15 @@ import os
 import shutil
 import subprocess
 import sys
+import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "ucmx", "_lib")
 OUT = os.path.join(OUT_DIR, "libucmx.so")
 STAMP = os.path.join(OUT_DIR, "libucmx.stamp")
+PY_SRC = os.path.join(CSRC, "pybackend.c")
+PY_OUT = os.path.join(OUT_DIR, "_ucmx_fast" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
@@ -41,6 +45,7 @@ def _digest() -> str:
     h = hashlib.sha256()
     files = _sources() + [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cuh")]
     files.append(os.path.join(INCLUDE, "ucmx.h"))
+    files.append(PY_SRC)
     for f in files:
         with open(f, "rb") as fh:
             h.update(f.encode())
@@ -50,7 +55,7 @@ def _digest() -> str:
 
 
 def up_to_date() -> bool:
-    if not (os.path.exists(OUT) and os.path.exists(STAMP)):
+    if not (os.path.exists(OUT) and os.path.exists(STAMP) and os.path.exists(PY_OUT)):
         return False
     with open(STAMP) as fh:
         return fh.read().strip() == _digest()
@@ -85,9 +90,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
     subprocess.run(link, check=True)
     for o in objs:
         os.remove(o)
+    build_python_front()
     with open(STAMP, "w") as fh:
         fh.write(_digest())
     return OUT
+
+
+def build_python_front() -> str:
+    """gcc: the CPython module that fronts ucmx_retrieval_* (no CUDA, no link against libucmx.so)."""
+    import numpy
+    cc = os.environ.get("CC") or shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        raise RuntimeError("no C compiler found (set CC)")
+    cmd = [cc, "-O2", "-fPIC", "-shared", "-Wall", "-o", PY_OUT, PY_SRC,
+           "-I", sysconfig.get_paths()["include"], "-I", numpy.get_include()]
+    subprocess.run(cmd, check=True)
+    return PY_OUT
 
 
 if __name__ == "__main__":

@@ -1,0 +1,196 @@
+/* CPython front of the retrieval object, the counterpart of the reference's pybind11 module
+ * (ucm/sparse/esa/retrieval/cpy/retrieval_backend.cpp:200-225): submit / wait / get_result with numpy arrays in and
+ * out, calling the C ABI (ucmx_retrieval_*) directly.  ESA makes three of these calls per request and layer
+ * (ucm/sparse/esa/esa.py:286-339), so what a call costs on the host is what the plug-in's retrieval costs once the
+ * GPU work is one launch per layer; through ctypes a call is 3-5 us, here well under one.
+ *
+ * The module does not link against the library: ucmx/retrieval.py hands it the addresses of the three entry points
+ * once (bind), so the C ABI stays the only boundary.  Arrays that are not plain C-contiguous float32 / int32 make
+ * submit return None; the Python side then converts and calls again.  A status other than success (all of them are
+ * negative) comes back as it is and the Python side raises what the ctypes route raises. */
+#define PY_SSIZE_T_CLEAN
+#include <Python.h>
+#define NPY_NO_DEPRECATED_API NPY_1_7_API_VERSION
+#include <numpy/arrayobject.h>
+#include <stdint.h>
+
+typedef int32_t (*submit_fn)(void*, const float*, int32_t, int32_t, int32_t, const int32_t*, int32_t, int32_t*);
+typedef int32_t (*wait_fn)(void*, int32_t);
+typedef int32_t (*get_fn)(void*, int32_t, int32_t*, float*);
+
+static submit_fn g_submit;
+static wait_fn g_wait;
+static get_fn g_get;
+
+#define SHAPE_SLOTS 8192   /* results outstanding per object; a request id maps to id % SHAPE_SLOTS */
+
+typedef struct {
+    PyObject_HEAD
+    void* handle;
+    int32_t dim;
+    struct {
+        int32_t rid, rows, k;
+    } shape[SHAPE_SLOTS];
+} FastBackend;
+
+static int fb_init(FastBackend* self, PyObject* args, PyObject* kw)
+{
+    unsigned long long h = 0;
+    int dim = 0;
+    (void)kw;
+    if (!PyArg_ParseTuple(args, "Ki", &h, &dim)) return -1;
+    self->handle = (void*)(uintptr_t)h;
+    self->dim = dim;
+    for (int i = 0; i < SHAPE_SLOTS; ++i) self->shape[i].rid = -1;
+    return 0;
+}
+
+static int plain(PyObject* o, int typenum)
+{
+    if (!PyArray_CheckExact(o)) return 0;
+    PyArrayObject* a = (PyArrayObject*)o;
+    return PyArray_TYPE(a) == typenum && PyArray_NDIM(a) == 2 && PyArray_IS_C_CONTIGUOUS(a);
+}
+
+/* submit(query float32 [b, dim], topk, indexes int32 [b, n]) -> request id (>= 0) | status (< 0) | None (convert first) */
+static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t nargs)
+{
+    if (nargs != 3) {
+        PyErr_SetString(PyExc_TypeError, "submit(query, topk, indexes)");
+        return NULL;
+    }
+    if (!g_submit) {
+        PyErr_SetString(PyExc_RuntimeError, "not bound to the library");
+        return NULL;
+    }
+    PyObject *q = args[0], *idx = args[2];
+    if (!plain(q, NPY_FLOAT32) || !plain(idx, NPY_INT32)) {
+        /* one- or three-dimensional plain arrays are shape errors, anything else is for the Python side to convert */
+        if (PyArray_CheckExact(q) && PyArray_CheckExact(idx) && PyArray_TYPE((PyArrayObject*)q) == NPY_FLOAT32 &&
+            PyArray_TYPE((PyArrayObject*)idx) == NPY_INT32 && PyArray_IS_C_CONTIGUOUS((PyArrayObject*)q) &&
+            PyArray_IS_C_CONTIGUOUS((PyArrayObject*)idx)) {
+            if (PyArray_NDIM((PyArrayObject*)q) != 2) {
+                PyErr_SetString(PyExc_RuntimeError, "Query dim mismatch");
+                return NULL;
+            }
+            PyErr_SetString(PyExc_RuntimeError, "Query and indexes batch mismatch");
+            return NULL;
+        }
+        Py_RETURN_NONE;
+    }
+    const long topk = PyLong_AsLong(args[1]);
+    if (topk == -1 && PyErr_Occurred()) return NULL;
+    PyArrayObject *qa = (PyArrayObject*)q, *ia = (PyArrayObject*)idx;
+    const npy_intp rows = PyArray_DIM(qa, 0), dim = PyArray_DIM(qa, 1), n = PyArray_DIM(ia, 1);
+    if (dim != self->dim) {
+        PyErr_SetString(PyExc_RuntimeError, "Query dim mismatch");
+        return NULL;
+    }
+    if (PyArray_DIM(ia, 0) != rows) {
+        PyErr_SetString(PyExc_RuntimeError, "Query and indexes batch mismatch");
+        return NULL;
+    }
+    int32_t rid = -1;
+    const int32_t st = g_submit(self->handle, (const float*)PyArray_DATA(qa), (int32_t)rows, (int32_t)dim, (int32_t)topk,
+                                (const int32_t*)PyArray_DATA(ia), (int32_t)n, &rid);
+    if (st != 0) return PyLong_FromLong(st < 0 ? (long)st : -1L);
+    const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
+    self->shape[slot].rid = rid;
+    self->shape[slot].rows = (int32_t)rows;
+    self->shape[slot].k = (int32_t)(topk < n ? topk : n);
+    return PyLong_FromLong(rid);
+}
+
+/* wait(req_id) -> status of ucmx_retrieval_wait (the GIL is released while the stream is waited for) */
+static PyObject* fb_wait(FastBackend* self, PyObject* arg)
+{
+    const long rid = PyLong_AsLong(arg);
+    if (rid == -1 && PyErr_Occurred()) return NULL;
+    int32_t st;
+    Py_BEGIN_ALLOW_THREADS
+    st = g_wait(self->handle, (int32_t)rid);
+    Py_END_ALLOW_THREADS
+    return PyLong_FromLong(st);
+}
+
+/* get_result(req_id) -> {"indices": int32 [b, k], "scores": float32 [b, k]} | status (an int) when it is not success |
+ * None when this object never saw the request */
+static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
+{
+    const long rid = PyLong_AsLong(arg);
+    if (rid == -1 && PyErr_Occurred()) return NULL;
+    const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
+    if (rid < 0 || self->shape[slot].rid != (int32_t)rid) Py_RETURN_NONE;
+    npy_intp dims[2] = {self->shape[slot].rows, self->shape[slot].k};
+    PyObject* indices = PyArray_SimpleNew(2, dims, NPY_INT32);
+    PyObject* scores = PyArray_SimpleNew(2, dims, NPY_FLOAT32);
+    if (!indices || !scores) {
+        Py_XDECREF(indices);
+        Py_XDECREF(scores);
+        return NULL;
+    }
+    const int32_t st = g_get(self->handle, (int32_t)rid, (int32_t*)PyArray_DATA((PyArrayObject*)indices),
+                             (float*)PyArray_DATA((PyArrayObject*)scores));
+    if (st != 0) {
+        Py_DECREF(indices);
+        Py_DECREF(scores);
+        return PyLong_FromLong(st);
+    }
+    self->shape[slot].rid = -1;
+    PyObject* d = PyDict_New();
+    if (!d || PyDict_SetItemString(d, "indices", indices) < 0 || PyDict_SetItemString(d, "scores", scores) < 0) {
+        Py_XDECREF(d);
+        d = NULL;
+    }
+    Py_DECREF(indices);
+    Py_DECREF(scores);
+    return d;
+}
+
+static PyMethodDef fb_methods[] = {
+    {"submit", (PyCFunction)(void (*)(void))fb_submit, METH_FASTCALL, "submit(query, topk, indexes)"},
+    {"wait", (PyCFunction)fb_wait, METH_O, "wait(req_id) -> status"},
+    {"get_result", (PyCFunction)fb_get_result, METH_O, "get_result(req_id)"},
+    {NULL, NULL, 0, NULL}};
+
+static PyTypeObject FastBackendType = {
+    PyVarObject_HEAD_INIT(NULL, 0).tp_name = "_ucmx_fast.Backend",
+    .tp_basicsize = sizeof(FastBackend),
+    .tp_flags = Py_TPFLAGS_DEFAULT,
+    .tp_new = PyType_GenericNew,
+    .tp_init = (initproc)fb_init,
+    .tp_methods = fb_methods,
+};
+
+/* bind(submit_address, wait_address, get_result_address): the entry points of the loaded library */
+static PyObject* mod_bind(PyObject* self, PyObject* args)
+{
+    unsigned long long a = 0, b = 0, c = 0;
+    (void)self;
+    if (!PyArg_ParseTuple(args, "KKK", &a, &b, &c)) return NULL;
+    g_submit = (submit_fn)(uintptr_t)a;
+    g_wait = (wait_fn)(uintptr_t)b;
+    g_get = (get_fn)(uintptr_t)c;
+    Py_RETURN_NONE;
+}
+
+static PyMethodDef mod_methods[] = {{"bind", mod_bind, METH_VARARGS, "bind(submit, wait, get_result addresses)"},
+                                    {NULL, NULL, 0, NULL}};
+
+static struct PyModuleDef moddef = {PyModuleDef_HEAD_INIT, "_ucmx_fast", "CPython front of ucmx_retrieval_*", -1, mod_methods,
+                                    NULL, NULL, NULL, NULL};
+
+PyMODINIT_FUNC PyInit__ucmx_fast(void)
+{
+    import_array();
+    if (PyType_Ready(&FastBackendType) < 0) return NULL;
+    PyObject* m = PyModule_Create(&moddef);
+    if (!m) return NULL;
+    Py_INCREF(&FastBackendType);
+    if (PyModule_AddObject(m, "Backend", (PyObject*)&FastBackendType) < 0) {
+        Py_DECREF(&FastBackendType);
+        Py_DECREF(m);
+        return NULL;
+    }
+    return m;
+}

@@ -9,14 +9,37 @@ collected (or on flush()).  poll() is an event query.
 Host arrays in, host arrays out: submit copies the query and the index matrix to the device,
 get_result returns numpy arrays, exactly like the pybind11 module it replaces.  Errors the
 reference raises as std::runtime_error surface as RuntimeError with the same text.
+
+submit / wait / get_result - three calls per request and layer in ESA's pattern - go through a small
+CPython module (csrc/pybackend.c, built beside the library) that calls the C ABI directly; the other
+methods go through ctypes.
 """
 from __future__ import annotations
 
 import ctypes as C
+import importlib.util
+import os
 
 import numpy as np
 
 from . import _native as N
+
+
+def _load_fast():
+    """The CPython front of ucmx_retrieval_* (built by build.py next to libucmx.so), bound to the loaded library."""
+    lib_dir = os.path.dirname(N.LIB_PATH)
+    names = [f for f in os.listdir(lib_dir) if f.startswith("_ucmx_fast") and f.endswith(".so")] if os.path.isdir(lib_dir) else []
+    if not names:
+        raise ImportError(f"_ucmx_fast is missing from {lib_dir}: run unified-cache-management_b200/build.py")
+    spec = importlib.util.spec_from_file_location("_ucmx_fast", os.path.join(lib_dir, sorted(names)[0]))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    addr = lambda fn: C.cast(fn, C.c_void_p).value   # noqa: E731
+    mod.bind(addr(N.lib.ucmx_retrieval_submit), addr(N.lib.ucmx_retrieval_wait), addr(N.lib.ucmx_retrieval_get_result))
+    return mod
+
+
+_fast = _load_fast()
 
 
 class RetrievalWorkerBackend:
@@ -34,24 +57,24 @@ class RetrievalWorkerBackend:
         st = N.lib.ucmx_retrieval_create(arr.ctypes.data_as(C.c_void_p), self.n_items, self.dim, dt, device,
                                          C.byref(self._h))
         N.check("ucmx_retrieval_create", st, 0)
-        self._shapes = {}                      # request id -> (rows, k) of its result
+        self._fb = _fast.Backend(self._h.value, self.dim)
+        self._fsubmit, self._fwait, self._fget = self._fb.submit, self._fb.wait, self._fb.get_result
 
     # -- the reference's four methods -------------------------------------------------------------
     def submit(self, query, topk: int, indexes) -> int:
-        # arrays that are already what the C side reads (the common case) go through untouched
-        q = query if _is_plain(query, np.float32) else np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
-        idx = indexes if _is_plain(indexes, np.int32) else np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
-        if q.ndim != 2 or q.shape[1] != self.dim:
-            raise RuntimeError("Query dim mismatch")
-        if idx.ndim != 2 or idx.shape[0] != q.shape[0]:
-            raise RuntimeError("Query and indexes batch mismatch")
-        rid = C.c_int32(-1)
-        st = _submit(self._h, q.__array_interface__["data"][0], q.shape[0], q.shape[1], int(topk),
-                     idx.__array_interface__["data"][0], idx.shape[1], C.byref(rid))
-        if st != N.OK:
-            N.check("ucmx_retrieval_submit", st, 0)
-        self._shapes[rid.value] = (q.shape[0], min(int(topk), idx.shape[1]))
-        return rid.value
+        rid = self._fsubmit(query, topk, indexes)
+        if rid is None:
+            # not plain C-contiguous float32 / int32 arrays: convert, then the same call
+            q = np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
+            idx = np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
+            if q.ndim != 2 or q.shape[1] != self.dim:
+                raise RuntimeError("Query dim mismatch")
+            if idx.ndim != 2 or idx.shape[0] != q.shape[0]:
+                raise RuntimeError("Query and indexes batch mismatch")
+            rid = self._fsubmit(q, int(topk), idx)
+        if rid < 0:
+            N.check("ucmx_retrieval_submit", rid, 0)
+        return rid
 
     def flush(self) -> None:
         """Send everything submitted so far to the GPU now (otherwise the first poll/wait/get_result does it)."""
@@ -63,25 +86,20 @@ class RetrievalWorkerBackend:
         return bool(ready.value)
 
     def wait(self, req_id: int) -> None:
-        st = _wait(self._h, req_id)
-        if st == N.ENOOBJ:
-            raise RuntimeError("Bad req_id")
-        if st != N.OK:
+        st = self._fwait(req_id)
+        if st:
+            if st == N.ENOOBJ:
+                raise RuntimeError("Bad req_id")
             N.check("ucmx_retrieval_wait", st, 0)
 
     def get_result(self, req_id: int) -> dict:
-        shape = self._shapes.get(req_id)
-        if shape is None:
+        res = self._fget(req_id)
+        if type(res) is dict:
+            return res
+        if res is None or res == N.ENOOBJ:
             raise RuntimeError("Result not ready")
-        indices = np.empty(shape, np.int32)
-        scores = np.empty(shape, np.float32)
-        st = _get(self._h, req_id, indices.__array_interface__["data"][0], scores.__array_interface__["data"][0])
-        if st == N.ENOOBJ:
-            raise RuntimeError("Result not ready")
-        del self._shapes[req_id]
-        if st != N.OK:
-            N.check("ucmx_retrieval_get_result", st, 0)
-        return {"indices": indices, "scores": scores}
+        N.check("ucmx_retrieval_get_result", res, 0)
+        raise RuntimeError("Result not ready")
 
     # -- additions ---------------------------------------------------------------------------------
     def update_rows(self, slots, rows) -> None:
@@ -115,15 +133,6 @@ class RetrievalWorkerBackend:
             self.close()
         except Exception:
             pass
-
-
-_submit = N.lib.ucmx_retrieval_submit
-_wait = N.lib.ucmx_retrieval_wait
-_get = N.lib.ucmx_retrieval_get_result
-
-
-def _is_plain(x, dtype) -> bool:
-    return type(x) is np.ndarray and x.dtype == dtype and x.flags.c_contiguous
 
 
 def _as_numpy(x):
