@@ -121,18 +121,25 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+// sixteen accumulator columns of this thread's row, without waiting for them ...
+__device__ __forceinline__ void tmem_ld16_start(uint32_t taddr, uint32_t (&v)[16])
 {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// ... and the wait for everything started so far.  The registers are passed through the wait so that no use of them
+// can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld16_wait(uint32_t (&v)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                   "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
 }
 
 // byte offset of element (row, k) inside a [128 x 128] bf16 K-major tile stored as two swizzled halves
@@ -140,22 +147,6 @@ __device__ __forceinline__ uint32_t sw_offset(int row, int k)
 {
     const int half = k >> 6, c = (k & 63) >> 3;
     return (uint32_t)(half * kHalfBytes + row * 128 + ((c ^ (row & 7)) << 4) + ((k & 7) << 1));
-}
-
-// output row of tile row m, or -1 when that vector's code is not stored
-__device__ __forceinline__ int64_t out_row_of(const TcParams& p, int64_t tile, int m)
-{
-    if (p.paged) {
-        const int64_t blk = tile / p.tiles_per_block;
-        const int sub = (int)(tile - blk * p.tiles_per_block);
-        const int id = checked_block_id(p.ids, blk, p.cache_blocks, p.err);
-        const int64_t slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, p.err);
-        const int t = sub * (kTileM / p.H) + m / p.H, h = m % p.H;
-        if (id < 0 || slot < 0) return -1;
-        return p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
-    }
-    const int64_t v = tile * kTileM + m;
-    return v < p.n_vec ? v : -1;
 }
 
 struct alignas(8) Barriers {
@@ -403,8 +394,51 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         // ------------------------------------------------------------------ epilogue: signs, margin test, exact fallback
         const int q = warp & 3;                  // the TMEM lane quarter this warp may read
         const int m = q * 32 + lane;             // tile row = vector
+        // Paged: which list entry and which tile of its block a tile is, advanced without divisions; the entry's cache
+        // block and code-table row group are asked for one tile ahead, so the stores at the end of a tile never wait.
+        int tok = 0, h = 0, blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0, nxt_slot = 0;
+        if (p.paged) {
+            tok = m / p.H;
+            h = m - tok * p.H;
+            blk = (int)(first / p.tiles_per_block);
+            sub = (int)(first - (int64_t)blk * p.tiles_per_block);
+            step_blk = (int)(stride / p.tiles_per_block);
+            step_sub = (int)(stride - (int64_t)step_blk * p.tiles_per_block);
+            if (my_tiles > 0) {
+                nxt_id = __ldg(p.ids + blk);
+                nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
+            }
+        }
         for (int64_t it = 0; it < my_tiles; ++it) {
             const int s = (int)(it % kStagesA), a = (int)(it & 1);
+            int64_t orow;                         // where this row's code goes (-1: nowhere)
+            if (p.paged) {
+                int id = nxt_id;
+                int64_t slot = nxt_slot;
+                if (id >= 0 && (int64_t)id >= p.cache_blocks) {
+                    if (p.err) atomicExch(p.err, 3);
+                    id = -1;
+                }
+                if (slot >= 0 && slot >= p.out_rows) {
+                    if (p.err) atomicExch(p.err, 3);
+                    slot = -1;
+                }
+                const int tk = sub * (kTileM / p.H) + tok;
+                orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + tk : (slot * p.T + tk) * p.H + h;
+                sub += step_sub;
+                blk += step_blk;
+                if (sub >= p.tiles_per_block) {
+                    sub -= p.tiles_per_block;
+                    ++blk;
+                }
+                if (it + 1 < my_tiles) {
+                    nxt_id = __ldg(p.ids + blk);
+                    nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
+                }
+            } else {
+                const int64_t v = (first + it * stride) * kTileM + m;
+                orow = v < p.n_vec ? v : -1;
+            }
             if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it >> 1) & 1))) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 1);
@@ -453,33 +487,45 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 thr = any ? INFINITY : -1.0f;
                 keep = any ? 0xffffffffu : 0u;
             }
+            // The accumulator comes in eight pieces of sixteen columns, the next one on its way while the signs and
+            // margins of the one at hand are worked out (what a warp waits for here is the round trip to tensor
+            // memory, not the arithmetic).
+            // Sign bits: shift each accumulator's sign into a word, highest column first (one funnel shift per value).
+            // A set sign bit means "not positive"; an exact zero has a clear sign bit but is below any threshold, so
+            // it is settled by the exact chain like every doubtful bit.  Then the smallest magnitude of each group
+            // of eight columns (one min per value): only groups that dip under the threshold are looked at column
+            // by column.
             uint32_t code[4], doubt[4];
+            {
+                uint32_t v[2][16];
+                const uint32_t acc_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kBits);
+                tmem_ld16_start(acc_addr + 7 * 16, v[1]);       // pieces are taken from the highest column down
+                uint32_t neg = 0, unsure = 0;
 #pragma unroll
-            for (int cw = 0; cw < 4; ++cw) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kBits + cw * 32), v);
-                // Sign bits: shift each accumulator's sign into a word, highest column first (one funnel
-                // shift per value).  A set sign bit means "not positive"; an exact zero has a clear sign bit
-                // but is below any threshold, so it is settled by the exact chain like every doubtful bit.
-                uint32_t neg = 0;
+                for (int pc = 7; pc >= 0; --pc) {
+                    uint32_t (&cur)[16] = v[pc & 1];
+                    tmem_ld16_wait(cur);
+                    if (pc > 0) tmem_ld16_start(acc_addr + (pc - 1) * 16, v[(pc - 1) & 1]);
 #pragma unroll
-                for (int j = 31; j >= 0; --j) neg = __funnelshift_l(v[j], neg, 1);
-                // Smallest magnitude of each group of eight columns (one min per value); only groups that
-                // dip under the threshold are looked at column by column.
-                uint32_t unsure = 0;
+                    for (int j = 15; j >= 0; --j) neg = __funnelshift_l(cur[j], neg, 1);
 #pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {
-                    float mn = fabsf(__uint_as_float(v[g8 * 8]));
+                    for (int g8 = 0; g8 < 2; ++g8) {
+                        float mn = fabsf(__uint_as_float(cur[g8 * 8]));
 #pragma unroll
-                    for (int j = 1; j < 8; ++j) mn = fminf(mn, fabsf(__uint_as_float(v[g8 * 8 + j])));
-                    if (mn <= thr) {
+                        for (int j = 1; j < 8; ++j) mn = fminf(mn, fabsf(__uint_as_float(cur[g8 * 8 + j])));
+                        if (mn <= thr) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            unsure |= (fabsf(__uint_as_float(v[g8 * 8 + j])) <= thr ? 1u : 0u) << (g8 * 8 + j);
+                            for (int j = 0; j < 8; ++j)
+                                unsure |= (fabsf(__uint_as_float(cur[g8 * 8 + j])) <= thr ? 1u : 0u) << ((pc & 1) * 16 + g8 * 8 + j);
+                        }
+                    }
+                    if ((pc & 1) == 0) {                        // a 32-bit word of the code is complete
+                        code[pc >> 1] = ~neg & keep;
+                        doubt[pc >> 1] = unsure;
+                        neg = 0;
+                        unsure = 0;
                     }
                 }
-                code[cw] = ~neg & keep;
-                doubt[cw] = unsure;
             }
             // the accumulator is read: hand it back to the MMA warp
             tc_fence_before();
@@ -591,19 +637,10 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     __syncwarp();
                 }
             }
-            // store the settled words of the code, then tell the fixer, which releases the stage when it has
-            // what it needs of the tile
-            const int64_t orow = out_row_of(p, first + it * stride, m);
-            if (orow >= 0) {
-                if (queued && (doubt[0] | doubt[1] | doubt[2] | doubt[3])) {
-                    uint32_t* o32 = reinterpret_cast<uint32_t*>(p.out + orow * 16);
-#pragma unroll
-                    for (int cw = 0; cw < 4; ++cw)
-                        if (!doubt[cw]) o32[cw] = code[cw];
-                } else {
-                    *reinterpret_cast<uint4*>(p.out + orow * 16) = make_uint4(code[0], code[1], code[2], code[3]);
-                }
-            }
+            // store the code, then tell the fixer, which releases the stage when it has what it needs of the tile
+            // (a word the fixer still has to settle is stored as it stands; the fixer's store comes after the barrier
+            // below and therefore after this one)
+            if (orow >= 0) *reinterpret_cast<uint4*>(p.out + orow * 16) = make_uint4(code[0], code[1], code[2], code[3]);
             mbar_arrive(&bars->fix_ready[s]);
         }
     }
