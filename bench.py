@@ -494,6 +494,8 @@ def run_tp_long(args, rank, world, local_rank, dev, barrier, *, layers, steps, w
                "allreduce": ("fused into the scoring and top-k kernels over peer memory" if peer is not None
                              else ("nccl all_reduce between the kernels" if world > 1 else "none")),
                "cuda_graph": use_graph, "order": "block position ascending", **stages,
+               "stage_times_note": "launched call by call with an event pair each: every stage time includes the host's launch "
+                                   "latency (10-40 us), which the replayed step does not pay",
                "scored_tokens_per_s": eng.tokens_scored_per_step() / (ms * 1e-3),
                "gather_gbs": eng.bytes_gather_layer() / (stages["gather_us"] * 1e-6) / 1e9,
                "tp_selection_identical": identical, "agreement_with_nccl_route": agree, "device_error": err}
