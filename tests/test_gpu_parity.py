@@ -489,7 +489,8 @@ def test_score_dot_heads_matches_checker_and_reference(ops, oracle):
     np.testing.assert_allclose(one * 8, esa, rtol=0, atol=0.06)      # esa rounds the group mean of q to bf16 (values ~ +-10)
 
 
-@pytest.mark.parametrize("Hq,Hkv,D,R", [(8, 8, 128, 2), (64, 8, 128, 1), (4, 2, 64, 5), (32, 1, 32, 3)])
+@pytest.mark.parametrize("Hq,Hkv,D,R", [(8, 8, 128, 2), (64, 8, 128, 1), (4, 2, 64, 5), (32, 1, 32, 3), (32, 8, 128, 2), (16, 4, 128, 4),
+                                        (8, 1, 128, 2), (64, 8, 128, 4), (16, 8, 128, 2)])
 def test_score_dot_heads_shapes(ops, oracle, Hq, Hkv, D, R):
     rng = np.random.default_rng(Hq * 131 + R)
     n_slots = 50

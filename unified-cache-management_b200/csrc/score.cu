@@ -1096,6 +1096,97 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_heads_kernel(ScoreHea
     }
 }
 
+// The same weights for the shapes GSA runs with - 128 channels per head, 2 or 4 representatives - with the whole row in
+// flight (as in score_dot_reps_kernel): a warp-wide load brings two representative vectors, one per half-warp, and
+// each half-warp takes the dot products of its vector with the G query heads of the KV head at hand (the query rows
+// come from L1: a warp's candidates belong to one request for long stretches).
+template <int NV, int R, int G>
+__global__ void __launch_bounds__(kScoreThreads) score_dot_heads_rows_kernel(ScoreHeadsParams p)
+{
+    constexpr int kLoadsPerHead = R / 2;
+    constexpr int kHeads = NV / kLoadsPerHead;
+    const int lane = threadIdx.x & 31, pc = lane & 15;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int64_t W = (int64_t)gridDim.x * warps_per_cta;
+    const int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int begin = (int)((int64_t)p.total * w / W);
+    const int end = (int)((int64_t)p.total * (w + 1) / W);
+    if (begin >= end) return;
+    const unsigned char* base = reinterpret_cast<const unsigned char*>(p.reps);
+    constexpr size_t kRowBytes = (size_t)NV * 512;
+    const float inv = 1.0f / (float)(kHeads * G);
+    int slot_next = checked_slot(p.slot_ids, begin, p.n_slots, p.err);
+    int r = find_request(p.offsets, p.n_req, begin);
+    int r_end = __ldg(p.offsets + r + 1);
+    for (int c = begin; c < end; ++c) {
+        const int slot = slot_next;
+        if (c + 1 < end) slot_next = checked_slot(p.slot_ids, c + 1, p.n_slots, p.err);
+        if (slot < 0) {
+            if (lane == 0) p.out[c] = -INFINITY;
+            continue;
+        }
+        uint4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] = ld_stream16(base + (size_t)slot * kRowBytes + (size_t)i * 512 + (size_t)lane * 16);
+        while (c >= r_end) {
+            ++r;
+            r_end = __ldg(p.offsets + r + 1);
+        }
+        const uint16_t* qr = p.q + (int64_t)r * p.q_stride + pc * 8;
+        float total = 0.0f;
+#pragma unroll
+        for (int h = 0; h < kHeads; ++h) {
+            float best[G];
+            uint4 qv[G];
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                qv[gi] = __ldg(reinterpret_cast<const uint4*>(qr + (size_t)(h * G + gi) * 128));
+                best[gi] = -INFINITY;
+            }
+#pragma unroll
+            for (int j = 0; j < kLoadsPerHead; ++j) {
+                const uint4 x = v[h * kLoadsPerHead + j];
+                const float x0 = bf16lo(x.x), x1 = bf16hi(x.x), x2 = bf16lo(x.y), x3 = bf16hi(x.y);
+                const float x4 = bf16lo(x.z), x5 = bf16hi(x.z), x6 = bf16lo(x.w), x7 = bf16hi(x.w);
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    float acc = bf16lo(qv[gi].x) * x0;
+                    acc = fmaf(bf16hi(qv[gi].x), x1, acc);
+                    acc = fmaf(bf16lo(qv[gi].y), x2, acc);
+                    acc = fmaf(bf16hi(qv[gi].y), x3, acc);
+                    acc = fmaf(bf16lo(qv[gi].z), x4, acc);
+                    acc = fmaf(bf16hi(qv[gi].z), x5, acc);
+                    acc = fmaf(bf16lo(qv[gi].w), x6, acc);
+                    acc = fmaf(bf16hi(qv[gi].w), x7, acc);
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    best[gi] = fmaxf(best[gi], acc);
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) total += fmaxf(best[gi], __shfl_xor_sync(0xffffffffu, best[gi], 16));
+        }
+        if (lane == 0) {
+            float wgt = total * inv;
+            if (p.include_mask && __ldg(p.include_mask + c)) wgt = INFINITY;
+            if (p.exclude_mask && __ldg(p.exclude_mask + c)) wgt = -INFINITY;
+            p.out[c] = wgt;
+        }
+    }
+}
+
+template <int NV, int R>
+bool launch_heads_rows(const ScoreHeadsParams& p, int g, int grid, cudaStream_t st)
+{
+    switch (g) {
+        case 1: score_dot_heads_rows_kernel<NV, R, 1><<<grid, kScoreThreads, 0, st>>>(p); return true;
+        case 2: score_dot_heads_rows_kernel<NV, R, 2><<<grid, kScoreThreads, 0, st>>>(p); return true;
+        case 4: score_dot_heads_rows_kernel<NV, R, 4><<<grid, kScoreThreads, 0, st>>>(p); return true;
+        case 8: score_dot_heads_rows_kernel<NV, R, 8><<<grid, kScoreThreads, 0, st>>>(p); return true;
+        default: return false;
+    }
+}
+
 }  // namespace
 }  // namespace ucmx
 
@@ -1135,6 +1226,22 @@ extern "C" int32_t ucmx_score_dot_heads(const void* reps, int64_t n_slots, int32
     p.D = head_dim;
     const int warps_per_cta = kScoreThreads / 32;
     int64_t want = ((int64_t)total + warps_per_cta - 1) / warps_per_cta;
+    if (head_dim == 128 && (query_stride % 8) == 0 && !((uintptr_t)reps & 15) && !((uintptr_t)query & 15)) {
+        // GSA's shapes: the whole row in flight
+        const int64_t cap4 = (int64_t)sm_count() * 3;
+        const int grid = (int)(want > cap4 ? cap4 : want);
+        bool done = false;
+        if (n_rep == 2 && n_kv_heads == 8) done = launch_heads_rows<8, 2>(p, g, grid, (cudaStream_t)stream);
+        else if (n_rep == 2 && n_kv_heads == 4) done = launch_heads_rows<4, 2>(p, g, grid, (cudaStream_t)stream);
+        else if (n_rep == 2 && n_kv_heads == 2) done = launch_heads_rows<2, 2>(p, g, grid, (cudaStream_t)stream);
+        else if (n_rep == 2 && n_kv_heads == 1) done = launch_heads_rows<1, 2>(p, g, grid, (cudaStream_t)stream);
+        else if (n_rep == 4 && n_kv_heads == 8) done = launch_heads_rows<16, 4>(p, g, grid, (cudaStream_t)stream);
+        else if (n_rep == 4 && n_kv_heads == 4) done = launch_heads_rows<8, 4>(p, g, grid, (cudaStream_t)stream);
+        if (done) {
+            UCMX_LAUNCH_CHECK("score_dot_heads_rows_kernel");
+            return UCMX_OK;
+        }
+    }
     const int64_t cap = (int64_t)sm_count() * 8;
     score_dot_heads_kernel<<<(int)(want > cap ? cap : want), kScoreThreads, 0, (cudaStream_t)stream>>>(p);
     UCMX_LAUNCH_CHECK("score_dot_heads_kernel");
