@@ -267,20 +267,23 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
         UCMX_LAUNCH_CHECK("xfer_plain_kernel");
         return UCMX_OK;
     }
-    // Measured: the same 24 chunks of 8 KiB in flight per SM either way, as two CTAs with rings of twelve for slices
-    // of 128 KiB and more (256 KiB: 6.7 TB/s against 6.0) and as three CTAs with rings of eight for smaller ones
-    // (32 KiB: 6.5 TB/s against 6.1; 64 KiB: 6.7 against 6.4).
+    // Two thread blocks per SM with rings of seven 8 KiB chunks.  Alone, a gather runs as fast with anything from 2 x 5
+    // to 2 x 12 chunks per SM (6.5-6.6 TB/s for slices of 64 and 256 KiB, 6.1-6.3 for 32 KiB), and three blocks of eight
+    // are a little faster still for 64 KiB slices; inside a decode step the small footprint wins by far, because it
+    // leaves more than half of an SM's shared memory to the scoring and top-k kernels of the next layer, which then
+    // run beside the gather instead of between two gathers (measured per layer, next layer's selection on a second
+    // stream: 32 KiB slices 334 us against 369 with 3 x 8; 64 KiB 664 against 724; 256 KiB 9.79 ms per 32-layer step
+    // against 9.91 with 2 x 12).  Four chunks per block are too few (10.4 ms).
     constexpr int k_chunk = 8192;
-    const bool large = p.slice_bytes >= 131072;
-    const int k_stages = large ? 12 : 8;
-    const int k_per_sm = large ? 2 : 3;
+    constexpr int k_stages = 7;
+    constexpr int k_per_sm = 2;
     p.chunk_bytes = k_chunk;
     if (p.slice_bytes < p.chunk_bytes) p.chunk_bytes = (int32_t)p.slice_bytes;
     p.chunks_per_slice = (int32_t)((p.slice_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
     p.items = p.n * (p.mode == 1 ? 1 : p.n_planes) * p.chunks_per_slice;
     const size_t smem = 128 + (size_t)k_stages * p.chunk_bytes;
     if (smem > 220 * 1024) return UCMX_EUNSUPPORTED;
-    void (*kern)(XferParams) = k_stages == 12 ? xfer_bulk_kernel<12> : xfer_bulk_kernel<8>;
+    void (*kern)(XferParams) = xfer_bulk_kernel<k_stages>;
     UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int ctas_per_sm = k_per_sm;
     while (ctas_per_sm > 1 && (size_t)ctas_per_sm * (smem + 1024) > 227 * 1024) --ctas_per_sm;
