@@ -9,12 +9,12 @@ pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 
 
-def make_engine():
+def make_engine(overlap=False):
     from ucmx.engine import DecodeRetrievalEngine
     from ucmx.workloads import KvShape, ragged_decode_batch
     shape = KvShape(n_q_heads=32, n_kv_heads=8, head_dim=128, block_tokens=128, n_layers=3)
     batch = ragged_decode_batch(seed=31, n_req=6, min_ctx=2048, max_ctx=8192, ratio=0.1, min_k=4)
-    return DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=True)
+    return DecodeRetrievalEngine(shape, batch, DEV, with_kv_pool=True, overlap=overlap)
 
 
 def test_selection_on_a_second_stream_changes_nothing():
@@ -44,8 +44,9 @@ def test_selection_on_a_second_stream_changes_nothing():
     assert _native.device_error() == 0
 
 
-def test_host_step_and_its_graph_match_the_device_step():
-    eng = make_engine()
+@pytest.mark.parametrize("overlap", [False, True])
+def test_host_step_and_its_graph_match_the_device_step(overlap):
+    eng = make_engine(overlap)
     eng.make_queries()
     eng.step()
     torch.cuda.synchronize()

@@ -306,6 +306,29 @@ class DecodeRetrievalEngine:
                 self._q_ready[l].record(cs)
         if self.kv_pool is not None:
             self.pool_all_layers()
+        if self.overlap:
+            # selection on its own stream, as in all_layers: layer l+1 is scored and selected (and its ids leave for
+            # the host) while layer l's blocks move
+            side = self._select_stream
+            pooled = torch.cuda.Event()
+            pooled.record(main)
+            side.wait_event(pooled)
+            for l in range(self.L):
+                with torch.cuda.stream(side):
+                    side.wait_event(self._q_ready[l])
+                    self.score_layer(l)
+                    self.topk_layer(l)
+                    self._layer_done[l].record(side)
+                with torch.cuda.stream(cs):
+                    cs.wait_event(self._layer_done[l])
+                    self.sel_host[l].copy_(self.sel_ids[l], non_blocking=True)
+                    self.cnt_host[l].copy_(self.sel_counts[l], non_blocking=True)
+                main.wait_event(self._layer_done[l])
+                if self.kv_pool is not None:
+                    self.gather_layer(l)
+            main.wait_stream(side)
+            main.wait_stream(cs)
+            return
         for l in range(self.L):
             main.wait_event(self._q_ready[l])
             self.layer_step(l)
