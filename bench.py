@@ -720,7 +720,7 @@ def run_kernel_workload(args, dev):
                     dtype="bf16", config={"workload": "GSA scoring with two representatives per head, the 64-request ragged batch",
                                           "blocks": int(batch.total), "l2_policy": "three 137 MB tables in rotation"},
                     roofline=roofline("score_dot_reps_kernel<8 loads, 2 representatives>", nbytes, us_gen),
-                    per_head_weights={"kernel": "score_dot_heads_kernel", "us": us_heads, "gbs": nbytes / us_heads / 1e3,
+                    per_head_weights={"kernel": "score_dot_heads_rows_kernel<8 loads, 2 representatives, 4 query heads per KV head>", "us": us_heads, "gbs": nbytes / us_heads / 1e3,
                                       "frac": nbytes / us_heads / 1e3 / peak})
     elif name == "kvstar":
         Mp, dp, xq, Hq = 64, 32, 8, shape.n_q_heads
