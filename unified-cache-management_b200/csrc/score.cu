@@ -21,8 +21,8 @@ namespace {
 constexpr int kScoreThreads = 256;
 constexpr int kMaxRingStages = 16;
 constexpr int kMaxSmemOffsets = 2049;        // request offsets kept in shared memory (more requests: read from global)
-constexpr int kRingSmemPerSm = 200 * 1024;   // shared memory the row rings of one SM may take
-constexpr int kRingStages = 4;               // rows a warp keeps in flight: two pairs (measured at 2 KiB rows: 6 is slower)
+constexpr int kSmemPerSm = 227 * 1024;       // shared memory of an SM that thread blocks can have
+constexpr int kRingStages = 4;               // rows of 2 KiB and more a warp keeps in flight: two pairs (measured: six are 7 % slower)
 
 // ------------------------------------------------------------------ query group mean
 
@@ -305,7 +305,9 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
     // does not depend on anything is therefore requested first and used late: the request offsets (one coalesced
     // read per thread block, searched in shared memory afterwards) and the slot ids; the rows follow as soon as
     // the slot ids are there, and the query while the rows are on their way.
-    __shared__ int32_t s_off[kMaxSmemOffsets];
+    // (the offsets sit behind the rings in dynamic shared memory, sized for this batch: a fixed array for the largest
+    // batch would cost every launch 8 KiB that the rings can use)
+    int32_t* s_off = reinterpret_cast<int32_t*>(smem + (size_t)kWarps * kMaxRingStages * 8 + (size_t)kWarps * stages * kRowBytes);
     const bool off_in_smem = p.n_req + 1 <= kMaxSmemOffsets;
     constexpr int kOffIters = (kMaxSmemOffsets + kScoreThreads - 1) / kScoreThreads;
     int32_t off_reg[kOffIters];
@@ -709,17 +711,22 @@ struct RingGeometry {
     size_t smem;
 };
 
-RingGeometry ring_geometry(int32_t total, uint32_t row_bytes)
+RingGeometry ring_geometry(int32_t total, uint32_t row_bytes, int32_t n_req, size_t static_bytes)
 {
     constexpr int warps_per_cta = kScoreThreads / 32;
     const size_t bar_bytes = (size_t)warps_per_cta * kMaxRingStages * 8;
+    const size_t off_bytes = n_req + 1 <= kMaxSmemOffsets ? (((size_t)n_req + 1) * 4 + 15) / 16 * 16 : 0;
+    // what a thread block has for its rings when `ctas` of them share an SM (1 KiB per block is the system's)
+    auto ring_room = [&](int ctas) -> int64_t {
+        return (int64_t)kSmemPerSm / ctas - 1024 - (int64_t)static_bytes - (int64_t)bar_bytes - (int64_t)off_bytes;
+    };
     int ctas_per_sm = 2;
-    int stages = (int)((kRingSmemPerSm / ctas_per_sm - bar_bytes) / ((size_t)warps_per_cta * row_bytes));
+    int stages = (int)(ring_room(2) / (int64_t)((size_t)warps_per_cta * row_bytes));
     if (stages < 2) {                         // very wide rows: one thread block per SM gets all of it
         ctas_per_sm = 1;
-        stages = (int)((kRingSmemPerSm - bar_bytes) / ((size_t)warps_per_cta * row_bytes));
+        stages = (int)(ring_room(1) / (int64_t)((size_t)warps_per_cta * row_bytes));
     }
-    // about 8 KiB in flight per warp: four buffers for rows of 2 KiB and more, up to sixteen for narrower ones
+    // four buffers for rows of 2 KiB and more (more do not help: measured), eight of 1 KiB, sixteen below
     const int cap = row_bytes >= 2048 ? kRingStages : row_bytes >= 1024 ? 8 : kMaxRingStages;
     if (stages > cap) stages = cap;
     RingGeometry g;
@@ -728,7 +735,7 @@ RingGeometry ring_geometry(int32_t total, uint32_t row_bytes)
     if (grid > want) grid = want;
     g.grid = (int)(grid < 1 ? 1 : grid);
     g.stages = stages;
-    g.smem = bar_bytes + (size_t)warps_per_cta * stages * row_bytes;
+    g.smem = bar_bytes + (size_t)warps_per_cta * stages * row_bytes + off_bytes;
     return g;
 }
 
@@ -736,7 +743,9 @@ template <int DT, int QN, bool FUSEQ>
 int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
 {
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
-    const RingGeometry g = ring_geometry(p.total, kRowBytes);
+    // static shared memory of the kernel: the staged queries of the fused variant
+    const size_t static_bytes = FUSEQ ? (size_t)3 * QN * 32 * 4 + 64 : 64;
+    const RingGeometry g = ring_geometry(p.total, kRowBytes, p.n_req, static_bytes);
     if (g.stages < 1) return UCMX_EUNSUPPORTED;
     static int smem_set[64];                  // per device: dynamic shared memory limit already raised to this
     int dev = 0;
