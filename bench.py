@@ -628,7 +628,7 @@ def _time_launches(fn, iters, reps=3):
 
 
 def run_kernel_workload(args, dev):
-    """hamming | hash | pool | gsa | kvstar | connector | filestore: one kernel (or one call path) of the other benchmark
+    """score | hamming | hash | pool | gsa | kvstar | connector | filestore: one kernel (or one call path) of the other benchmark
     configurations, timed alone on inputs larger than L2 (or rotated over several tables)."""
     import numpy as np
     import torch
@@ -701,6 +701,46 @@ def run_kernel_workload(args, dev):
                     roofline=roofline("pool_blocks_kernel<mean>", nbytes, res["mean"]),
                     max_pooling={"us": res["max"], "gbs": nbytes / res["max"] / 1e3},
                     decode_64_blocks={"us": small, "gbs": 64 * (shape.slice_bytes + 2048) / small / 1e3})
+    elif name == "score":
+        # the headline batch's scoring kernel on its own: 33 391 rows of 2 KiB per launch out of three tables in rotation
+        # (a launch reads 68 MB; the next launch's table is not in L2), with the query mean folded in and with fp32 queries
+        n_tables = 3
+        reps = [(torch.randn((batch.n_slots, H, 1, D), generator=g, device=dev) * 0.0884).to(torch.bfloat16) for _ in range(n_tables)]
+        q = torch.randn((batch.n_req, shape.n_q_heads, D), generator=g, device=dev).to(torch.bfloat16)
+        qbar = ops.query_group_mean(q, H)
+        scores = torch.empty((batch.total,), dtype=torch.float32, device=dev)
+        nbytes = batch.total * (H * D * 2 + 8)
+
+        def graph_us(fn, n=24):
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                fn(0)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for i in range(n):
+                    fn(i)
+            best = float("inf")
+            for _ in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                gr.replay()
+                b.record()
+                torch.cuda.synchronize()
+                best = min(best, a.elapsed_time(b) * 1e3 / n)
+            return best
+
+        us_fused = graph_us(lambda i: ops.score_dot_query(reps[i % n_tables], off, q, total=batch.total, slot_ids=table, n_kv_heads=H, out=scores))
+        us_f32q = graph_us(lambda i: ops.score_dot(reps[i % n_tables], off, qbar, total=batch.total, slot_ids=table, n_kv_heads=H,
+                                                   head_dim=D, out=scores))
+        line.update(metric="scored_kv_tokens_per_s", unit=UNIT, value=batch.total * T / (us_fused * 1e-6), ms_per_step=us_fused * 1e-3,
+                    dtype="bf16", config={"workload": "dot scoring of the 64-request ragged batch, one launch per graph node",
+                                          "blocks": int(batch.total), "l2_policy": "three 73 MB tables in rotation"},
+                    roofline=roofline("score_dot_ring_kernel<bf16, 32, query mean folded in>", nbytes, us_fused),
+                    fp32_queries={"kernel": "score_dot_ring_kernel<bf16, 32>", "us": us_f32q, "gbs": nbytes / us_f32q / 1e3,
+                                  "frac": nbytes / us_f32q / 1e3 / peak})
     elif name == "gsa":
         # GSA's two scoring forms on the 64-request batch with two representatives per head (config 1's pooling, at
         # config 2's size): sum over heads of the best representative's dot product (host-side SelectTopKBS semantics,
@@ -900,7 +940,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline numbers only: no parity check, plug-in timing or tp_long object")
     ap.add_argument("--layers", type=int, default=None, help=argparse.SUPPRESS)
     ap.add_argument("--workload", default="decode64",
-                    choices=["decode64", "decode64-delta", "tp-long", "offload", "hamming", "hash", "pool", "gsa", "kvstar",
+                    choices=["decode64", "decode64-delta", "tp-long", "offload", "score", "hamming", "hash", "pool", "gsa", "kvstar",
                              "connector", "filestore"],
                     help="decode64: the 64-request ragged decode batch, data parallel over requests (default); "
                          "decode64-delta: the same batch with a resident working set per request and layer - queries drift "
@@ -950,7 +990,7 @@ def main():
     if args.workload == "offload":
         run_offload(args, rank, world, local_rank, dev, barrier)
         return finish()
-    if args.workload in ("hamming", "hash", "pool", "gsa", "kvstar", "connector", "filestore"):
+    if args.workload in ("score", "hamming", "hash", "pool", "gsa", "kvstar", "connector", "filestore"):
         if rank == 0:
             run_kernel_workload(args, dev)
         return finish()

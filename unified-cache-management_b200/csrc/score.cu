@@ -110,104 +110,57 @@ struct RowDot {
             }
         }
     }
-    // q from the raw bf16 query [Hq, D]: mean over the head group in fp32 (heads in ascending
-    // order, times 1/group), optionally rounded to bf16 — the arithmetic of query_group_mean_kernel.
-    // All loads of a lane are requested before the first one is used (the query comes from L2 or HBM).
-    template <int G>
-    __device__ __forceinline__ void load_q_raw_g(const uint16_t* __restrict__ qreq, int lane, int rep, int D, bool mean,
-                                                 int round_bf16)
-    {
-        constexpr int kChunks = QN / 4;      // four consecutive elements of the flattened [Hkv, D] query each
-        constexpr int kBatch = kChunks * G > 32 ? (32 / G) : kChunks;   // at most 32 loads of 8 bytes in flight
-        const float inv = 1.0f / (float)G;
-#pragma unroll
-        for (int c0 = 0; c0 < kChunks; c0 += kBatch) {
-            uint2 w[kBatch][G];
-#pragma unroll
-            for (int cc = 0; cc < kBatch; ++cc) {
-                const int c = c0 + cc;
-                const int e0 = ((c / (kPerPiece / 4)) * 32 + lane) * kPerPiece + (c % (kPerPiece / 4)) * 4;
-                const int h = e0 / D, d = e0 - h * D;
-                const uint16_t* src = qreq + (int64_t)((h / rep) * G) * D + d;
-#pragma unroll
-                for (int j = 0; j < G; ++j) w[cc][j] = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * D));
-            }
-#pragma unroll
-            for (int cc = 0; cc < kBatch; ++cc) {
-                const int c = c0 + cc;
-                float a0 = bf16lo(w[cc][0].x), a1 = bf16hi(w[cc][0].x), a2 = bf16lo(w[cc][0].y), a3 = bf16hi(w[cc][0].y);
-#pragma unroll
-                for (int j = 1; j < G; ++j) {
-                    a0 += bf16lo(w[cc][j].x);
-                    a1 += bf16hi(w[cc][j].x);
-                    a2 += bf16lo(w[cc][j].y);
-                    a3 += bf16hi(w[cc][j].y);
-                }
-                if (mean) {
-                    a0 *= inv;
-                    a1 *= inv;
-                    a2 *= inv;
-                    a3 *= inv;
-                    if (round_bf16) {
-                        a0 = bf16_round(a0);
-                        a1 = bf16_round(a1);
-                        a2 = bf16_round(a2);
-                        a3 = bf16_round(a3);
-                    }
-                }
-                q[c * 4 + 0] = a0;
-                q[c * 4 + 1] = a1;
-                q[c * 4 + 2] = a2;
-                q[c * 4 + 3] = a3;
-            }
-        }
-    }
+    // q from the raw bf16 query [Hq, D]: mean over the head group in fp32 (heads in ascending order, times 1/group),
+    // optionally rounded to bf16 - the arithmetic of query_group_mean_kernel.  This is the warp's own route for a
+    // request the thread block has not staged (a slice that touches more than a few requests); it is kept small
+    // rather than fast: rolled loops, one head at a time.
     __device__ __forceinline__ void load_q_raw(const uint16_t* __restrict__ qreq, int lane, int Hq, int Hkv, int D,
                                                int round_bf16)
     {
         const int g = Hq >= Hkv ? Hq / Hkv : 1;
         const int rep = Hq >= Hkv ? 1 : Hkv / Hq;
-        const bool mean = Hq >= Hkv;
-        switch (g) {
-            case 1: load_q_raw_g<1>(qreq, lane, rep, D, mean, round_bf16); return;
-            case 2: load_q_raw_g<2>(qreq, lane, rep, D, mean, round_bf16); return;
-            case 4: load_q_raw_g<4>(qreq, lane, rep, D, mean, round_bf16); return;
-            case 8: load_q_raw_g<8>(qreq, lane, rep, D, mean, round_bf16); return;
-            default: break;
-        }
-        const float inv = 1.0f / (float)g;      // any other group size: one head at a time
-#pragma unroll
-        for (int i = 0; i < kPieces; ++i) {
-#pragma unroll
-            for (int half = 0; half < kPerPiece / 4; ++half) {
-                const int e0 = (i * 32 + lane) * kPerPiece + half * 4;
-                const int h = e0 / D, d = e0 - h * D;
-                const uint16_t* src = qreq + (int64_t)((h / rep) * g) * D + d;
-                uint2 w = __ldg(reinterpret_cast<const uint2*>(src));
-                float a0 = bf16lo(w.x), a1 = bf16hi(w.x), a2 = bf16lo(w.y), a3 = bf16hi(w.y);
-                for (int j = 1; j < g; ++j) {
-                    w = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * D));
-                    a0 += bf16lo(w.x);
-                    a1 += bf16hi(w.x);
-                    a2 += bf16lo(w.y);
-                    a3 += bf16hi(w.y);
-                }
-                a0 *= inv;
-                a1 *= inv;
-                a2 *= inv;
-                a3 *= inv;
-                if (round_bf16) {
-                    a0 = bf16_round(a0);
-                    a1 = bf16_round(a1);
-                    a2 = bf16_round(a2);
-                    a3 = bf16_round(a3);
-                }
-                q[i * kPerPiece + half * 4 + 0] = a0;
-                q[i * kPerPiece + half * 4 + 1] = a1;
-                q[i * kPerPiece + half * 4 + 2] = a2;
-                q[i * kPerPiece + half * 4 + 3] = a3;
+        const float inv = Hq >= Hkv ? 1.0f / (float)g : 1.0f;
+        const bool rnd = Hq >= Hkv && round_bf16;
+#pragma unroll 1
+        for (int c = 0; c < QN / 4; ++c) {
+            const int i = c / (kPerPiece / 4), half = c % (kPerPiece / 4);
+            const int e0 = (i * 32 + lane) * kPerPiece + half * 4;
+            const int h = e0 / D, d = e0 - h * D;
+            const uint16_t* src = qreq + (int64_t)((h / rep) * g) * D + d;
+            uint2 w = __ldg(reinterpret_cast<const uint2*>(src));
+            float a0 = bf16lo(w.x), a1 = bf16hi(w.x), a2 = bf16lo(w.y), a3 = bf16hi(w.y);
+#pragma unroll 1
+            for (int j = 1; j < g; ++j) {
+                w = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)j * D));
+                a0 += bf16lo(w.x);
+                a1 += bf16hi(w.x);
+                a2 += bf16lo(w.y);
+                a3 += bf16hi(w.y);
             }
+            a0 *= inv;
+            a1 *= inv;
+            a2 *= inv;
+            a3 *= inv;
+            if (rnd) {
+                a0 = bf16_round(a0);
+                a1 = bf16_round(a1);
+                a2 = bf16_round(a2);
+                a3 = bf16_round(a3);
+            }
+            set_q4(c, a0, a1, a2, a3);
         }
+    }
+    // q[4c .. 4c+3] = values, c known only at run time (a chain of selects: the array must stay in registers)
+    __device__ __forceinline__ void set_q4(int c, float a0, float a1, float a2, float a3)
+    {
+#pragma unroll
+        for (int k = 0; k < QN / 4; ++k)
+            if (k == c) {
+                q[k * 4 + 0] = a0;
+                q[k * 4 + 1] = a1;
+                q[k * 4 + 2] = a2;
+                q[k * 4 + 3] = a3;
+            }
     }
     __device__ __forceinline__ void load_row(const void* row, int lane, uint4 (&buf)[kPieces]) const
     {
