@@ -999,7 +999,16 @@ def main():
         res = run_tp_long(args, rank, world, local_rank, dev, barrier, layers=layers, steps=args.steps, warmup=args.warmup,
                           allreduce=args.allreduce)
         if rank == 0:
+            peak, peak_kind = measured_peaks()
+            gather_bytes = res["gather_gbs"] * 1e9 * res["gather_us"] * 1e-6          # per rank and layer
+            layer_gbs = gather_bytes / (res["us_per_layer"] * 1e-6) / 1e9
+            roofline = {"kernel": "xfer_bulk_kernel (gather of the selected K,V head slices, one layer, one rank)", "bound": "hbm",
+                        "achieved": layer_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": layer_gbs / peak,
+                        "traffic": None, "algorithmic_bytes_per_launch": gather_bytes,
+                        "note": "a lower bound: the gather's bytes over the WHOLE layer time of the replayed step (scoring, exchange "
+                                "and top-k of the next layer run beside the gather on a second stream)"}
             print(json.dumps({
+                "roofline": roofline,
                 "metric": METRIC, "value": res["scored_tokens_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
