@@ -5,9 +5,10 @@
  * GPU work is one launch per layer; through ctypes a call is 3-5 us, here well under one.
  *
  * The module does not link against the library: ucmx/retrieval.py hands it the addresses of the three entry points
- * once (bind), so the C ABI stays the only boundary.  Arrays that are not plain C-contiguous float32 / int32 make
- * submit return None; the Python side then converts and calls again.  A status other than success (all of them are
- * negative) comes back as it is and the Python side raises what the ctypes route raises. */
+ * once (bind), so the C ABI stays the only boundary.  ucmx.retrieval.RetrievalWorkerBackend derives from the type
+ * defined here, so the three methods are called without a Python frame in between.  Arrays that are not plain
+ * C-contiguous float32 / int32 go to the subclass's _submit_converted, which converts and calls submit again; a status
+ * other than success goes to the callable given to bind, which raises what the ctypes route raises. */
 #define PY_SSIZE_T_CLEAN
 #include <Python.h>
 #define NPY_NO_DEPRECATED_API NPY_1_7_API_VERSION
@@ -21,6 +22,20 @@ typedef int32_t (*get_fn)(void*, int32_t, int32_t*, float*);
 static submit_fn g_submit;
 static wait_fn g_wait;
 static get_fn g_get;
+static PyObject* g_on_error;   /* callable(function name, status): raises */
+
+#define UCMX_ENOOBJ (-50005)
+
+static PyObject* raise_status(const char* fn, int32_t st)
+{
+    if (g_on_error) {
+        PyObject* r = PyObject_CallFunction(g_on_error, "si", fn, (int)st);
+        Py_XDECREF(r);
+        if (PyErr_Occurred()) return NULL;
+    }
+    PyErr_Format(PyExc_RuntimeError, "%s failed with status %d", fn, (int)st);
+    return NULL;
+}
 
 #define SHAPE_SLOTS 8192   /* results outstanding per object; a request id maps to id % SHAPE_SLOTS */
 
@@ -38,7 +53,7 @@ static int fb_init(FastBackend* self, PyObject* args, PyObject* kw)
     unsigned long long h = 0;
     int dim = 0;
     (void)kw;
-    if (!PyArg_ParseTuple(args, "Ki", &h, &dim)) return -1;
+    if (!PyArg_ParseTuple(args, "Ki", &h, &dim)) return -1;   /* (a subclass calls this once it has its handle) */
     self->handle = (void*)(uintptr_t)h;
     self->dim = dim;
     for (int i = 0; i < SHAPE_SLOTS; ++i) self->shape[i].rid = -1;
@@ -52,7 +67,7 @@ static int plain(PyObject* o, int typenum)
     return PyArray_TYPE(a) == typenum && PyArray_NDIM(a) == 2 && PyArray_IS_C_CONTIGUOUS(a);
 }
 
-/* submit(query float32 [b, dim], topk, indexes int32 [b, n]) -> request id (>= 0) | status (< 0) | None (convert first) */
+/* submit(query float32 [b, dim], topk, indexes int32 [b, n]) -> request id */
 static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t nargs)
 {
     if (nargs != 3) {
@@ -61,6 +76,10 @@ static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t 
     }
     if (!g_submit) {
         PyErr_SetString(PyExc_RuntimeError, "not bound to the library");
+        return NULL;
+    }
+    if (!self->handle) {
+        PyErr_SetString(PyExc_RuntimeError, "the retrieval object is closed");
         return NULL;
     }
     PyObject *q = args[0], *idx = args[2];
@@ -76,7 +95,7 @@ static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t 
             PyErr_SetString(PyExc_RuntimeError, "Query and indexes batch mismatch");
             return NULL;
         }
-        Py_RETURN_NONE;
+        return PyObject_CallMethod((PyObject*)self, "_submit_converted", "OOO", q, args[1], idx);
     }
     const long topk = PyLong_AsLong(args[1]);
     if (topk == -1 && PyErr_Occurred()) return NULL;
@@ -93,7 +112,7 @@ static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t 
     int32_t rid = -1;
     const int32_t st = g_submit(self->handle, (const float*)PyArray_DATA(qa), (int32_t)rows, (int32_t)dim, (int32_t)topk,
                                 (const int32_t*)PyArray_DATA(ia), (int32_t)n, &rid);
-    if (st != 0) return PyLong_FromLong(st < 0 ? (long)st : -1L);
+    if (st != 0) return raise_status("ucmx_retrieval_submit", st);
     const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
     self->shape[slot].rid = rid;
     self->shape[slot].rows = (int32_t)rows;
@@ -101,26 +120,41 @@ static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t 
     return PyLong_FromLong(rid);
 }
 
-/* wait(req_id) -> status of ucmx_retrieval_wait (the GIL is released while the stream is waited for) */
+/* wait(req_id): returns when the request's result is on the host (the GIL is released while the stream is waited for) */
 static PyObject* fb_wait(FastBackend* self, PyObject* arg)
 {
     const long rid = PyLong_AsLong(arg);
     if (rid == -1 && PyErr_Occurred()) return NULL;
+    if (!self->handle || !g_wait) {
+        PyErr_SetString(PyExc_RuntimeError, "the retrieval object is closed");
+        return NULL;
+    }
     int32_t st;
     Py_BEGIN_ALLOW_THREADS
     st = g_wait(self->handle, (int32_t)rid);
     Py_END_ALLOW_THREADS
-    return PyLong_FromLong(st);
+    if (st == 0) Py_RETURN_NONE;
+    if (st == UCMX_ENOOBJ) {
+        PyErr_SetString(PyExc_RuntimeError, "Bad req_id");
+        return NULL;
+    }
+    return raise_status("ucmx_retrieval_wait", st);
 }
 
-/* get_result(req_id) -> {"indices": int32 [b, k], "scores": float32 [b, k]} | status (an int) when it is not success |
- * None when this object never saw the request */
+/* get_result(req_id) -> {"indices": int32 [b, k], "scores": float32 [b, k]}; the request is forgotten afterwards */
 static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
 {
     const long rid = PyLong_AsLong(arg);
     if (rid == -1 && PyErr_Occurred()) return NULL;
+    if (!self->handle || !g_wait) {
+        PyErr_SetString(PyExc_RuntimeError, "the retrieval object is closed");
+        return NULL;
+    }
     const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
-    if (rid < 0 || self->shape[slot].rid != (int32_t)rid) Py_RETURN_NONE;
+    if (rid < 0 || self->shape[slot].rid != (int32_t)rid) {
+        PyErr_SetString(PyExc_RuntimeError, "Result not ready");
+        return NULL;
+    }
     npy_intp dims[2] = {self->shape[slot].rows, self->shape[slot].k};
     PyObject* indices = PyArray_SimpleNew(2, dims, NPY_INT32);
     PyObject* scores = PyArray_SimpleNew(2, dims, NPY_FLOAT32);
@@ -134,7 +168,11 @@ static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
     if (st != 0) {
         Py_DECREF(indices);
         Py_DECREF(scores);
-        return PyLong_FromLong(st);
+        if (st == UCMX_ENOOBJ) {
+            PyErr_SetString(PyExc_RuntimeError, "Result not ready");
+            return NULL;
+        }
+        return raise_status("ucmx_retrieval_get_result", st);
     }
     self->shape[slot].rid = -1;
     PyObject* d = PyDict_New();
@@ -149,32 +187,37 @@ static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
 
 static PyMethodDef fb_methods[] = {
     {"submit", (PyCFunction)(void (*)(void))fb_submit, METH_FASTCALL, "submit(query, topk, indexes)"},
-    {"wait", (PyCFunction)fb_wait, METH_O, "wait(req_id) -> status"},
+    {"wait", (PyCFunction)fb_wait, METH_O, "wait(req_id)"},
     {"get_result", (PyCFunction)fb_get_result, METH_O, "get_result(req_id)"},
     {NULL, NULL, 0, NULL}};
 
 static PyTypeObject FastBackendType = {
     PyVarObject_HEAD_INIT(NULL, 0).tp_name = "_ucmx_fast.Backend",
     .tp_basicsize = sizeof(FastBackend),
-    .tp_flags = Py_TPFLAGS_DEFAULT,
+    .tp_flags = Py_TPFLAGS_DEFAULT | Py_TPFLAGS_BASETYPE,
     .tp_new = PyType_GenericNew,
     .tp_init = (initproc)fb_init,
     .tp_methods = fb_methods,
 };
 
-/* bind(submit_address, wait_address, get_result_address): the entry points of the loaded library */
+/* bind(submit_address, wait_address, get_result_address, on_error): the entry points of the loaded library and the
+ * callable that turns a failed status into the package's exception */
 static PyObject* mod_bind(PyObject* self, PyObject* args)
 {
     unsigned long long a = 0, b = 0, c = 0;
+    PyObject* on_error = NULL;
     (void)self;
-    if (!PyArg_ParseTuple(args, "KKK", &a, &b, &c)) return NULL;
+    if (!PyArg_ParseTuple(args, "KKKO", &a, &b, &c, &on_error)) return NULL;
     g_submit = (submit_fn)(uintptr_t)a;
     g_wait = (wait_fn)(uintptr_t)b;
     g_get = (get_fn)(uintptr_t)c;
+    Py_XINCREF(on_error);
+    Py_XDECREF(g_on_error);
+    g_on_error = on_error;
     Py_RETURN_NONE;
 }
 
-static PyMethodDef mod_methods[] = {{"bind", mod_bind, METH_VARARGS, "bind(submit, wait, get_result addresses)"},
+static PyMethodDef mod_methods[] = {{"bind", mod_bind, METH_VARARGS, "bind(submit, wait, get_result addresses, on_error)"},
                                     {NULL, NULL, 0, NULL}};
 
 static struct PyModuleDef moddef = {PyModuleDef_HEAD_INIT, "_ucmx_fast", "CPython front of ucmx_retrieval_*", -1, mod_methods,

@@ -10,9 +10,9 @@ Host arrays in, host arrays out: submit copies the query and the index matrix to
 get_result returns numpy arrays, exactly like the pybind11 module it replaces.  Errors the
 reference raises as std::runtime_error surface as RuntimeError with the same text.
 
-submit / wait / get_result - three calls per request and layer in ESA's pattern - go through a small
-CPython module (csrc/pybackend.c, built beside the library) that calls the C ABI directly; the other
-methods go through ctypes.
+submit / wait / get_result - three calls per request and layer in ESA's pattern - are methods of a small
+CPython type (csrc/pybackend.c, built beside the library) that calls the C ABI directly, and
+RetrievalWorkerBackend derives from it; the other methods go through ctypes.
 """
 from __future__ import annotations
 
@@ -35,14 +35,23 @@ def _load_fast():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     addr = lambda fn: C.cast(fn, C.c_void_p).value   # noqa: E731
-    mod.bind(addr(N.lib.ucmx_retrieval_submit), addr(N.lib.ucmx_retrieval_wait), addr(N.lib.ucmx_retrieval_get_result))
+    mod.bind(addr(N.lib.ucmx_retrieval_submit), addr(N.lib.ucmx_retrieval_wait), addr(N.lib.ucmx_retrieval_get_result),
+             _raise_status)
     return mod
+
+
+def _raise_status(fn_name: str, status: int) -> None:
+    raise N.UcmxError(fn_name, status, N.last_error())
 
 
 _fast = _load_fast()
 
 
-class RetrievalWorkerBackend:
+class RetrievalWorkerBackend(_fast.Backend):
+    """submit(query float32 [b, dim], topk, indexes int32 [b, max_idx], -1 = pad) -> req_id; wait(req_id);
+    get_result(req_id) -> {"indices": int32 [b, k], "scores": float32 [b, k]} are inherited from the C type; poll,
+    flush and the rest are below."""
+
     def __init__(self, data, *, device: int = 0, table_dtype: str = "bf16"):
         """data: float32 [n_items, dim] (numpy array or CPU torch tensor).
 
@@ -57,24 +66,17 @@ class RetrievalWorkerBackend:
         st = N.lib.ucmx_retrieval_create(arr.ctypes.data_as(C.c_void_p), self.n_items, self.dim, dt, device,
                                          C.byref(self._h))
         N.check("ucmx_retrieval_create", st, 0)
-        self._fb = _fast.Backend(self._h.value, self.dim)
-        self._fsubmit, self._fwait, self._fget = self._fb.submit, self._fb.wait, self._fb.get_result
+        _fast.Backend.__init__(self, self._h.value, self.dim)
 
-    # -- the reference's four methods -------------------------------------------------------------
-    def submit(self, query, topk: int, indexes) -> int:
-        rid = self._fsubmit(query, topk, indexes)
-        if rid is None:
-            # not plain C-contiguous float32 / int32 arrays: convert, then the same call
-            q = np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
-            idx = np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
-            if q.ndim != 2 or q.shape[1] != self.dim:
-                raise RuntimeError("Query dim mismatch")
-            if idx.ndim != 2 or idx.shape[0] != q.shape[0]:
-                raise RuntimeError("Query and indexes batch mismatch")
-            rid = self._fsubmit(q, int(topk), idx)
-        if rid < 0:
-            N.check("ucmx_retrieval_submit", rid, 0)
-        return rid
+    def _submit_converted(self, query, topk, indexes) -> int:
+        """Called by submit for anything that is not a plain C-contiguous float32 / int32 numpy array."""
+        q = np.ascontiguousarray(_as_numpy(query), dtype=np.float32)
+        idx = np.ascontiguousarray(_as_numpy(indexes), dtype=np.int32)
+        if q.ndim != 2 or q.shape[1] != self.dim:
+            raise RuntimeError("Query dim mismatch")
+        if idx.ndim != 2 or idx.shape[0] != q.shape[0]:
+            raise RuntimeError("Query and indexes batch mismatch")
+        return self.submit(q, int(topk), idx)
 
     def flush(self) -> None:
         """Send everything submitted so far to the GPU now (otherwise the first poll/wait/get_result does it)."""
@@ -84,22 +86,6 @@ class RetrievalWorkerBackend:
         ready = C.c_int32(0)
         N.check("ucmx_retrieval_poll", N.lib.ucmx_retrieval_poll(self._h, req_id, C.byref(ready)), 0)
         return bool(ready.value)
-
-    def wait(self, req_id: int) -> None:
-        st = self._fwait(req_id)
-        if st:
-            if st == N.ENOOBJ:
-                raise RuntimeError("Bad req_id")
-            N.check("ucmx_retrieval_wait", st, 0)
-
-    def get_result(self, req_id: int) -> dict:
-        res = self._fget(req_id)
-        if type(res) is dict:
-            return res
-        if res is None or res == N.ENOOBJ:
-            raise RuntimeError("Result not ready")
-        N.check("ucmx_retrieval_get_result", res, 0)
-        raise RuntimeError("Result not ready")
 
     # -- additions ---------------------------------------------------------------------------------
     def update_rows(self, slots, rows) -> None:
@@ -127,6 +113,7 @@ class RetrievalWorkerBackend:
         if self._h:
             N.lib.ucmx_retrieval_destroy(self._h)
             self._h = C.c_void_p()
+            _fast.Backend.__init__(self, 0, self.dim)      # the C side forgets the handle too
 
     def __del__(self):  # pragma: no cover
         try:
