@@ -87,11 +87,16 @@ __device__ __forceinline__ float ex2(float x)
 
 // ------------------------------------------------------------------------------------ PTX wrappers
 
+// The representations are read once: evict-first, so that the gigabyte passing through L2 does not push out the
+// 74 MB of (maximum, sum) pairs this pass writes and the two small kernels after it read.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, int x, int y, uint64_t* bar)
 {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
-                     "r"(smem_u32(dst)), "l"(m), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
+    const uint64_t pol = l2_evict_first_policy();
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::
+            "r"(smem_u32(dst)),
+        "l"(m), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 {
