@@ -108,7 +108,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+                 "-lms", "25", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
