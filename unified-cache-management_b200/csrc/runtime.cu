@@ -10,6 +10,7 @@
 #include <mutex>
 #include <new>
 #include <thread>
+#include <atomic>
 #include <unordered_map>
 #include <vector>
 
@@ -248,6 +249,7 @@ struct Batch {
     int32_t open = 0;          // requests whose result has not been collected yet
     int32_t kmax = 1;
     bool launched = false, failed = false;
+    std::atomic<bool> finished{false};   // the batch's event has been seen complete: no more driver calls for its requests
     size_t o_counts = 0, o_idx = 0;   // byte offsets inside h_out once launched
     void reset()
     {
@@ -258,6 +260,7 @@ struct Batch {
         open = 0;
         kmax = 1;
         launched = failed = false;
+        finished.store(false, std::memory_order_relaxed);
     }
 };
 
@@ -289,15 +292,18 @@ namespace {
 
 struct DeviceGuard {
     int prev = -1;
-    bool ok = true;
+    bool ok = true, changed = false;
     explicit DeviceGuard(int dev)
     {
         if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+        if (prev != dev) {
+            ok = cudaSetDevice(dev) == cudaSuccess;
+            changed = ok;
+        }
     }
     ~DeviceGuard()
     {
-        if (prev >= 0) cudaSetDevice(prev);
+        if (changed && prev >= 0) cudaSetDevice(prev);   // (nothing to undo when the caller was on this device already)
     }
 };
 
@@ -518,9 +524,12 @@ extern "C" int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_qu
     const size_t cand = (size_t)batch * max_idx;
     // The index lists are in host memory here, so a bad one is refused before anything reaches the GPU
     // (-1 pads a row; the reference bounds its loop by the table it owns, retrieval_backend.cpp:170-181).
-    for (size_t i = 0; i < cand; ++i) {
-        const int32_t v = host_indexes[i];
-        if (v < -1 || (int64_t)v >= r->n_items) {
+    {
+        // one pass without branches (it vectorises): v + 1 as unsigned must be at most n_items
+        const uint32_t limit = (uint32_t)(r->n_items < 0x7fffffffll ? r->n_items : 0x7fffffffll);
+        uint32_t bad = 0;
+        for (size_t i = 0; i < cand; ++i) bad |= (uint32_t)((uint32_t)host_indexes[i] + 1u > limit);
+        if (bad) {
             set_last_text("ucmx_retrieval_submit: an index is outside the table (allowed: -1 for padding, 0 .. n_items-1)");
             return UCMX_EPARAM;
         }
@@ -616,17 +625,23 @@ extern "C" int32_t ucmx_retrieval_wait(ucmx_retrieval* r, int32_t req_id)
     using namespace ucmx;
     if (!r) return UCMX_EPARAM;
     cudaEvent_t ev = nullptr;
+    Batch* b = nullptr;
     {
-        DeviceGuard g(r->device);
         std::lock_guard<std::mutex> lk(r->mu);
         auto it = r->live.find(req_id);
         if (it == r->live.end()) return UCMX_ENOOBJ;  // "Bad req_id"
-        Batch* b = it->second.batch;
-        if (!b->launched) flush_locked(r);
+        b = it->second.batch;
+        // ESA waits for every request of a layer in turn: all but the first find their batch already complete
+        if (b->launched && !b->failed && b->finished.load(std::memory_order_acquire)) return UCMX_OK;
+        if (!b->launched) {
+            DeviceGuard g(r->device);
+            flush_locked(r);
+        }
         if (b->failed) return UCMX_ERROR;
         ev = b->done;
     }
     UCMX_CUDA(cudaEventSynchronize(ev));
+    b->finished.store(true, std::memory_order_release);
     return UCMX_OK;
 }
 
@@ -645,25 +660,31 @@ extern "C" int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, 
 {
     using namespace ucmx;
     if (!r || !host_indices || !host_scores) return UCMX_EPARAM;
-    DeviceGuard g(r->device);
     std::lock_guard<std::mutex> lk(r->mu);
     auto it = r->live.find(req_id);
     if (it == r->live.end()) return UCMX_ENOOBJ;
     const Request rq = it->second;
     Batch* b = rq.batch;
-    if (!b->launched) flush_locked(r);
+    if (!b->launched) {
+        DeviceGuard g(r->device);
+        flush_locked(r);
+    }
     if (b->failed) {
         r->live.erase(it);
         b->open -= 1;
         retire_if_done(r, b);
         return UCMX_ERROR;
     }
-    const cudaError_t e = cudaEventQuery(b->done);
-    if (e == cudaErrorNotReady) {
-        cudaGetLastError();
-        return UCMX_ENOOBJ;  // "Result not ready"
+    if (!b->finished.load(std::memory_order_acquire)) {
+        DeviceGuard g(r->device);
+        const cudaError_t e = cudaEventQuery(b->done);
+        if (e == cudaErrorNotReady) {
+            cudaGetLastError();
+            return UCMX_ENOOBJ;  // "Result not ready"
+        }
+        if (e != cudaSuccess) return cuda_status("cudaEventQuery", e);
+        b->finished.store(true, std::memory_order_release);
     }
-    if (e != cudaSuccess) return cuda_status("cudaEventQuery", e);
     const int32_t k = rq.k;
     const int32_t* counts = (const int32_t*)b->h_out.p;
     const int32_t* idx = (const int32_t*)(b->h_out.p + b->o_counts);
