@@ -284,7 +284,15 @@ int32_t launch_xfer(XferParams& p, bool host_memory, cudaStream_t st)
     const size_t smem = 128 + (size_t)k_stages * p.chunk_bytes;
     if (smem > 220 * 1024) return UCMX_EUNSUPPORTED;
     void (*kern)(XferParams) = xfer_bulk_kernel<k_stages>;
-    UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+        static int smem_set[64];                  // per device: dynamic shared memory limit already raised to this
+        int dev = 0;
+        UCMX_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || smem_set[dev] < (int)smem) {
+            UCMX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (dev >= 0 && dev < 64) smem_set[dev] = (int)smem;
+        }
+    }
     int ctas_per_sm = k_per_sm;
     while (ctas_per_sm > 1 && (size_t)ctas_per_sm * (smem + 1024) > 227 * 1024) --ctas_per_sm;
     int64_t grid = (int64_t)sms * ctas_per_sm;
