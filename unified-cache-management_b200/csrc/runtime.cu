@@ -242,7 +242,6 @@ struct PinnedBuf {
 struct Batch {
     PinnedBuf h_q, h_idx, h_out;
     std::vector<int32_t> off{0}, kk, ooff{0};   // CSR of candidates, k per row, CSR of outputs
-    PinnedBuf h_meta;
     unsigned char* d_buf = nullptr;
     size_t d_cap = 0;
     cudaEvent_t done = nullptr;
@@ -253,7 +252,7 @@ struct Batch {
     size_t o_counts = 0, o_idx = 0;   // byte offsets inside h_out once launched
     void reset()
     {
-        h_q.size = h_idx.size = h_out.size = h_meta.size = 0;
+        h_q.size = h_idx.size = h_out.size = 0;
         off.assign(1, 0);
         kk.clear();
         ooff.assign(1, 0);
@@ -318,7 +317,6 @@ void free_batch(Batch* b)
     b->h_q.release();
     b->h_idx.release();
     b->h_out.release();
-    b->h_meta.release();
     if (b->d_buf) cudaFree(b->d_buf);
     if (b->done) cudaEventDestroy(b->done);
     delete b;
@@ -356,16 +354,20 @@ int32_t flush_locked(ucmx_retrieval* r)
         if (e != cudaSuccess) return fail(cuda_status("cudaMalloc(batch)", e));
         b->d_cap = dev_bytes + dev_bytes / 2;
     }
+    // One copy in instead of three: the candidate lists and the CSR arrays are laid behind the query rows in the same
+    // page-locked buffer, in the order the device buffer has them (133 KB moved by the CPU costs less than two more DMAs).
     int32_t rc = b->h_out.reserve(out_bytes);
-    if (rc == UCMX_OK) rc = b->h_meta.reserve(s_meta);
+    if (rc == UCMX_OK) rc = b->h_q.reserve(s_q + s_idx + s_meta);
     if (rc != UCMX_OK) return fail(rc);
     if (!b->done) {
         const cudaError_t e = cudaEventCreateWithFlags(&b->done, cudaEventDisableTiming);
         if (e != cudaSuccess) return fail(cuda_status("cudaEventCreate", e));
     }
-    memcpy(b->h_meta.p, b->off.data(), (rows + 1) * 4);
-    memcpy(b->h_meta.p + m_off, b->ooff.data(), (rows + 1) * 4);
-    memcpy(b->h_meta.p + 2 * m_off, b->kk.data(), rows * 4);
+    memcpy(b->h_q.p + s_q, b->h_idx.p, total * 4);
+    unsigned char* h_meta = b->h_q.p + s_q + s_idx;
+    memcpy(h_meta, b->off.data(), (rows + 1) * 4);
+    memcpy(h_meta + m_off, b->ooff.data(), (rows + 1) * 4);
+    memcpy(h_meta + 2 * m_off, b->kk.data(), rows * 4);
 
     unsigned char* d = b->d_buf;
     float* d_q = (float*)d;
@@ -380,9 +382,7 @@ int32_t flush_locked(ucmx_retrieval* r)
     float* d_osc = (float*)(d_out + b->o_counts + b->o_idx);
 
     cudaStream_t st = r->stream;
-    cudaError_t e = cudaMemcpyAsync(d_q, b->h_q.p, b->h_q.size, cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(d_slots, b->h_idx.p, total * 4, cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(d_off, b->h_meta.p, s_meta, cudaMemcpyHostToDevice, st);
+    cudaError_t e = cudaMemcpyAsync(d_q, b->h_q.p, s_q + s_idx + s_meta, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return fail(cuda_status("submit H2D", e));
     rc = ucmx_score_dot(r->table, r->dtype, r->n_items, 1, 1, r->dim, d_off, d_slots, d_q, (int32_t)rows, (int32_t)total,
                         1.0f, d_scores, nullptr, st);
