@@ -153,6 +153,15 @@ int32_t ucmx_score_dot(const void* reps, int32_t reps_dtype, int64_t n_slots, in
                        float scale, float* out_scores, const ucmx_peer_exchange* exchange /* host */,
                        ucmx_stream_t stream);
 
+/* Early start for the dot-scoring calls (ucmx_score_dot, ucmx_score_dot_query) the calling thread makes from now
+ * on (on != 0) or no longer (on == 0); returns the previous setting.  With it a scoring kernel is launched so that
+ * it may begin while the kernel ahead of it in the stream is still running (programmatic dependent launch, also
+ * inside a stream capture): it reads the table, the slot list, the offsets and the queries right away and waits
+ * for that kernel's end only before it stores its first score.  The caller promises that none of those four
+ * inputs is written by the kernel ahead; out_scores may be (a top-k that still reads the previous scores is the
+ * usual case).  Calls with an `exchange`, and shapes that do not take the row-ring kernel, are launched as ever. */
+int32_t ucmx_set_early_start(int32_t on);
+
 /* GSA's device-side weights (cal_topk, ucm/sparse/gsa/gsa.py:386-412): weight of a block = mean over the
  * QUERY heads of max over the block's n_rep representatives of dot(query head, representative of its KV
  * head); no softmax scale (the reference computes one and does not apply it).  query is raw bf16

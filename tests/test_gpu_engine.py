@@ -44,6 +44,64 @@ def test_selection_on_a_second_stream_changes_nothing():
     assert _native.device_error() == 0
 
 
+def test_scoring_launched_early_behind_a_topk_changes_nothing():
+    """Scoring kernels allowed to begin under the tail of the top-k ahead of them (they share the score buffer with it
+    and store only after its end): same scores and same selections as plain launches, call by call and replayed from
+    a graph, on a batch that fills every SM."""
+    from ucmx import _native, ops
+    from ucmx.workloads import ragged_decode_batch
+    batch = ragged_decode_batch(seed=77, n_req=48, min_ctx=16384, max_ctx=65536, ratio=0.1, min_k=4)
+    g = torch.Generator(device=DEV).manual_seed(77)
+    H, D, n_tab = 8, 128, 4
+    off = torch.from_numpy(batch.offsets).to(DEV)
+    table = torch.from_numpy(batch.block_table).to(DEV)
+    kk = torch.from_numpy(batch.k_per_req).to(DEV)
+    reps = [(torch.randn((batch.n_slots, H, 1, D), generator=g, device=DEV) * 0.09).to(torch.bfloat16) for _ in range(n_tab)]
+    q = torch.randn((n_tab, batch.n_req, 32, D), generator=g, device=DEV).to(torch.bfloat16)
+    stride = int(batch.k_per_req.max())
+    scores = torch.empty((batch.total,), dtype=torch.float32, device=DEV)
+
+    def run(early, ids, vals, kept):
+        for i in range(n_tab):
+            ops.score_dot_query(reps[i], off, q[i], total=batch.total, slot_ids=table, n_kv_heads=H, out=scores,
+                                early=early and i > 0)
+            if kept is not None:
+                kept[i].copy_(scores)
+            ops.topk_ragged(scores, off, kk, out_stride=stride, id_map=table, out_idx=ids[i], out_scores=vals[i])
+
+    def fresh():
+        return (torch.full((n_tab, batch.n_req, stride), -7, dtype=torch.int32, device=DEV),
+                torch.zeros((n_tab, batch.n_req, stride), dtype=torch.float32, device=DEV))
+
+    want_ids, want_vals = fresh()
+    want_scores = torch.empty((n_tab, batch.total), dtype=torch.float32, device=DEV)
+    run(False, want_ids, want_vals, want_scores)
+    torch.cuda.synchronize()
+    got_ids, got_vals = fresh()
+    got_scores = torch.empty_like(want_scores)
+    run(True, got_ids, got_vals, got_scores)
+    torch.cuda.synchronize()
+    assert torch.equal(got_scores, want_scores)
+    assert torch.equal(got_ids, want_ids) and torch.equal(got_vals, want_vals)
+
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run(True, got_ids, got_vals, None)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run(True, got_ids, got_vals, None)
+    for _ in range(4):
+        got_ids.fill_(-7)
+        got_vals.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(got_ids, want_ids) and torch.equal(got_vals, want_vals)
+    assert _native.device_error() == 0
+
+
 @pytest.mark.parametrize("overlap", [False, True])
 def test_host_step_and_its_graph_match_the_device_step(overlap):
     eng = make_engine(overlap)

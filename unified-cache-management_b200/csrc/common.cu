@@ -66,11 +66,22 @@ int32_t* error_word()
     return g_error_word;
 }
 
+static thread_local int32_t g_early_start = 0;
+
+bool early_start() { return g_early_start != 0; }
+
 }  // namespace ucmx
 
 extern "C" {
 
 int32_t ucmx_version(void) { return 100; }
+
+int32_t ucmx_set_early_start(int32_t on)
+{
+    const int32_t was = ucmx::g_early_start;
+    ucmx::g_early_start = on ? 1 : 0;
+    return was;
+}
 
 int32_t ucmx_compiled_arch(void) { return 100; }
 

@@ -17,6 +17,7 @@ void set_last_text(const char* text);
 int32_t* error_word();  // device-visible int that bounded waits report into (NULL if unavailable)
 int32_t cuda_status(const char* what, cudaError_t e);
 int sm_count();  // multiprocessors of the current device (cached)
+bool early_start();  // this thread asked for scoring launches that may begin before the kernel ahead of them ends
 
 // scoring with an explicit error word (NULL: out-of-range ids and lost copies are skipped without a report)
 int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, int32_t n_kv_heads, int32_t n_rep,
@@ -135,6 +136,13 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 }
 // The same with an L2 eviction policy: data that is read (or written) once and not again soon is marked
 // evict-first, so that a pass over gigabytes does not push the small hot arrays of the next kernels out of L2.
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may begin while the
+// kernel ahead of it in the stream is still running; early_start_wait() returns once that kernel has finished and its
+// writes are visible, early_start_allow() lets the kernel behind this one begin.  Both do nothing in a launch
+// without the attribute.
+__device__ __forceinline__ void early_start_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void early_start_allow() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t l2_evict_first_policy()
 {
     uint64_t pol;

@@ -69,6 +69,7 @@ struct ScoreParams {
     int32_t d_shift;         // log2(D) when D is a power of two, else -1
     PeerPush px;             // px.world == 0: single rank
     int32_t* err;
+    int32_t early;           // launched so that it may begin before the kernel ahead of it in the stream has ended
 };
 
 // Element layout per lane: a row is cut into 16-byte pieces; piece j of a row belongs to lane
@@ -233,6 +234,10 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
     const int w = (int)blockIdx.x * kWarps + warp;
     const int begin = min(w * p.rows_per_warp, p.total);
     const int end = min(begin + p.rows_per_warp, p.total);
+    // An early launch reads its inputs (offsets, slot ids, table rows, queries: none of them written by the kernel
+    // ahead) while that kernel's last thread blocks are still running, and waits for its end only before its own
+    // first store; the kernel behind this one is let in right away on the same terms.
+    if (p.early) early_start_allow();
 
     using RD = RowDot<DT, QN>;
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
@@ -416,6 +421,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
         bool failed = false;
         auto flush = [&](int upto) {   // rows [flush_from, upto), upto - flush_from <= 32
             const int row = flush_from + lane;
+            if (p.early) early_start_wait();
             if (row < upto) {
                 if (p.out) p.out[row] = mine;
                 for (int t = 0; t < p.px.world; ++t)
@@ -714,7 +720,23 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
     p.d_shift = -1;
     for (int sh = 0; sh < 16; ++sh)
         if ((1 << sh) == p.D) p.d_shift = sh;
-    score_dot_ring_kernel<DT, QN, FUSEQ><<<g.grid, kScoreThreads, g.smem, st>>>(p);
+    // (ranks that exchange scores read the round counter the kernel ahead may still be writing: never early)
+    p.early = early_start() && p.px.world == 0 ? 1 : 0;
+    if (p.early) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)g.grid);
+        cfg.blockDim = dim3(kScoreThreads);
+        cfg.dynamicSmemBytes = g.smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        UCMX_CUDA(cudaLaunchKernelEx(&cfg, score_dot_ring_kernel<DT, QN, FUSEQ>, p));
+    } else {
+        score_dot_ring_kernel<DT, QN, FUSEQ><<<g.grid, kScoreThreads, g.smem, st>>>(p);
+    }
     UCMX_LAUNCH_CHECK("score_dot_ring_kernel");
     return UCMX_OK;
 }

@@ -160,6 +160,9 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
 
     const int r = blockIdx.x;
     const int tid = threadIdx.x;
+    // A scoring kernel launched for an early start behind this one may begin now: it stores nothing before this
+    // kernel has ended.  (Not with a peer exchange: that scoring kernel is never launched early.)
+    if (!PEER) early_start_allow();
     const int base = __ldg(p.offsets + r);
     const int n = __ldg(p.offsets + r + 1) - base;
     const int k = __ldg(p.k_per_req + r);

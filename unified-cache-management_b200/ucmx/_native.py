@@ -56,6 +56,7 @@ _pi32 = C.POINTER(C.c_int32)
 # name -> argtypes; every entry returns int32 unless listed in _RESTYPES
 SIGNATURES = {
     "ucmx_version": [],
+    "ucmx_set_early_start": [_i32],
     "ucmx_compiled_arch": [],
     "ucmx_last_error": [],
     "ucmx_device_error": [_pi32, _i32],

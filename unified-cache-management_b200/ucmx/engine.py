@@ -129,14 +129,16 @@ class DecodeRetrievalEngine:
         """Representatives of every block of the pool (what the last prefill chunk does)."""
         ops.pool_blocks(self.kv_pool[0], self.block_table, out_slots=self.block_table, out_bf16=self.rep_tables[layer])
 
-    def score_layer(self, layer: int) -> None:
+    def score_layer(self, layer: int, early: bool = False) -> None:
+        """early: the kernel ahead in the stream writes none of the scoring inputs (it is the previous layer's top-k or
+        block move), so the scoring kernel may begin under its tail; it stores its scores only after that kernel's end."""
         if self.peer_exchange is not None:
             # the partial scores go straight into every rank's inbox; nothing is kept locally
             ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
                                 slot_ids=self.block_table, n_kv_heads=self.H, exchange=self.peer_exchange)
             return
         ops.score_dot_query(self.rep_tables[layer], self.offsets, self.q_dev[layer], total=self.batch.total,
-                            slot_ids=self.block_table, n_kv_heads=self.H, out=self.scores)
+                            slot_ids=self.block_table, n_kv_heads=self.H, out=self.scores, early=early)
         if self.score_reduce is not None:
             self.score_reduce(self.scores)
 
@@ -179,10 +181,10 @@ class DecodeRetrievalEngine:
     def loads_of_last_step(self) -> int:
         return int(sum(int(o[3].sum().item()) for o in self.remap_out))
 
-    def layer_step(self, layer: int, gather_events=None) -> None:
+    def layer_step(self, layer: int, gather_events=None, early: bool = False) -> None:
         """Score, select and gather one layer (pooling of new blocks is done for all layers at the start of a step).
         gather_events: an optional (before, after) pair of CUDA events recorded around the gather launch."""
-        self.score_layer(layer)
+        self.score_layer(layer, early=early)
         self.topk_layer(layer)
         if self.kv_pool is not None:
             if gather_events is not None:
@@ -209,7 +211,7 @@ class DecodeRetrievalEngine:
             return
         if not self.exchanges_scores:
             for l in range(self.L):
-                self.layer_step(l, None if gather_events is None else gather_events[l])
+                self.layer_step(l, None if gather_events is None else gather_events[l], early=l > 0 and gather_events is None)
             return
         self.score_layer(0)
         for l in range(self.L):
@@ -241,7 +243,7 @@ class DecodeRetrievalEngine:
         for l in range(self.L):
             if l + 1 < self.L:
                 with torch.cuda.stream(side):
-                    self.score_layer(l + 1)
+                    self.score_layer(l + 1, early=True)     # behind layer l's top-k on this stream
                     self.topk_layer(l + 1)
                     selected[l + 1].record(side)
             main.wait_event(selected[l])

@@ -101,10 +101,12 @@ def query_group_mean(query: torch.Tensor, n_kv_heads: int, *, round_bf16: bool =
 
 def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *, total: int,
               slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, head_dim: int, n_rep: int = 1,
-              scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None) -> torch.Tensor:
+              scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None, early: bool = False) -> torch.Tensor:
     """Ragged query-to-block dot scores. reps: bf16 or fp32 table [slots, n_kv_heads, n_rep, head_dim]
     (any shape with that memory layout); q fp32 [n_req, n_kv_heads*head_dim]. Returns fp32 [total].
-    exchange: a parallel.PeerScoreExchange under tensor parallelism; the scores then also go to every rank's inbox."""
+    exchange: a parallel.PeerScoreExchange under tensor parallelism; the scores then also go to every rank's inbox.
+    early: the kernel may begin before the kernel ahead of it in the stream has ended (ucmx_set_early_start); the
+    caller vouches that reps, req_offsets, slot_ids and q are not outputs of that kernel."""
     _need_cuda(reps, req_offsets, q, slot_ids, out)
     if reps.dtype == torch.bfloat16:
         dt = DT_BF16
@@ -120,18 +122,27 @@ def score_dot(reps: torch.Tensor, req_offsets: torch.Tensor, q: torch.Tensor, *,
     if out is None and exchange is None:
         out = torch.empty((total,), dtype=torch.float32, device=reps.device)
     n_slots = reps.numel() // (n_kv_heads * n_rep * head_dim)
-    st = N.lib.ucmx_score_dot(_ptr(reps), dt, n_slots, n_kv_heads, n_rep, head_dim, _ptr(_i32(req_offsets, "req_offsets")),
-                              _ptr(_i32(slot_ids, "slot_ids")), _ptr(q), n_req, total, float(scale), _ptr(out),
-                              _exchange(exchange), _stream(reps))
+    if early:
+        N.lib.ucmx_set_early_start(1)
+    try:
+        st = N.lib.ucmx_score_dot(_ptr(reps), dt, n_slots, n_kv_heads, n_rep, head_dim, _ptr(_i32(req_offsets, "req_offsets")),
+                                  _ptr(_i32(slot_ids, "slot_ids")), _ptr(q), n_req, total, float(scale), _ptr(out),
+                                  _exchange(exchange), _stream(reps))
+    finally:
+        if early:
+            N.lib.ucmx_set_early_start(0)
     N.check("ucmx_score_dot", st, 1 if total and n_req else 0)
     return out
 
 
 def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.Tensor, *, total: int,
                     slot_ids: Optional[torch.Tensor] = None, n_kv_heads: int, round_bf16: bool = True,
-                    scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None) -> torch.Tensor:
+                    scale: float = 1.0, out: Optional[torch.Tensor] = None, exchange=None,
+                    early: bool = False) -> torch.Tensor:
     """score_dot with the per-KV-head query mean folded in: query is the raw bf16 [n_req, n_q_heads, head_dim].
-    Shapes the single-pass kernel does not cover go through query_group_mean + score_dot (two launches)."""
+    Shapes the single-pass kernel does not cover go through query_group_mean + score_dot (two launches).
+    early: the kernel may begin before the kernel ahead of it in the stream has ended (ucmx_set_early_start); the
+    caller vouches that reps, req_offsets, slot_ids and query are not outputs of that kernel."""
     _need_cuda(reps, req_offsets, query, slot_ids, out)
     if query.dim() != 3 or query.dtype != torch.bfloat16:
         raise ValueError("query must be bf16 [n_req, n_q_heads, head_dim]")
@@ -146,9 +157,15 @@ def score_dot_query(reps: torch.Tensor, req_offsets: torch.Tensor, query: torch.
     if out is None and exchange is None:
         out = torch.empty((total,), dtype=torch.float32, device=reps.device)
     n_slots = reps.numel() // (n_kv_heads * D)
-    st = N.lib.ucmx_score_dot_query(_ptr(reps), dt, n_slots, n_kv_heads, D, _ptr(_i32(req_offsets, "req_offsets")),
-                                    _ptr(_i32(slot_ids, "slot_ids")), _ptr(query), Hq, query.stride(0), int(round_bf16),
-                                    n_req, total, float(scale), _ptr(out), _exchange(exchange), _stream(reps))
+    if early:
+        N.lib.ucmx_set_early_start(1)
+    try:
+        st = N.lib.ucmx_score_dot_query(_ptr(reps), dt, n_slots, n_kv_heads, D, _ptr(_i32(req_offsets, "req_offsets")),
+                                        _ptr(_i32(slot_ids, "slot_ids")), _ptr(query), Hq, query.stride(0), int(round_bf16),
+                                        n_req, total, float(scale), _ptr(out), _exchange(exchange), _stream(reps))
+    finally:
+        if early:
+            N.lib.ucmx_set_early_start(0)
     if st == N.EUNSUPPORTED:
         qbar = query_group_mean(query, n_kv_heads, round_bf16=round_bf16)
         return score_dot(reps, req_offsets, qbar, total=total, slot_ids=slot_ids, n_kv_heads=n_kv_heads, head_dim=D,
