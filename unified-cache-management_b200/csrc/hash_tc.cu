@@ -31,13 +31,17 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kDim = 128;
 constexpr int kBits = 128;
-constexpr int kStagesA = 2;                       // with two CTAs per SM that is four tiles in flight per SM
+constexpr int kStagesA = 5;                       // tile buffers of the one thread block an SM holds
+constexpr int kAcc = 4;                           // accumulators in tensor memory (4 x 128 columns: all of it)
+constexpr int kSets = 3;                          // epilogue warp sets; tile i of the thread block goes to set i % kSets
+constexpr int kFixers = 3;                        // fixer warps (warps 0, 2 and 3); tile i goes to fixer i % kFixers
 constexpr int kHalfBytes = kTileM * 128;          // one 64-element K half of a tile: 128 rows x 128 B
 constexpr int kTileBytes = 2 * kHalfBytes;        // 32 KiB
-constexpr int kThreads = 192;                     // warp 0: exact-chain fixer, warp 1: TMA + MMA issue and TMEM owner, warps 2-5: epilogue
+constexpr int kFirstSetWarp = 4;                  // a multiple of four: warp w reads TMEM lanes 32 (w % 4) ...
+constexpr int kThreads = 32 * (kFirstSetWarp + 4 * kSets);   // warps 0, 2, 3: exact-chain fixers, warp 1: TMA + MMA issue and TMEM owner, warps 4-15: epilogue sets
 constexpr float kTau = 1.0f / 32768.0f;           // 2^-15
 constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
-constexpr int kFixSlots = 256;                    // code words with doubtful bits the fixer warp takes per tile (about 20 are typical)
+constexpr int kFixSlots = 128;                    // code words with doubtful bits a fixer warp takes per tile (about 5 are typical)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -149,8 +153,8 @@ __device__ __forceinline__ uint32_t sw_offset(int row, int k)
     return (uint32_t)(half * kHalfBytes + row * 128 + ((c ^ (row & 7)) << 4) + ((k & 7) << 1));
 }
 
-struct alignas(8) Barriers {
-    uint64_t full[kStagesA], empty[kStagesA], acc_full[2], acc_empty[2], fix_ready[kStagesA];
+struct alignas(16) Barriers {      // (what follows it in shared memory is accessed 16 bytes at a time)
+    uint64_t full[kStagesA], empty[kStagesA], acc_full[kAcc], acc_empty[kAcc], fix_ready[kStagesA];
     uint32_t tmem_base;
     int32_t abort_flag;
     uint32_t fix_n[kStagesA];   // code words queued for the fixer, per stage
@@ -169,7 +173,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity)   // o
     return ok != 0;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
 {
     extern __shared__ unsigned char smem_raw[];
@@ -180,9 +184,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     unsigned char* sB = smem + kStagesA * kTileBytes;            // W^T as the B operand: row = bit, K = d
     float* wnorm = reinterpret_cast<float*>(sB + kTileBytes);    // |w_j|
     Barriers* bars = reinterpret_cast<Barriers*>(wnorm + kBits);
-    uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // 4 epilogue warps x kFallbackSlots
-    uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kFallbackSlots);
-    uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kFallbackSlots);   // max_j |w_j|
+    uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // epilogue warps x kFallbackSlots
+    uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kSets * kFallbackSlots);
+    uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kSets * kFallbackSlots);   // max_j |w_j|
     uint4* fixq = reinterpret_cast<uint4*>(wmax_bits + 4);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -195,7 +199,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             mbar_init(&bars->fix_ready[s], 128);    // every epilogue thread has queued its doubtful words and stored the others
             bars->fix_n[s] = 0;
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kAcc; ++a) {
             mbar_init(&bars->acc_full[a], 1);
             mbar_init(&bars->acc_empty[a], 128);
         }
@@ -228,7 +232,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     fence_proxy_async();            // the hand-written B tile must be visible to the MMA unit
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
-                     "r"(256)
+                     "r"(kAcc * kBits)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -248,24 +252,39 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         const uint32_t b_addr = smem_u32(sB);
         int64_t ld = 0, mm = 0;
         uint32_t idle = 0;
+        // paged: list entry and tile of its block of the next tile to load, advanced without divisions; the entry's
+        // cache block is asked for one tile ahead (this thread issues every load and every MMA of the SM: a trip to
+        // memory per tile would be most of its time)
+        int blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0;
+        if (p.paged) {
+            blk = (int)(first / p.tiles_per_block);
+            sub = (int)(first - (int64_t)blk * p.tiles_per_block);
+            step_blk = (int)(stride / p.tiles_per_block);
+            step_sub = (int)(stride - (int64_t)step_blk * p.tiles_per_block);
+            if (my_tiles > 0) nxt_id = __ldg(p.ids + blk);
+        }
         while (mm < my_tiles) {
             bool progress = false;
             if (ld < my_tiles) {
                 const int s = (int)(ld % kStagesA);
                 if (mbar_test(&bars->empty[s], (uint32_t)(((ld / kStagesA) & 1) ^ 1))) {
-                    const int64_t tile = first + ld * stride;
                     unsigned char* dst = sA + (size_t)s * kTileBytes;
                     mbar_expect_tx(&bars->full[s], kTileBytes);
                     if (p.paged) {
-                        const int64_t blk = tile / p.tiles_per_block;
-                        const int sub = (int)(tile - blk * p.tiles_per_block);
-                        const int id = __ldg(p.ids + blk);
+                        const int id = nxt_id;
                         const int t0 = sub * (kTileM / p.H);
                         // an id outside the cache reads outside the tensor map: TMA fills zeros, the tile's codes are not stored
                         tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
                         tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
+                        sub += step_sub;
+                        blk += step_blk;
+                        if (sub >= p.tiles_per_block) {
+                            sub -= p.tiles_per_block;
+                            ++blk;
+                        }
+                        if (ld + 1 < my_tiles) nxt_id = __ldg(p.ids + blk);
                     } else {
-                        const int row0 = (int)(tile * kTileM);
+                        const int row0 = (int)((first + ld * stride) * kTileM);
                         tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
                         tma_load_2d(dst + kHalfBytes, &tmap, 64, row0, &bars->full[s]);
                     }
@@ -274,9 +293,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 }
             }
             if (mm < ld) {
-                const int s = (int)(mm % kStagesA), a = (int)(mm & 1);
+                const int s = (int)(mm % kStagesA), a = (int)(mm % kAcc);
                 if (mbar_test(&bars->full[s], (uint32_t)((mm / kStagesA) & 1)) &&
-                    mbar_test(&bars->acc_empty[a], (uint32_t)(((mm >> 1) & 1) ^ 1))) {
+                    mbar_test(&bars->acc_empty[a], (uint32_t)(((mm / kAcc) & 1) ^ 1))) {
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileBytes);
 #pragma unroll
@@ -298,14 +317,14 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 break;
             }
         }
-    } else if (warp == 0) {
+    } else if (warp == 0 || warp == 2 || warp == 3) {
         // ------------------------------------------------------------------ fixer: exact chains for the queued bits
         // The fp32 FMA chain over d, in order, from the tile and the weights in shared memory; one lane per
         // queued code word (usually one doubtful bit in it).  The lane settles the bits and stores the word.
         // The stage is held until the vector is in registers, and with two stages that delay goes straight
         // into the load of the tile after next: what does not depend on the queue (where the tile's codes
         // go) is worked out while waiting.
-        for (int64_t it = 0; it < my_tiles; ++it) {
+        for (int64_t it = (warp + 1) >> 1; it < my_tiles; it += kFixers) {     // warps 0, 2, 3 -> fixers 0, 1, 2
             const int s = (int)(it % kStagesA);
             const uint32_t par = (uint32_t)((it / kStagesA) & 1);
             const int64_t tile = first + it * stride;
@@ -317,13 +336,15 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 id = checked_block_id(p.ids, blk, p.cache_blocks, nullptr);
                 slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, nullptr);
             }
-            if (!mbar_wait(&bars->fix_ready[s], par)) {
+            // First the tile's landing, then its epilogue.  The order matters: a parity wait is only right for a
+            // barrier that is at most one phase behind, and this warp may come here while the buffer's previous
+            // tile (another fixer's) is still in its epilogue; the landing of this tile, however, comes after that.
+            if (!mbar_wait(&bars->full[s], par) || !mbar_wait(&bars->fix_ready[s], par)) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 1);
                 break;
             }
             if (*(volatile int32_t*)&bars->abort_flag) break;
-            (void)mbar_wait(&bars->full[s], par);              // already complete: acquires the TMA-written tile
             const int n = (int)min(*(volatile uint32_t*)&bars->fix_n[s], (uint32_t)kFixSlots);
             const unsigned char* xa = sA + (size_t)s * kTileBytes;
             const uint4* q = fixq + s * kFixSlots;
@@ -365,6 +386,13 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     pend &= pend - 1;
                     const int col = cw * 32 + j;
                     float acc = 0.0f;
+                    // (the vector stays packed: without this the compiler widens all 128 values to fp32 ahead of the
+                    // loop over the doubtful bits and spills half of them)
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4)
+                        asm volatile("" : "+r"(xv[c].x), "+r"(xv[c].y), "+r"(xv[c].z), "+r"(xv[c].w), "+r"(xv[c + 1].x), "+r"(xv[c + 1].y),
+                                          "+r"(xv[c + 1].z), "+r"(xv[c + 1].w), "+r"(xv[c + 2].x), "+r"(xv[c + 2].y), "+r"(xv[c + 2].z),
+                                          "+r"(xv[c + 2].w), "+r"(xv[c + 3].x), "+r"(xv[c + 3].y), "+r"(xv[c + 3].z), "+r"(xv[c + 3].w));
 #pragma unroll
                     for (int c = 0; c < 16; ++c) {
                         const uint4 wv = *reinterpret_cast<const uint4*>(sB + sw_offset(col, c * 8));
@@ -390,27 +418,29 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 if (orow >= 0) reinterpret_cast<uint32_t*>(p.out + orow * 16)[cw] = word;
             }
         }
-    } else if (warp >= 2) {
+    } else if (warp >= kFirstSetWarp) {
         // ------------------------------------------------------------------ epilogue: signs, margin test, exact fallback
         const int q = warp & 3;                  // the TMEM lane quarter this warp may read
         const int m = q * 32 + lane;             // tile row = vector
         // Paged: which list entry and which tile of its block a tile is, advanced without divisions; the entry's cache
         // block and code-table row group are asked for one tile ahead, so the stores at the end of a tile never wait.
+        const int set = (warp - kFirstSetWarp) >> 2;
         int tok = 0, h = 0, blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0, nxt_slot = 0;
         if (p.paged) {
             tok = m / p.H;
             h = m - tok * p.H;
-            blk = (int)(first / p.tiles_per_block);
-            sub = (int)(first - (int64_t)blk * p.tiles_per_block);
-            step_blk = (int)(stride / p.tiles_per_block);
-            step_sub = (int)(stride - (int64_t)step_blk * p.tiles_per_block);
-            if (my_tiles > 0) {
+            const int64_t mine0 = first + (int64_t)set * stride, step = (int64_t)kSets * stride;   // this set's first tile, and its stride
+            blk = (int)(mine0 / p.tiles_per_block);
+            sub = (int)(mine0 - (int64_t)blk * p.tiles_per_block);
+            step_blk = (int)(step / p.tiles_per_block);
+            step_sub = (int)(step - (int64_t)step_blk * p.tiles_per_block);
+            if (set < my_tiles) {
                 nxt_id = __ldg(p.ids + blk);
                 nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
             }
         }
-        for (int64_t it = 0; it < my_tiles; ++it) {
-            const int s = (int)(it % kStagesA), a = (int)(it & 1);
+        for (int64_t it = set; it < my_tiles; it += kSets) {
+            const int s = (int)(it % kStagesA), a = (int)(it % kAcc);
             int64_t orow;                         // where this row's code goes (-1: nowhere)
             if (p.paged) {
                 int id = nxt_id;
@@ -431,7 +461,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     sub -= p.tiles_per_block;
                     ++blk;
                 }
-                if (it + 1 < my_tiles) {
+                if (it + kSets < my_tiles) {
                     nxt_id = __ldg(p.ids + blk);
                     nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
                 }
@@ -439,7 +469,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 const int64_t v = (first + it * stride) * kTileM + m;
                 orow = v < p.n_vec ? v : -1;
             }
-            if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it >> 1) & 1))) {
+            if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it / kAcc) & 1))) {
                 bars->abort_flag = 1;
                 if (p.err) atomicExch(p.err, 1);
                 break;
@@ -575,8 +605,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 }
                 const int total = __shfl_sync(0xffffffffu, incl, 31);
                 if (total > 0) {
-                    uint16_t* list = fb_list + (warp - 2) * kFallbackSlots;
-                    uint8_t* res = fb_res + (warp - 2) * kFallbackSlots;
+                    uint16_t* list = fb_list + (warp - kFirstSetWarp) * kFallbackSlots;
+                    uint8_t* res = fb_res + (warp - kFirstSetWarp) * kFallbackSlots;
                     int pos = incl - mine;
 #pragma unroll
                     for (int cw = 0; cw < 4; ++cw) {
@@ -649,7 +679,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAcc * kBits) : "memory");
     }
 }
 
@@ -703,9 +733,9 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.n_tiles = (n_vec + kTileM - 1) / kTileM;
     }
     if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
-    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
+    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
     UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int64_t grid = (int64_t)sm_count() * 2;
+    int64_t grid = (int64_t)sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
     hash_encode_tc_kernel<<<(unsigned)grid, kThreads, smem, st>>>(tmap, p);
     UCMX_LAUNCH_CHECK("hash_encode_tc_kernel");
