@@ -41,6 +41,7 @@ constexpr int kFirstSetWarp = 4;                  // a multiple of four: warp w 
 constexpr int kThreads = 32 * (kFirstSetWarp + 4 * kSets);   // warps 0, 2, 3: exact-chain fixers, warp 1: TMA + MMA issue and TMEM owner, warps 4-15: epilogue sets
 constexpr float kTau = 1.0f / 32768.0f;           // 2^-15
 constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
+constexpr int kIdAhead = 8;                       // block ids the issuing thread asks for ahead of the tile it loads
 constexpr int kFixSlots = 128;                    // code words with doubtful bits a fixer warp takes per tile (about 5 are typical)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -187,7 +188,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // epilogue warps x kFallbackSlots
     uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kSets * kFallbackSlots);
     uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kSets * kFallbackSlots);   // max_j |w_j|
-    uint4* fixq = reinterpret_cast<uint4*>(wmax_bits + 4);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
+    int32_t* id_ring = reinterpret_cast<int32_t*>(wmax_bits + 4);   // kIdAhead block ids on their way to the issuing thread
+    uint4* fixq = reinterpret_cast<uint4*>(id_ring + kIdAhead);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -252,16 +254,28 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         const uint32_t b_addr = smem_u32(sB);
         int64_t ld = 0, mm = 0;
         uint32_t idle = 0;
-        // paged: list entry and tile of its block of the next tile to load, advanced without divisions; the entry's
-        // cache block is asked for one tile ahead (this thread issues every load and every MMA of the SM: a trip to
-        // memory per tile would be most of its time)
-        int blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0;
+        // paged: the tile of its block the next tile to load is, and the list entry of the tile kIdAhead further on,
+        // both advanced without divisions.  This thread issues every load and every MMA of the SM, so a trip to
+        // memory per tile for the entry's cache block would be most of its time: the ids come through a small ring
+        // in shared memory filled by asynchronous 4-byte copies, one commit group per tile, kIdAhead tiles ahead.
+        int sub = 0, step_blk = 0, step_sub = 0, ablk = 0, asub = 0;
+        auto ask_id = [&](int64_t t) {                  // the id of this thread block's tile t, into the ring
+            if (t < my_tiles)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(id_ring + (t % kIdAhead))), "l"(p.ids + ablk) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asub += step_sub;
+            ablk += step_blk;
+            if (asub >= p.tiles_per_block) {
+                asub -= p.tiles_per_block;
+                ++ablk;
+            }
+        };
         if (p.paged) {
-            blk = (int)(first / p.tiles_per_block);
-            sub = (int)(first - (int64_t)blk * p.tiles_per_block);
+            ablk = (int)(first / p.tiles_per_block);
+            sub = asub = (int)(first - (int64_t)ablk * p.tiles_per_block);
             step_blk = (int)(stride / p.tiles_per_block);
             step_sub = (int)(stride - (int64_t)step_blk * p.tiles_per_block);
-            if (my_tiles > 0) nxt_id = __ldg(p.ids + blk);
+            for (int t = 0; t < kIdAhead; ++t) ask_id(t);
         }
         while (mm < my_tiles) {
             bool progress = false;
@@ -271,18 +285,15 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     unsigned char* dst = sA + (size_t)s * kTileBytes;
                     mbar_expect_tx(&bars->full[s], kTileBytes);
                     if (p.paged) {
-                        const int id = nxt_id;
+                        asm volatile("cp.async.wait_group %0;" ::"n"(kIdAhead - 1) : "memory");   // this tile's id has arrived
+                        const int id = *(volatile int32_t*)(id_ring + (ld % kIdAhead));
                         const int t0 = sub * (kTileM / p.H);
                         // an id outside the cache reads outside the tensor map: TMA fills zeros, the tile's codes are not stored
                         tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
                         tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
+                        ask_id(ld + kIdAhead);                  // (into the slot just read)
                         sub += step_sub;
-                        blk += step_blk;
-                        if (sub >= p.tiles_per_block) {
-                            sub -= p.tiles_per_block;
-                            ++blk;
-                        }
-                        if (ld + 1 < my_tiles) nxt_id = __ldg(p.ids + blk);
+                        if (sub >= p.tiles_per_block) sub -= p.tiles_per_block;
                     } else {
                         const int row0 = (int)((first + ld * stride) * kTileM);
                         tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
@@ -733,7 +744,7 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.n_tiles = (n_vec + kTileM - 1) / kTileM;
     }
     if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
-    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
+    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + kIdAhead * 4 + (size_t)kStagesA * kFixSlots * 16 + 128;
     UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = (int64_t)sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
