@@ -4,7 +4,9 @@
 // blocks, N = K = 128; about 120 flop per byte moved), so it belongs on tcgen05: 128-vector tiles of
 // the paged cache are brought in by tiled TMA loads (128-byte swizzle, the layout the MMA unit reads),
 // one elected thread issues eight tcgen05.mma (M128 N128 K16, bf16 in, fp32 accumulate in TMEM) per
-// tile, and four epilogue warps read the accumulator back with tcgen05.ld, take signs and pack bits.
+// tile, and sets of four epilogue warps read the accumulator back with tcgen05.ld, take signs and pack bits.
+// One thread block per SM: five tile buffers, four accumulators (all 512 TMEM columns), three epilogue sets
+// that take the tiles in turn, three fixer warps (below) and one thread that issues every load and MMA.
 //
 // Codes must be bit-identical to the checker's definition - the sign of an fp32 fused-multiply-add
 // chain over d = 0..127 - while the tensor core adds in its own order.  With S the exact sum, the chain
@@ -332,9 +334,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         // ------------------------------------------------------------------ fixer: exact chains for the queued bits
         // The fp32 FMA chain over d, in order, from the tile and the weights in shared memory; one lane per
         // queued code word (usually one doubtful bit in it).  The lane settles the bits and stores the word.
-        // The stage is held until the vector is in registers, and with two stages that delay goes straight
-        // into the load of the tile after next: what does not depend on the queue (where the tile's codes
-        // go) is worked out while waiting.
+        // The tile's buffer is held until the vectors are in registers; what does not depend on the queue
+        // (where the tile's codes go) is worked out while waiting.
         for (int64_t it = (warp + 1) >> 1; it < my_tiles; it += kFixers) {     // warps 0, 2, 3 -> fixers 0, 1, 2
             const int s = (int)(it % kStagesA);
             const uint32_t par = (uint32_t)((it / kStagesA) & 1);
