@@ -92,28 +92,40 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs.  nvidia-smi takes a while to
+    deliver its first line (longer than a short timed region), so it is started ahead of the warm-up steps, waited
+    for, and the lines are picked by their time stamps: those between begin() and stop(), else - a timed region
+    shorter than the sampling period - those of the warm-up steps of the same workload just before it."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.t_begin = None
 
-    def start(self):
+    def start(self, wait_s: float = 3.0):
         try:
             fd, self.path = tempfile.mkstemp(prefix="ucmx_clocks_", suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                  "-lms", "25", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+            t0 = time.time()
+            while time.time() - t0 < wait_s and os.path.getsize(self.path) == 0:     # until the first line is there
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
+    def begin(self):
+        """The timed region starts now."""
+        self.t_begin = time.time()
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        t_end = time.time()
         if self.proc is None:
             return out
         try:
@@ -126,21 +138,26 @@ class ClockSampler:
             os.remove(self.path)
         except Exception:
             return out
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        parsed = []
         for r in rows:
-            if len(r) < 6:
+            if len(r) < 7:
                 continue
             try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
+                ts = datetime.datetime.strptime(r[0].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                parsed.append((ts, float(r[1]), float(r[2]), [n for n, v in zip(names, r[3:7]) if v.strip().lower() == "active"]))
             except ValueError:
                 continue
-            for name, v in zip(names, r[2:6]):
-                if v.strip().lower() == "active":
-                    reasons.add(name)
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        begin = self.t_begin if self.t_begin is not None else 0.0
+        window = "timed region"
+        picked = [x for x in parsed if begin <= x[0] <= t_end]
+        if not picked:
+            window = "warm-up steps just before the timed region (the region is shorter than the sampling period)"
+            picked = [x for x in parsed if begin - 0.25 <= x[0] <= t_end + 0.05]
+        if picked:
+            out.update(sm_mhz=statistics.median(x[1] for x in picked), sm_max_mhz=max(x[2] for x in picked),
+                       reasons=sorted({n for x in picked for n in x[3]}), samples=len(picked), window=window)
         return out
 
 
@@ -585,9 +602,10 @@ def run_offload(args, rank, world, local_rank, dev, barrier):
     link_h2d = payload / timed(lambda: stage.copy_(host, non_blocking=True), 2) / 1e6
     sampler = ClockSampler(local_rank)
     launches_before = _native.launch_count
+    sampler.start()
     barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.begin()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(args.steps):
@@ -1109,6 +1127,8 @@ def main():
             eng.drift_queries()            # the next decode step's queries (device-side, part of the step's input)
         eng.step()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         one_step()
     torch.cuda.synchronize()
@@ -1118,12 +1138,11 @@ def main():
     if not use_graph:
         gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                for _ in range(args.steps * ((eng.L + every - 1) // every))]
-    sampler = ClockSampler(local_rank)
     launches_before = _native.launch_count
     loads = []
     barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.begin()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     if use_graph:

@@ -236,8 +236,9 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
     const int end = min(begin + p.rows_per_warp, p.total);
     // An early launch reads its inputs (offsets, slot ids, table rows, queries: none of them written by the kernel
     // ahead) while that kernel's last thread blocks are still running, and waits for its end only before its own
-    // first store; the kernel behind this one is let in right away on the same terms.
-    if (p.early) early_start_allow();
+    // first store.  The kernel behind this one is let in right away, whichever it is: another scoring launch on the
+    // same terms, or the top-k, which is always launched that way and waits for this kernel's end before it reads.
+    early_start_allow();
 
     using RD = RowDot<DT, QN>;
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);

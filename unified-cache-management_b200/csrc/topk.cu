@@ -163,6 +163,9 @@ __global__ void __launch_bounds__(1024) topk_ragged_kernel(TopkParams p)
     // A scoring kernel launched for an early start behind this one may begin now: it stores nothing before this
     // kernel has ended.  (Not with a peer exchange: that scoring kernel is never launched early.)
     if (!PEER) early_start_allow();
+    // This kernel itself is launched so that its thread blocks may be placed while the kernel ahead of it (the
+    // scoring) is still running; everything it reads comes from that kernel, so it waits for its end right here.
+    early_start_wait();
     const int base = __ldg(p.offsets + r);
     const int n = __ldg(p.offsets + r + 1) - base;
     const int k = __ldg(p.k_per_req + r);
@@ -541,7 +544,22 @@ static int32_t topk_launch(const void* scores, int32_t score_dtype, const int32_
     // block size: enough threads for a few candidates each (the host does not know the ragged sizes, only the
     // output width, so k is the hint), never fewer than the rank sort of up to 256 winners needs
     const int threads = out_stride <= 64 ? 512 : 1024;     // measured on 64 requests of ~520 candidates: 512 threads 6.9 us, 256 7.2, 128 8.3
-    kern<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
+    if (px.world == 0) {
+        // (the launch latency of this small kernel is a fifth of its run time: let it overlap the tail of the scoring)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_req);
+        cfg.blockDim = dim3((unsigned)threads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        UCMX_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    } else {
+        kern<<<n_req, threads, smem, (cudaStream_t)stream>>>(p);
+    }
     UCMX_LAUNCH_CHECK("topk_ragged_kernel");
     return UCMX_OK;
 }
