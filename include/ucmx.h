@@ -228,7 +228,10 @@ int32_t ucmx_score_hamming(const uint8_t* codes, int64_t n_slots, int32_t n_kv_h
  * out_offsets[r+1]-out_offsets[r] (<= out_stride) entries, which packs the rows back to back.
  * Entries beyond out_counts[r] are left untouched.  out_idx[j] is the candidate's position within
  * its request, or id_map[req_offsets[r]+position] when id_map is given.  out_scores (same dtype as
- * scores) may be NULL. */
+ * scores) may be NULL.
+ * The kernel is launched with programmatic stream serialization and waits for the end of the kernel
+ * ahead of it before it reads anything: stream order is what it always was, only the kernel's
+ * placement on the SMs overlaps the tail of the scoring kernel in front of it. */
 #define UCMX_WIN_NONE 0
 #define UCMX_WIN_FORCE 1
 #define UCMX_WIN_EXCLUDE 2
