@@ -61,10 +61,17 @@ def test_scoring_launched_early_behind_a_topk_changes_nothing():
     stride = int(batch.k_per_req.max())
     scores = torch.empty((batch.total,), dtype=torch.float32, device=DEV)
 
+    qbar = [ops.query_group_mean(q[i], H) for i in range(n_tab)]     # (made ahead of time: an early launch may not read
+    torch.cuda.synchronize()                                          #  what the kernel in front of it writes)
+
     def run(early, ids, vals, kept):
         for i in range(n_tab):
-            ops.score_dot_query(reps[i], off, q[i], total=batch.total, slot_ids=table, n_kv_heads=H, out=scores,
-                                early=early and i > 0)
+            if i % 2 == 0:
+                ops.score_dot_query(reps[i], off, q[i], total=batch.total, slot_ids=table, n_kv_heads=H, out=scores,
+                                    early=early and i > 0)
+            else:                                                     # the two-call form, fp32 queries
+                ops.score_dot(reps[i], off, qbar[i], total=batch.total, slot_ids=table, n_kv_heads=H, head_dim=D,
+                              out=scores, early=early)
             if kept is not None:
                 kept[i].copy_(scores)
             ops.topk_ragged(scores, off, kk, out_stride=stride, id_map=table, out_idx=ids[i], out_scores=vals[i])

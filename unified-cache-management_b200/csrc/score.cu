@@ -596,6 +596,44 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
     }
 }
 
+// N partial sums per lane, each to be added up over the 16 lanes of a half-warp: instead of N butterflies of four
+// steps, the lanes first split the values between them - at distance 1 the even lanes keep the lower half of the
+// values and the odd lanes the upper half, each adding what its neighbour sends, and so on with half as many values
+// at twice the distance - and the steps that are left finish the one value a lane still holds.  The lane ends up
+// with the total of value number (bit 0 of the lane, bit 1, ...) read as a binary number from the top:
+// N - 1 + (4 - log2 N) shuffles instead of 4 N.
+template <int N, int DIST>
+__device__ __forceinline__ float half_warp_sums(float (&v)[N], int lane)
+{
+    if constexpr (N == 1) {
+        float x = v[0];
+#pragma unroll
+        for (int o = DIST; o < 16; o <<= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        return x;
+    } else {
+        static_assert(DIST < 16, "at most sixteen values");
+        float w[N / 2];
+        const bool upper = (lane & DIST) != 0;
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            const float keep = upper ? v[i + N / 2] : v[i];
+            const float send = upper ? v[i] : v[i + N / 2];
+            w[i] = keep + __shfl_xor_sync(0xffffffffu, send, DIST);
+        }
+        return half_warp_sums<N / 2, DIST * 2>(w, lane);
+    }
+}
+
+// eight products of fp32 q with a 16-byte piece of bf16 values, as four packed multiply-adds
+__device__ __forceinline__ float dot8_packed(const float4& q0, const float4& q1, const uint4& x)
+{
+    float2 s0 = __fmul2_rn(make_float2(q0.x, q0.y), make_float2(bf16lo(x.x), bf16hi(x.x)));
+    float2 s1 = __fmul2_rn(make_float2(q0.z, q0.w), make_float2(bf16lo(x.y), bf16hi(x.y)));
+    s0 = __ffma2_rn(make_float2(q1.x, q1.y), make_float2(bf16lo(x.z), bf16hi(x.z)), s0);
+    s1 = __ffma2_rn(make_float2(q1.z, q1.w), make_float2(bf16lo(x.w), bf16hi(x.w)), s1);
+    return (s0.x + s1.x) + (s0.y + s1.y);
+}
+
 // The same for the shape GSA uses - bf16, 128 channels per head, a power-of-two number of representatives - with
 // the whole row in flight at once: a vector of 128 bf16 is 16 lanes of 16 bytes, so a warp-wide load brings two
 // vectors (for two representatives per head: both representatives of one head), NV = H * n_rep / 2 loads bring the
@@ -635,30 +673,24 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_reps_kernel(ScoreGenP
             r_end = __ldg(p.offsets + r + 1);
         }
         const float* qr = p.q + (int64_t)r * kHeads * 128 + pc * 8;
-        float total = 0.0f;
+        // every load's dot product with its head's query (this lane's eight channels), then all NV of them summed
+        // over the half-warp at once: the lane is left with the product of load number sel(lane)
+        float part[NV];
 #pragma unroll
         for (int h = 0; h < kHeads; ++h) {
             const float4 q0 = __ldg(reinterpret_cast<const float4*>(qr + h * 128));
             const float4 q1 = __ldg(reinterpret_cast<const float4*>(qr + h * 128) + 1);
-            float best = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < kLoadsPerHead; ++j) {
-                const uint4 x = v[h * kLoadsPerHead + j];
-                float acc = q0.x * bf16lo(x.x);
-                acc = fmaf(q0.y, bf16hi(x.x), acc);
-                acc = fmaf(q0.z, bf16lo(x.y), acc);
-                acc = fmaf(q0.w, bf16hi(x.y), acc);
-                acc = fmaf(q1.x, bf16lo(x.z), acc);
-                acc = fmaf(q1.y, bf16hi(x.z), acc);
-                acc = fmaf(q1.z, bf16lo(x.w), acc);
-                acc = fmaf(q1.w, bf16hi(x.w), acc);
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                best = fmaxf(best, acc);
-            }
-            best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 16));
-            total += best;
+            for (int j = 0; j < kLoadsPerHead; ++j) part[h * kLoadsPerHead + j] = dot8_packed(q0, q1, v[h * kLoadsPerHead + j]);
         }
+        float total = half_warp_sums<NV, 1>(part, lane);
+        // load i = h * kLoadsPerHead + j sits in the lane whose low bits, most significant first, spell i: the loads of
+        // one head differ in the lane bits from kHeads upwards, the heads in the bits below
+#pragma unroll
+        for (int o = kHeads; o < NV; o <<= 1) total = fmaxf(total, __shfl_xor_sync(0xffffffffu, total, o));
+        total = fmaxf(total, __shfl_xor_sync(0xffffffffu, total, 16));        // the other half-warp's representatives
+#pragma unroll
+        for (int o = 1; o < kHeads; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if (lane == 0) p.out[c] = total * p.scale;
         (void)half;
     }
@@ -1118,39 +1150,36 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_heads_rows_kernel(Sco
             r_end = __ldg(p.offsets + r + 1);
         }
         const uint16_t* qr = p.q + (int64_t)r * p.q_stride + pc * 8;
+        // Per KV head: the G x kLoadsPerHead dot products of this lane's eight channels, summed over the half-warp all
+        // at once (half_warp_sums); value gi * kLoadsPerHead + j ends up in the lane whose low bits spell it, so the
+        // maximum over a head's loads is taken between lanes G and more apart, the other half-warp holds the other
+        // representatives, and each lane adds up the best of "its" query head over the KV heads.
         float total = 0.0f;
 #pragma unroll
         for (int h = 0; h < kHeads; ++h) {
-            float best[G];
-            uint4 qv[G];
+            float part[G * kLoadsPerHead];
 #pragma unroll
             for (int gi = 0; gi < G; ++gi) {
-                qv[gi] = __ldg(reinterpret_cast<const uint4*>(qr + (size_t)(h * G + gi) * 128));
-                best[gi] = -INFINITY;
-            }
+                const uint4 qv = __ldg(reinterpret_cast<const uint4*>(qr + (size_t)(h * G + gi) * 128));
+                const float2 qa = make_float2(bf16lo(qv.x), bf16hi(qv.x)), qb = make_float2(bf16lo(qv.y), bf16hi(qv.y));
+                const float2 qc = make_float2(bf16lo(qv.z), bf16hi(qv.z)), qd = make_float2(bf16lo(qv.w), bf16hi(qv.w));
 #pragma unroll
-            for (int j = 0; j < kLoadsPerHead; ++j) {
-                const uint4 x = v[h * kLoadsPerHead + j];
-                const float x0 = bf16lo(x.x), x1 = bf16hi(x.x), x2 = bf16lo(x.y), x3 = bf16hi(x.y);
-                const float x4 = bf16lo(x.z), x5 = bf16hi(x.z), x6 = bf16lo(x.w), x7 = bf16hi(x.w);
-#pragma unroll
-                for (int gi = 0; gi < G; ++gi) {
-                    float acc = bf16lo(qv[gi].x) * x0;
-                    acc = fmaf(bf16hi(qv[gi].x), x1, acc);
-                    acc = fmaf(bf16lo(qv[gi].y), x2, acc);
-                    acc = fmaf(bf16hi(qv[gi].y), x3, acc);
-                    acc = fmaf(bf16lo(qv[gi].z), x4, acc);
-                    acc = fmaf(bf16hi(qv[gi].z), x5, acc);
-                    acc = fmaf(bf16lo(qv[gi].w), x6, acc);
-                    acc = fmaf(bf16hi(qv[gi].w), x7, acc);
-#pragma unroll
-                    for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                    best[gi] = fmaxf(best[gi], acc);
+                for (int j = 0; j < kLoadsPerHead; ++j) {
+                    const uint4 x = v[h * kLoadsPerHead + j];
+                    float2 s0 = __fmul2_rn(qa, make_float2(bf16lo(x.x), bf16hi(x.x)));
+                    float2 s1 = __fmul2_rn(qb, make_float2(bf16lo(x.y), bf16hi(x.y)));
+                    s0 = __ffma2_rn(qc, make_float2(bf16lo(x.z), bf16hi(x.z)), s0);
+                    s1 = __ffma2_rn(qd, make_float2(bf16lo(x.w), bf16hi(x.w)), s1);
+                    part[gi * kLoadsPerHead + j] = (s0.x + s1.x) + (s0.y + s1.y);
                 }
             }
+            float best = half_warp_sums<G * kLoadsPerHead, 1>(part, lane);
 #pragma unroll
-            for (int gi = 0; gi < G; ++gi) total += fmaxf(best[gi], __shfl_xor_sync(0xffffffffu, best[gi], 16));
+            for (int o = G; o < G * kLoadsPerHead; o <<= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+            total += fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 16));
         }
+#pragma unroll
+        for (int o = 1; o < G; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if (lane == 0) {
             float wgt = total * inv;
             if (p.include_mask && __ldg(p.include_mask + c)) wgt = INFINITY;
