@@ -23,6 +23,7 @@ static submit_fn g_submit;
 static wait_fn g_wait;
 static get_fn g_get;
 static PyObject* g_on_error;   /* callable(function name, status): raises */
+static PyObject *g_key_indices, *g_key_scores;   /* the result dictionary's keys, made once */
 
 #define UCMX_ENOOBJ (-50005)
 
@@ -176,7 +177,7 @@ static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
     }
     self->shape[slot].rid = -1;
     PyObject* d = PyDict_New();
-    if (!d || PyDict_SetItemString(d, "indices", indices) < 0 || PyDict_SetItemString(d, "scores", scores) < 0) {
+    if (!d || PyDict_SetItem(d, g_key_indices, indices) < 0 || PyDict_SetItem(d, g_key_scores, scores) < 0) {
         Py_XDECREF(d);
         d = NULL;
     }
@@ -227,6 +228,9 @@ PyMODINIT_FUNC PyInit__ucmx_fast(void)
 {
     import_array();
     if (PyType_Ready(&FastBackendType) < 0) return NULL;
+    g_key_indices = PyUnicode_InternFromString("indices");
+    g_key_scores = PyUnicode_InternFromString("scores");
+    if (!g_key_indices || !g_key_scores) return NULL;
     PyObject* m = PyModule_Create(&moddef);
     if (!m) return NULL;
     Py_INCREF(&FastBackendType);

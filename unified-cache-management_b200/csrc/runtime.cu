@@ -11,6 +11,7 @@
 #include <new>
 #include <thread>
 #include <atomic>
+#include <optional>
 #include <unordered_map>
 #include <vector>
 
@@ -212,7 +213,7 @@ struct PinnedBuf {
         size_t ncap = cap ? cap : (size_t)64 << 10;
         while (ncap < want) ncap *= 2;
         unsigned char* np = nullptr;
-        UCMX_CUDA(cudaHostAlloc((void**)&np, ncap, cudaHostAllocPortable));
+        UCMX_CUDA(cudaHostAlloc((void**)&np, ncap, cudaHostAllocPortable | cudaHostAllocMapped));   // (kernels of any device may write into it)
         if (p) {
             memcpy(np, p, size);
             cudaFreeHost(p);
@@ -268,6 +269,53 @@ struct Request {
     int32_t row0 = 0, rows = 0, k = 0;
 };
 
+// The requests that have been submitted and not collected yet, by request id.  Ids are handed out in sequence and
+// collected soon after, so a request lives in the slot its id's low bits name (no allocation per request, which is
+// what a node-based map costs on each submit and each get_result); an id whose slot is still taken by a request
+// from kLiveSlots ids ago goes to a map instead.
+constexpr int32_t kLiveSlots = 1 << 14;
+struct LiveTable {
+    struct Slot {
+        int32_t id = -1;
+        Request rq;
+    };
+    std::vector<Slot> slots{(size_t)kLiveSlots};
+    std::unordered_map<int32_t, Request> spill;
+
+    Request* find(int32_t id)
+    {
+        if (id < 0) return nullptr;
+        Slot& s = slots[(size_t)(id & (kLiveSlots - 1))];
+        if (s.id == id) return &s.rq;
+        if (spill.empty()) return nullptr;
+        auto it = spill.find(id);
+        return it == spill.end() ? nullptr : &it->second;
+    }
+    void insert(int32_t id, const Request& rq)
+    {
+        Slot& s = slots[(size_t)(id & (kLiveSlots - 1))];
+        if (s.id < 0) {
+            s.id = id;
+            s.rq = rq;
+        } else {
+            spill[id] = rq;
+        }
+    }
+    void erase(int32_t id)
+    {
+        Slot& s = slots[(size_t)(id & (kLiveSlots - 1))];
+        if (s.id == id) s.id = -1;
+        else spill.erase(id);
+    }
+    template <typename F>
+    void for_each(F&& f)
+    {
+        for (Slot& s : slots)
+            if (s.id >= 0) f(s.rq);
+        for (auto& kv : spill) f(kv.second);
+    }
+};
+
 }  // namespace
 }  // namespace ucmx
 
@@ -281,7 +329,7 @@ struct ucmx_retrieval {
     std::mutex mu;
     int32_t next_id = 0;
     int64_t launches = 0;
-    std::unordered_map<int32_t, ucmx::Request> live;
+    ucmx::LiveTable live;
     ucmx::Batch* building = nullptr;
     std::vector<ucmx::Batch*> pool;
 };
@@ -376,7 +424,10 @@ int32_t flush_locked(ucmx_retrieval* r)
     int32_t* d_ooff = (int32_t*)((unsigned char*)d_off + m_off);
     int32_t* d_k = (int32_t*)((unsigned char*)d_off + 2 * m_off);
     float* d_scores = (float*)(d + s_q + s_idx + s_meta);
-    unsigned char* d_out = (unsigned char*)d_scores + s_scores;
+    // The selection goes straight into the pinned host buffer (mapped into every device's address space; with unified
+    // addressing the host pointer is the device pointer): 8 bytes per winner, written once by the top-k kernel, and a
+    // copy back - one more operation for the stream and for the host to wait for - is not needed.
+    unsigned char* d_out = b->h_out.p;
     int32_t* d_counts = (int32_t*)d_out;
     int32_t* d_oidx = (int32_t*)(d_out + b->o_counts);
     float* d_osc = (float*)(d_out + b->o_counts + b->o_idx);
@@ -391,10 +442,9 @@ int32_t flush_locked(ucmx_retrieval* r)
                               d_slots, b->kmax, d_ooff, d_oidx, d_osc, d_counts, st);
     if (rc != UCMX_OK) return fail(rc);
     r->launches += ksum > 0 ? 2 : 1;
-    if (ksum == 0) e = cudaMemsetAsync(d_counts, 0, rows * 4, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(b->h_out.p, d_out, out_bytes, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaEventRecord(b->done, st);
-    if (e != cudaSuccess) return fail(cuda_status("submit D2H", e));
+    if (ksum == 0) memset(d_counts, 0, rows * 4);          // (nothing was launched that writes there)
+    e = cudaEventRecord(b->done, st);
+    if (e != cudaSuccess) return fail(cuda_status("submit event", e));
     return UCMX_OK;
 }
 
@@ -534,12 +584,19 @@ extern "C" int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_qu
             return UCMX_EPARAM;
         }
     }
-    DeviceGuard g(r->device);
-    if (!g.ok) return UCMX_EPARAM;
     std::lock_guard<std::mutex> lk(r->mu);
 
     Batch* b = r->building;
-    if (b && ((int32_t)b->kk.size() + batch > kFlushRows || (size_t)b->off.back() + cand > kFlushCandidates)) {
+    const bool full = b && ((int32_t)b->kk.size() + batch > kFlushRows || (size_t)b->off.back() + cand > kFlushCandidates);
+    // (the object's device is made current only for a CUDA call: a launch, or pinned memory for a buffer that grows;
+    // an ordinary submit is two memcpys into buffers that are there already)
+    const bool grows = !b || full || b->h_q.size + (size_t)batch * r->dim * 4 > b->h_q.cap || b->h_idx.size + cand * 4 > b->h_idx.cap;
+    std::optional<DeviceGuard> g;
+    if (grows) {
+        g.emplace(r->device);
+        if (!g->ok) return UCMX_EPARAM;
+    }
+    if (full) {
         flush_locked(r);           // a failure is recorded in that batch and reported to its own requests
         b = nullptr;
     }
@@ -574,7 +631,7 @@ extern "C" int32_t ucmx_retrieval_submit(ucmx_retrieval* r, const float* host_qu
     if (k > b->kmax) b->kmax = k;
     b->open += 1;
     const int32_t id = r->next_id++;
-    r->live[id] = rq;
+    r->live.insert(id, rq);
     *req_id = id;
     return UCMX_OK;
 }
@@ -603,9 +660,9 @@ extern "C" int32_t ucmx_retrieval_poll(ucmx_retrieval* r, int32_t req_id, int32_
     DeviceGuard g(r->device);
     std::lock_guard<std::mutex> lk(r->mu);
     *ready = 0;
-    auto it = r->live.find(req_id);
-    if (it == r->live.end()) return UCMX_OK;  // the reference's poll answers "not there" with false, not an error
-    Batch* b = it->second.batch;
+    Request* found = r->live.find(req_id);
+    if (!found) return UCMX_OK;  // the reference's poll answers "not there" with false, not an error
+    Batch* b = found->batch;
     if (!b->launched) flush_locked(r);
     if (b->failed) return UCMX_ERROR;
     const cudaError_t e = cudaEventQuery(b->done);
@@ -628,9 +685,9 @@ extern "C" int32_t ucmx_retrieval_wait(ucmx_retrieval* r, int32_t req_id)
     Batch* b = nullptr;
     {
         std::lock_guard<std::mutex> lk(r->mu);
-        auto it = r->live.find(req_id);
-        if (it == r->live.end()) return UCMX_ENOOBJ;  // "Bad req_id"
-        b = it->second.batch;
+        Request* found = r->live.find(req_id);
+        if (!found) return UCMX_ENOOBJ;  // "Bad req_id"
+        b = found->batch;
         // ESA waits for every request of a layer in turn: all but the first find their batch already complete
         if (b->launched && !b->failed && b->finished.load(std::memory_order_acquire)) return UCMX_OK;
         if (!b->launched) {
@@ -649,10 +706,10 @@ extern "C" int32_t ucmx_retrieval_result_shape(ucmx_retrieval* r, int32_t req_id
 {
     if (!r) return UCMX_EPARAM;
     std::lock_guard<std::mutex> lk(r->mu);
-    auto it = r->live.find(req_id);
-    if (it == r->live.end()) return UCMX_ENOOBJ;
-    if (batch) *batch = it->second.rows;
-    if (topk) *topk = it->second.k;
+    ucmx::Request* found = r->live.find(req_id);
+    if (!found) return UCMX_ENOOBJ;
+    if (batch) *batch = found->rows;
+    if (topk) *topk = found->k;
     return UCMX_OK;
 }
 
@@ -661,16 +718,16 @@ extern "C" int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, 
     using namespace ucmx;
     if (!r || !host_indices || !host_scores) return UCMX_EPARAM;
     std::lock_guard<std::mutex> lk(r->mu);
-    auto it = r->live.find(req_id);
-    if (it == r->live.end()) return UCMX_ENOOBJ;
-    const Request rq = it->second;
+    Request* found = r->live.find(req_id);
+    if (!found) return UCMX_ENOOBJ;
+    const Request rq = *found;
     Batch* b = rq.batch;
     if (!b->launched) {
         DeviceGuard g(r->device);
         flush_locked(r);
     }
     if (b->failed) {
-        r->live.erase(it);
+        r->live.erase(req_id);
         b->open -= 1;
         retire_if_done(r, b);
         return UCMX_ERROR;
@@ -698,7 +755,7 @@ extern "C" int32_t ucmx_retrieval_get_result(ucmx_retrieval* r, int32_t req_id, 
             host_scores[(size_t)i * k + j] = valid ? sc[o + j] : -INFINITY;
         }
     }
-    r->live.erase(it);
+    r->live.erase(req_id);
     b->open -= 1;
     retire_if_done(r, b);
     return UCMX_OK;
@@ -711,10 +768,10 @@ extern "C" int32_t ucmx_retrieval_destroy(ucmx_retrieval* r)
     DeviceGuard g(r->device);
     if (r->stream) cudaStreamSynchronize(r->stream);
     std::vector<Batch*> seen;
-    for (auto& kv : r->live) {
-        Batch* b = kv.second.batch;
+    r->live.for_each([&](Request& rq) {
+        Batch* b = rq.batch;
         if (b != r->building && std::find(seen.begin(), seen.end(), b) == seen.end()) seen.push_back(b);
-    }
+    });
     for (Batch* b : seen) free_batch(b);
     free_batch(r->building);
     for (Batch* b : r->pool) free_batch(b);
