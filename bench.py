@@ -807,7 +807,8 @@ def run_kernel_workload(args, dev):
     elif name == "gsa":
         # GSA's two scoring forms on the 64-request batch with two representatives per head (config 1's pooling, at
         # config 2's size): sum over heads of the best representative's dot product (host-side SelectTopKBS semantics,
-        # score_dot_general_kernel) and the device-side block weights of gsa.py:386-412 (score_dot_heads_kernel)
+        # the row-ring kernel with the maximum over representatives in its reduction) and the device-side block weights of
+        # gsa.py:386-412 (score_dot_heads_rows_kernel)
         R = 2
         n_tables = 3
         reps = [(torch.randn((batch.n_slots, H, R, D), generator=g, device=dev) * 0.0884).to(torch.bfloat16) for _ in range(n_tables)]
@@ -822,7 +823,7 @@ def run_kernel_workload(args, dev):
         line.update(metric="gsa_scored_kv_tokens_per_s", unit=UNIT, value=batch.total * T / (us_gen * 1e-6), ms_per_step=us_gen * 1e-3,
                     dtype="bf16", config={"workload": "GSA scoring with two representatives per head, the 64-request ragged batch",
                                           "blocks": int(batch.total), "l2_policy": "three 137 MB tables in rotation"},
-                    roofline=roofline("score_dot_reps_kernel<8 loads, 2 representatives>", nbytes, us_gen),
+                    roofline=roofline("score_dot_ring_kernel<bf16, 4 KiB rows, 2 representatives per head>", nbytes, us_gen),
                     per_head_weights={"kernel": "score_dot_heads_rows_kernel<8 loads, 2 representatives, 4 query heads per KV head>", "us": us_heads, "gbs": nbytes / us_heads / 1e3,
                                       "frac": nbytes / us_heads / 1e3 / peak})
     elif name == "kvstar":

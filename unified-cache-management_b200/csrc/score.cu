@@ -72,14 +72,98 @@ struct ScoreParams {
     int32_t early;           // launched so that it may begin before the kernel ahead of it in the stream has ended
 };
 
+// N partial sums per lane, each to be added up over the 16 lanes of a half-warp: instead of N butterflies of four
+// steps, the lanes first split the values between them - at distance 1 the even lanes keep the lower half of the
+// values and the odd lanes the upper half, each adding what its neighbour sends, and so on with half as many values
+// at twice the distance - and the steps that are left finish the one value a lane still holds.  The lane ends up
+// with the total of value number (bit 0 of the lane, bit 1, ...) read as a binary number from the top:
+// N - 1 + (4 - log2 N) shuffles instead of 4 N.
+template <int N, int DIST>
+__device__ __forceinline__ float half_warp_sums(float (&v)[N], int lane)
+{
+    if constexpr (N == 1) {
+        float x = v[0];
+#pragma unroll
+        for (int o = DIST; o < 16; o <<= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        return x;
+    } else {
+        static_assert(DIST < 16, "at most sixteen values");
+        float w[N / 2];
+        const bool upper = (lane & DIST) != 0;
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            const float keep = upper ? v[i + N / 2] : v[i];
+            const float send = upper ? v[i] : v[i + N / 2];
+            w[i] = keep + __shfl_xor_sync(0xffffffffu, send, DIST);
+        }
+        return half_warp_sums<N / 2, DIST * 2>(w, lane);
+    }
+}
+
+// eight products of fp32 q with a 16-byte piece of bf16 values, as four packed multiply-adds
+__device__ __forceinline__ float dot8_packed(const float4& q0, const float4& q1, const uint4& x)
+{
+    float2 s0 = __fmul2_rn(make_float2(q0.x, q0.y), make_float2(bf16lo(x.x), bf16hi(x.x)));
+    float2 s1 = __fmul2_rn(make_float2(q0.z, q0.w), make_float2(bf16lo(x.y), bf16hi(x.y)));
+    s0 = __ffma2_rn(make_float2(q1.x, q1.y), make_float2(bf16lo(x.z), bf16hi(x.z)), s0);
+    s1 = __ffma2_rn(make_float2(q1.z, q1.w), make_float2(bf16lo(x.w), bf16hi(x.w)), s1);
+    return (s0.x + s1.x) + (s0.y + s1.y);
+}
+
 // Element layout per lane: a row is cut into 16-byte pieces; piece j of a row belongs to lane
 // j % 32.  A piece holds 8 bf16 or 4 fp32 values.  QN = E/32 values of q per lane.
-template <int DT, int QN>
+// With R >= 2 representatives per head (bf16, 128 channels per head: GSA's tables) a 128-channel vector is 16 pieces,
+// so lanes 0-15 hold one vector of piece i and lanes 16-31 the next: the two (of R) representatives i * 2 and
+// i * 2 + 1 of head i / (R / 2).  The score is then the sum over heads of the best representative's dot product.
+template <int DT, int QN, int R = 1>
 struct RowDot {
     static constexpr int kPerPiece = (DT == UCMX_DT_BF16) ? 8 : 4;
     static constexpr int kPieces = QN / kPerPiece;
+    static constexpr int kLoadsPerHead = R >= 2 ? R / 2 : 1;
+    static constexpr int kHeads = kPieces / kLoadsPerHead;       // (R >= 2)
 
     float q[QN];
+
+    // R >= 2: this lane's eight channels of every head's query; qrow is fp32 [kHeads][128]
+    __device__ __forceinline__ void load_q_reps(const float* __restrict__ qrow, int lane)
+    {
+#pragma unroll
+        for (int h = 0; h < kHeads; ++h) {
+            const float4* src = reinterpret_cast<const float4*>(qrow + h * 128 + (lane & 15) * 8);
+            const float4 f0 = __ldg(src), f1 = __ldg(src + 1);
+            q[h * 8 + 0] = f0.x;
+            q[h * 8 + 1] = f0.y;
+            q[h * 8 + 2] = f0.z;
+            q[h * 8 + 3] = f0.w;
+            q[h * 8 + 4] = f1.x;
+            q[h * 8 + 5] = f1.y;
+            q[h * 8 + 6] = f1.z;
+            q[h * 8 + 7] = f1.w;
+        }
+    }
+    // R >= 2: every piece's dot product with its head's query (this lane's eight channels) ...
+    __device__ __forceinline__ void partial_reps(const uint4 (&buf)[kPieces], float (&part)[kPieces]) const
+    {
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const int h = i / kLoadsPerHead;
+            part[i] = dot8_packed(make_float4(q[h * 8 + 0], q[h * 8 + 1], q[h * 8 + 2], q[h * 8 + 3]),
+                                  make_float4(q[h * 8 + 4], q[h * 8 + 5], q[h * 8 + 6], q[h * 8 + 7]), buf[i]);
+        }
+    }
+    // ... and the score in every lane: all pieces summed over the half-warps at once (piece i = h * kLoadsPerHead + j
+    // ends up in the lane whose low bits, most significant first, spell i), the maximum over a head's pieces (lanes
+    // kHeads and more apart) and over the two half-warps, the sum over the heads (the lane bits below)
+    __device__ __forceinline__ float reduce_reps(float (&part)[kPieces], int lane) const
+    {
+        float t = half_warp_sums<kPieces, 1>(part, lane);
+#pragma unroll
+        for (int o = kHeads; o < kPieces; o <<= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 16));
+#pragma unroll
+        for (int o = 1; o < kHeads; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        return t;
+    }
 
     __device__ __forceinline__ void load_q(const float* __restrict__ qrow, int lane)
     {
@@ -225,9 +309,10 @@ struct RowDot {
 // The kernel is as much bound by instruction issue as by memory (a row of 2 KiB is 130 instructions of a warp
 // against 50 ns of HBM time per SM), so everything outside the row loop is kept short: no 64-bit divisions, the
 // stage index counted instead of computed, slot ids read once.
-template <int DT, int QN, bool FUSEQ>
+template <int DT, int QN, bool FUSEQ, int R = 1>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreParams p)
 {
+    static_assert(R == 1 || (!FUSEQ && DT == UCMX_DT_BF16), "several representatives per head: bf16 tables, fp32 queries");
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int kWarps = kScoreThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -240,9 +325,9 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
     // same terms, or the top-k, which is always launched that way and waits for this kernel's end before it reads.
     early_start_allow();
 
-    using RD = RowDot<DT, QN>;
+    using RD = RowDot<DT, QN, R>;
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
-    constexpr int E = QN * 32;
+    constexpr int E = QN * 32 / R;            // elements of a query row
     const int stages = p.stages;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem) + warp * kMaxRingStages;
     unsigned char* ring = smem + (size_t)kWarps * kMaxRingStages * 8 + (size_t)warp * stages * kRowBytes;
@@ -410,6 +495,8 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
             if (FUSEQ) {
                 if (req >= r_cta && req < r_cta + kStagedReq) rd.load_q_smem(&s_q[(req - r_cta) * E], lane);
                 else rd.load_q_raw(p.q_raw + (int64_t)req * p.q_raw_stride, lane, p.Hq, Hkv, p.D, p.round_bf16);
+            } else if (R > 1) {
+                rd.load_q_reps(p.q + (int64_t)req * E, lane);
             } else {
                 rd.load_q(p.q + (int64_t)req * E, lane);
             }
@@ -465,7 +552,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
                 fetch_q(r);
             }
             const int cs1 = cs + 1 == stages ? 0 : cs + 1;
-            if (QN <= 32 && row + 1 < end && row + 1 < r_end) {        // (the widest rows leave no registers for a pair)
+            if (R == 1 && QN <= 32 && row + 1 < end && row + 1 < r_end) {        // (the widest rows leave no registers for a pair)
                 // two rows of one request: independent chains, one interleaved reduction
                 const int n0 = slot_of(row + stages), n1 = slot_of(row + 1 + stages);   // in flight during the waits
                 uint4 a[RD::kPieces], b[RD::kPieces];
@@ -497,10 +584,19 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
                 const int n0 = slot_of(row + stages);
                 uint4 a[RD::kPieces];
                 const bool ha = take(cs, a);
-                float x = rd.dot(a);
-                __syncwarp();
-                if (!failed) fetch(cs, n0);
-                x = warp_sum(x);
+                float x;
+                if constexpr (R == 1) {
+                    x = rd.dot(a);
+                    __syncwarp();
+                    if (!failed) fetch(cs, n0);
+                    x = warp_sum(x);
+                } else {
+                    float part[RD::kPieces];
+                    rd.partial_reps(a, part);
+                    __syncwarp();
+                    if (!failed) fetch(cs, n0);
+                    x = rd.reduce_reps(part, lane);
+                }
                 keep(row, ha, x);
                 row += 1;
                 cs = cs1;
@@ -594,44 +690,6 @@ __global__ void __launch_bounds__(kScoreThreads) score_dot_general_kernel(ScoreG
         }
         if (lane == 0) p.out[c] = total * p.scale;
     }
-}
-
-// N partial sums per lane, each to be added up over the 16 lanes of a half-warp: instead of N butterflies of four
-// steps, the lanes first split the values between them - at distance 1 the even lanes keep the lower half of the
-// values and the odd lanes the upper half, each adding what its neighbour sends, and so on with half as many values
-// at twice the distance - and the steps that are left finish the one value a lane still holds.  The lane ends up
-// with the total of value number (bit 0 of the lane, bit 1, ...) read as a binary number from the top:
-// N - 1 + (4 - log2 N) shuffles instead of 4 N.
-template <int N, int DIST>
-__device__ __forceinline__ float half_warp_sums(float (&v)[N], int lane)
-{
-    if constexpr (N == 1) {
-        float x = v[0];
-#pragma unroll
-        for (int o = DIST; o < 16; o <<= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-        return x;
-    } else {
-        static_assert(DIST < 16, "at most sixteen values");
-        float w[N / 2];
-        const bool upper = (lane & DIST) != 0;
-#pragma unroll
-        for (int i = 0; i < N / 2; ++i) {
-            const float keep = upper ? v[i + N / 2] : v[i];
-            const float send = upper ? v[i] : v[i + N / 2];
-            w[i] = keep + __shfl_xor_sync(0xffffffffu, send, DIST);
-        }
-        return half_warp_sums<N / 2, DIST * 2>(w, lane);
-    }
-}
-
-// eight products of fp32 q with a 16-byte piece of bf16 values, as four packed multiply-adds
-__device__ __forceinline__ float dot8_packed(const float4& q0, const float4& q1, const uint4& x)
-{
-    float2 s0 = __fmul2_rn(make_float2(q0.x, q0.y), make_float2(bf16lo(x.x), bf16hi(x.x)));
-    float2 s1 = __fmul2_rn(make_float2(q0.z, q0.w), make_float2(bf16lo(x.y), bf16hi(x.y)));
-    s0 = __ffma2_rn(make_float2(q1.x, q1.y), make_float2(bf16lo(x.z), bf16hi(x.z)), s0);
-    s1 = __ffma2_rn(make_float2(q1.z, q1.w), make_float2(bf16lo(x.w), bf16hi(x.w)), s1);
-    return (s0.x + s1.x) + (s0.y + s1.y);
 }
 
 // The same for the shape GSA uses - bf16, 128 channels per head, a power-of-two number of representatives - with
@@ -731,7 +789,7 @@ RingGeometry ring_geometry(int32_t total, uint32_t row_bytes, int32_t n_req, siz
     return g;
 }
 
-template <int DT, int QN, bool FUSEQ>
+template <int DT, int QN, bool FUSEQ, int R = 1>
 int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
 {
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
@@ -743,7 +801,7 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
     int dev = 0;
     UCMX_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && smem_set[dev] < (int)g.smem) {
-        UCMX_CUDA(cudaFuncSetAttribute(score_dot_ring_kernel<DT, QN, FUSEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        UCMX_CUDA(cudaFuncSetAttribute(score_dot_ring_kernel<DT, QN, FUSEQ, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)g.smem));
         smem_set[dev] = (int)g.smem;
     }
@@ -766,12 +824,35 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        UCMX_CUDA(cudaLaunchKernelEx(&cfg, score_dot_ring_kernel<DT, QN, FUSEQ>, p));
+        UCMX_CUDA(cudaLaunchKernelEx(&cfg, score_dot_ring_kernel<DT, QN, FUSEQ, R>, p));
     } else {
-        score_dot_ring_kernel<DT, QN, FUSEQ><<<g.grid, kScoreThreads, g.smem, st>>>(p);
+        score_dot_ring_kernel<DT, QN, FUSEQ, R><<<g.grid, kScoreThreads, g.smem, st>>>(p);
     }
     UCMX_LAUNCH_CHECK("score_dot_ring_kernel");
     return UCMX_OK;
+}
+
+// several representatives per head (bf16 tables of 128-channel vectors): rows of 512 B to 4 KiB
+int32_t launch_ring_reps(const ScoreParams& p, int qn, int n_rep, cudaStream_t st)
+{
+    if (n_rep == 2) {
+        switch (qn) {
+            case 8: return launch_ring_one<UCMX_DT_BF16, 8, false, 2>(p, st);
+            case 16: return launch_ring_one<UCMX_DT_BF16, 16, false, 2>(p, st);
+            case 32: return launch_ring_one<UCMX_DT_BF16, 32, false, 2>(p, st);
+            case 64: return launch_ring_one<UCMX_DT_BF16, 64, false, 2>(p, st);
+            default: return UCMX_EUNSUPPORTED;
+        }
+    }
+    if (n_rep == 4) {
+        switch (qn) {
+            case 16: return launch_ring_one<UCMX_DT_BF16, 16, false, 4>(p, st);
+            case 32: return launch_ring_one<UCMX_DT_BF16, 32, false, 4>(p, st);
+            case 64: return launch_ring_one<UCMX_DT_BF16, 64, false, 4>(p, st);
+            default: return UCMX_EUNSUPPORTED;
+        }
+    }
+    return UCMX_EUNSUPPORTED;
 }
 
 template <int DT, bool FUSEQ>
@@ -982,6 +1063,29 @@ int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, in
         p.err = err;
         if (reps_dtype == UCMX_DT_BF16) return launch_ring<UCMX_DT_BF16, false>(p, qn, st);
         return launch_ring<UCMX_DT_F32, false>(p, qn, st);
+    }
+    if (reps_dtype == UCMX_DT_BF16 && head_dim == 128 && (n_rep == 2 || n_rep == 4) && !ex) {
+        // GSA's tables: the row ring with the per-head maximum over representatives folded into the reduction
+        const int64_t row_elems = E * n_rep;
+        const int qn_r = (int)(row_elems / 32);
+        if ((qn_r == 8 || qn_r == 16 || qn_r == 32 || qn_r == 64) && (n_rep == 2 || qn_r >= 16)) {
+            ScoreParams p{};
+            p.reps = reps;
+            p.n_slots = n_slots;
+            p.offsets = req_offsets;
+            p.slot_ids = slot_ids;
+            p.q = q;
+            p.D = head_dim;
+            p.out = out_scores;
+            p.n_req = n_req;
+            p.total = total;
+            p.E = (int32_t)E;
+            p.scale = scale;
+            p.px = px;
+            p.err = err;
+            const int32_t rr = launch_ring_reps(p, qn_r, n_rep, st);
+            if (rr != UCMX_EUNSUPPORTED) return rr;
+        }
     }
     ScoreGenParams g{reps, n_slots, req_offsets, slot_ids, q, out_scores, n_req, total, n_kv_heads, n_rep, head_dim, scale, px, err};
     if (n_rep == 1) {
