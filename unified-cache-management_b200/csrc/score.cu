@@ -1106,13 +1106,9 @@ int32_t score_dot_impl(const void* reps, int32_t reps_dtype, int64_t n_slots, in
         int64_t g4 = (int64_t)sm_count() * 4;          // four thread blocks of 8 warps per SM: 128 KiB of rows in flight
         const int64_t want4 = ((int64_t)total + 7) / 8;
         const int grid2 = (int)(g4 < want4 ? g4 : (want4 < 1 ? 1 : want4));
+        // (rows up to 4 KiB went to the row ring above: what is left is four representatives of eight heads, 8 KiB)
         bool done = true;
-        if (n_rep == 2 && n_kv_heads == 8) score_dot_reps_kernel<8, 2><<<grid2, kScoreThreads, 0, st>>>(g);
-        else if (n_rep == 2 && n_kv_heads == 4) score_dot_reps_kernel<4, 2><<<grid2, kScoreThreads, 0, st>>>(g);
-        else if (n_rep == 2 && n_kv_heads == 2) score_dot_reps_kernel<2, 2><<<grid2, kScoreThreads, 0, st>>>(g);
-        else if (n_rep == 2 && n_kv_heads == 1) score_dot_reps_kernel<1, 2><<<grid2, kScoreThreads, 0, st>>>(g);
-        else if (n_rep == 4 && n_kv_heads == 8) score_dot_reps_kernel<16, 4><<<grid2, kScoreThreads, 0, st>>>(g);
-        else if (n_rep == 4 && n_kv_heads == 4) score_dot_reps_kernel<8, 4><<<grid2, kScoreThreads, 0, st>>>(g);
+        if (n_rep == 4 && n_kv_heads == 8) score_dot_reps_kernel<16, 4><<<grid2, kScoreThreads, 0, st>>>(g);
         else done = false;
         if (done) {
             UCMX_LAUNCH_CHECK("score_dot_reps_kernel");
