@@ -489,6 +489,28 @@ def test_score_dot_heads_matches_checker_and_reference(ops, oracle):
     np.testing.assert_allclose(one * 8, esa, rtol=0, atol=0.06)      # esa rounds the group mean of q to bf16 (values ~ +-10)
 
 
+@pytest.mark.parametrize("Hq,Hkv,R", [(32, 8, 2), (64, 8, 2), (16, 4, 4)])
+def test_score_dot_heads_many_short_requests(ops, oracle, Hq, Hkv, R):
+    """Requests of one to three candidates: a thread block's candidates then belong to more requests than it keeps
+    queries for in shared memory, so both ways of fetching a query are taken inside one launch."""
+    rng = np.random.default_rng(Hq + R)
+    counts = rng.integers(1, 4, size=90)
+    off = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    total = int(off[-1])
+    n_slots = total + 7
+    reps = H.randn_bf16(rng, (n_slots, Hkv, R, 128), 0.5)
+    q = H.randn_bf16(rng, (len(counts), Hq, 128))
+    ids = rng.permutation(n_slots)[:total].astype(np.int32)
+    ids[[5, total - 2]] = -1
+    dev = "cuda:0"
+    bf = lambda u: torch.from_numpy(u.view(np.int16).copy()).to(dev).view(torch.bfloat16)
+    got = ops.score_dot_heads(bf(reps), torch.from_numpy(off).to(dev), bf(q), total=total, slot_ids=torch.from_numpy(ids).to(dev)).cpu().numpy()
+    want = oracle.score_dot_gsa_heads(H.bf16_to_f32(reps), off, ids, q)
+    fin = np.isfinite(want)
+    assert np.array_equal(np.isneginf(got), np.isneginf(want)) and (~fin).sum() == 2
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,R", [(8, 8, 128, 2), (64, 8, 128, 1), (4, 2, 64, 5), (32, 1, 32, 3), (32, 8, 128, 2), (16, 4, 128, 4),
                                         (8, 1, 128, 2), (64, 8, 128, 4), (16, 8, 128, 2)])
 def test_score_dot_heads_shapes(ops, oracle, Hq, Hkv, D, R):
