@@ -35,3 +35,16 @@ def test_parameter_errors_need_no_gpu():
     assert N.lib.ucmx_topk_ragged(None, 1, None, None, 3, 0, 0, 0, 0, None, 4, None, None, None, None, None) == N.EPARAM
     assert N.lib.ucmx_score_dot(None, 0, 0, 8, 1, 128, None, None, None, 0, 0, 1.0, None, None, None) == N.OK  # empty batch
     assert N.lib.ucmx_ring_release(None, 0) == N.EPARAM
+
+
+def test_early_start_switch_is_per_thread_and_returns_the_previous_setting():
+    import threading
+    from ucmx import _native as N
+    assert N.lib.ucmx_set_early_start(1) == 0
+    seen = []
+    t = threading.Thread(target=lambda: seen.append(N.lib.ucmx_set_early_start(0)))
+    t.start()
+    t.join()
+    assert seen == [0]                       # another thread has its own setting
+    assert N.lib.ucmx_set_early_start(0) == 1
+    assert N.lib.ucmx_set_early_start(0) == 0
