@@ -62,3 +62,31 @@ def test_backend_short_rows_update_and_many_requests(oracle):
             assert np.array_equal(res["indices"][r, :m], wi)
             assert (res["indices"][r, m:] == -1).all() and np.isneginf(res["scores"][r, m:]).all()
     be.close()
+
+
+def test_twenty_thousand_requests_outstanding(oracle):
+    """More requests in flight than the object's slot table (16 384) and the Python front's shape table (8 192)
+    hold: the overflow paths give the same answers, in any order of collection."""
+    from ucmx.retrieval import RetrievalWorkerBackend
+    rng = np.random.default_rng(62)
+    data = H.bf16_to_f32(H.randn_bf16(rng, (64, 32), 0.1))
+    be = RetrievalWorkerBackend(data)
+    n = 20_000
+    q = H.bf16_to_f32(H.randn_bf16(rng, (n, 32)))
+    idx = np.stack([rng.permutation(64)[:6] for _ in range(n)]).astype(np.int32)
+    rids = [be.submit(q[i:i + 1], 2 + i % 3, idx[i:i + 1]) for i in range(n)]
+    assert len(set(rids)) == n
+    order = rng.permutation(n)
+    check = set(order[:300].tolist()) | {0, 8191, 8192, 16383, 16384, n - 1}
+    for i in order:
+        be.wait(rids[i])
+        res = be.get_result(rids[i])
+        k = 2 + i % 3
+        assert res["indices"].shape == (1, k)
+        if int(i) in check:
+            s = oracle.score_dot_esa(data, np.array([0, 6], np.int32), idx[i], q[i:i + 1])
+            wi, _ = oracle.topk_esa(s, k, idx[i])
+            assert np.array_equal(res["indices"][0], wi)
+    with pytest.raises(RuntimeError, match="Result not ready"):
+        be.get_result(rids[0])
+    be.close()

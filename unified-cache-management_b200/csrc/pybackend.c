@@ -18,10 +18,12 @@
 typedef int32_t (*submit_fn)(void*, const float*, int32_t, int32_t, int32_t, const int32_t*, int32_t, int32_t*);
 typedef int32_t (*wait_fn)(void*, int32_t);
 typedef int32_t (*get_fn)(void*, int32_t, int32_t*, float*);
+typedef int32_t (*shape_fn)(void*, int32_t, int32_t*, int32_t*);
 
 static submit_fn g_submit;
 static wait_fn g_wait;
 static get_fn g_get;
+static shape_fn g_shape;
 static PyObject* g_on_error;   /* callable(function name, status): raises */
 static PyObject *g_key_indices, *g_key_scores;   /* the result dictionary's keys, made once */
 
@@ -38,12 +40,14 @@ static PyObject* raise_status(const char* fn, int32_t st)
     return NULL;
 }
 
-#define SHAPE_SLOTS 8192   /* results outstanding per object; a request id maps to id % SHAPE_SLOTS */
+#define SHAPE_SLOTS 8192   /* result shapes kept here, by id % SHAPE_SLOTS; a request whose slot has been taken over by a
+                              newer one asks the library for its shape instead */
 
 typedef struct {
     PyObject_HEAD
     void* handle;
     int32_t dim;
+    int32_t last_rid;   /* the largest request id a submit of this object has returned (-1: none yet) */
     struct {
         int32_t rid, rows, k;
     } shape[SHAPE_SLOTS];
@@ -57,6 +61,7 @@ static int fb_init(FastBackend* self, PyObject* args, PyObject* kw)
     if (!PyArg_ParseTuple(args, "Ki", &h, &dim)) return -1;   /* (a subclass calls this once it has its handle) */
     self->handle = (void*)(uintptr_t)h;
     self->dim = dim;
+    self->last_rid = -1;
     for (int i = 0; i < SHAPE_SLOTS; ++i) self->shape[i].rid = -1;
     return 0;
 }
@@ -115,6 +120,7 @@ static PyObject* fb_submit(FastBackend* self, PyObject* const* args, Py_ssize_t 
                                 (const int32_t*)PyArray_DATA(ia), (int32_t)n, &rid);
     if (st != 0) return raise_status("ucmx_retrieval_submit", st);
     const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
+    if (rid > self->last_rid) self->last_rid = rid;
     self->shape[slot].rid = rid;
     self->shape[slot].rows = (int32_t)rows;
     self->shape[slot].k = (int32_t)(topk < n ? topk : n);
@@ -152,11 +158,15 @@ static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
         return NULL;
     }
     const int slot = (int)((uint32_t)rid % SHAPE_SLOTS);
-    if (rid < 0 || self->shape[slot].rid != (int32_t)rid) {
+    int32_t rows = 0, k = 0;
+    if (rid >= 0 && self->shape[slot].rid == (int32_t)rid) {
+        rows = self->shape[slot].rows;
+        k = self->shape[slot].k;
+    } else if (rid < 0 || rid > self->last_rid || !g_shape || g_shape(self->handle, (int32_t)rid, &rows, &k) != 0) {
         PyErr_SetString(PyExc_RuntimeError, "Result not ready");
         return NULL;
     }
-    npy_intp dims[2] = {self->shape[slot].rows, self->shape[slot].k};
+    npy_intp dims[2] = {rows, k};
     PyObject* indices = PyArray_SimpleNew(2, dims, NPY_INT32);
     PyObject* scores = PyArray_SimpleNew(2, dims, NPY_FLOAT32);
     if (!indices || !scores) {
@@ -175,7 +185,7 @@ static PyObject* fb_get_result(FastBackend* self, PyObject* arg)
         }
         return raise_status("ucmx_retrieval_get_result", st);
     }
-    self->shape[slot].rid = -1;
+    if (self->shape[slot].rid == (int32_t)rid) self->shape[slot].rid = -1;
     PyObject* d = PyDict_New();
     if (!d || PyDict_SetItem(d, g_key_indices, indices) < 0 || PyDict_SetItem(d, g_key_scores, scores) < 0) {
         Py_XDECREF(d);
@@ -201,24 +211,25 @@ static PyTypeObject FastBackendType = {
     .tp_methods = fb_methods,
 };
 
-/* bind(submit_address, wait_address, get_result_address, on_error): the entry points of the loaded library and the
- * callable that turns a failed status into the package's exception */
+/* bind(submit_address, wait_address, get_result_address, result_shape_address, on_error): the entry points of the
+ * loaded library and the callable that turns a failed status into the package's exception */
 static PyObject* mod_bind(PyObject* self, PyObject* args)
 {
-    unsigned long long a = 0, b = 0, c = 0;
+    unsigned long long a = 0, b = 0, c = 0, d = 0;
     PyObject* on_error = NULL;
     (void)self;
-    if (!PyArg_ParseTuple(args, "KKKO", &a, &b, &c, &on_error)) return NULL;
+    if (!PyArg_ParseTuple(args, "KKKKO", &a, &b, &c, &d, &on_error)) return NULL;
     g_submit = (submit_fn)(uintptr_t)a;
     g_wait = (wait_fn)(uintptr_t)b;
     g_get = (get_fn)(uintptr_t)c;
+    g_shape = (shape_fn)(uintptr_t)d;
     Py_XINCREF(on_error);
     Py_XDECREF(g_on_error);
     g_on_error = on_error;
     Py_RETURN_NONE;
 }
 
-static PyMethodDef mod_methods[] = {{"bind", mod_bind, METH_VARARGS, "bind(submit, wait, get_result addresses, on_error)"},
+static PyMethodDef mod_methods[] = {{"bind", mod_bind, METH_VARARGS, "bind(submit, wait, get_result, result_shape addresses, on_error)"},
                                     {NULL, NULL, 0, NULL}};
 
 static struct PyModuleDef moddef = {PyModuleDef_HEAD_INIT, "_ucmx_fast", "CPython front of ucmx_retrieval_*", -1, mod_methods,

@@ -36,7 +36,7 @@ def _load_fast():
     spec.loader.exec_module(mod)
     addr = lambda fn: C.cast(fn, C.c_void_p).value   # noqa: E731
     mod.bind(addr(N.lib.ucmx_retrieval_submit), addr(N.lib.ucmx_retrieval_wait), addr(N.lib.ucmx_retrieval_get_result),
-             _raise_status)
+             addr(N.lib.ucmx_retrieval_result_shape), _raise_status)
     return mod
 
 
