@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
     }
     const uint64_t read_once = l2_evict_first_policy();      // every table row is read exactly once
 
-    // slot id of a row (the same value in every lane); one outside the table is reported and treated as empty
+    // slot id of a row; one outside the table is reported and treated as empty
     auto slot_of = [&](int row) -> int {
         if (row >= end) return -1;
         int v = p.slot_ids ? __ldg(p.slot_ids + row) : row;
@@ -386,10 +386,21 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
             valid &= ~(1u << s);
         }
     };
+    // Slot ids come 32 at a time, one per lane with one coalesced read, a batch ahead of the rows that need them (a
+    // warp of the decode batch has about fifteen rows: one read), and are handed round by shuffles: no row waits for
+    // a trip to memory for its id.
+    int ids_base = begin;                                    // ids_cur: rows [ids_base, ids_base + 32), ids_nxt: the 32 after
+    int ids_cur = slot_of(begin + lane), ids_nxt = slot_of(begin + 32 + lane);
+    auto slot_at = [&](int row) -> int {                     // (called by the whole warp, rows in ascending order)
+        if (row - ids_base >= 32) {                          // into the next batch: the one after it is asked for now
+            ids_base += 32;
+            ids_cur = ids_nxt;
+            ids_nxt = slot_of(ids_base + 32 + lane);
+        }
+        return __shfl_sync(0xffffffffu, ids_cur, (row - ids_base) & 31);
+    };
     if (begin < end) {
-        // the first `stages` slot ids with one coalesced read, then one copy each
-        const int mine_slot = lane < stages ? slot_of(begin + lane) : -1;
-        for (int s = 0; s < stages; ++s) fetch(s, __shfl_sync(0xffffffffu, mine_slot, s));
+        for (int s = 0; s < stages; ++s) fetch(s, slot_at(begin + s));
     }
     if (off_in_smem) {
 #pragma unroll
@@ -554,7 +565,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
             const int cs1 = cs + 1 == stages ? 0 : cs + 1;
             if (R == 1 && QN <= 32 && row + 1 < end && row + 1 < r_end) {        // (the widest rows leave no registers for a pair)
                 // two rows of one request: independent chains, one interleaved reduction
-                const int n0 = slot_of(row + stages), n1 = slot_of(row + 1 + stages);   // in flight during the waits
+                const int n0 = slot_at(row + stages), n1 = slot_at(row + 1 + stages);
                 uint4 a[RD::kPieces], b[RD::kPieces];
                 const bool ha = take(cs, a);
                 const bool hb = take(cs1, b);
@@ -581,7 +592,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
                 row += 2;
                 cs = cs1 + 1 == stages ? 0 : cs1 + 1;
             } else {
-                const int n0 = slot_of(row + stages);
+                const int n0 = slot_at(row + stages);
                 uint4 a[RD::kPieces];
                 const bool ha = take(cs, a);
                 float x;
