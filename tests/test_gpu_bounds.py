@@ -19,7 +19,8 @@ def dev_bf16(u16):
     return torch.from_numpy(np.ascontiguousarray(u16).view(np.int16)).to(DEV).view(torch.bfloat16)
 
 
-@pytest.mark.parametrize("Hkv,D,n_rep", [(8, 128, 1), (1, 128, 1), (2, 64, 2)])   # copy-engine rows, narrow rows, general kernel
+@pytest.mark.parametrize("Hkv,D,n_rep", [(8, 128, 1), (1, 128, 1), (2, 64, 2), (8, 128, 2), (4, 128, 4), (8, 128, 4)])
+# (copy-engine rows, narrow rows, general kernel, copy-engine rows with two and four representatives, whole row in flight)
 def test_score_dot_skips_slots_beyond_the_table(oracle, Hkv, D, n_rep):
     from ucmx import _native, ops
     rng = np.random.default_rng(201)

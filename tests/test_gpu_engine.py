@@ -5,6 +5,8 @@ import numpy as np
 import pytest
 import torch
 
+import helpers as H_
+
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 
@@ -107,6 +109,52 @@ def test_scoring_launched_early_behind_a_topk_changes_nothing():
         torch.cuda.synchronize()
         assert torch.equal(got_ids, want_ids) and torch.equal(got_vals, want_vals)
     assert _native.device_error() == 0
+
+
+def test_multi_representative_scoring_launched_early(oracle):
+    """The row-ring kernel with two representatives per head, launched early behind a top-k that still reads the score
+    buffer, replayed from a graph: the scores of the CPU checker, every time."""
+    from ucmx import ops
+    from ucmx.workloads import ragged_decode_batch
+    batch = ragged_decode_batch(seed=78, n_req=24, min_ctx=8192, max_ctx=32768, ratio=0.1, min_k=4)
+    rng = np.random.default_rng(78)
+    Hkv, R, D, n_tab = 8, 2, 128, 3
+    reps16 = [H_.randn_bf16(rng, (batch.n_slots, Hkv, R, D), 0.09) for _ in range(n_tab)]
+    q = H_.bf16_to_f32(H_.randn_bf16(rng, (batch.n_req, Hkv * D)))
+    want = [oracle.score_dot_gsa(H_.bf16_to_f32(r), Hkv, R, D, batch.offsets, batch.block_table, q) for r in reps16]
+    bf = lambda u: torch.from_numpy(u.view(np.int16).copy()).to(DEV).view(torch.bfloat16)
+    reps = [bf(r) for r in reps16]
+    off = torch.from_numpy(batch.offsets).to(DEV)
+    table = torch.from_numpy(batch.block_table).to(DEV)
+    kk = torch.from_numpy(batch.k_per_req).to(DEV)
+    qd = torch.from_numpy(q).to(DEV)
+    scores = torch.empty((batch.total,), dtype=torch.float32, device=DEV)
+    kept = torch.empty((n_tab, batch.total), dtype=torch.float32, device=DEV)
+    stride = int(batch.k_per_req.max())
+
+    def run():
+        for i in range(n_tab):
+            ops.score_dot(reps[i], off, qd, total=batch.total, slot_ids=table, n_kv_heads=Hkv, head_dim=D, n_rep=R,
+                          out=scores, early=i > 0)
+            kept[i].copy_(scores)
+            ops.topk_ragged(scores, off, kk, out_stride=stride)
+
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    for _ in range(3):
+        kept.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        got = kept.cpu().numpy()
+        for i in range(n_tab):
+            np.testing.assert_allclose(got[i], want[i], rtol=1e-3, atol=1e-3 * float(np.abs(want[i]).std()))
 
 
 @pytest.mark.parametrize("overlap", [False, True])
