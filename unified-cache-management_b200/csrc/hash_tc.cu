@@ -43,7 +43,6 @@ constexpr int kFirstSetWarp = 4;                  // a multiple of four: warp w 
 constexpr int kThreads = 32 * (kFirstSetWarp + 4 * kSets);   // warps 0, 2, 3: exact-chain fixers, warp 1: TMA + MMA issue and TMEM owner, warps 4-15: epilogue sets
 constexpr float kTau = 1.0f / 32768.0f;           // 2^-15
 constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
-constexpr int kIdAhead = 8;                       // block ids the issuing thread asks for ahead of the tile it loads
 constexpr int kFixSlots = 128;                    // code words with doubtful bits a fixer warp takes per tile (about 5 are typical)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -157,7 +156,7 @@ __device__ __forceinline__ uint32_t sw_offset(int row, int k)
 }
 
 struct alignas(16) Barriers {      // (what follows it in shared memory is accessed 16 bytes at a time)
-    uint64_t full[kStagesA], empty[kStagesA], acc_full[kAcc], acc_empty[kAcc], fix_ready[kStagesA];
+    uint64_t full[kStagesA], acc_full[kAcc], acc_empty[kAcc], fix_ready[kStagesA];
     uint32_t tmem_base;
     int32_t abort_flag;
     uint32_t fix_n[kStagesA];   // code words queued for the fixer, per stage
@@ -176,6 +175,22 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity)   // o
     return ok != 0;
 }
 
+// One thread starts the load of a tile: expect the bytes on the buffer's barrier, then the two halves of the tile.
+// Paged: (cache block id, tile of the block) name the box; an id outside the cache reads outside the tensor map -
+// TMA fills zeros and the tile's codes are not stored.  Dense: the first row.
+__device__ __forceinline__ void start_tile_load(const CUtensorMap* tmap, unsigned char* dst, uint64_t* bar, bool paged, int id,
+                                                int t0, int row0)
+{
+    mbar_expect_tx(bar, kTileBytes);
+    if (paged) {
+        tma_load_4d(dst, tmap, 0, 0, t0, id, bar);
+        tma_load_4d(dst + kHalfBytes, tmap, 64, 0, t0, id, bar);
+    } else {
+        tma_load_2d(dst, tmap, 0, row0, bar);
+        tma_load_2d(dst + kHalfBytes, tmap, 64, row0, bar);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
 {
@@ -190,8 +205,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     uint16_t* fb_list = reinterpret_cast<uint16_t*>(bars + 1);           // epilogue warps x kFallbackSlots
     uint8_t* fb_res = reinterpret_cast<uint8_t*>(fb_list + 4 * kSets * kFallbackSlots);
     uint32_t* wmax_bits = reinterpret_cast<uint32_t*>(fb_res + 4 * kSets * kFallbackSlots);   // max_j |w_j|
-    int32_t* id_ring = reinterpret_cast<int32_t*>(wmax_bits + 4);   // kIdAhead block ids on their way to the issuing thread
-    uint4* fixq = reinterpret_cast<uint4*>(id_ring + kIdAhead);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
+    uint4* fixq = reinterpret_cast<uint4*>(wmax_bits + 4);   // kStagesA x kFixSlots: {row | word index << 8, doubtful bits, word, -}
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -199,7 +213,6 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     if (tid == 0) {
         for (int s = 0; s < kStagesA; ++s) {
             mbar_init(&bars->full[s], 1);
-            mbar_init(&bars->empty[s], 1);          // the fixer lets a stage go
             mbar_init(&bars->fix_ready[s], 128);    // every epilogue thread has queued its doubtful words and stored the others
             bars->fix_n[s] = 0;
         }
@@ -249,80 +262,44 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + stride - 1) / stride : 0;
 
     if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------------ TMA and MMA issue, one thread
-        // Both jobs are a few instructions per tile.  The thread polls without blocking: whichever of "a
-        // stage is free -> load the next tile" and "a tile has landed and an accumulator is free -> issue
-        // its MMAs" is possible is done; neither ever waits for the other.
+        // ------------------------------------------------------------------ MMA issue (and the first loads), one thread
+        // This thread is the kernel's serial resource - under load every one of its shared-memory operations (a
+        // barrier poll, an MMA that reads its operands there) takes hundreds of cycles - so it does nothing but the
+        // eight MMAs of a tile: it starts the loads of the first kStagesA tiles, and from then on the fixer warp that
+        // is done with a tile's buffer starts the load of the tile that goes there next.
         const uint32_t b_addr = smem_u32(sB);
-        int64_t ld = 0, mm = 0;
-        uint32_t idle = 0;
-        // paged: the tile of its block the next tile to load is, and the list entry of the tile kIdAhead further on,
-        // both advanced without divisions.  This thread issues every load and every MMA of the SM, so a trip to
-        // memory per tile for the entry's cache block would be most of its time: the ids come through a small ring
-        // in shared memory filled by asynchronous 4-byte copies, one commit group per tile, kIdAhead tiles ahead.
-        int sub = 0, step_blk = 0, step_sub = 0, ablk = 0, asub = 0;
-        auto ask_id = [&](int64_t t) {                  // the id of this thread block's tile t, into the ring
-            if (t < my_tiles)
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(id_ring + (t % kIdAhead))), "l"(p.ids + ablk) : "memory");
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asub += step_sub;
-            ablk += step_blk;
-            if (asub >= p.tiles_per_block) {
-                asub -= p.tiles_per_block;
-                ++ablk;
+        for (int64_t ld = 0; ld < my_tiles && ld < kStagesA; ++ld) {
+            const int64_t tile = first + ld * stride;
+            int id = 0, t0 = 0;
+            if (p.paged) {
+                const int64_t blk = tile / p.tiles_per_block;
+                id = __ldg(p.ids + blk);
+                t0 = (int)(tile - blk * p.tiles_per_block) * (kTileM / p.H);
             }
-        };
-        if (p.paged) {
-            ablk = (int)(first / p.tiles_per_block);
-            sub = asub = (int)(first - (int64_t)ablk * p.tiles_per_block);
-            step_blk = (int)(stride / p.tiles_per_block);
-            step_sub = (int)(stride - (int64_t)step_blk * p.tiles_per_block);
-            for (int t = 0; t < kIdAhead; ++t) ask_id(t);
+            start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], p.paged != 0, id, t0, (int)(tile * kTileM));
         }
-        while (mm < my_tiles) {
-            bool progress = false;
-            if (ld < my_tiles) {
-                const int s = (int)(ld % kStagesA);
-                if (mbar_test(&bars->empty[s], (uint32_t)(((ld / kStagesA) & 1) ^ 1))) {
-                    unsigned char* dst = sA + (size_t)s * kTileBytes;
-                    mbar_expect_tx(&bars->full[s], kTileBytes);
-                    if (p.paged) {
-                        asm volatile("cp.async.wait_group %0;" ::"n"(kIdAhead - 1) : "memory");   // this tile's id has arrived
-                        const int id = *(volatile int32_t*)(id_ring + (ld % kIdAhead));
-                        const int t0 = sub * (kTileM / p.H);
-                        // an id outside the cache reads outside the tensor map: TMA fills zeros, the tile's codes are not stored
-                        tma_load_4d(dst, &tmap, 0, 0, t0, id, &bars->full[s]);
-                        tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, t0, id, &bars->full[s]);
-                        ask_id(ld + kIdAhead);                  // (into the slot just read)
-                        sub += step_sub;
-                        if (sub >= p.tiles_per_block) sub -= p.tiles_per_block;
-                    } else {
-                        const int row0 = (int)((first + ld * stride) * kTileM);
-                        tma_load_2d(dst, &tmap, 0, row0, &bars->full[s]);
-                        tma_load_2d(dst + kHalfBytes, &tmap, 64, row0, &bars->full[s]);
-                    }
-                    ++ld;
-                    progress = true;
-                }
-            }
-            if (mm < ld) {
-                const int s = (int)(mm % kStagesA), a = (int)(mm % kAcc);
-                if (mbar_test(&bars->full[s], (uint32_t)((mm / kStagesA) & 1)) &&
-                    mbar_test(&bars->acc_empty[a], (uint32_t)(((mm / kAcc) & 1) ^ 1))) {
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileBytes);
+        int mm_s = 0, mm_a = 0;
+        uint32_t full_par = 0, acc_par = 1, idle = 0;
+        for (int64_t mm = 0; mm < my_tiles;) {
+            if (mbar_test(&bars->full[mm_s], full_par) && mbar_test(&bars->acc_empty[mm_a], acc_par)) {
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sA + (size_t)mm_s * kTileBytes);
 #pragma unroll
-                    for (int k = 0; k < kDim / 16; ++k) {
-                        const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
-                        umma_bf16(tmem_base + (uint32_t)a * kBits, smem_desc_sw128(a_addr + koff), smem_desc_sw128(b_addr + koff),
-                                  k > 0 ? 1u : 0u);
-                    }
-                    umma_commit(&bars->acc_full[a]);   // arrives when the eight MMAs above have completed
-                    ++mm;
-                    progress = true;
+                for (int k = 0; k < kDim / 16; ++k) {
+                    const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
+                    umma_bf16(tmem_base + (uint32_t)mm_a * kBits, smem_desc_sw128(a_addr + koff), smem_desc_sw128(b_addr + koff),
+                              k > 0 ? 1u : 0u);
                 }
-            }
-            if (progress) {
+                umma_commit(&bars->acc_full[mm_a]);   // arrives when the eight MMAs above have completed
+                ++mm;
+                if (++mm_s == kStagesA) {
+                    mm_s = 0;
+                    full_par ^= 1u;
+                }
+                if (++mm_a == kAcc) {
+                    mm_a = 0;
+                    acc_par ^= 1u;
+                }
                 idle = 0;
             } else if (++idle > (1u << 24) || *(volatile int32_t*)&bars->abort_flag) {
                 bars->abort_flag = 1;
@@ -348,6 +325,16 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 id = checked_block_id(p.ids, blk, p.cache_blocks, nullptr);
                 slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, nullptr);
             }
+            // the tile that goes into this buffer next (kStagesA tiles on): lane 0 starts its load as soon as this
+            // tile's vectors are in registers; what it needs for that is asked for now, ahead of the waits
+            const int64_t nt = it + kStagesA;
+            int n_id = 0, n_t0 = 0;
+            const int64_t n_tile = first + nt * stride;
+            if (p.paged && nt < my_tiles) {
+                const int64_t nblk = n_tile / p.tiles_per_block;
+                n_id = __ldg(p.ids + nblk);
+                n_t0 = (int)(n_tile - nblk * p.tiles_per_block) * (kTileM / p.H);
+            }
             // First the tile's landing, then its epilogue.  The order matters: a parity wait is only right for a
             // barrier that is at most one phase behind, and this warp may come here while the buffer's previous
             // tile (another fixer's) is still in its epilogue; the landing of this tile, however, comes after that.
@@ -367,7 +354,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 __syncwarp();                                  // every lane has read the count before it is reset
                 if (lane == 0) {
                     bars->fix_n[s] = 0;
-                    mbar_arrive(&bars->empty[s]);
+                    if (nt < my_tiles)
+                        start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], p.paged != 0, n_id, n_t0, (int)(n_tile * kTileM));
                 }
             }
             for (int ps = 0; ps < passes; ++ps) {
@@ -388,7 +376,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     const unsigned seen = __ballot_sync(0xffffffffu, fold != 0x9e3779b9u);
                     if (lane == 0 && seen != 0xdeadbeefu) {
                         bars->fix_n[s] = 0;
-                        mbar_arrive(&bars->empty[s]);          // the stage may be loaded again
+                        if (nt < my_tiles)                      // the buffer is free: the tile that goes there next
+                            start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], p.paged != 0, n_id, n_t0, (int)(n_tile * kTileM));
                     }
                 }
                 if (!live) continue;
@@ -745,7 +734,7 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.n_tiles = (n_vec + kTileM - 1) / kTileM;
     }
     if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
-    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + kIdAhead * 4 + (size_t)kStagesA * kFixSlots * 16 + 128;
+    const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
     UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = (int64_t)sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
