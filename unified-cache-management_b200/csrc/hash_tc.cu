@@ -6,7 +6,8 @@
 // one elected thread issues eight tcgen05.mma (M128 N128 K16, bf16 in, fp32 accumulate in TMEM) per
 // tile, and sets of four epilogue warps read the accumulator back with tcgen05.ld, take signs and pack bits.
 // One thread block per SM: five tile buffers, four accumulators (all 512 TMEM columns), three epilogue sets
-// that take the tiles in turn, three fixer warps (below) and one thread that issues every load and MMA.
+// that take the tiles in turn, three fixer warps (below; they also start the reload of a buffer they are done with)
+// and one thread that issues every MMA.
 //
 // Codes must be bit-identical to the checker's definition - the sign of an fp32 fused-multiply-add
 // chain over d = 0..127 - while the tensor core adds in its own order.  With S the exact sum, the chain
@@ -40,7 +41,7 @@ constexpr int kFixers = 3;                        // fixer warps (warps 0, 2 and
 constexpr int kHalfBytes = kTileM * 128;          // one 64-element K half of a tile: 128 rows x 128 B
 constexpr int kTileBytes = 2 * kHalfBytes;        // 32 KiB
 constexpr int kFirstSetWarp = 4;                  // a multiple of four: warp w reads TMEM lanes 32 (w % 4) ...
-constexpr int kThreads = 32 * (kFirstSetWarp + 4 * kSets);   // warps 0, 2, 3: exact-chain fixers, warp 1: TMA + MMA issue and TMEM owner, warps 4-15: epilogue sets
+constexpr int kThreads = 32 * (kFirstSetWarp + 4 * kSets);   // warps 0, 2, 3: exact-chain fixers (and reloads), warp 1: MMA issue and TMEM owner, warps 4-15: epilogue sets
 constexpr float kTau = 1.0f / 32768.0f;           // 2^-15
 constexpr int kFallbackSlots = 256;               // doubtful bits one warp pools per tile when the fixer's queue is full
 constexpr int kFixSlots = 128;                    // code words with doubtful bits a fixer warp takes per tile (about 5 are typical)
