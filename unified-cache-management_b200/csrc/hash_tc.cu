@@ -529,34 +529,42 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             // by column.
             uint32_t code[4], doubt[4];
             {
+                // One code word (two pieces) per pass of a loop that is NOT unrolled: the kernel's instruction stream
+                // is large, sixteen warps of three kinds share the instruction caches, and instruction fetch was the
+                // most frequent stall; four copies of this body added 9 KB to it.
                 uint32_t v[2][16];
                 const uint32_t acc_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kBits);
                 tmem_ld16_start(acc_addr + 7 * 16, v[1]);       // pieces are taken from the highest column down
-                uint32_t neg = 0, unsure = 0;
+#pragma unroll 1
+                for (int pp = 3; pp >= 0; --pp) {
+                    uint32_t neg = 0, unsure = 0;
 #pragma unroll
-                for (int pc = 7; pc >= 0; --pc) {
-                    uint32_t (&cur)[16] = v[pc & 1];
-                    tmem_ld16_wait(cur);
-                    if (pc > 0) tmem_ld16_start(acc_addr + (pc - 1) * 16, v[(pc - 1) & 1]);
+                    for (int half = 1; half >= 0; --half) {
+                        uint32_t (&cur)[16] = v[half];
+                        tmem_ld16_wait(cur);
+                        if (half == 1) tmem_ld16_start(acc_addr + (uint32_t)(pp * 2) * 16, v[0]);
+                        else if (pp > 0) tmem_ld16_start(acc_addr + (uint32_t)(pp * 2 - 1) * 16, v[1]);
 #pragma unroll
-                    for (int j = 15; j >= 0; --j) neg = __funnelshift_l(cur[j], neg, 1);
+                        for (int j = 15; j >= 0; --j) neg = __funnelshift_l(cur[j], neg, 1);
 #pragma unroll
-                    for (int g8 = 0; g8 < 2; ++g8) {
-                        float mn = fabsf(__uint_as_float(cur[g8 * 8]));
+                        for (int g8 = 0; g8 < 2; ++g8) {
+                            float mn = fabsf(__uint_as_float(cur[g8 * 8]));
 #pragma unroll
-                        for (int j = 1; j < 8; ++j) mn = fminf(mn, fabsf(__uint_as_float(cur[g8 * 8 + j])));
-                        if (mn <= thr) {
+                            for (int j = 1; j < 8; ++j) mn = fminf(mn, fabsf(__uint_as_float(cur[g8 * 8 + j])));
+                            if (mn <= thr) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                unsure |= (fabsf(__uint_as_float(cur[g8 * 8 + j])) <= thr ? 1u : 0u) << ((pc & 1) * 16 + g8 * 8 + j);
+                                for (int j = 0; j < 8; ++j)
+                                    unsure |= (fabsf(__uint_as_float(cur[g8 * 8 + j])) <= thr ? 1u : 0u) << (half * 16 + g8 * 8 + j);
+                            }
                         }
                     }
-                    if ((pc & 1) == 0) {                        // a 32-bit word of the code is complete
-                        code[pc >> 1] = ~neg & keep;
-                        doubt[pc >> 1] = unsure;
-                        neg = 0;
-                        unsure = 0;
-                    }
+                    const uint32_t word = ~neg & keep;          // (selects, not an indexed store: the arrays stay in registers)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (k == pp) {
+                            code[k] = word;
+                            doubt[k] = unsure;
+                        }
                 }
             }
             // the accumulator is read: hand it back to the MMA warp
