@@ -309,7 +309,11 @@ struct RowDot {
 // The kernel is as much bound by instruction issue as by memory (a row of 2 KiB is 130 instructions of a warp
 // against 50 ns of HBM time per SM), so everything outside the row loop is kept short: no 64-bit divisions, the
 // stage index counted instead of computed, slot ids read once.
-template <int DT, int QN, bool FUSEQ, int R = 1>
+// PEER: the scores also go to the ranks' inboxes (tensor-parallel retrieval).  A template switch rather than a test of
+// p.px.world: the exchange's stores and round counters are inlined wherever scores leave, a fifth of the kernel's
+// instruction stream, and a single rank's launches - short kernels that start with cold instruction caches - should
+// not carry them.
+template <int DT, int QN, bool FUSEQ, int R = 1, bool PEER = false>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreParams p)
 {
     static_assert(R == 1 || (!FUSEQ && DT == UCMX_DT_BF16), "several representatives per head: bf16 tables, fp32 queries");
@@ -341,7 +345,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
 
     uint32_t round = 0;
     int64_t push_off = 0;
-    if (p.px.world > 0) {
+    if (PEER) {
         round = peer_round_now(p.px);
         push_off = peer_inbox_offset(p.px, round, p.px.my_rank);
     }
@@ -523,8 +527,10 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
             if (p.early) early_start_wait();
             if (row < upto) {
                 if (p.out) p.out[row] = mine;
-                for (int t = 0; t < p.px.world; ++t)
-                    reinterpret_cast<float*>(p.px.bases[t] + push_off)[row] = mine;
+                if (PEER) {
+                    for (int t = 0; t < p.px.world; ++t)
+                        reinterpret_cast<float*>(p.px.bases[t] + push_off)[row] = mine;
+                }
             }
             flush_from = upto;
         };
@@ -615,7 +621,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_dot_ring_kernel(ScoreP
         }
         flush(end);
     }
-    if (p.px.world > 0) peer_publish_round(p.px, round);
+    if (PEER) peer_publish_round(p.px, round);
 }
 
 // ------------------------------------------------------------------ general path: any n_rep
@@ -800,8 +806,19 @@ RingGeometry ring_geometry(int32_t total, uint32_t row_bytes, int32_t n_req, siz
     return g;
 }
 
+template <int DT, int QN, bool FUSEQ, int R, bool PEER>
+int32_t launch_ring_pick(ScoreParams p, cudaStream_t st);
+
 template <int DT, int QN, bool FUSEQ, int R = 1>
-int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
+int32_t launch_ring_one(const ScoreParams& p, cudaStream_t st)
+{
+    // (several representatives per head are scored on one rank only)
+    if (R == 1 && p.px.world > 0) return launch_ring_pick<DT, QN, FUSEQ, 1, true>(p, st);
+    return launch_ring_pick<DT, QN, FUSEQ, R, false>(p, st);
+}
+
+template <int DT, int QN, bool FUSEQ, int R, bool PEER>
+int32_t launch_ring_pick(ScoreParams p, cudaStream_t st)
 {
     constexpr uint32_t kRowBytes = (uint32_t)QN * 32u * (DT == UCMX_DT_BF16 ? 2u : 4u);
     // static shared memory of the kernel: the staged queries of the fused variant
@@ -812,7 +829,7 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
     int dev = 0;
     UCMX_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && smem_set[dev] < (int)g.smem) {
-        UCMX_CUDA(cudaFuncSetAttribute(score_dot_ring_kernel<DT, QN, FUSEQ, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        UCMX_CUDA(cudaFuncSetAttribute(score_dot_ring_kernel<DT, QN, FUSEQ, R, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)g.smem));
         smem_set[dev] = (int)g.smem;
     }
@@ -835,9 +852,9 @@ int32_t launch_ring_one(ScoreParams p, cudaStream_t st)
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        UCMX_CUDA(cudaLaunchKernelEx(&cfg, score_dot_ring_kernel<DT, QN, FUSEQ, R>, p));
+        UCMX_CUDA(cudaLaunchKernelEx(&cfg, score_dot_ring_kernel<DT, QN, FUSEQ, R, PEER>, p));
     } else {
-        score_dot_ring_kernel<DT, QN, FUSEQ, R><<<g.grid, kScoreThreads, g.smem, st>>>(p);
+        score_dot_ring_kernel<DT, QN, FUSEQ, R, PEER><<<g.grid, kScoreThreads, g.smem, st>>>(p);
     }
     UCMX_LAUNCH_CHECK("score_dot_ring_kernel");
     return UCMX_OK;
