@@ -102,7 +102,7 @@ def test_repeated_runs_are_identical(oracle):
 
 def test_every_bit_doubtful_on_every_sm(oracle):
     """Every bit of every vector is doubtful (squares underflow, so no tensor-core sign is trusted) and every thread
-    block gets several tiles: the fixer warp's queue (256 words a tile) overflows in each of them, so most words are
+    block gets many tiles: the fixer warps' queue (128 words a tile) overflows in each of them, so most words are
     settled by the epilogue warps' pooled fallback.  Same bytes as the checker either way."""
     from ucmx import ops
     rng = np.random.default_rng(106)
