@@ -192,6 +192,9 @@ __device__ __forceinline__ void start_tile_load(const CUtensorMap* tmap, unsigne
     }
 }
 
+// PAGED: the vectors are key blocks of a paged cache named by a list (else: a dense array of vectors).  A template switch:
+// the kernel stalls on instruction fetch more than on anything else, so it does not carry the other form's code.
+template <bool PAGED>
 __global__ void __launch_bounds__(kThreads, 1)
 hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
 {
@@ -272,12 +275,12 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         for (int64_t ld = 0; ld < my_tiles && ld < kStagesA; ++ld) {
             const int64_t tile = first + ld * stride;
             int id = 0, t0 = 0;
-            if (p.paged) {
+            if (PAGED) {
                 const int64_t blk = tile / p.tiles_per_block;
                 id = __ldg(p.ids + blk);
                 t0 = (int)(tile - blk * p.tiles_per_block) * (kTileM / p.H);
             }
-            start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], p.paged != 0, id, t0, (int)(tile * kTileM));
+            start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], PAGED, id, t0, (int)(tile * kTileM));
         }
         int mm_s = 0, mm_a = 0;
         uint32_t full_par = 0, acc_par = 1, idle = 0;
@@ -320,7 +323,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             const int64_t tile = first + it * stride;
             int64_t blk = 0, slot = 0;
             int sub = 0, id = 0;
-            if (p.paged) {
+            if (PAGED) {
                 blk = tile / p.tiles_per_block;
                 sub = (int)(tile - blk * p.tiles_per_block);
                 id = checked_block_id(p.ids, blk, p.cache_blocks, nullptr);
@@ -331,7 +334,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             const int64_t nt = it + kStagesA;
             int n_id = 0, n_t0 = 0;
             const int64_t n_tile = first + nt * stride;
-            if (p.paged && nt < my_tiles) {
+            if (PAGED && nt < my_tiles) {
                 const int64_t nblk = n_tile / p.tiles_per_block;
                 n_id = __ldg(p.ids + nblk);
                 n_t0 = (int)(n_tile - nblk * p.tiles_per_block) * (kTileM / p.H);
@@ -356,7 +359,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 if (lane == 0) {
                     bars->fix_n[s] = 0;
                     if (nt < my_tiles)
-                        start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], p.paged != 0, n_id, n_t0, (int)(n_tile * kTileM));
+                        start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, (int)(n_tile * kTileM));
                 }
             }
             for (int ps = 0; ps < passes; ++ps) {
@@ -378,7 +381,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     if (lane == 0 && seen != 0xdeadbeefu) {
                         bars->fix_n[s] = 0;
                         if (nt < my_tiles)                      // the buffer is free: the tile that goes there next
-                            start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], p.paged != 0, n_id, n_t0, (int)(n_tile * kTileM));
+                            start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, (int)(n_tile * kTileM));
                     }
                 }
                 if (!live) continue;
@@ -410,7 +413,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     word = (word & ~(1u << j)) | ((acc > 0.0f ? 1u : 0u) << j);
                 }
                 int64_t orow;
-                if (p.paged) {
+                if (PAGED) {
                     const int t = sub * (kTileM / p.H) + row / p.H, h = row % p.H;
                     orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
                 } else {
@@ -428,7 +431,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         // block and code-table row group are asked for one tile ahead, so the stores at the end of a tile never wait.
         const int set = (warp - kFirstSetWarp) >> 2;
         int tok = 0, h = 0, blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0, nxt_slot = 0;
-        if (p.paged) {
+        if (PAGED) {
             tok = m / p.H;
             h = m - tok * p.H;
             const int64_t mine0 = first + (int64_t)set * stride, step = (int64_t)kSets * stride;   // this set's first tile, and its stride
@@ -444,7 +447,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         for (int64_t it = set; it < my_tiles; it += kSets) {
             const int s = (int)(it % kStagesA), a = (int)(it % kAcc);
             int64_t orow;                         // where this row's code goes (-1: nowhere)
-            if (p.paged) {
+            if (PAGED) {
                 int id = nxt_id;
                 int64_t slot = nxt_slot;
                 if (id >= 0 && (int64_t)id >= p.cache_blocks) {
@@ -744,10 +747,12 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
     }
     if (r != CUDA_SUCCESS) return UCMX_EUNSUPPORTED;
     const size_t smem = 1024 + (size_t)kStagesA * kTileBytes + kTileBytes + kBits * sizeof(float) + sizeof(Barriers) + 4 * kSets * kFallbackSlots * 3 + 16 + (size_t)kStagesA * kFixSlots * 16 + 128;
-    UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    UCMX_CUDA(cudaFuncSetAttribute(hash_encode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = (int64_t)sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
-    hash_encode_tc_kernel<<<(unsigned)grid, kThreads, smem, st>>>(tmap, p);
+    if (p.paged) hash_encode_tc_kernel<true><<<(unsigned)grid, kThreads, smem, st>>>(tmap, p);
+    else hash_encode_tc_kernel<false><<<(unsigned)grid, kThreads, smem, st>>>(tmap, p);
     UCMX_LAUNCH_CHECK("hash_encode_tc_kernel");
     return UCMX_OK;
 }
