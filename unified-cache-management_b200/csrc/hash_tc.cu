@@ -72,6 +72,7 @@ struct TcParams {
     int64_t n_vec;         // dense: number of vectors
     int64_t n_tiles;
     int32_t paged, H, T, head_major, tiles_per_block;
+    int32_t h_shift, tok_per_tile;   // H is a power of two (it divides the 128 rows of a tile): log2 H, and 128 / H
     const int32_t* ids;
     const int32_t* out_slots;
     int64_t cache_blocks, out_rows;   // paged: blocks in the cache, rows of the code table
@@ -276,9 +277,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             const int64_t tile = first + ld * stride;
             int id = 0, t0 = 0;
             if (PAGED) {
-                const int64_t blk = tile / p.tiles_per_block;
+                const uint32_t blk = (uint32_t)tile / (uint32_t)p.tiles_per_block;      // (tile numbers fit in 31 bits)
                 id = __ldg(p.ids + blk);
-                t0 = (int)(tile - blk * p.tiles_per_block) * (kTileM / p.H);
+                t0 = (int)((uint32_t)tile - blk * (uint32_t)p.tiles_per_block) * p.tok_per_tile;
             }
             start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], PAGED, id, t0, (int)(tile * kTileM));
         }
@@ -324,8 +325,8 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             int64_t blk = 0, slot = 0;
             int sub = 0, id = 0;
             if (PAGED) {
-                blk = tile / p.tiles_per_block;
-                sub = (int)(tile - blk * p.tiles_per_block);
+                blk = (int64_t)((uint32_t)tile / (uint32_t)p.tiles_per_block);
+                sub = (int)((uint32_t)tile - (uint32_t)blk * (uint32_t)p.tiles_per_block);
                 id = checked_block_id(p.ids, blk, p.cache_blocks, nullptr);
                 slot = id < 0 ? -1 : checked_out_row(p.out_slots, blk, p.out_rows, nullptr);
             }
@@ -335,9 +336,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             int n_id = 0, n_t0 = 0;
             const int64_t n_tile = first + nt * stride;
             if (PAGED && nt < my_tiles) {
-                const int64_t nblk = n_tile / p.tiles_per_block;
+                const uint32_t nblk = (uint32_t)n_tile / (uint32_t)p.tiles_per_block;
                 n_id = __ldg(p.ids + nblk);
-                n_t0 = (int)(n_tile - nblk * p.tiles_per_block) * (kTileM / p.H);
+                n_t0 = (int)((uint32_t)n_tile - nblk * (uint32_t)p.tiles_per_block) * p.tok_per_tile;
             }
             // First the tile's landing, then its epilogue.  The order matters: a parity wait is only right for a
             // barrier that is at most one phase behind, and this warp may come here while the buffer's previous
@@ -414,7 +415,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 }
                 int64_t orow;
                 if (PAGED) {
-                    const int t = sub * (kTileM / p.H) + row / p.H, h = row % p.H;
+                    const int t = sub * p.tok_per_tile + (row >> p.h_shift), h = row & (p.H - 1);
                     orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
                 } else {
                     const int64_t v = tile * kTileM + row;
@@ -432,7 +433,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         const int set = (warp - kFirstSetWarp) >> 2;
         int tok = 0, h = 0, blk = 0, sub = 0, step_blk = 0, step_sub = 0, nxt_id = 0, nxt_slot = 0;
         if (PAGED) {
-            tok = m / p.H;
+            tok = m >> p.h_shift;
             h = m - tok * p.H;
             const int64_t mine0 = first + (int64_t)set * stride, step = (int64_t)kSets * stride;   // this set's first tile, and its stride
             blk = (int)(mine0 / p.tiles_per_block);
@@ -458,7 +459,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     if (p.err) atomicExch(p.err, 3);
                     slot = -1;
                 }
-                const int tk = sub * (kTileM / p.H) + tok;
+                const int tk = sub * p.tok_per_tile + tok;
                 orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + tk : (slot * p.T + tk) * p.H + h;
                 sub += step_sub;
                 blk += step_blk;
@@ -728,11 +729,14 @@ int32_t hash_encode_tc(const void* x, int64_t n_vec, int64_t x_stride, const ucm
         p.T = T;
         p.head_major = head_major;
         p.tiles_per_block = T * H / kTileM;
+        p.tok_per_tile = kTileM / H;
+        for (p.h_shift = 0; (1 << p.h_shift) < H; ++p.h_shift) {}
         p.ids = ids;
         p.out_slots = out_slots;
         p.cache_blocks = g->reserved;
         p.out_rows = n_out_rows;
         p.n_tiles = (int64_t)n_blocks * p.tiles_per_block;
+        if (p.n_tiles > 0x7fffffffll) return UCMX_EUNSUPPORTED;
     } else {
         if (x_stride % 8 || n_vec < 1 || n_vec > 0x7fffffffll) return UCMX_EUNSUPPORTED;
         const cuuint64_t dims[2] = {(cuuint64_t)kDim, (cuuint64_t)n_vec};
