@@ -263,8 +263,10 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
-    const int64_t first = blockIdx.x, stride = gridDim.x;
-    const int64_t my_tiles = first < p.n_tiles ? (p.n_tiles - first + stride - 1) / stride : 0;
+    // (tile numbers fit in 31 bits - the launch checks it - so everything below counts in 32 bits: the 64-bit
+    // divisions and remainders of a tile counter by 5, 4 and the tiles of a block were a good part of each role's code)
+    const int first = (int)blockIdx.x, stride = (int)gridDim.x;
+    const int my_tiles = (int64_t)first < p.n_tiles ? (int)((p.n_tiles - first + stride - 1) / stride) : 0;
 
     if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issue (and the first loads), one thread
@@ -273,19 +275,19 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         // eight MMAs of a tile: it starts the loads of the first kStagesA tiles, and from then on the fixer warp that
         // is done with a tile's buffer starts the load of the tile that goes there next.
         const uint32_t b_addr = smem_u32(sB);
-        for (int64_t ld = 0; ld < my_tiles && ld < kStagesA; ++ld) {
-            const int64_t tile = first + ld * stride;
+        for (int ld = 0; ld < my_tiles && ld < kStagesA; ++ld) {
+            const int tile = first + ld * stride;
             int id = 0, t0 = 0;
             if (PAGED) {
                 const uint32_t blk = (uint32_t)tile / (uint32_t)p.tiles_per_block;      // (tile numbers fit in 31 bits)
                 id = __ldg(p.ids + blk);
                 t0 = (int)((uint32_t)tile - blk * (uint32_t)p.tiles_per_block) * p.tok_per_tile;
             }
-            start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], PAGED, id, t0, (int)(tile * kTileM));
+            start_tile_load(&tmap, sA + (size_t)ld * kTileBytes, &bars->full[ld], PAGED, id, t0, tile * kTileM);
         }
         int mm_s = 0, mm_a = 0;
         uint32_t full_par = 0, acc_par = 1, idle = 0;
-        for (int64_t mm = 0; mm < my_tiles;) {
+        for (int mm = 0; mm < my_tiles;) {
             if (mbar_test(&bars->full[mm_s], full_par) && mbar_test(&bars->acc_empty[mm_a], acc_par)) {
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(sA + (size_t)mm_s * kTileBytes);
@@ -318,10 +320,10 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         // queued code word (usually one doubtful bit in it).  The lane settles the bits and stores the word.
         // The tile's buffer is held until the vectors are in registers; what does not depend on the queue
         // (where the tile's codes go) is worked out while waiting.
-        for (int64_t it = (warp + 1) >> 1; it < my_tiles; it += kFixers) {     // warps 0, 2, 3 -> fixers 0, 1, 2
-            const int s = (int)(it % kStagesA);
+        for (int it = (warp + 1) >> 1; it < my_tiles; it += kFixers) {     // warps 0, 2, 3 -> fixers 0, 1, 2
+            const int s = it % kStagesA;
             const uint32_t par = (uint32_t)((it / kStagesA) & 1);
-            const int64_t tile = first + it * stride;
+            const int tile = first + it * stride;
             int64_t blk = 0, slot = 0;
             int sub = 0, id = 0;
             if (PAGED) {
@@ -332,9 +334,9 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
             }
             // the tile that goes into this buffer next (kStagesA tiles on): lane 0 starts its load as soon as this
             // tile's vectors are in registers; what it needs for that is asked for now, ahead of the waits
-            const int64_t nt = it + kStagesA;
+            const int nt = it + kStagesA;
             int n_id = 0, n_t0 = 0;
-            const int64_t n_tile = first + nt * stride;
+            const int n_tile = first + nt * stride;
             if (PAGED && nt < my_tiles) {
                 const uint32_t nblk = (uint32_t)n_tile / (uint32_t)p.tiles_per_block;
                 n_id = __ldg(p.ids + nblk);
@@ -360,7 +362,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                 if (lane == 0) {
                     bars->fix_n[s] = 0;
                     if (nt < my_tiles)
-                        start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, (int)(n_tile * kTileM));
+                        start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, n_tile * kTileM);
                 }
             }
             for (int ps = 0; ps < passes; ++ps) {
@@ -382,7 +384,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     if (lane == 0 && seen != 0xdeadbeefu) {
                         bars->fix_n[s] = 0;
                         if (nt < my_tiles)                      // the buffer is free: the tile that goes there next
-                            start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, (int)(n_tile * kTileM));
+                            start_tile_load(&tmap, sA + (size_t)s * kTileBytes, &bars->full[s], PAGED, n_id, n_t0, n_tile * kTileM);
                     }
                 }
                 if (!live) continue;
@@ -418,7 +420,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     const int t = sub * p.tok_per_tile + (row >> p.h_shift), h = row & (p.H - 1);
                     orow = (id < 0 || slot < 0) ? -1 : p.head_major ? (slot * p.H + h) * p.T + t : (slot * p.T + t) * p.H + h;
                 } else {
-                    const int64_t v = tile * kTileM + row;
+                    const int64_t v = (int64_t)tile * kTileM + row;
                     orow = v < p.n_vec ? v : -1;
                 }
                 if (orow >= 0) reinterpret_cast<uint32_t*>(p.out + orow * 16)[cw] = word;
@@ -435,18 +437,18 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
         if (PAGED) {
             tok = m >> p.h_shift;
             h = m - tok * p.H;
-            const int64_t mine0 = first + (int64_t)set * stride, step = (int64_t)kSets * stride;   // this set's first tile, and its stride
-            blk = (int)(mine0 / p.tiles_per_block);
-            sub = (int)(mine0 - (int64_t)blk * p.tiles_per_block);
-            step_blk = (int)(step / p.tiles_per_block);
-            step_sub = (int)(step - (int64_t)step_blk * p.tiles_per_block);
+            const int mine0 = first + set * stride, step = kSets * stride;   // this set's first tile, and its stride
+            blk = mine0 / p.tiles_per_block;
+            sub = mine0 - blk * p.tiles_per_block;
+            step_blk = step / p.tiles_per_block;
+            step_sub = step - step_blk * p.tiles_per_block;
             if (set < my_tiles) {
                 nxt_id = __ldg(p.ids + blk);
                 nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
             }
         }
-        for (int64_t it = set; it < my_tiles; it += kSets) {
-            const int s = (int)(it % kStagesA), a = (int)(it % kAcc);
+        for (int it = set; it < my_tiles; it += kSets) {
+            const int s = it % kStagesA, a = it % kAcc;
             int64_t orow;                         // where this row's code goes (-1: nowhere)
             if (PAGED) {
                 int id = nxt_id;
@@ -472,7 +474,7 @@ hash_encode_tc_kernel(const __grid_constant__ CUtensorMap tmap, TcParams p)
                     nxt_slot = p.out_slots ? __ldg(p.out_slots + blk) : blk;
                 }
             } else {
-                const int64_t v = (first + it * stride) * kTileM + m;
+                const int64_t v = (int64_t)(first + it * stride) * kTileM + m;
                 orow = v < p.n_vec ? v : -1;
             }
             if (!mbar_wait(&bars->acc_full[a], (uint32_t)((it / kAcc) & 1))) {
